@@ -1,0 +1,551 @@
+// Bandwidth-bound decode: one query token per sequence against contiguous K/V.
+//
+// Grid = (split, kv head x head group, sequence).  A CTA owns up to
+// blocks_per_split attended blocks of one (sequence, kv head): a producer warp
+// streams their K and V tiles (64 tokens x D, 128-byte-swizzled TMA boxes) through
+// a 3-stage shared-memory ring, and four consumer warps each take 16 tokens of
+// every tile.  The q heads of the kv group are stacked into the 16 rows of an
+// m16n8k16 tensor-core tile, so K/V are read from HBM once per group, and the
+// per-token work is a handful of ldmatrix + mma instructions, which keeps the
+// kernel on the memory roofline.  Each warp keeps its own online-softmax state;
+// warps are merged through shared memory at the end and the CTA writes either
+// the final (O, LSE) (one split) or an fp32 partial that merge_kernel combines.
+//
+// Semantics follow the q_len == 1 case of
+// dkernel/ops/sparse_attn_inference.py:503-514: positions are re-based to the
+// first real token, the pattern row is (len - 1) / block_size, every real token
+// of an attended block is visible.
+#include "ptx.cuh"
+
+namespace bsa {
+
+__device__ int g_wait_status = 0;  // first bounded wait that gave up (0 = none)
+
+namespace {
+
+constexpr int kStages = 3;
+constexpr int kTok = 64;                 // tokens per pipeline stage
+constexpr int kConsumers = 4;            // consumer warps
+constexpr int kDecThreads = 32 * (kConsumers + 1);
+constexpr int kMaxUnits = 64;            // stage-units per CTA
+
+template <typename T> struct MmaType;
+template <> struct MmaType<__half> {
+  static __device__ __forceinline__ void mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
+                                             uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+};
+template <> struct MmaType<__nv_bfloat16> {
+  static __device__ __forceinline__ void mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
+                                             uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+        "{%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+};
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
+                                        uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
+                                          uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+
+struct DecodeSmem {
+  // after the 1024-aligned stage ring
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  int unit_pos[kMaxUnits];  // first position of each stage-unit
+  float wm[kConsumers][16];
+  float wl[kConsumers][16];
+};
+
+// byte offset of 16-byte chunk `chunk` (0 .. D/8-1) of token row `tok` in a tile
+// stored as D/64 sub-tiles of [64 tokens][128 bytes], 128-byte swizzled
+__device__ __forceinline__ uint32_t tile_off(int tok, int chunk) {
+  return (uint32_t)((chunk >> 3) * (kTok * 128) + tok * 128 + (((chunk & 7) ^ (tok & 7)) << 4));
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kDecThreads)
+decode_kernel(const __grid_constant__ Tmap4 tmK, const __grid_constant__ Tmap4 tmV,
+              bsa_decode_params p, int nsplit, int* wait_status) {
+  constexpr int kTileBytes = kTok * D * 2;
+  constexpr int kStageBytes = 2 * kTileBytes;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint8_t* ring = smem;
+  T* Qs = reinterpret_cast<T*>(smem + kStages * kStageBytes);  // [16][D]
+  DecodeSmem* sm = reinterpret_cast<DecodeSmem*>(smem + kStages * kStageBytes + 16 * D * 2);
+
+  if (*reinterpret_cast<volatile int*>(wait_status) != 0) return;  // an earlier wait gave up
+  const int sp = blockIdx.x, b = blockIdx.z;
+  const int G = p.hq / p.hkv;
+  const int GH = p.heads_per_cta;
+  const int groups_per_kv = G / GH;
+  const int kvh = blockIdx.y / groups_per_kv;
+  const int h0 = kvh * G + (blockIdx.y % groups_per_kv) * GH;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int bs = p.block_size;
+
+  const int ks = p.k_start ? p.k_start[b] : 0;
+  const int ke = p.k_end ? p.k_end[b] : p.sk;
+  const int local_len = ke - ks;
+  const int pos0 = p.k_pos0 ? p.k_pos0[b] : 0;
+  const int total = p.k_total ? p.k_total[b] : pos0 + local_len;
+  const int end_pos = min(total, pos0 + local_len);
+
+  // ---- which attended blocks belong to this CTA
+  int n_units = 0;
+  if (total > 0 && local_len > 0) {
+    const int row = (total - 1) / bs;
+    const int hp = pattern_head(h0, p.h_pat, p.hq, p.hkv);
+    int c_beg = 0, c_end = 0;
+    if (row < p.n_rows) {
+      const int32_t* cr = p.crow + (int64_t)hp * p.crow_sh;
+      c_beg = cr[row];
+      c_end = cr[row + 1];
+    }
+    const int32_t* cols = p.col + (int64_t)hp * p.col_sh;
+    int lo = c_beg;
+    while (lo < c_end && cols[lo] * bs < pos0) ++lo;
+    const int first = lo + sp * p.blocks_per_split;
+    const int last = min(c_end, first + p.blocks_per_split);
+    const int subs = bs / kTok;
+    for (int e = first; e < last; ++e) {
+      const int base = cols[e] * bs;
+      for (int s = 0; s < subs; ++s) {
+        const int pos = base + s * kTok;
+        if (pos < end_pos && n_units < kMaxUnits) {
+          if (tid == 0) sm->unit_pos[n_units] = pos;
+          ++n_units;
+        }
+      }
+    }
+  }
+
+  if (n_units == 0) {  // nothing attended here: an empty partial (uniform exit)
+    for (int i = tid; i < GH * D; i += kDecThreads) {
+      const int h = h0 + i / D, d = i % D;
+      if (nsplit == 1) {
+        reinterpret_cast<T*>(p.o)[(int64_t)b * p.o_sb + (int64_t)h * p.o_sh + d] = Elem<T>::from_f(0.f);
+      } else {
+        p.ws[(((int64_t)b * p.hq + h) * nsplit + sp) * D + d] = 0.f;
+      }
+    }
+    for (int i = tid; i < GH; i += kDecThreads) {
+      const int h = h0 + i;
+      if (nsplit == 1) {
+        if (p.lse) p.lse[(int64_t)b * p.lse_sb + (int64_t)h * p.lse_sh] = -INFINITY;
+      } else {
+        p.ws[(int64_t)p.batch * p.hq * nsplit * D + ((int64_t)b * p.hq + h) * nsplit + sp] = -INFINITY;
+      }
+    }
+    return;
+  }
+
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&sm->full[s], 1);
+      mbar_init(&sm->empty[s], kConsumers);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&tmK.map);
+    tma_prefetch_desc(&tmV.map);
+  }
+  // q heads of the group -> rows of the 16-row A tile (rows >= GH are zero)
+  for (int i = tid; i < 16 * D; i += kDecThreads) {
+    const int r = i / D, d = i % D;
+    T v = Elem<T>::from_f(0.f);
+    if (r < GH)
+      v = reinterpret_cast<const T*>(p.q)[(int64_t)b * p.q_sb + (int64_t)(h0 + r) * p.q_sh + d];
+    Qs[i] = v;
+  }
+  __syncthreads();
+
+  const int g = lane >> 2, tq = lane & 3;
+  float oacc[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f;
+
+  if (warp == kConsumers) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) {
+      for (int u = 0; u < n_units; ++u) {
+        const int s = u % kStages;
+        const uint32_t ph = (u / kStages) & 1;
+        if (!mbar_wait(&sm->empty[s], ph ^ 1, wait_status, 101)) break;
+        mbar_expect_tx(&sm->full[s], kStageBytes);
+        const int tok = ks + (sm->unit_pos[u] - pos0);
+        uint8_t* kdst = ring + s * kStageBytes;
+        uint8_t* vdst = kdst + kTileBytes;
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) {
+          tma_load_tile(kdst + c * (kTok * 128), &tmK, &sm->full[s], c * 64, tok, kvh, b);
+          tma_load_tile(vdst + c * (kTok * 128), &tmV, &sm->full[s], c * 64, tok, kvh, b);
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ consumers
+    uint32_t qa[D / 16][4];
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+      const uint32_t* q32 = reinterpret_cast<const uint32_t*>(Qs);
+      qa[kk][0] = q32[(g * D + kk * 16 + tq * 2) >> 1];
+      qa[kk][1] = q32[((g + 8) * D + kk * 16 + tq * 2) >> 1];
+      qa[kk][2] = q32[(g * D + kk * 16 + 8 + tq * 2) >> 1];
+      qa[kk][3] = q32[((g + 8) * D + kk * 16 + 8 + tq * 2) >> 1];
+    }
+    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+    const float scale2 = p.sm_scale * kLog2e;
+    const uint32_t ring_u32 = smem_u32(ring);
+    bool alive = true;
+
+    for (int u = 0; u < n_units && alive; ++u) {
+      const int s = u % kStages;
+      const uint32_t ph = (u / kStages) & 1;
+      alive = mbar_wait(&sm->full[s], ph, wait_status, 102);
+      if (!alive) break;
+      const int pos_u = sm->unit_pos[u];
+      const uint32_t kbase = ring_u32 + s * kStageBytes;
+      const uint32_t vbase = kbase + kTileBytes;
+      const int valid = end_pos - pos_u;  // tokens of this unit that exist (may exceed 64)
+      if (valid < kTok) {
+        // rows past the end of the sequence may hold anything: clear them in V so
+        // that 0 * garbage cannot produce NaN
+        uint8_t* vgen = ring + s * kStageBytes + kTileBytes;
+        for (int t = warp * 16; t < warp * 16 + 16; ++t) {
+          if (t >= valid) {
+#pragma unroll
+            for (int c = 0; c < D / 64; ++c)
+              reinterpret_cast<uint32_t*>(vgen + c * (kTok * 128) + t * 128)[lane] = 0u;
+          }
+        }
+        fence_proxy_async();  // order these writes before the next TMA into the stage
+        __syncwarp();
+      }
+      // S = Q K^T for this warp's 16 tokens
+      float sacc[2][4];
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.f;
+        const int tok = warp * 16 + nt * 8 + (lane & 7);
+#pragma unroll
+        for (int kk = 0; kk < D / 32; ++kk) {
+          uint32_t r0, r1, r2, r3;
+          ldsm_x4(kbase + tile_off(tok, kk * 4 + (lane >> 3)), r0, r1, r2, r3);
+          MmaType<T>::mma(sacc[nt], qa[2 * kk], r0, r1);
+          MmaType<T>::mma(sacc[nt], qa[2 * kk + 1], r2, r3);
+        }
+      }
+      // mask + online softmax (rows g and g+8)
+      float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int t = warp * 16 + nt * 8 + tq * 2 + e;
+          const bool ok = t < valid;
+          sacc[nt][e] = ok ? sacc[nt][e] * scale2 : -INFINITY;
+          sacc[nt][2 + e] = ok ? sacc[nt][2 + e] * scale2 : -INFINITY;
+          mx_lo = fmaxf(mx_lo, sacc[nt][e]);
+          mx_hi = fmaxf(mx_hi, sacc[nt][2 + e]);
+        }
+      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+      const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+      const float ms_lo = mn_lo == -INFINITY ? 0.f : mn_lo;
+      const float ms_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
+      const float a_lo = exp2f(m_lo - ms_lo), a_hi = exp2f(m_hi - ms_hi);
+      m_lo = mn_lo;
+      m_hi = mn_hi;
+      uint32_t pa[4];
+      {
+        const float p00 = exp2f(sacc[0][0] - ms_lo), p01 = exp2f(sacc[0][1] - ms_lo);
+        const float p02 = exp2f(sacc[0][2] - ms_hi), p03 = exp2f(sacc[0][3] - ms_hi);
+        const float p10 = exp2f(sacc[1][0] - ms_lo), p11 = exp2f(sacc[1][1] - ms_lo);
+        const float p12 = exp2f(sacc[1][2] - ms_hi), p13 = exp2f(sacc[1][3] - ms_hi);
+        l_lo = l_lo * a_lo + (p00 + p01 + p10 + p11);
+        l_hi = l_hi * a_hi + (p02 + p03 + p12 + p13);
+        pa[0] = MmaType<T>::pack(p00, p01);
+        pa[1] = MmaType<T>::pack(p02, p03);
+        pa[2] = MmaType<T>::pack(p10, p11);
+        pa[3] = MmaType<T>::pack(p12, p13);
+      }
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i) {
+        oacc[i][0] *= a_lo; oacc[i][1] *= a_lo;
+        oacc[i][2] *= a_hi; oacc[i][3] *= a_hi;
+      }
+      // O += P V over this warp's 16 tokens
+#pragma unroll
+      for (int dn = 0; dn < D / 16; ++dn) {
+        const int mi = lane >> 3;
+        const int tok = warp * 16 + (mi & 1) * 8 + (lane & 7);
+        uint32_t r0, r1, r2, r3;
+        ldsm_x4_t(vbase + tile_off(tok, dn * 2 + (mi >> 1)), r0, r1, r2, r3);
+        MmaType<T>::mma(oacc[2 * dn], pa, r0, r1);
+        MmaType<T>::mma(oacc[2 * dn + 1], pa, r2, r3);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sm->empty[s]);
+    }
+    // quad-reduce the row sums
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+    if (tq == 0) {
+      sm->wm[warp][g] = m_lo; sm->wm[warp][g + 8] = m_hi;
+      sm->wl[warp][g] = l_lo; sm->wl[warp][g + 8] = l_hi;
+    }
+  }
+  __syncthreads();  // every tile has been consumed: the ring is free
+  if (warp < kConsumers) {
+    float* Omw = reinterpret_cast<float*>(ring);  // [kConsumers][16][D]
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      const int d = i * 8 + tq * 2;
+      float* lo = Omw + ((warp * 16 + g) * D + d);
+      float* hi = Omw + ((warp * 16 + g + 8) * D + d);
+      lo[0] = oacc[i][0]; lo[1] = oacc[i][1];
+      hi[0] = oacc[i][2]; hi[1] = oacc[i][3];
+    }
+  }
+  __syncthreads();  // partial outputs are in shared memory
+
+  const float* Om = reinterpret_cast<const float*>(ring);
+  for (int i = tid; i < GH * D; i += kDecThreads) {
+    const int r = i / D, d = i % D;
+    float mf = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kConsumers; ++w) mf = fmaxf(mf, sm->wm[w][r]);
+    const float msafe = mf == -INFINITY ? 0.f : mf;
+    float acc = 0.f, l = 0.f;
+#pragma unroll
+    for (int w = 0; w < kConsumers; ++w) {
+      const float sc = exp2f(sm->wm[w][r] - msafe);
+      acc += Om[(w * 16 + r) * D + d] * sc;
+      l += sm->wl[w][r] * sc;
+    }
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    const float lse = l > 0.f ? (mf + log2f(l)) * kLn2 : -INFINITY;
+    const int h = h0 + r;
+    if (nsplit == 1) {
+      reinterpret_cast<T*>(p.o)[(int64_t)b * p.o_sb + (int64_t)h * p.o_sh + d] =
+          Elem<T>::from_f(acc * inv);
+      if (d == 0 && p.lse) p.lse[(int64_t)b * p.lse_sb + (int64_t)h * p.lse_sh] = lse;
+    } else {
+      p.ws[(((int64_t)b * p.hq + h) * nsplit + sp) * D + d] = acc * inv;
+      if (d == 0)
+        p.ws[(int64_t)p.batch * p.hq * nsplit * D + ((int64_t)b * p.hq + h) * nsplit + sp] = lse;
+    }
+  }
+}
+
+// out[row] = sum_p o_p[row] * softmax_p(lse_p[row]); merged lse = logsumexp_p.
+template <typename Tin, typename Tout>
+__global__ void merge_kernel(const Tin* __restrict__ o_parts, const float* __restrict__ lse_parts,
+                             int P, int64_t rows, int d, int64_t pso, int64_t rso, int64_t psl,
+                             int64_t rsl, Tout* __restrict__ o, int64_t ors,
+                             float* __restrict__ lse) {
+  const int64_t total = rows * d;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / d;
+    const int c = (int)(i - r * d);
+    float mx = -INFINITY;
+    for (int q = 0; q < P; ++q) mx = fmaxf(mx, lse_parts[q * psl + r * rsl]);
+    const float ms = mx == -INFINITY ? 0.f : mx;
+    float den = 0.f, acc = 0.f;
+    for (int q = 0; q < P; ++q) {
+      const float w = __expf(lse_parts[q * psl + r * rsl] - ms);
+      den += w;
+      if (w != 0.f) acc += w * Elem<Tin>::to_f(o_parts[q * pso + r * rso + c]);
+    }
+    o[r * ors + c] = Elem<Tout>::from_f(den > 0.f ? acc / den : 0.f);
+    if (c == 0 && lse) lse[r] = den > 0.f ? ms + __logf(den) : -INFINITY;
+  }
+}
+
+template <typename Tin, typename Tout>
+int launch_merge(const void* o_parts, const float* lse_parts, int P, int64_t rows, int d,
+                 int64_t pso, int64_t rso, int64_t psl, int64_t rsl, void* o, int64_t ors,
+                 float* lse, cudaStream_t s) {
+  const int64_t total = rows * d;
+  if (total == 0) return BSA_OK;
+  int64_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  merge_kernel<Tin, Tout><<<(unsigned)blocks, 256, 0, s>>>(
+      reinterpret_cast<const Tin*>(o_parts), lse_parts, P, rows, d, pso, rso, psl, rsl,
+      reinterpret_cast<Tout*>(o), ors, lse);
+  return check_launch("merge_kernel");
+}
+
+int decode_nsplit(const bsa_decode_params* p) {
+  const int bps = p->blocks_per_split > 0 ? p->blocks_per_split : 8;
+  const int n = (p->max_row_nnz + bps - 1) / bps;
+  return n < 1 ? 1 : n;
+}
+
+template <typename T, int D>
+int launch_decode(const bsa_decode_params* p, cudaStream_t s) {
+  Tmap4 tmK, tmV;
+  const bool bf16 = p->dtype == BSA_BF16;
+  int rc = make_tmap_4d(&tmK, p->k, 2, D, p->sk, p->hkv, p->batch, p->k_ss * 2, p->k_sh * 2,
+                        p->k_sb * 2, 64, kTok, true, bf16);
+  if (rc) return rc;
+  rc = make_tmap_4d(&tmV, p->v, 2, D, p->sk, p->hkv, p->batch, p->v_ss * 2, p->v_sh * 2,
+                    p->v_sb * 2, 64, kTok, true, bf16);
+  if (rc) return rc;
+  const int nsplit = decode_nsplit(p);
+  const size_t smem = 1024 + kStages * 2 * kTok * D * 2 + 16 * D * 2 + sizeof(DecodeSmem);
+  auto kern = decode_kernel<T, D>;
+  BSA_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const int G = p->hq / p->hkv;
+  dim3 grid(nsplit, p->hkv * (G / p->heads_per_cta), p->batch);
+  bsa_decode_params q = *p;
+  if (q.blocks_per_split <= 0) q.blocks_per_split = 8;
+  int* status = wait_status_ptr();
+  if (!status) return BSA_E_CUDA;
+  kern<<<grid, kDecThreads, smem, s>>>(tmK, tmV, q, nsplit, status);
+  rc = check_launch("decode_kernel");
+  if (rc) return rc;
+  if (nsplit > 1) {
+    const int64_t rows = (int64_t)p->batch * p->hq;
+    float* ws_lse = p->ws + rows * nsplit * D;
+    // partial o: (rows, nsplit, D) -> partition stride D, row stride nsplit*D
+    // the merged rows are written through (o_sb, o_sh): one launch per batch row
+    // layout unless o is contiguous over (batch, head)
+    if (p->o_sb == (int64_t)p->hq * p->o_sh && (!p->lse || (p->lse_sb == (int64_t)p->hq * p->lse_sh &&
+                                                             p->lse_sh == 1))) {
+      if (bf16)
+        return launch_merge<float, __nv_bfloat16>(p->ws, ws_lse, nsplit, rows, D, D,
+                                                  (int64_t)nsplit * D, 1, nsplit, p->o, p->o_sh,
+                                                  p->lse, s);
+      return launch_merge<float, __half>(p->ws, ws_lse, nsplit, rows, D, D, (int64_t)nsplit * D, 1,
+                                         nsplit, p->o, p->o_sh, p->lse, s);
+    }
+    set_error("bsa_decode: o must be contiguous over (batch, head) and lse contiguous");
+    return BSA_E_UNSUPPORTED;
+  }
+  return BSA_OK;
+}
+
+}  // namespace
+
+size_t decode_workspace_bytes(const bsa_decode_params* p) {
+  const int nsplit = decode_nsplit(p);
+  if (nsplit <= 1) return 0;
+  return sizeof(float) * (size_t)p->batch * p->hq * nsplit * (p->d + 1);
+}
+
+int decode_run(const bsa_decode_params* p, cudaStream_t s) {
+  BSA_CHECK_ARG(p && p->q && p->k && p->v && p->o && p->crow && p->col, "bsa_decode: null pointer");
+  BSA_CHECK_ARG(p->batch >= 0 && p->hq >= 1 && p->hkv >= 1 && p->hq % p->hkv == 0,
+                "bsa_decode: bad head counts hq=%d hkv=%d", p->hq, p->hkv);
+  const int G = p->hq / p->hkv;
+  BSA_CHECK_ARG(p->heads_per_cta >= 1 && p->heads_per_cta <= 16 && G % p->heads_per_cta == 0,
+                "bsa_decode: heads_per_cta=%d must divide the group size %d and be <= 16",
+                p->heads_per_cta, G);
+  BSA_CHECK_ARG(p->h_pat == 1 || p->h_pat == p->hkv || p->h_pat == p->hq,
+                "bsa_decode: pattern has %d heads, expected 1, %d or %d", p->h_pat, p->hkv, p->hq);
+  if (p->batch == 0) return BSA_OK;
+  if (!(p->dtype == BSA_F16 || p->dtype == BSA_BF16) || !(p->d == 64 || p->d == 128) ||
+      !(p->block_size == 64 || p->block_size == 128)) {
+    set_error("bsa_decode: needs f16/bf16, head dim 64 or 128 and block size 64 or 128 "
+              "(got dtype %d, d %d, block %d)", p->dtype, p->d, p->block_size);
+    return BSA_E_UNSUPPORTED;
+  }
+  if (!tma_compatible(p->k, 2, p->k_ss, p->k_sh, p->k_sb) ||
+      !tma_compatible(p->v, 2, p->v_ss, p->v_sh, p->v_sb)) {
+    set_error("bsa_decode: K/V need a 16-byte aligned base and strides that are multiples of 16 bytes");
+    return BSA_E_UNSUPPORTED;
+  }
+  const int bps = p->blocks_per_split > 0 ? p->blocks_per_split : 8;
+  if (bps * (p->block_size / kTok) > kMaxUnits) {
+    set_error("bsa_decode: blocks_per_split=%d too large (limit %d tiles of 64 tokens per CTA)", bps,
+              kMaxUnits);
+    return BSA_E_TOOBIG;
+  }
+  const int nsplit = decode_nsplit(p);
+  BSA_CHECK_ARG(nsplit == 1 || p->ws, "bsa_decode: workspace required for %d splits", nsplit);
+  if (p->dtype == BSA_BF16)
+    return p->d == 128 ? launch_decode<__nv_bfloat16, 128>(p, s) : launch_decode<__nv_bfloat16, 64>(p, s);
+  return p->d == 128 ? launch_decode<__half, 128>(p, s) : launch_decode<__half, 64>(p, s);
+}
+
+int merge_partials(const void* o_parts, const float* lse_parts, int P, int64_t rows, int d,
+                   int64_t pso, int64_t rso, int64_t psl, int64_t rsl, void* o, int64_t ors,
+                   float* lse, int dtype, cudaStream_t s) {
+  BSA_CHECK_ARG(o_parts && lse_parts && o, "bsa_merge_partials: null pointer");
+  BSA_CHECK_ARG(P >= 1 && rows >= 0 && d >= 1, "bsa_merge_partials: bad sizes P=%d d=%d", P, d);
+  switch (dtype) {
+    case BSA_F16: return launch_merge<__half, __half>(o_parts, lse_parts, P, rows, d, pso, rso, psl, rsl, o, ors, lse, s);
+    case BSA_BF16: return launch_merge<__nv_bfloat16, __nv_bfloat16>(o_parts, lse_parts, P, rows, d, pso, rso, psl, rsl, o, ors, lse, s);
+    case BSA_F32: return launch_merge<float, float>(o_parts, lse_parts, P, rows, d, pso, rso, psl, rsl, o, ors, lse, s);
+  }
+  set_error("bsa_merge_partials: unknown dtype %d", dtype);
+  return BSA_E_BADARG;
+}
+
+}  // namespace bsa
+
+namespace bsa {
+// Device address of the status word of the current device (the symbol name is
+// only a host-side handle; kernels get the real address as an argument).
+int* wait_status_ptr() {
+  static int* cache[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    set_error("cudaGetDevice failed or device index out of range");
+    return nullptr;
+  }
+  if (!cache[dev]) {
+    void* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&ptr, g_wait_status);
+    if (e != cudaSuccess) {
+      set_error("cudaGetSymbolAddress(g_wait_status) failed: %s", cudaGetErrorString(e));
+      return nullptr;
+    }
+    cache[dev] = static_cast<int*>(ptr);
+  }
+  return cache[dev];
+}
+
+int read_wait_status(int* out, int reset) {
+  BSA_CHECK_ARG(out, "bsa_wait_status: null pointer");
+  BSA_CHECK_CUDA(cudaDeviceSynchronize());
+  BSA_CHECK_CUDA(cudaMemcpyFromSymbol(out, g_wait_status, sizeof(int)));
+  if (reset && *out != 0) {
+    const int zero = 0;
+    BSA_CHECK_CUDA(cudaMemcpyToSymbol(g_wait_status, &zero, sizeof(int)));
+  }
+  return BSA_OK;
+}
+}  // namespace bsa

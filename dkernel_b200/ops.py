@@ -1,0 +1,454 @@
+"""Autograd dispatcher: the counterpart of dkernel/ops/__init__.py.
+
+``_sparse_attention.apply`` keeps the reference's argument list
+(dkernel/ops/__init__.py:12-23) and routing: 3-D inputs -> packed variable-length
+batch, ``left_paddings``/``seqlens`` -> padded batch, otherwise the training
+forward, whose backward is available.  Every route ends in one C-ABI call
+(``bsa_fwd``, ``bsa_decode`` or ``bsa_bwd``) on the current CUDA stream; nothing
+synchronises with the host.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from typing import Dict, Optional, Tuple, Union
+
+import torch
+from torch import Tensor
+
+from . import _lib
+
+
+# --------------------------------------------------------------------------- helpers
+def _last_dim_contig(t: Tensor) -> Tensor:
+    return t if t.stride(-1) == 1 else t.contiguous()
+
+
+def _tma_friendly(t: Tensor) -> Tensor:
+    """Tensor-map requirements of the tcgen05 / decode kernels: 16-byte aligned
+    base and strides that are multiples of 16 bytes.  Anything else is copied."""
+    t = _last_dim_contig(t)
+    if t.element_size() != 2:
+        return t
+    ok = t.data_ptr() % 16 == 0 and all(s % 8 == 0 for s in t.stride()[:-1])
+    return t if ok else t.contiguous()
+
+
+def _strides_bsh(t: Tensor, seq_dim: Optional[int]) -> Tuple[int, int, int]:
+    """(batch, seq, head) element strides of a 4-D (seq_dim 1 or 2) or packed 3-D tensor."""
+    if t.dim() == 3:
+        return 0, t.stride(0), t.stride(1)
+    hdim = 3 - seq_dim
+    return t.stride(0), t.stride(seq_dim), t.stride(hdim)
+
+
+class _Plan:
+    """Kernel-side view of a module's layouts: block-level CSR/CSC and what the
+    launchers need to know without touching the device."""
+
+    def __init__(self, crow: Tensor, col: Tensor, ccol: Tensor, row: Tensor, block_size: int,
+                 max_row_nnz: int):
+        self.crow, self.col, self.ccol, self.row = crow, col, ccol, row
+        self.block_size = block_size
+        self.max_row_nnz = max_row_nnz
+        self._group_shared: Dict[int, bool] = {}
+
+    def heads_shared_in_group(self, hq: int, hkv: int) -> bool:
+        """True when all q heads of a kv group use the same pattern rows (then the
+        decode kernel stacks them into one tensor-core tile)."""
+        hp = self.crow.size(0)
+        if hp == 1 or hp == hkv or hq == hkv:
+            return True
+        if hkv not in self._group_shared:
+            g = hq // hkv
+            cr = self.crow.reshape(hkv, g, -1)
+            cc = self.col.reshape(hkv, g, -1)
+            same = bool((cr == cr[:, :1]).all().item()) and bool((cc == cc[:, :1]).all().item())
+            self._group_shared[hkv] = same
+        return self._group_shared[hkv]
+
+
+def _fill_layout(p, plan: _Plan) -> None:
+    p.crow, p.col = _lib.ptr(plan.crow), _lib.ptr(plan.col)
+    p.crow_sh = plan.crow.stride(0) if plan.crow.size(0) > 1 else 0
+    p.col_sh = plan.col.stride(0) if plan.col.size(0) > 1 else 0
+    p.h_pat = plan.crow.size(0)
+    p.n_rows = plan.crow.size(1) - 1
+    p.block_size = plan.block_size
+
+
+def _fwd_params(q, k, v, o, lse, seq_dim, plan: _Plan, sm_scale, causal, row_mode,
+                q_start=None, q_end=None, k_start=None, k_end=None, total_q=0, impl=0):
+    p = _lib.FwdParams()
+    p.q, p.k, p.v, p.o, p.lse = _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(lse)
+    p.q_sb, p.q_ss, p.q_sh = _strides_bsh(q, seq_dim)
+    p.k_sb, p.k_ss, p.k_sh = _strides_bsh(k, seq_dim)
+    p.v_sb, p.v_ss, p.v_sh = _strides_bsh(v, seq_dim)
+    p.o_sb, p.o_ss, p.o_sh = _strides_bsh(o, seq_dim)
+    if q.dim() == 3:
+        p.batch = q_start.numel()
+        p.hq, p.hkv, p.d = q.size(1), k.size(1), q.size(2)
+        p.sq, p.sk = q.size(0), k.size(0)
+        if lse is not None:          # (Hq, total tokens)
+            p.lse_sb, p.lse_sh = 0, lse.stride(0)
+    else:
+        hdim = 3 - seq_dim
+        p.batch, p.hq, p.hkv, p.d = q.size(0), q.size(hdim), k.size(hdim), q.size(3)
+        p.sq, p.sk = q.size(seq_dim), k.size(seq_dim)
+        if lse is not None:          # (B, Hq, Sq)
+            p.lse_sb, p.lse_sh = lse.stride(0), lse.stride(1)
+    p.total_q = total_q
+    p.q_start, p.q_end = _lib.ptr(q_start), _lib.ptr(q_end)
+    p.k_start, p.k_end = _lib.ptr(k_start), _lib.ptr(k_end)
+    _fill_layout(p, plan)
+    p.causal = 1 if causal else 0
+    p.row_mode = row_mode
+    p.dtype = _lib.dtype_code(q.dtype)
+    p.impl = impl
+    p.sm_scale = float(sm_scale)
+    return p
+
+
+def _check_inputs(q: Tensor, k: Tensor, v: Tensor) -> None:
+    for n, t in (("q", q), ("k", k), ("v", v)):
+        _lib.require_cuda(t, n)
+    assert q.dtype == k.dtype == v.dtype, f"q/k/v dtypes differ: {q.dtype}, {k.dtype}, {v.dtype}"
+    assert q.device == k.device == v.device
+    _lib.dtype_code(q.dtype)
+
+
+_IMPL_NAMES = {None: _lib.IMPL_AUTO, "auto": _lib.IMPL_AUTO, "generic": _lib.IMPL_GENERIC,
+               "sm100": _lib.IMPL_SM100}
+
+
+def _decode_eligible(q: Tensor, plan: _Plan, impl: int) -> bool:
+    return (impl != _lib.IMPL_GENERIC and q.dtype in (torch.float16, torch.bfloat16)
+            and q.size(-1) in (64, 128) and plan.block_size in (64, 128))
+
+
+def _pick_heads_per_cta(g: int) -> int:
+    for c in range(min(g, 16), 0, -1):
+        if g % c == 0:
+            return c
+    return 1
+
+
+def decode(q: Tensor, k: Tensor, v: Tensor, plan: _Plan, sm_scale: float, *, seq_dim: Optional[int],
+           k_start: Optional[Tensor] = None, k_end: Optional[Tensor] = None,
+           k_pos0: Optional[Tensor] = None, k_total: Optional[Tensor] = None,
+           out: Optional[Tensor] = None, blocks_per_split: int = 0,
+           workspace: Optional[Tensor] = None) -> Tuple[Tensor, Tensor]:
+    """One query token per sequence (split-KV decode kernel).
+
+    q: (B,1,Hq,D)/(B,Hq,1,D) or packed (B,Hq,D); k, v: 4-D with the module's
+    seq_dim, or packed (T,Hkv,D) with ``k_start``/``k_end`` = cu_seqlens slices.
+    ``k_pos0``/``k_total`` describe a KV shard (see include/bsa.h).
+    Returns (out shaped like q, lse fp32 (B,Hq))."""
+    lib = _lib.lib()
+    if q.dim() == 4:
+        B = q.size(0)
+        hdim = 3 - seq_dim
+        hq, d = q.size(hdim), q.size(3)
+        q_sb, q_sh = q.stride(0), q.stride(hdim)
+    else:
+        B, hq, d = q.shape
+        q_sb, q_sh = q.stride(0), q.stride(1)
+    o = out if out is not None else torch.empty(q.shape, dtype=q.dtype, device=q.device)
+    assert o.is_contiguous(), "decode output must be contiguous"
+    lse = torch.empty((B, hq), dtype=torch.float32, device=q.device)
+    p = _lib.DecodeParams()
+    k = _tma_friendly(k)
+    v = _tma_friendly(v)
+    q = _last_dim_contig(q)
+    p.q, p.k, p.v, p.o, p.lse = _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(lse)
+    p.q_sb, p.q_sh = q_sb, q_sh
+    p.k_sb, p.k_ss, p.k_sh = _strides_bsh(k, seq_dim)
+    p.v_sb, p.v_ss, p.v_sh = _strides_bsh(v, seq_dim)
+    p.o_sb, p.o_sh = hq * d, d
+    p.lse_sb, p.lse_sh = hq, 1
+    if k.dim() == 3:
+        hkv, sk = k.size(1), k.size(0)
+    else:
+        hkv, sk = k.size(3 - seq_dim), k.size(seq_dim)
+    p.batch, p.hq, p.hkv, p.d, p.sk = B, hq, hkv, d, sk
+    p.k_start, p.k_end = _lib.ptr(k_start), _lib.ptr(k_end)
+    p.k_pos0, p.k_total = _lib.ptr(k_pos0), _lib.ptr(k_total)
+    _fill_layout(p, plan)
+    g = hq // hkv
+    p.heads_per_cta = _pick_heads_per_cta(g) if plan.heads_shared_in_group(hq, hkv) else 1
+    p.blocks_per_split = blocks_per_split if blocks_per_split > 0 else 8
+    p.max_row_nnz = plan.max_row_nnz
+    p.dtype = _lib.dtype_code(q.dtype)
+    p.sm_scale = float(sm_scale)
+    need = lib.bsa_decode_workspace_bytes(C.byref(p))
+    ws = None
+    if need:
+        if workspace is not None and workspace.numel() * workspace.element_size() >= need:
+            ws = workspace
+        else:
+            ws = torch.empty((need + 3) // 4, dtype=torch.float32, device=q.device)
+    p.ws = _lib.ptr(ws)
+    with torch.cuda.device(q.device):
+        _lib.check(lib.bsa_decode(C.byref(p), _lib.stream_of(q)), "bsa_decode")
+    return o, lse
+
+
+# --------------------------------------------------------------------------- routes
+def _varlen(q, k, v, cu_seqlens_k, cu_seqlens_q, sm_scale, plan, causal, out, impl, return_lse):
+    """Packed variable-length batch (dkernel/ops/sparse_attn_inference.py:150-287).
+    Unlike the reference nothing is copied to the host: the kernels read the
+    cu_seqlens on the device and enumerate q tiles themselves."""
+    assert q.dim() == k.dim() == v.dim() == 3
+    assert q.size(1) % k.size(1) == 0
+    assert q.size(2) == k.size(2)
+    assert k.shape == v.shape
+    assert cu_seqlens_k.dim() == 1
+    batch = cu_seqlens_k.size(0) - 1
+    cu_k = cu_seqlens_k.to(device=q.device, dtype=torch.int32).contiguous()
+    decoding = False
+    if cu_seqlens_q is None:
+        if q.size(0) == batch and q.size(0) != k.size(0):
+            decoding = True
+        elif q.size(0) == k.size(0):
+            cu_q = cu_k
+        else:
+            raise ValueError("cu_seqlens_q must be specified if it mix of prefilling and decoding.")
+    else:
+        assert cu_seqlens_k.size(0) == cu_seqlens_q.size(0)
+        cu_q = cu_seqlens_q.to(device=q.device, dtype=torch.int32).contiguous()
+    if decoding and _decode_eligible(q, plan, impl):
+        o, lse = decode(q, k, v, plan, sm_scale, seq_dim=None, k_start=cu_k[:-1], k_end=cu_k[1:],
+                        out=out)
+        return o, (lse.transpose(0, 1) if return_lse else None)
+    if decoding:
+        cu_q = torch.arange(0, batch + 1, dtype=torch.int32, device=q.device)
+    q, k, v = _tma_friendly(q), _tma_friendly(k), _tma_friendly(v)
+    o = out if out is not None else torch.empty(q.shape, dtype=q.dtype, device=q.device)
+    lse = torch.full((q.size(1), q.size(0)), float("-inf"), dtype=torch.float32, device=q.device) \
+        if return_lse else None
+    p = _fwd_params(q, k, v, o, lse, None, plan, sm_scale, causal, _lib.ROWS_BY_POSITION,
+                    cu_q[:-1], cu_q[1:], cu_k[:-1], cu_k[1:], total_q=q.size(0), impl=impl)
+    with torch.cuda.device(q.device):
+        _lib.check(_lib.lib().bsa_fwd(C.byref(p), _lib.stream_of(q)), "bsa_fwd")
+    return o, lse
+
+
+def _padded(q, k, v, sm_scale, plan, left_paddings, seqlens, seq_dim, max_seqlen, causal, out,
+            impl, return_lse):
+    """Left/right padded batch (dkernel/ops/sparse_attn_inference.py:10-147): pad
+    rows of the output are zero, positions are re-based to the first real token."""
+    assert seq_dim in (1, 2)
+    hdim = 3 - seq_dim
+    batches = q.size(0)
+    q_len, k_len = q.size(seq_dim), k.size(seq_dim)
+    assert q.dim() == k.dim() == v.dim() == 4
+    assert q.size(hdim) % k.size(hdim) == 0
+    assert q.size(0) == k.size(0) and q.size(3) == k.size(3)
+    assert k.shape == v.shape
+    assert q_len == 1 or q_len == k_len, \
+        (f"q length can only 1 for decoding or the same as k length for prefilling, "
+         f"but got {q_len=}, {k_len=}.")
+    if max_seqlen:
+        assert k_len <= max_seqlen, f"k has seqlen {k_len} while max sequence length is set to {max_seqlen}."
+    dev = q.device
+    if left_paddings is not None:
+        assert left_paddings.shape == (batches,)
+        k_starts = left_paddings.to(dev, dtype=torch.int32).contiguous()
+    else:
+        k_starts = torch.zeros((batches,), dtype=torch.int32, device=dev)
+    if seqlens is not None:
+        k_ends = k_starts + seqlens.to(dev, dtype=torch.int32)
+    else:
+        k_ends = torch.full_like(k_starts, k_len)
+    if q_len == 1 and _decode_eligible(q, plan, impl):
+        o, lse = decode(q, k, v, plan, sm_scale, seq_dim=seq_dim, k_start=k_starts, k_end=k_ends, out=out)
+        return o, (lse.unsqueeze(-1) if return_lse else None)
+    if q_len == 1:
+        q_starts = torch.zeros_like(k_starts)
+        q_ends = q_starts + 1
+    else:
+        q_starts, q_ends = k_starts, k_ends
+    q, k, v = _tma_friendly(q), _tma_friendly(k), _tma_friendly(v)
+    o = out if out is not None else torch.zeros(q.shape, dtype=q.dtype, device=dev)
+    lse = torch.full((batches, q.size(hdim), q_len), float("-inf"), dtype=torch.float32, device=dev) \
+        if return_lse else None
+    p = _fwd_params(q, k, v, o, lse, seq_dim, plan, sm_scale, causal, _lib.ROWS_BY_POSITION,
+                    q_starts, q_ends, k_starts, k_ends, impl=impl)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().bsa_fwd(C.byref(p), _lib.stream_of(q)), "bsa_fwd")
+    return o, lse
+
+
+def _train_forward(ctx, q, k, v, sm_scale, plan, seq_dim, causal, out, impl, need_lse, inference):
+    """Un-padded forward (dkernel/ops/sparse_attn_fwd.py:383-567).  Pattern rows are
+    q tile indices; a single query token uses the row of the last key block
+    (:435-440)."""
+    assert seq_dim in (1, 2)
+    hdim = 3 - seq_dim
+    assert q.shape[-1] == k.shape[-1] == v.shape[-1]
+    assert k.shape[seq_dim] == v.shape[seq_dim]
+    qlen, klen = q.size(seq_dim), k.size(seq_dim)
+    hq, hkv = q.size(hdim), k.size(hdim)
+    assert hq % hkv == 0
+    dev = q.device
+    if qlen == 1 and klen > 1 and inference and _decode_eligible(q, plan, impl):
+        o, lse = decode(q, k, v, plan, sm_scale, seq_dim=seq_dim, out=out)
+        return o, lse.unsqueeze(-1)
+    row_mode = _lib.ROWS_BY_POSITION if qlen == 1 else _lib.ROWS_BY_TILE
+    q, k, v = _tma_friendly(q), _tma_friendly(k), _tma_friendly(v)
+    o = out if out is not None else torch.empty(q.shape, dtype=q.dtype, device=dev)
+    lse = torch.empty((q.size(0), hq, qlen), dtype=torch.float32, device=dev) if need_lse else None
+    p = _fwd_params(q, k, v, o, lse, seq_dim, plan, sm_scale, causal, row_mode, impl=impl)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().bsa_fwd(C.byref(p), _lib.stream_of(q)), "bsa_fwd")
+    if ctx is not None and not inference:
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.sm_scale, ctx.seq_dim, ctx.causal, ctx.plan, ctx.impl = sm_scale, seq_dim, causal, plan, impl
+    return o, lse
+
+
+def _backward(ctx, do: Tensor, dlse: Optional[Tensor], dq=None, dk=None, dv=None):
+    """dQ / dK / dV of the un-padded forward (dkernel/ops/sparse_attn_bwd.py:724-852)."""
+    q, k, v, o, lse = ctx.saved_tensors
+    seq_dim, plan = ctx.seq_dim, ctx.plan
+    do = _tma_friendly(do)
+    if dq is None:
+        dq = torch.empty_like(q, memory_format=torch.contiguous_format)
+    if dk is None:
+        dk = torch.empty_like(k, memory_format=torch.contiguous_format)
+    if dv is None:
+        dv = torch.empty_like(v, memory_format=torch.contiguous_format)
+    for n, t in (("dq", dq), ("dk", dk), ("dv", dv)):
+        assert t.stride(-1) == 1, f"{n} must be contiguous in the head dimension"
+    bp = _lib.BwdParams()
+    bp.f = _fwd_params(q, k, v, o, lse, seq_dim, plan, ctx.sm_scale, ctx.causal, _lib.ROWS_BY_TILE,
+                       impl=ctx.impl)
+    bp.d_o = _lib.ptr(do)
+    bp.do_sb, bp.do_ss, bp.do_sh = _strides_bsh(do, seq_dim)
+    if dlse is not None:
+        dlse = dlse.to(torch.float32).contiguous()     # (B, Hq, Sq), same strides as lse
+        assert dlse.shape == lse.shape
+    bp.d_lse = _lib.ptr(dlse)
+    bp.dq, bp.dk, bp.dv = _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv)
+    bp.dq_sb, bp.dq_ss, bp.dq_sh = _strides_bsh(dq, seq_dim)
+    bp.dk_sb, bp.dk_ss, bp.dk_sh = _strides_bsh(dk, seq_dim)
+    bp.dv_sb, bp.dv_ss, bp.dv_sh = _strides_bsh(dv, seq_dim)
+    bp.ccol, bp.row = _lib.ptr(plan.ccol), _lib.ptr(plan.row)
+    bp.ccol_sh = plan.ccol.stride(0) if plan.ccol.size(0) > 1 else 0
+    bp.row_sh = plan.row.stride(0) if plan.row.size(0) > 1 else 0
+    bp.n_cols = plan.ccol.size(1) - 1
+    delta = torch.empty(lse.shape, dtype=torch.float32, device=q.device)
+    bp.delta = _lib.ptr(delta)
+    with torch.cuda.device(q.device):
+        _lib.check(_lib.lib().bsa_bwd(C.byref(bp), _lib.stream_of(q)), "bsa_bwd")
+    return dq, dk, dv
+
+
+# --------------------------------------------------------------------------- autograd
+class _sparse_attention(torch.autograd.Function):
+
+    @staticmethod
+    def forward(ctx,
+                q: Tensor,
+                k: Optional[Tensor],
+                v: Optional[Tensor],
+                sm_scale: float,
+                layout_csr: Tuple[Tensor, Tensor, int, int],
+                layout_csc: Tuple[Tensor, Tensor, int, int],
+                seq_dim: Optional[int],
+                inf_kwargs: Dict,
+                kwargs: Dict):
+        (q, k, v), (packed_shape, packed_mode, split_qkv) = \
+            get_qkv_and_pack_mode(q, k, v, split_qkv=kwargs.get("split_qkv", None))
+        ctx.packed_shape, ctx.packed_mode, ctx.split_qkv = packed_shape, packed_mode, split_qkv
+        _check_inputs(q, k, v)
+
+        plan: _Plan = kwargs["_plan"]
+        seq_dim = 1 if seq_dim is None else seq_dim
+        max_seqlen = kwargs.get("max_seqlen", None)
+        causal = kwargs.get("causal", True)
+        return_lse = kwargs.get("return_lse", False)
+        out = kwargs.get("out", None)
+        impl = _IMPL_NAMES[kwargs.get("impl", None)]
+
+        hdim = 3 - (seq_dim or 1) if q.dim() == 4 else 1
+        n_pat = layout_csr[0].size(0)
+        assert n_pat in [1, k.size(hdim), q.size(hdim)], \
+            (f"Input (q, k) have ({q.size(hdim)}, {k.size(hdim)}) heads"
+             f"but the number of heads in the sparse pattern is {n_pat}")
+        sm_scale = sm_scale or 1. / math.sqrt(float(q.size(-1)))
+        assert q.dim() in (3, 4)
+
+        needs_grad = q.requires_grad or k.requires_grad or v.requires_grad
+        if q.dim() == 3:
+            assert inf_kwargs.get("cu_seqlen_k", None) is not None
+            ctx.support_backward = False
+            ctx.message = "Currently does not suppoort variable length inputs. WIP."
+            output, lse = _varlen(q, k, v, inf_kwargs["cu_seqlen_k"], inf_kwargs.get("cu_seqlen_q", None),
+                                  sm_scale, plan, causal, out, impl, return_lse)
+        else:
+            assert k.size(seq_dim) <= max_seqlen, \
+                (f"Input length {k.size(seq_dim)} is larger "
+                 f"than the maximum length allowed ({max_seqlen})")
+            left_paddings = inf_kwargs.get("left_paddings", None)
+            seqlens = inf_kwargs.get("seqlens", None)
+            if (left_paddings is not None) or (seqlens is not None):
+                ctx.support_backward = False
+                ctx.message = "Currently does not support paddings in inputs. WIP."
+                output, lse = _padded(q, k, v, sm_scale, plan, left_paddings, seqlens, seq_dim,
+                                      max_seqlen, causal, out, impl, return_lse)
+            else:
+                ctx.support_backward = True
+                ctx.message = ""
+                inference = kwargs.get("inference", None)
+                if inference is None:
+                    inference = not needs_grad
+                output, lse = _train_forward(ctx, q, k, v, sm_scale, plan, seq_dim, causal, out, impl,
+                                             need_lse=return_lse or not inference, inference=inference)
+        if not return_lse:
+            lse = None
+        if lse is not None and not ctx.support_backward:
+            ctx.mark_non_differentiable(lse)
+        return output, lse
+
+    @staticmethod
+    def backward(ctx, do: Tensor, dlse: Optional[Tensor]) -> Tuple[Union[Tensor, None], ...]:
+        assert ctx.support_backward, ctx.message
+        q, k = ctx.saved_tensors[:2]
+        dq, dk, dv = None, None, None
+        if ctx.packed_mode == 'packed_qkv':
+            dqkv = q.new_empty(ctx.packed_shape)
+            dq, dk, dv = ctx.split_qkv(dqkv)
+        elif ctx.packed_mode == 'packed_kv':
+            dkv = k.new_empty(ctx.packed_shape)
+            dk, dv = ctx.split_qkv(dkv)
+        dq, dk, dv = _backward(ctx, do, dlse, dq=dq, dk=dk, dv=dv)
+        if ctx.packed_mode == 'packed_qkv':
+            grads = (dqkv, None, None)
+        elif ctx.packed_mode == 'packed_kv':
+            grads = (dq, dkv, None)
+        else:
+            grads = (dq, dk, dv)
+        return grads + (None,) * 6
+
+
+def get_qkv_and_pack_mode(q: Tensor, k: Optional[Tensor], v: Optional[Tensor],
+                          split_qkv: Optional[callable] = None):
+    """dkernel/ops/__init__.py:128-149: unpack a packed qkv (k, v None) or a packed
+    kv (v None) through the user's ``split_qkv`` callable."""
+    qkv_pack_mode = 'split_qkv'
+    packed_shape = None
+    if v is None:
+        assert split_qkv is not None, "Callable `split_qkv` must be specified if qkv or kv are packed."
+        if k is None:
+            packed_shape = q.shape
+            q, k, v = split_qkv(q)
+            qkv_pack_mode = 'packed_qkv'
+        else:
+            packed_shape = k.shape
+            k, v = split_qkv(k)
+            qkv_pack_mode = 'packed_kv'
+    return (q, k, v), (packed_shape, qkv_pack_mode, split_qkv)
+
+
+__all__ = ["_sparse_attention", "get_qkv_and_pack_mode", "decode"]

@@ -1,0 +1,235 @@
+/* bsa.h -- C ABI of the B200 block-sparse attention library (libbsa_b200.so).
+ *
+ * The reference (linxihui/dkernel) has no FFI: its device boundary is a set of
+ * Triton launches made from Python.  Each entry point below replaces one of
+ * those launch sites (cited per function, paths relative to the reference
+ * project).  The host package calls them through ctypes.
+ *
+ * Conventions
+ *  - Every pointer is a device pointer owned by the caller (PyTorch allocates
+ *    inputs, outputs, layouts and workspaces); the library never allocates or
+ *    frees device memory and never synchronises.  Work is enqueued on `stream`
+ *    (a cudaStream_t passed as void*).
+ *  - Strides are in ELEMENTS, the head dimension is contiguous (stride 1).
+ *  - Return value: 0 on success, a negative BSA_E_* code otherwise; the text of
+ *    the last error of the calling thread is available from bsa_last_error().
+ *    Nothing aborts, traps or throws across the boundary.
+ *  - Thread safety: entry points may be called concurrently from several host
+ *    threads and for several devices; the current CUDA device of the calling
+ *    thread must be the one that owns the pointers.
+ */
+#ifndef BSA_B200_H_
+#define BSA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BSA_ABI_VERSION 1
+
+enum {
+  BSA_OK = 0,
+  BSA_E_BADARG = -1,      /* null pointer, negative size, inconsistent shapes   */
+  BSA_E_UNSUPPORTED = -2, /* shape / dtype / stride not handled by any kernel   */
+  BSA_E_CUDA = -3,        /* a CUDA runtime or driver call failed               */
+  BSA_E_TOOBIG = -4       /* problem exceeds a documented fixed limit           */
+};
+
+enum { BSA_F16 = 0, BSA_BF16 = 1, BSA_F32 = 2 };
+
+/* which kernel family serves a call */
+enum { BSA_IMPL_AUTO = 0, BSA_IMPL_GENERIC = 1, BSA_IMPL_SM100 = 2 };
+
+/* how the pattern row of a query tile is chosen */
+enum {
+  BSA_ROWS_BY_TILE = 0,    /* row = q tile index (training path,
+                              dkernel/ops/sparse_attn_fwd.py:289-291)           */
+  BSA_ROWS_BY_POSITION = 1 /* row = (past_len + tile start) / block, positions
+                              re-based per sequence (inference path,
+                              dkernel/ops/sparse_attn_inference.py:503-514)     */
+};
+
+int bsa_abi_version(void);
+const char* bsa_last_error(void);
+
+/* ---------------------------------------------------------------------------
+ * Sparse-layout builder.  Replaces the CPU/numpy round trip of
+ * dkernel/utils.py:105-229 (get_sparse_attn_mask) and :19-65,:91-95
+ * (dense_to_crow_col / dense_to_ccol_row).
+ * ------------------------------------------------------------------------- */
+typedef struct {
+  int32_t num_heads;          /* q heads described (rows of the mask's head axis) */
+  int32_t num_kv_heads;       /* <= num_heads, divides it                         */
+  int32_t num_dense_heads;    /* last kv heads that are dense                     */
+  int32_t q_blocks;           /* rows of the block mask before trimming           */
+  int32_t kv_blocks;
+  int32_t q_start_block;      /* q_start_position / block_size                    */
+  int32_t kv_start_block;     /* kv_start_position / block_size                   */
+  int32_t trim_q_blocks;      /* cdiv(past_len, block_size): rows dropped on top  */
+  int32_t local_left;         /* local_blocks (left, including the diagonal)      */
+  int32_t local_right;        /* 1 when causal                                    */
+  int32_t vert_stride;
+  int32_t head_sliding_step;  /* already resolved: max(1, vert_stride/num_heads)  */
+  int32_t head_sliding_offset;
+  int32_t causal;
+  int32_t absolute_vert;      /* 1 = absolute vertical positions, 0 = relative    */
+} bsa_local_stride_params;
+
+/* Writes the uint8 block mask (num_heads, q_blocks - trim_q_blocks, kv_blocks),
+ * contiguous.  dkernel/utils.py:182-220. */
+int bsa_local_stride_mask(const bsa_local_stride_params* p, uint8_t* mask, void* stream);
+
+/* CSR row pointers of a (H, M, N) uint8 mask with arbitrary element strides:
+ * crow (H, M+1) int32 contiguous, nnz (H,) int32 = crow[:, M].
+ * For the CSC layout pass the mask with its last two strides swapped.
+ * dkernel/utils.py:19-24 (to_csr: cumsum of row counts). */
+int bsa_csr_row_ptr(const uint8_t* mask, int32_t H, int32_t M, int32_t N,
+                    int64_t stride_h, int64_t stride_m, int64_t stride_n,
+                    int32_t* crow, int32_t* nnz, void* stream);
+
+/* Column indices in row-major order, every head padded with -1 up to `width`
+ * entries (width >= max nnz).  With val != NULL the value of each non-zero is
+ * stored too (0 in the padding): the (col, value) pairs of
+ * dense_to_crow_col(include_values=True) are written interleaved when
+ * interleave_values != 0 (col has 2*width ints per head).
+ * dkernel/utils.py:47-61. */
+int bsa_csr_fill_cols(const uint8_t* mask, int32_t H, int32_t M, int32_t N,
+                      int64_t stride_h, int64_t stride_m, int64_t stride_n,
+                      const int32_t* crow, int32_t* col, int32_t width,
+                      int32_t interleave_values, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Attention forward.  Replaces the launches of _sparse_fwd_kernel
+ * (dkernel/ops/sparse_attn_fwd.py:519-546) and _fwd_kernel_batch_inference
+ * (dkernel/ops/sparse_attn_inference.py:113-145, :245-285).
+ * ------------------------------------------------------------------------- */
+typedef struct {
+  const void* q; const void* k; const void* v; void* o;
+  float* lse;                 /* may be NULL; natural-log LSE of scaled logits  */
+  int64_t q_sb, q_ss, q_sh;   /* batch / sequence / head strides                */
+  int64_t k_sb, k_ss, k_sh;
+  int64_t v_sb, v_ss, v_sh;
+  int64_t o_sb, o_ss, o_sh;
+  int64_t lse_sb, lse_sh;     /* LSE sequence stride is 1                       */
+  int32_t batch, hq, hkv, d;
+  int32_t sq, sk;             /* storage lengths of the sequence axis           */
+  int32_t total_q;            /* packed batch: upper bound of sum(q lengths); the
+                                 q tiles of all sequences are then enumerated
+                                 back to back.  0 = dense (batch, sq) grid        */
+  /* optional per-sequence storage ranges, (batch,) int32; NULL = [0,sq)/[0,sk).
+   * A packed (varlen) batch passes batch strides 0 and the cu_seqlens slices.   */
+  const int32_t* q_start; const int32_t* q_end;
+  const int32_t* k_start; const int32_t* k_end;
+  /* block-level CSR of the pattern: crow (h_pat, n_rows+1), col (h_pat, *)      */
+  const int32_t* crow; const int32_t* col;
+  int64_t crow_sh, col_sh;    /* head strides (0 for one shared pattern)        */
+  int32_t h_pat;              /* 1, hkv or hq                                   */
+  int32_t n_rows;             /* pattern rows available in crow                 */
+  int32_t block_size;         /* sparse block size (power of two, 16..128)      */
+  int32_t causal;
+  int32_t row_mode;           /* BSA_ROWS_BY_*                                  */
+  int32_t dtype;              /* BSA_F16 / BSA_BF16 / BSA_F32                   */
+  int32_t impl;               /* BSA_IMPL_*                                     */
+  float sm_scale;
+} bsa_fwd_params;
+
+int bsa_fwd(const bsa_fwd_params* p, void* stream);
+
+/* 1 if the tcgen05 kernel serves these parameters, 0 if the generic kernel
+ * does, negative on invalid parameters. */
+int bsa_fwd_uses_sm100(const bsa_fwd_params* p);
+
+/* ---------------------------------------------------------------------------
+ * Attention backward.  Replaces _bwd_preprocess + _sparse_bwd_kernel
+ * (dkernel/ops/sparse_attn_bwd.py:781-788, :811-850).  dQ walks the CSR, dK/dV
+ * walk the CSC; every gradient tile is written once (no atomics).
+ * ------------------------------------------------------------------------- */
+typedef struct {
+  bsa_fwd_params f;           /* same problem description; f.o = forward output,
+                                 f.lse = forward LSE (required)                 */
+  const void* d_o;            /* dO, strides do_*                               */
+  const float* d_lse;         /* optional gradient w.r.t. LSE, strides as f.lse */
+  int64_t do_sb, do_ss, do_sh;
+  void* dq; void* dk; void* dv;
+  int64_t dq_sb, dq_ss, dq_sh;
+  int64_t dk_sb, dk_ss, dk_sh;
+  int64_t dv_sb, dv_ss, dv_sh;
+  const int32_t* ccol; const int32_t* row;   /* CSC of the pattern              */
+  int64_t ccol_sh, row_sh;
+  int32_t n_cols;             /* pattern columns available in ccol              */
+  float* delta;               /* workspace (batch*hq*sq) fp32                   */
+} bsa_bwd_params;
+
+int bsa_bwd(const bsa_bwd_params* p, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Decode: one query token per sequence against contiguous (un-paged) K/V.
+ * Replaces the q_len == 1 launches of _fwd_kernel_batch_inference
+ * (dkernel/ops/sparse_attn_inference.py:83-88, :141) and the sliced-crow decode
+ * of _forward (dkernel/ops/sparse_attn_fwd.py:435-440).  Split-KV: every
+ * (sequence, kv head, split) is one CTA; partial (O, m, l) go to the workspace
+ * and are merged by a second kernel.
+ * ------------------------------------------------------------------------- */
+typedef struct {
+  const void* q;              /* (batch, hq, d), strides q_sb, q_sh             */
+  const void* k; const void* v;
+  void* o; float* lse;        /* o like q; lse (batch, hq) or NULL              */
+  int64_t q_sb, q_sh;
+  int64_t k_sb, k_ss, k_sh;
+  int64_t v_sb, v_ss, v_sh;
+  int64_t o_sb, o_sh;
+  int64_t lse_sb, lse_sh;
+  int32_t batch, hq, hkv, d, sk;
+  const int32_t* k_start;     /* (batch,) first stored token, NULL = 0          */
+  const int32_t* k_end;       /* (batch,) one past the last stored token, NULL = sk */
+  /* KV sharding: the stored tokens of sequence b are positions
+   * [k_pos0[b], k_pos0[b] + k_end[b]-k_start[b]) of a sequence whose full
+   * length is k_total[b].  NULL = not sharded (pos0 = 0, total = stored).      */
+  const int32_t* k_pos0; const int32_t* k_total;
+  const int32_t* crow; const int32_t* col;
+  int64_t crow_sh, col_sh;
+  int32_t h_pat, n_rows, block_size;
+  int32_t heads_per_cta;      /* q heads of one kv group handled together;
+                                 they must share one pattern row (1 = safe)     */
+  int32_t blocks_per_split;   /* attended blocks per CTA                        */
+  int32_t max_row_nnz;        /* longest pattern row: bounds the split count    */
+  int32_t dtype;
+  float sm_scale;
+  float* ws;                  /* workspace, bsa_decode_workspace_bytes()        */
+} bsa_decode_params;
+
+size_t bsa_decode_workspace_bytes(const bsa_decode_params* p);
+int bsa_decode(const bsa_decode_params* p, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Merge of attention partials over key/value partitions.  Replaces the eager
+ * torch ops of combine_attn_partitions (dkernel/interface.py:319-324).
+ * o_parts: (P, rows, d) with stride part_stride_o between partitions and
+ * row_stride_o between rows; lse_parts: (P, rows) with strides part_stride_lse
+ * and row_stride_lse.  Writes o (rows, d) and, if non-NULL, the merged lse
+ * (rows, contiguous).  Partitions with LSE = -inf contribute nothing; a row
+ * whose partitions are all -inf gives o = 0, lse = -inf.
+ * ------------------------------------------------------------------------- */
+int bsa_merge_partials(const void* o_parts, const float* lse_parts, int32_t P,
+                       int64_t rows, int32_t d, int64_t part_stride_o,
+                       int64_t row_stride_o, int64_t part_stride_lse,
+                       int64_t row_stride_lse, void* o, int64_t o_row_stride,
+                       float* lse, int32_t dtype, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Device-side waits (on TMA / tensor-core completion barriers) are bounded.  A
+ * wait that gives up records a non-zero code in a device status word and the
+ * kernels of the library become no-ops until it is cleared.  This call
+ * synchronises the device, copies the word to *status and clears it when
+ * `reset` is non-zero.  0 = every wait completed.  No counterpart in the
+ * reference (Triton kernels have no such waits).
+ * ------------------------------------------------------------------------- */
+int bsa_wait_status(int32_t* status, int32_t reset);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BSA_B200_H_ */
