@@ -1,7 +1,478 @@
+// Prefill / training forward on the 5th-generation tensor cores.
+//
+// One CTA = one 128-row query tile made of two 64-row halves that share a kv
+// head, so every K/V block fetched by TMA feeds a full M=128 tcgen05.mma:
+//   * PAIR_HEADS (GQA, even group size): the halves are two q heads of one kv
+//     group at the same q block -- identical block lists, no wasted work;
+//   * PAIR_ROWS (otherwise): the halves are two adjacent q blocks of one head;
+//     the CTA walks the union of their block lists and a half that does not
+//     attend a block contributes P = 0 for it.
+// The per-head CSR rows of both halves are merged in shared memory (bitmaps ->
+// ordered list) before the pipeline starts.
+//
+// Warp roles (192 threads):  warps 0-3 softmax (thread r owns tile row r = TMEM
+// lane r: no cross-lane reductions at all), warp 4 TMA producer, warp 5 MMA issuer
+// and TMEM owner.  Per kv block j:
+//   S[j&1] = Q K_j^T          tcgen05.mma, A/B from 128B-swizzled smem, fp32 in TMEM
+//   P = exp2(S*c - m)          softmax warps: tcgen05.ld -> registers -> bf16/fp16 ->
+//                              tcgen05.st into the columns S occupied
+//   O += P V_j                 tcgen05.mma, A = P from TMEM, B = V (MN-major) from smem
+// S is double buffered so Q K_{j+1}^T overlaps softmax j; the running maximum is
+// only raised when it grows by more than 2^8 (the accumulator then gets rescaled
+// in TMEM), so the correction step is rare.  Two CTAs fit per SM (about 101 KB of
+// shared memory and 256 TMEM columns each), which lets one CTA's tensor-core
+// work hide the other's softmax.  Math follows
+// dkernel/ops/sparse_attn_fwd.py:90-165, :351-363 (base-2 online softmax, LSE).
 #include "ptx.cuh"
+
 namespace bsa {
-bool sm100_fwd_supported(const bsa_fwd_params*, const char** why) { *why = "not built yet"; return false; }
-int sm100_fwd(const bsa_fwd_params*, cudaStream_t) { return BSA_E_UNSUPPORTED; }
-bool sm100_bwd_supported(const bsa_bwd_params*, const char** why) { *why = "not built yet"; return false; }
-int sm100_bwd(const bsa_bwd_params*, cudaStream_t) { return BSA_E_UNSUPPORTED; }
+namespace {
+
+constexpr int kD = 128;
+constexpr int kBS = 64;
+constexpr int kFwdThreads = 192;
+constexpr int kMaxList = 1024;          // kv blocks per sequence (64K tokens)
+constexpr int kQBytes = 128 * kD * 2;   // 32 KB
+constexpr int kKVBytes = kBS * kD * 2;  // 16 KB per K or V tile
+constexpr int kStagesF = 2;
+constexpr float kRescaleThreshold = 8.0f;
+
+enum { kPairHeads = 0, kPairRows = 1 };
+
+struct FwdTail {
+  uint64_t q_full;
+  uint64_t k_full[kStagesF], v_full[kStagesF], k_empty[kStagesF], v_empty[kStagesF];
+  uint64_t s_full[2], p_full[2];
+  uint64_t pv_done;
+  uint32_t tmem_base;
+  int n_list;
+  uint32_t bits[2][kMaxList / 32];
+  uint32_t list[kMaxList];
+};
+
+constexpr size_t kFwdSmem = 1024 + kQBytes + kStagesF * 2 * kKVBytes + sizeof(FwdTail);
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
+
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  if (BF16) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+  } else {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+}
+
+struct Half {
+  int head, qblk, valid;
+};
+
+template <bool BF16>
+__global__ void __launch_bounds__(kFwdThreads, 2)
+fwd_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap4 tmK,
+                 const __grid_constant__ Tmap4 tmV, bsa_fwd_params p, int mode, int* wait_status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sKV = smem + kQBytes;  // stage s: K at s*32K, V at s*32K + 16K
+  FwdTail* tl = reinterpret_cast<FwdTail*>(smem + kQBytes + kStagesF * 2 * kKVBytes);
+
+  if (*reinterpret_cast<volatile int*>(wait_status) != 0) return;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  // ---------------------------------------------------------------- work item
+  const int G = p.hq / p.hkv;
+  const int tile_rows = mode == kPairHeads ? 64 : 128;
+  int b = blockIdx.z, tile;
+  if (p.total_q > 0) {
+    int acc = 0, found = 0;
+    tile = 0;
+    for (int i = 0; i < p.batch; ++i) {
+      const int len = p.q_end[i] - p.q_start[i];
+      const int n = len > 0 ? (len + tile_rows - 1) / tile_rows : 0;
+      if ((int)blockIdx.x < acc + n) { b = i; tile = blockIdx.x - acc; found = 1; break; }
+      acc += n;
+    }
+    if (!found) return;
+  } else {
+    tile = gridDim.x - 1 - blockIdx.x;  // long rows first
+  }
+  const int q_start = p.q_start ? p.q_start[b] : 0;
+  const int q_len = (p.q_end ? p.q_end[b] : p.sq) - q_start;
+  const int k_start = p.k_start ? p.k_start[b] : 0;
+  const int k_len = (p.k_end ? p.k_end[b] : p.sk) - k_start;
+  if (tile * tile_rows >= q_len) return;
+  const int past = (p.causal || p.row_mode == BSA_ROWS_BY_POSITION) ? k_len - q_len : 0;
+
+  Half hf[2];
+  int kvh;
+  if (mode == kPairHeads) {
+    const int pairs = G / 2;
+    kvh = blockIdx.y / pairs;
+    const int h0 = kvh * G + 2 * (blockIdx.y % pairs);
+    hf[0] = {h0, tile, 1};
+    hf[1] = {h0 + 1, tile, 1};
+  } else {
+    const int h = blockIdx.y;
+    kvh = h / G;
+    hf[0] = {h, 2 * tile, 1};
+    hf[1] = {h, 2 * tile + 1, (2 * tile + 1) * kBS < q_len ? 1 : 0};
+  }
+  const int nkb = min((k_len + kBS - 1) / kBS, kMaxList);
+
+  // ---------------------------------------------------------------- setup
+  if (tid == 0) {
+    mbar_init(&tl->q_full, 1);
+    for (int s = 0; s < kStagesF; ++s) {
+      mbar_init(&tl->k_full[s], 1);
+      mbar_init(&tl->v_full[s], 1);
+      mbar_init(&tl->k_empty[s], 1);
+      mbar_init(&tl->v_empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&tl->s_full[s], 1);
+      mbar_init(&tl->p_full[s], 128);
+    }
+    mbar_init(&tl->pv_done, 1);
+    mbar_fence_init();
+    tma_prefetch_desc(&tmQ.map);
+    tma_prefetch_desc(&tmK.map);
+    tma_prefetch_desc(&tmV.map);
+  }
+  if (tid < 2 * (kMaxList / 32)) (&tl->bits[0][0])[tid] = 0u;
+  __syncthreads();
+  // union of the two halves' block lists
+  for (int t = 0; t < 2; ++t) {
+    if (!hf[t].valid) continue;
+    const int q_first = hf[t].qblk * kBS;
+    const int row = (p.row_mode == BSA_ROWS_BY_POSITION ? past + q_first : q_first) / kBS;
+    if (row >= p.n_rows) continue;
+    const int hp = pattern_head(hf[t].head, p.h_pat, p.hq, p.hkv);
+    const int32_t* cr = p.crow + (int64_t)hp * p.crow_sh;
+    const int32_t* cols = p.col + (int64_t)hp * p.col_sh;
+    const int c_beg = cr[row], c_end = cr[row + 1];
+    const int q_pos_last = past + min(q_first + kBS, q_len) - 1;
+    for (int i = c_beg + tid; i < c_end; i += kFwdThreads) {
+      const int blk = cols[i];
+      if (blk >= 0 && blk < nkb && !(p.causal && blk * kBS > q_pos_last))
+        atomicOr(&tl->bits[t][blk >> 5], 1u << (blk & 31));
+    }
+  }
+  __syncthreads();
+  if (warp == 0) {
+    const uint32_t u0 = tl->bits[0][lane], u1 = tl->bits[1][lane];
+    uint32_t u = u0 | u1;
+    const int cnt = __popc(u);
+    int incl = cnt;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += t;
+    }
+    int pos = incl - cnt;
+    while (u) {
+      const int bit = __ffs(u) - 1;
+      u &= u - 1;
+      tl->list[pos++] = (uint32_t)(lane * 32 + bit) | (((u0 >> bit) & 1u) << 16) |
+                        (((u1 >> bit) & 1u) << 17);
+    }
+    if (lane == 31) tl->n_list = incl;
+  }
+  if (warp == 5) {
+    tmem_alloc(&tl->tmem_base, 256);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const int n = tl->n_list;
+  const uint32_t tmem = tl->tmem_base;
+  const uint32_t tS[2] = {tmem, tmem + 64};
+  const uint32_t tO = tmem + 128;
+
+  if (n > 0 && warp == 4) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      const uint32_t qbytes = (hf[0].valid + hf[1].valid) * (kQBytes / 2);
+      mbar_expect_tx(&tl->q_full, qbytes);
+      for (int t = 0; t < 2; ++t) {
+        if (!hf[t].valid) continue;
+        for (int c = 0; c < 2; ++c)
+          tma_load_tile(sQ + c * 16384 + t * 8192, &tmQ, &tl->q_full, c * 64,
+                        q_start + hf[t].qblk * kBS, hf[t].head, b);
+      }
+      for (int j = 0; j < n; ++j) {
+        const int s = j % kStagesF;
+        const uint32_t ph = ((j / kStagesF) & 1) ^ 1;
+        const int tok = k_start + (int)(tl->list[j] & 0xffffu) * kBS;
+        uint8_t* kdst = sKV + s * 2 * kKVBytes;
+        uint8_t* vdst = kdst + kKVBytes;
+        if (!mbar_wait(&tl->k_empty[s], ph, wait_status, 201)) break;
+        mbar_expect_tx(&tl->k_full[s], kKVBytes);
+        tma_load_tile(kdst, &tmK, &tl->k_full[s], 0, tok, kvh, b);
+        tma_load_tile(kdst + 8192, &tmK, &tl->k_full[s], 64, tok, kvh, b);
+        if (!mbar_wait(&tl->v_empty[s], ph, wait_status, 202)) break;
+        mbar_expect_tx(&tl->v_full[s], kKVBytes);
+        tma_load_tile(vdst, &tmV, &tl->v_full[s], 0, tok, kvh, b);
+        tma_load_tile(vdst + 8192, &tmV, &tl->v_full[s], 64, tok, kvh, b);
+      }
+    }
+  } else if (n > 0 && warp == 5) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc_qk = umma_idesc(BF16, 128, kBS, false, false);
+      const uint32_t idesc_pv = umma_idesc(BF16, 128, kD, false, true);
+      const uint32_t q_addr = smem_u32(sQ);
+      const uint32_t kv_addr = smem_u32(sKV);
+      bool ok = mbar_wait(&tl->q_full, 0, wait_status, 203);
+      auto issue_qk = [&](int j) {
+        const int s = j % kStagesF;
+        if (!mbar_wait(&tl->k_full[s], (j / kStagesF) & 1, wait_status, 204)) return false;
+        tc_fence_after();
+        const uint32_t kb = kv_addr + s * 2 * kKVBytes;
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            const uint64_t da = umma_desc_sw128(q_addr + c * 16384 + kk * 32, 16, 1024);
+            const uint64_t db = umma_desc_sw128(kb + c * 8192 + kk * 32, 16, 1024);
+            tc_mma_ss(tS[j & 1], da, db, idesc_qk, (c | kk) ? 1u : 0u);
+          }
+        tc_commit(&tl->k_empty[s]);
+        tc_commit(&tl->s_full[j & 1]);
+        return true;
+      };
+      if (ok) ok = issue_qk(0);
+      for (int j = 0; j < n && ok; ++j) {
+        if (j + 1 < n) ok = issue_qk(j + 1);
+        if (!ok) break;
+        const int s = j % kStagesF;
+        if (!mbar_wait(&tl->p_full[j & 1], (j >> 1) & 1, wait_status, 205)) break;
+        if (!mbar_wait(&tl->v_full[s], (j / kStagesF) & 1, wait_status, 206)) break;
+        tc_fence_after();
+        const uint32_t vb = kv_addr + s * 2 * kKVBytes + kKVBytes;
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          // V tile: rows = kv tokens (K of this product), 128 contiguous bytes = 64 head
+          // dims (N); the two 64-dim halves are 8 KB apart
+          const uint64_t db = umma_desc_sw128(vb + kk * 2048, 8192, 1024);
+          tc_mma_ts(tO, tS[j & 1] + kk * 8, db, idesc_pv, (j | kk) ? 1u : 0u);
+        }
+        tc_commit(&tl->v_empty[s]);
+        tc_commit(&tl->pv_done);
+      }
+    }
+    __syncwarp();
+  } else if (n > 0) {
+    // ------------------------------------------------------------ softmax (warps 0-3)
+    const int r = tid;            // tile row = TMEM lane
+    const int t = r >> 6;         // half
+    const int rr = r & 63;
+    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+    const float scale2 = p.sm_scale * kLog2e;
+    const int q_row = hf[t].qblk * kBS + rr;   // row inside the sequence
+    const int qpos = past + q_row;
+    float m_used = -INFINITY, l = 0.f;
+    bool alive = true;
+    for (int j = 0; j < n; ++j) {
+      if (!mbar_wait(&tl->s_full[j & 1], (j >> 1) & 1, wait_status, 207)) { alive = false; break; }
+      tc_fence_after();
+      uint32_t sv[64];
+      tmem_ld32(tS[j & 1] + lane_off, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
+      tmem_ld32(tS[j & 1] + lane_off + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
+      tmem_ld_wait();
+      const uint32_t ent = tl->list[j];
+      const int kbase = (int)(ent & 0xffffu) * kBS;
+      const bool att = ((ent >> (16 + t)) & 1u) != 0 && hf[t].valid;
+      float mx = -INFINITY;
+      if (att) {
+        const bool need_mask = (kbase + kBS > k_len) || (p.causal && kbase + kBS - 1 > qpos);
+#pragma unroll
+        for (int c = 0; c < 64; ++c) {
+          float x = __uint_as_float(sv[c]) * scale2;
+          if (need_mask) {
+            const int kpos = kbase + c;
+            if (!(kpos < k_len && (!p.causal || kpos <= qpos))) x = -INFINITY;
+          }
+          sv[c] = __float_as_uint(x);
+          mx = fmaxf(mx, x);
+        }
+      }
+      float alpha = 1.f;
+      bool need = false;
+      if (att && mx != -INFINITY) {
+        if (m_used == -INFINITY) {
+          m_used = mx;   // first attended block of this row: O row is still exactly 0
+        } else if (mx > m_used + kRescaleThreshold) {
+          alpha = ex2(m_used - mx);
+          m_used = mx;
+          l *= alpha;
+          need = true;
+        }
+      }
+      const bool any = __any_sync(0xffffffffu, need);
+      uint32_t pk[32];
+      if (att && m_used != -INFINITY) {
+        float sum = 0.f;
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const float p0 = ex2(__uint_as_float(sv[2 * c]) - m_used);
+          const float p1 = ex2(__uint_as_float(sv[2 * c + 1]) - m_used);
+          sum += p0 + p1;
+          pk[c] = pack2<BF16>(p0, p1);
+        }
+        l += sum;
+      } else {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) pk[c] = 0u;
+      }
+      tmem_st32(tS[j & 1] + lane_off, pk);
+      if (j > 0) {
+        // Every phase of pv_done is observed in order (a parity wait is only
+        // meaningful when the waiter is at most one phase behind).
+        if (!mbar_wait(&tl->pv_done, (j - 1) & 1, wait_status, 208)) { alive = false; break; }
+      }
+      if (any && j > 0) {
+        // rescale the accumulator rows whose maximum moved (P V_{j-1} has landed)
+        tc_fence_after();
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          uint32_t o[32];
+          tmem_ld32(tO + lane_off + ch * 32, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st32(tO + lane_off + ch * 32, o);
+        }
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&tl->p_full[j & 1]);
+    }
+    // ---- epilogue: O / l -> registers -> swizzled smem (the Q tile is dead) -> global
+    if (alive) alive = mbar_wait(&tl->pv_done, (n - 1) & 1, wait_status, 209);
+    tc_fence_after();
+    if (alive) {
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      uint8_t* stage = sQ + warp * 8192;  // this warp's 32 rows x 256 B
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t o[32];
+        tmem_ld32(tO + lane_off + ch * 32, o);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c4 = 0; c4 < 4; ++c4) {   // 4 chunks of 8 values = 16 bytes
+          uint4 w;
+          w.x = pack2<BF16>(__uint_as_float(o[c4 * 8 + 0]) * inv, __uint_as_float(o[c4 * 8 + 1]) * inv);
+          w.y = pack2<BF16>(__uint_as_float(o[c4 * 8 + 2]) * inv, __uint_as_float(o[c4 * 8 + 3]) * inv);
+          w.z = pack2<BF16>(__uint_as_float(o[c4 * 8 + 4]) * inv, __uint_as_float(o[c4 * 8 + 5]) * inv);
+          w.w = pack2<BF16>(__uint_as_float(o[c4 * 8 + 6]) * inv, __uint_as_float(o[c4 * 8 + 7]) * inv);
+          const int chunk = ch * 4 + c4;
+          *reinterpret_cast<uint4*>(stage + lane * 256 + ((chunk ^ (lane & 15)) << 4)) = w;
+        }
+      }
+      __syncwarp();
+      uint8_t* ob = reinterpret_cast<uint8_t*>(p.o);
+      for (int i = 0; i < 32; ++i) {
+        const int row = warp * 32 + i;
+        const int ht = row >> 6;
+        const int qr = hf[ht].qblk * kBS + (row & 63);
+        if (hf[ht].valid && qr < q_len) {
+          const int64_t off = ((int64_t)b * p.o_sb + (int64_t)hf[ht].head * p.o_sh +
+                               (int64_t)(q_start + qr) * p.o_ss) * 2 + lane * 8;
+          const uint2 w = *reinterpret_cast<const uint2*>(
+              stage + i * 256 + (((lane >> 1) ^ (i & 15)) << 4) + (lane & 1) * 8);
+          *reinterpret_cast<uint2*>(ob + off) = w;
+        }
+      }
+      if (p.lse && hf[t].valid && q_row < q_len)
+        p.lse[(int64_t)b * p.lse_sb + (int64_t)hf[t].head * p.lse_sh + q_start + q_row] =
+            l > 0.f ? (m_used + log2f(l)) * kLn2 : -INFINITY;
+    }
+  } else if (warp < 4) {
+    // no attended block at all: zero rows, LSE = -inf
+    const int r = tid, t = r >> 6;
+    const int q_row = hf[t].qblk * kBS + (r & 63);
+    if (hf[t].valid && q_row < q_len) {
+      uint4* dst = reinterpret_cast<uint4*>(
+          reinterpret_cast<uint8_t*>(p.o) +
+          ((int64_t)b * p.o_sb + (int64_t)hf[t].head * p.o_sh + (int64_t)(q_start + q_row) * p.o_ss) * 2);
+      // rows are only guaranteed 8-byte aligned
+      uint2* d2 = reinterpret_cast<uint2*>(dst);
+      for (int i = 0; i < 32; ++i) d2[i] = make_uint2(0u, 0u);
+      if (p.lse)
+        p.lse[(int64_t)b * p.lse_sb + (int64_t)hf[t].head * p.lse_sh + q_start + q_row] = -INFINITY;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) tmem_dealloc(tmem, 256);
+}
+
+}  // namespace
+
+bool sm100_fwd_supported(const bsa_fwd_params* p, const char** why) {
+  auto no = [&](const char* w) { *why = w; return false; };
+  if (!(p->dtype == BSA_F16 || p->dtype == BSA_BF16)) return no("dtype is not f16/bf16");
+  if (p->d != kD) return no("head dim is not 128");
+  if (p->block_size != kBS) return no("block size is not 64");
+  if (p->sk > kMaxList * kBS) return no("more than 65536 key positions");
+  if (!tma_compatible(p->q, 2, p->q_ss, p->q_sh, p->q_sb) ||
+      !tma_compatible(p->k, 2, p->k_ss, p->k_sh, p->k_sb) ||
+      !tma_compatible(p->v, 2, p->v_ss, p->v_sh, p->v_sb))
+    return no("q/k/v need 16-byte aligned bases and strides that are multiples of 16 bytes");
+  if (reinterpret_cast<uintptr_t>(p->o) % 8 || p->o_ss % 4 || p->o_sh % 4 || p->o_sb % 4)
+    return no("output rows are not 8-byte aligned");
+  if (p->sq == 0 || p->batch == 0) return no("empty problem");
+  return true;
+}
+
+int sm100_fwd(const bsa_fwd_params* p, cudaStream_t s) {
+  const bool bf16 = p->dtype == BSA_BF16;
+  Tmap4 tmQ, tmK, tmV;
+  int rc = make_tmap_4d(&tmQ, p->q, 2, kD, p->sq, p->hq, p->total_q > 0 ? 1 : p->batch, p->q_ss * 2,
+                        p->q_sh * 2, p->q_sb * 2, 64, 64, true, bf16);
+  if (rc) return rc;
+  rc = make_tmap_4d(&tmK, p->k, 2, kD, p->sk, p->hkv, p->total_q > 0 ? 1 : p->batch, p->k_ss * 2,
+                    p->k_sh * 2, p->k_sb * 2, 64, 64, true, bf16);
+  if (rc) return rc;
+  rc = make_tmap_4d(&tmV, p->v, 2, kD, p->sk, p->hkv, p->total_q > 0 ? 1 : p->batch, p->v_ss * 2,
+                    p->v_sh * 2, p->v_sb * 2, 64, 64, true, bf16);
+  if (rc) return rc;
+  const int G = p->hq / p->hkv;
+  const int mode = (G % 2 == 0) ? kPairHeads : kPairRows;
+  const int tile_rows = mode == kPairHeads ? 64 : 128;
+  const int head_items = mode == kPairHeads ? p->hq / 2 : p->hq;
+  dim3 grid;
+  if (p->total_q > 0)
+    grid = dim3(cdiv_i(p->total_q, tile_rows) + p->batch, head_items, 1);
+  else
+    grid = dim3(cdiv_i(p->sq, tile_rows), head_items, p->batch);
+  int* status = wait_status_ptr();
+  if (!status) return BSA_E_CUDA;
+  if (bf16) {
+    auto kern = fwd_sm100_kernel<true>;
+    BSA_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFwdSmem));
+    kern<<<grid, kFwdThreads, kFwdSmem, s>>>(tmQ, tmK, tmV, *p, mode, status);
+  } else {
+    auto kern = fwd_sm100_kernel<false>;
+    BSA_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFwdSmem));
+    kern<<<grid, kFwdThreads, kFwdSmem, s>>>(tmQ, tmK, tmV, *p, mode, status);
+  }
+  return check_launch("fwd_sm100_kernel");
+}
+
+bool sm100_bwd_supported(const bsa_bwd_params*, const char** why) {
+  *why = "the tcgen05 backward is not built yet";
+  return false;
+}
+int sm100_bwd(const bsa_bwd_params*, cudaStream_t) { return BSA_E_UNSUPPORTED; }
+
+}  // namespace bsa

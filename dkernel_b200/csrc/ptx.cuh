@@ -22,6 +22,7 @@ namespace bsa {
 struct Tmap4 {
   CUtensorMap map;
   int seq_pos, head_pos, batch_pos;
+  int head_bcast, batch_bcast;  // the dimension has extent 1 / stride 0: coordinate forced to 0
 };
 int make_tmap_4d(Tmap4* out, const void* base, int elem_bytes, uint64_t d, uint64_t seq,
                  uint64_t heads, uint64_t batch, int64_t seq_stride_b, int64_t head_stride_b,
@@ -89,6 +90,8 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, u
 // (d0, seq, head, batch) -> coordinates in the order the map stores them
 __device__ __forceinline__ void tma_load_tile(void* dst, const Tmap4* tm, uint64_t* bar, int d0,
                                               int s, int h, int b) {
+  if (tm->head_bcast) h = 0;
+  if (tm->batch_bcast) b = 0;
   const int c1 = tm->seq_pos == 1 ? s : (tm->head_pos == 1 ? h : b);
   const int c2 = tm->seq_pos == 2 ? s : (tm->head_pos == 2 ? h : b);
   const int c3 = tm->seq_pos == 3 ? s : (tm->head_pos == 3 ? h : b);

@@ -54,9 +54,11 @@ int make_tmap_4d(Tmap4* out, const void* base, int elem_bytes, uint64_t d, uint6
   // layout ((B,S,H,D), (B,H,S,D), packed (T,H,D), views of larger tensors).
   // Dimensions of extent 1 (their stride is irrelevant, possibly 0) go last.
   struct Dim { uint64_t extent; int64_t stride; int logical; uint32_t box; };
+  out->head_bcast = (heads <= 1 || head_stride_b <= 0) ? 1 : 0;
+  out->batch_bcast = (batch <= 1 || batch_stride_b <= 0) ? 1 : 0;
   Dim dims3[3] = {{seq ? seq : 1, seq_stride_b, 0, box_seq},
-                  {heads ? heads : 1, head_stride_b, 1, 1},
-                  {batch ? batch : 1, batch_stride_b, 2, 1}};
+                  {out->head_bcast ? 1 : heads, head_stride_b, 1, 1},
+                  {out->batch_bcast ? 1 : batch, batch_stride_b, 2, 1}};
   auto key = [](const Dim& x) { return x.extent <= 1 ? INT64_MAX : x.stride; };
   for (int i = 0; i < 3; ++i)
     for (int j = i + 1; j < 3; ++j)

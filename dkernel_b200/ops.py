@@ -303,7 +303,7 @@ def _train_forward(ctx, q, k, v, sm_scale, plan, seq_dim, causal, out, impl, nee
         _lib.check(_lib.lib().bsa_fwd(C.byref(p), _lib.stream_of(q)), "bsa_fwd")
     if ctx is not None and not inference:
         ctx.save_for_backward(q, k, v, o, lse)
-        ctx.sm_scale, ctx.seq_dim, ctx.causal, ctx.plan, ctx.impl = sm_scale, seq_dim, causal, plan, impl
+        ctx.sm_scale, ctx.seq_dim, ctx.causal, ctx.plan = sm_scale, seq_dim, causal, plan
     return o, lse
 
 
@@ -322,7 +322,7 @@ def _backward(ctx, do: Tensor, dlse: Optional[Tensor], dq=None, dk=None, dv=None
         assert t.stride(-1) == 1, f"{n} must be contiguous in the head dimension"
     bp = _lib.BwdParams()
     bp.f = _fwd_params(q, k, v, o, lse, seq_dim, plan, ctx.sm_scale, ctx.causal, _lib.ROWS_BY_TILE,
-                       impl=ctx.impl)
+                       impl=ctx.bwd_impl)
     bp.d_o = _lib.ptr(do)
     bp.do_sb, bp.do_ss, bp.do_sh = _strides_bsh(do, seq_dim)
     if dlse is not None:
@@ -370,6 +370,8 @@ class _sparse_attention(torch.autograd.Function):
         return_lse = kwargs.get("return_lse", False)
         out = kwargs.get("out", None)
         impl = _IMPL_NAMES[kwargs.get("impl", None)]
+        ctx.bwd_impl = _IMPL_NAMES[kwargs.get("bwd_impl", "generic" if kwargs.get("impl") == "generic"
+                                              else None)]
 
         hdim = 3 - (seq_dim or 1) if q.dim() == 4 else 1
         n_pat = layout_csr[0].size(0)

@@ -196,6 +196,12 @@ def get_sparse_attn_mask(num_heads: int,
         vert_stride=vert_stride, head_sliding_step=head_sliding_step,
         head_sliding_offset=head_sliding_offset, causal=1 if causal else 0,
         absolute_vert=1 if vert_position_type == "absolute" else 0)
+    if vert_position_type == "relative" and num_dense_heads in (0, num_kv_heads):
+        # every head has the same relative pattern: the reference returns one head
+        # (broadcast of (1, M, 1) against (1, 1, N), dkernel/utils.py:196-204)
+        p.num_heads = p.num_kv_heads = 1
+        p.num_dense_heads = 1 if num_dense_heads else 0
+        num_heads = 1
     with torch.cuda.device(dev):
         mask8 = torch.empty((num_heads, max(blocks - trim, 0), kv_blocks), dtype=torch.uint8, device=dev)
         _lib.check(_lib.lib().bsa_local_stride_mask(C.byref(p), _lib.ptr(mask8), _lib.stream_of(mask8)),

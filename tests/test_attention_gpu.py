@@ -51,7 +51,7 @@ def test_forward_and_backward_vs_oracle(B, Hq, Hkv, Sq, Sk, D, dtype, seq_dim, p
     bm = O.block_mask(Hq, Sk, **pk)
     scale = 1.0 / math.sqrt(D)
     # oracle in fp32 with autograd
-    qf, kf, vf = (t.float().requires_grad_() for t in (q, k, v))
+    qf, kf, vf = (t.detach().clone().float().requires_grad_() for t in (q, k, v))
     dense = O.token_mask(bm, bs, Sq, Sk, causal=causal)
     ref, ref_lse = O.masked_dense_attention(qf, kf, vf, dense, scale, seq_dim=seq_dim, return_lse=True)
     ref.backward(do.float())
@@ -119,7 +119,7 @@ def test_views_packing_and_out_kwarg():
     do = torch.randn(B, S, H, D, generator=g).to(torch.float16)
     bm = O.block_mask(H, S, **pk)
     dense = O.token_mask(bm, bs, S, S)
-    qf, kf, vf = (t.float().requires_grad_() for t in (q, k, v))
+    qf, kf, vf = (t.detach().clone().float().requires_grad_() for t in (q, k, v))
     ref = O.masked_dense_attention(qf, kf, vf, dense, None, seq_dim=1)
     ref.backward(do.float())
     mod = _module(H, S, pk, seq_dim=1)

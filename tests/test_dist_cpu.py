@@ -1,0 +1,141 @@
+"""Multi-rank host logic on CPU (gloo, world_size 2): head sharding, KV-sequence
+sharding and the one-message gather of decode partials.  The per-rank compute is
+done by the CPU oracle here (the GPU tests cover the kernels); what is checked is
+that the partitioning + gather + merge reproduce the un-partitioned result."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import dkernel_oracle as O
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from dkernel_b200.dist import head_shard, kv_shard_ranges, pack_kv_shard, gather_partials
+        torch.manual_seed(0)                      # identical inputs on every rank
+        B, Hq, Hkv, S, D, bs = 3, 4, 2, 512, 32, 64
+        q = torch.randn(B, 1, Hq, D)
+        k = torch.randn(B, S, Hkv, D)
+        v = torch.randn(B, S, Hkv, D)
+        lens = torch.tensor([512, 130, 64])
+        left = S - lens
+        bm = O.block_mask(Hq, S, bs, 2, 3, num_kv_heads=Hkv)
+        ref, ref_lse = O.decode_attention(q, k, v, bm, bs, left_paddings=left)
+
+        # ---- KV-sequence sharding: rank-local partial, one all-gather, merge
+        lo, hi = kv_shard_ranges(lens, rank, world, bs)
+        ks, vs, n = pack_kv_shard(k, v, left, lo, hi)
+        part_o = torch.zeros(B, 1, Hq, D)
+        part_l = torch.full((B, Hq, 1), float("-inf"))
+        for b in range(B):
+            if n[b] == 0:
+                continue
+            # the shard holds positions [lo, hi): evaluate with the block range restriction
+            o_b, l_b = O.decode_attention(q[b:b + 1], k[b:b + 1], v[b:b + 1], bm, bs,
+                                          left_paddings=left[b:b + 1],
+                                          kv_block_range=(int(lo[b]) // bs, (int(hi[b]) + bs - 1) // bs))
+            part_o[b], part_l[b] = o_b[0], l_b[0]
+            # and the packed shard really is that slice of the sequence
+            s0 = int(left[b] + lo[b])
+            assert torch.equal(ks[b, :int(n[b])], k[b, s0:s0 + int(n[b])])
+        o_parts, l_parts = gather_partials(part_o.reshape(B * Hq, D), part_l.reshape(B * Hq))
+        assert o_parts.shape == (world, B * Hq, D) and l_parts.shape == (world, B * Hq)
+        parts = [(o_parts[r].view(B, 1, Hq, D).transpose(1, 2), l_parts[r].view(B, Hq, 1)) for r in range(world)]
+        merged, mlse = O.combine_attn_partitions(*parts)
+        assert (merged.transpose(1, 2) - ref).abs().max() < 1e-5
+        assert (mlse - ref_lse).abs().max() < 1e-4
+
+        # ---- head sharding: rank-local heads, no collective; concatenation == whole
+        (h0, h1), (kv0, kv1) = head_shard(Hq, Hkv, rank, world)
+        qs = torch.randn(1, 256, Hq, D)
+        kk = torch.randn(1, 256, Hkv, D)
+        vv = torch.randn(1, 256, Hkv, D)
+        bm2 = O.block_mask(Hq, 256, bs, 2, 3, num_kv_heads=Hkv)
+        full, _ = O.block_sparse_attention(qs, kk, vv, bm2, bs, seq_dim=1)
+        mine, _ = O.block_sparse_attention(qs[:, :, h0:h1], kk[:, :, kv0:kv1], vv[:, :, kv0:kv1],
+                                           bm2[h0:h1], bs, seq_dim=1)
+        assert (mine - full[:, :, h0:h1]).abs().max() < 1e-5
+        gathered = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(gathered, mine.contiguous())       # test-side check only
+        assert (torch.cat(gathered, dim=2) - full).abs().max() < 1e-5
+        ret[rank] = "ok"
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_ranks_gloo():
+    world = 2
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
+    assert dict(ret) == {0: "ok", 1: "ok"}
+
+
+def test_planning_functions():
+    from dkernel_b200.dist import head_shard, kv_shard_ranges
+    # head shards tile the head range and keep kv groups whole
+    for hq, hkv, w in ((32, 8, 1), (32, 8, 2), (32, 8, 4), (32, 8, 8), (32, 32, 8), (8, 2, 2)):
+        seen_q, seen_kv = [], []
+        for r in range(w):
+            (a, b), (c, d) = head_shard(hq, hkv, r, w)
+            assert (b - a) == (d - c) * (hq // hkv) and a == c * (hq // hkv)
+            seen_q += list(range(a, b))
+            seen_kv += list(range(c, d))
+        assert seen_q == list(range(hq)) and seen_kv == list(range(hkv))
+    with pytest.raises(AssertionError):
+        head_shard(32, 8, 0, 3)
+    # kv shards: disjoint, block aligned, cover [0, len)
+    lens = torch.tensor([1, 63, 64, 65, 1024, 5263, 8192])
+    for w in (1, 2, 4, 8):
+        cover = torch.zeros_like(lens)
+        prev_hi = torch.zeros_like(lens)
+        for r in range(w):
+            lo, hi = kv_shard_ranges(lens, r, w, 64)
+            assert (lo % 64 == 0).all() and (hi >= lo).all() and (hi <= lens).all()
+            assert (lo == prev_hi).all() or ((hi - lo)[lo != prev_hi] == 0).all()
+            prev_hi = torch.where(hi > lo, hi, prev_hi)
+            cover += hi - lo
+        assert (cover == lens).all()
+        # balance: no rank holds more than one block above the ideal share
+        for r in range(w):
+            lo, hi = kv_shard_ranges(lens, r, w, 64)
+            assert ((hi - lo) <= (lens + w - 1) // w + 64).all()
+
+
+def test_host_logic_without_gpu():
+    """Package import, pack-mode splitting and the no-CPU-path errors."""
+    import dkernel_b200
+    from dkernel_b200.ops import get_qkv_and_pack_mode, _pick_heads_per_cta
+    from dkernel_b200.utils import multiple_of, zero_stride, cdiv
+    assert multiple_of(1000, 64) == 1024 and multiple_of(1024, 64) == 1024 and cdiv(65, 64) == 2
+    x = torch.zeros(1, 4, 5)
+    assert zero_stride(x).stride(0) == 0
+    q = torch.randn(2, 8, 6, 4)
+    (a, b, c), (shape, mode, fn) = get_qkv_and_pack_mode(q, None, None, split_qkv=lambda t: t.chunk(3, dim=2))
+    assert mode == "packed_qkv" and shape == q.shape and a.shape == (2, 8, 2, 4)
+    (a, b, c), (shape, mode, fn) = get_qkv_and_pack_mode(q, q, None, split_qkv=lambda t: t.chunk(2, dim=2))
+    assert mode == "packed_kv" and b.shape == (2, 8, 3, 4)
+    with pytest.raises(AssertionError):
+        get_qkv_and_pack_mode(q, None, None)
+    assert [_pick_heads_per_cta(g) for g in (1, 2, 4, 7, 16, 32, 24)] == [1, 2, 4, 7, 16, 16, 12]
+    if not torch.cuda.is_available():
+        with pytest.raises(RuntimeError, match="no CPU path"):
+            dkernel_b200.get_sparse_attn_mask(2, 128)
+        with pytest.raises(RuntimeError, match="no CPU path|CUDA"):
+            dkernel_b200.SparseAttention(64, torch.ones(2, 2))

@@ -1,0 +1,111 @@
+"""tcgen05 forward kernel: parity with the CPU oracle on small cases and with
+the generic CUDA-core kernel (same device, same inputs) on long sequences."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import dkernel_oracle as O
+from helpers import assert_out_close, assert_lse_close, seeded_qkv
+
+pytestmark = pytest.mark.gpu
+
+
+def _module(Hq, max_seq, pk, **kw):
+    from dkernel_b200 import LocalStrideSparseAttention
+    pk = dict(pk)
+    return LocalStrideSparseAttention.__wrapped__(Hq, max_seq, pk.pop("block_size"), pk.pop("local_blocks"),
+                                                  pk.pop("vert_stride"), **pk, **kw)
+
+
+def _wait_status_clean():
+    from dkernel_b200 import _lib
+    assert _lib.wait_status() == 0, "a device-side wait gave up"
+
+
+CASES = [
+    # B, Hq, Hkv, Sq, Sk, dtype, seq_dim, pattern kwargs
+    (1, 2, 2, 128, 128, torch.bfloat16, 1, dict(block_size=64, local_blocks=2, vert_stride=2)),
+    (2, 4, 4, 512, 512, torch.bfloat16, 1, dict(block_size=64, local_blocks=2, vert_stride=4)),
+    (1, 8, 2, 1024, 1024, torch.bfloat16, 2, dict(block_size=64, local_blocks=3, vert_stride=4, num_kv_heads=2)),
+    (1, 2, 2, 200, 200, torch.float16, 1, dict(block_size=64, local_blocks=2, vert_stride=2)),
+    (1, 3, 3, 1028, 1028, torch.bfloat16, 1, dict(block_size=64, local_blocks=4, vert_stride=4)),
+    (1, 4, 2, 15, 15, torch.float16, 2, dict(block_size=64, local_blocks=4, vert_stride=4, num_kv_heads=2)),
+    (1, 2, 2, 256, 256, torch.bfloat16, 2, dict(block_size=64, local_blocks=1, vert_stride=3, causal=False)),
+    (1, 2, 2, 256, 640, torch.bfloat16, 1, dict(block_size=64, local_blocks=2, vert_stride=3)),
+    (1, 6, 2, 448, 448, torch.float16, 1, dict(block_size=64, local_blocks=2, vert_stride=4, num_kv_heads=2)),
+    (1, 4, 4, 512, 512, torch.bfloat16, 1, dict(block_size=64, local_blocks=8, vert_stride=1)),
+]
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,Sq,Sk,dtype,seq_dim,pk", CASES)
+def test_sm100_forward_vs_oracle(B, Hq, Hkv, Sq, Sk, dtype, seq_dim, pk):
+    D = 128
+    causal = pk.get("causal", True)
+    bs = pk["block_size"]
+    shape = (lambda h, s: (B, h, s, D)) if seq_dim == 2 else (lambda h, s: (B, s, h, D))
+    q, k, v = seeded_qkv(20, shape(Hq, Sq), shape(Hkv, Sk), dtype)
+    bm = O.block_mask(Hq, Sk, **pk)
+    # q rows are tile rows of the pattern; with Sq < Sk the causal offset is Sk - Sq
+    ref, ref_lse = O.block_sparse_attention(q, k, v, bm, bs, None, seq_dim=seq_dim, causal=causal)
+    mod = _module(Hq, Sk, pk, seq_dim=seq_dim, impl="sm100")
+    with torch.no_grad():
+        out, lse = mod(q.cuda(), k.cuda(), v.cuda(), return_lse=True)
+    _wait_status_clean()
+    assert_out_close(out, ref)
+    assert_lse_close(lse, ref_lse)
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,S,pk", [
+    (1, 8, 2, 4096, dict(block_size=64, local_blocks=16, vert_stride=8, num_kv_heads=2)),
+    (1, 4, 4, 4096, dict(block_size=64, local_blocks=32, vert_stride=8)),
+    (2, 2, 2, 8192, dict(block_size=64, local_blocks=4, vert_stride=16)),
+])
+def test_sm100_matches_generic_on_long_sequences(B, Hq, Hkv, S, pk):
+    q, k, v = seeded_qkv(1, (B, S, Hq, 128), (B, S, Hkv, 128), torch.bfloat16, device="cuda")
+    fast = _module(Hq, S, pk, seq_dim=1, impl="sm100")
+    slow = _module(Hq, S, pk, seq_dim=1, impl="generic")
+    with torch.no_grad():
+        o1, l1 = fast(q, k, v, return_lse=True)
+        o2, l2 = slow(q, k, v, return_lse=True)
+    _wait_status_clean()
+    assert_out_close(o1, o2, max_abs=2e-2, mean_abs=1e-3)
+    assert_lse_close(l1, l2)
+    # deterministic: a second launch gives the same bits
+    with torch.no_grad():
+        o3 = fast(q, k, v)
+    assert torch.equal(o1, o3)
+
+
+def test_sm100_varlen_and_padded_routes():
+    from dkernel_b200 import SparseAttention
+    Hq, Hkv, D, bs, nb = 4, 4, 128, 64, 16
+    g = torch.Generator().manual_seed(0)
+    pat = torch.rand(Hq, nb, nb, generator=g) < 0.3
+    pat |= torch.eye(nb, dtype=torch.bool)[None]
+    pat &= torch.tril(torch.ones(nb, nb, dtype=torch.bool))[None]
+    lens = [512, 100, 333, 64, 1, 700]
+    T = sum(lens)
+    q, k, v = seeded_qkv(5, (T, Hq, D), (T, Hkv, D), torch.bfloat16)
+    cu = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32)
+    ref, ref_lse = O.varlen_attention(q.float(), k.float(), v.float(), cu, pat.numpy().astype(np.uint8), bs)
+    with pytest.warns(UserWarning):
+        mod = SparseAttention(bs, pat.cuda(), impl="sm100")
+    out, lse = mod(q.cuda(), k.cuda(), v.cuda(), cu_seqlen_k=cu.cuda(), return_lse=True)
+    _wait_status_clean()
+    assert_out_close(out, ref)
+    assert_lse_close(lse, ref_lse)
+    # left-padded prefill, GQA (head-pair tiles)
+    B, S, Hq, Hkv = 3, 512, 8, 2
+    pk = dict(block_size=64, local_blocks=2, vert_stride=4, num_kv_heads=Hkv)
+    q, k, v = seeded_qkv(6, (B, S, Hq, D), (B, S, Hkv, D), torch.bfloat16)
+    lens = torch.tensor([512, 77, 300])
+    left = S - lens
+    bm = O.block_mask(Hq, S, **pk)
+    ref, ref_lse = O.padded_attention(q.float(), k.float(), v.float(), bm, 64, left_paddings=left, seq_dim=1)
+    mod = _module(Hq, S, pk, seq_dim=1, impl="sm100")
+    out, lse = mod(q.cuda(), k.cuda(), v.cuda(), left_paddings=left.cuda(), return_lse=True)
+    _wait_status_clean()
+    assert_out_close(out, ref)
+    assert_lse_close(lse, ref_lse)
