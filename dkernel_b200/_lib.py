@@ -78,6 +78,8 @@ EXPORTS = {
     "bsa_bwd": (_i32, [C.POINTER(BwdParams), _vp]),
     "bsa_decode_workspace_bytes": (C.c_size_t, [C.POINTER(DecodeParams)]),
     "bsa_decode": (_i32, [C.POINTER(DecodeParams), _vp]),
+    "bsa_decode_static": (_i32, [C.POINTER(DecodeParams), _vp]),
+    "bsa_decode_static_capacity": (C.c_size_t, []),
     "bsa_merge_partials": (_i32, [_vp, _vp, _i32, _i64, _i32, _i64, _i64, _i64, _i64, _vp, _i64, _vp,
                                   _i32, _vp]),
     "bsa_wait_status": (_i32, [C.POINTER(_i32), _i32]),

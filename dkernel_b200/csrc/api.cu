@@ -106,6 +106,12 @@ int bsa_decode(const bsa_decode_params* p, void* stream) {
   return decode_run(p, static_cast<cudaStream_t>(stream));
 }
 
+int bsa_decode_static(const bsa_decode_params* p, void* stream) {
+  return decode_run_static(p, static_cast<cudaStream_t>(stream));
+}
+
+size_t bsa_decode_static_capacity(void) { return decode_static_capacity(); }
+
 int bsa_merge_partials(const void* o_parts, const float* lse_parts, int32_t P, int64_t rows,
                        int32_t d, int64_t part_stride_o, int64_t row_stride_o,
                        int64_t part_stride_lse, int64_t row_stride_lse, void* o,

@@ -83,6 +83,8 @@ bool sm100_bwd_supported(const bsa_bwd_params* p, const char** why);
 int sm100_bwd(const bsa_bwd_params* p, cudaStream_t s);
 size_t decode_workspace_bytes(const bsa_decode_params* p);
 int decode_run(const bsa_decode_params* p, cudaStream_t s);
+int decode_run_static(const bsa_decode_params* p, cudaStream_t s);
+size_t decode_static_capacity();
 int merge_partials(const void* o_parts, const float* lse_parts, int P, int64_t rows, int d,
                    int64_t pso, int64_t rso, int64_t psl, int64_t rsl, void* o, int64_t ors,
                    float* lse, int dtype, cudaStream_t s);

@@ -549,3 +549,62 @@ int read_wait_status(int* out, int reset) {
   return BSA_OK;
 }
 }  // namespace bsa
+
+// ---------------------------------------------------------------------------
+// Decode without any allocation by the caller.
+//
+// Some hosts of this library cannot hand it scratch memory: a serving runtime
+// that has pinned its whole device-memory budget to the KV cache, a plugin
+// loaded into a process whose allocator it must not touch, a language binding
+// that only passes through the tensors it was given.  For them the split-KV
+// partials live in a fixed array that is part of the library image.  Every GPU
+// that loads the library carries the array (kStaticScratchBytes) until the
+// process exits.
+// ---------------------------------------------------------------------------
+namespace bsa {
+
+constexpr size_t kStaticScratchBytes = size_t(8) << 20;  // 8 MiB
+static __device__ __align__(256) float g_decode_scratch[kStaticScratchBytes / sizeof(float)];
+
+// Device address of g_decode_scratch on the current device.  In host code the
+// array's name is only a handle for the runtime, not an address a kernel can
+// use, so the address is looked up once per device (with that device current)
+// and handed to the kernels as an ordinary pointer.
+static float* static_scratch_ptr() {
+  static float* cache[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    set_error("bsa_decode_static: cudaGetDevice failed or device index out of range");
+    return nullptr;
+  }
+  if (!cache[dev]) {
+    float* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress((void**)&ptr, g_decode_scratch);
+    if (e != cudaSuccess || ptr == nullptr) {
+      set_error("bsa_decode_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      return nullptr;
+    }
+    cache[dev] = ptr;
+  }
+  return cache[dev];
+}
+
+size_t decode_static_capacity() { return kStaticScratchBytes; }
+
+int decode_run_static(const bsa_decode_params* p, cudaStream_t s) {
+  BSA_CHECK_ARG(p, "bsa_decode_static: null params");
+  const size_t need = decode_workspace_bytes(p);
+  if (need > kStaticScratchBytes) {
+    set_error("bsa_decode_static: this call needs %zu bytes of split-KV scratch but the built-in "
+              "array holds %zu; lower batch*heads, raise blocks_per_split, or use bsa_decode with a "
+              "caller-provided workspace", need, (size_t)kStaticScratchBytes);
+    return BSA_E_TOOBIG;
+  }
+  float* scratch = static_scratch_ptr();
+  if (!scratch) return BSA_E_CUDA;
+  bsa_decode_params q = *p;
+  q.ws = scratch;  // every (sequence, head, split) slot in use is rewritten by the kernel
+  return decode_run(&q, s);
+}
+
+}  // namespace bsa

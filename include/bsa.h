@@ -205,6 +205,34 @@ size_t bsa_decode_workspace_bytes(const bsa_decode_params* p);
 int bsa_decode(const bsa_decode_params* p, void* stream);
 
 /* ---------------------------------------------------------------------------
+ * bsa_decode for callers that cannot allocate.  No counterpart in the reference.
+ *
+ * bsa_decode needs a caller-provided workspace for its split-KV partials.  Some
+ * callers have none to give: a serving runtime whose device-memory budget is
+ * entirely committed to the KV cache, a plugin living inside a process whose
+ * allocator it may not call, a thin language binding that can only forward the
+ * tensors it received.  This variant takes the same parameters, ignores p->ws
+ * and keeps the partials in a fixed array inside the library image
+ * (bsa_decode_static_capacity() bytes, currently 8 MiB, resident on every GPU
+ * that loads the library until the process exits).  It calls no cudaMalloc,
+ * cudaFree or allocating library routine; inputs and outputs are still the
+ * caller's.
+ *
+ *  - Limit: bsa_decode_workspace_bytes(p) must not exceed the capacity, else
+ *    BSA_E_TOOBIG is returned and nothing is launched (lower batch x heads or
+ *    raise blocks_per_split, or use bsa_decode).
+ *  - The first call on a device looks up the array's device address (once per
+ *    device, with that device current); make that first call outside any
+ *    stream capture.
+ *  - All calls share the one array and it keeps whatever the last call left in
+ *    it.  Nothing in it has to start at zero: every slot a launch reads is
+ *    written by the same launch first.  Two calls that overlap on the GPU (two
+ *    streams, or two host threads on one device) race on it: serialise them.
+ * ------------------------------------------------------------------------- */
+int bsa_decode_static(const bsa_decode_params* p, void* stream);
+size_t bsa_decode_static_capacity(void);
+
+/* ---------------------------------------------------------------------------
  * Merge of attention partials over key/value partitions.  Replaces the eager
  * torch ops of combine_attn_partitions (dkernel/interface.py:319-324).
  * o_parts: (P, rows, d) with stride part_stride_o between partitions and
