@@ -291,19 +291,21 @@ fwd_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap
       const uint32_t ent = tl->list[j];
       const int kbase = (int)(ent & 0xffffu) * kBS;
       const bool att = ((ent >> (16 + t)) & 1u) != 0 && hf[t].valid;
+      // Allowed columns of this block form a prefix: kpos < k_len and, when causal,
+      // kpos <= qpos.  Raw logits are compared (sm_scale > 0); the scale is folded
+      // into the exponent's FMA.
       float mx = -INFINITY;
       if (att) {
-        const bool need_mask = (kbase + kBS > k_len) || (p.causal && kbase + kBS - 1 > qpos);
+        int lim = k_len - kbase;
+        if (p.causal) lim = min(lim, qpos - kbase + 1);
+        if (lim < kBS) {
 #pragma unroll
-        for (int c = 0; c < 64; ++c) {
-          float x = __uint_as_float(sv[c]) * scale2;
-          if (need_mask) {
-            const int kpos = kbase + c;
-            if (!(kpos < k_len && (!p.causal || kpos <= qpos))) x = -INFINITY;
-          }
-          sv[c] = __float_as_uint(x);
-          mx = fmaxf(mx, x);
+          for (int c = 0; c < 64; ++c)
+            if (c >= lim) sv[c] = 0xff800000u;  // -inf
         }
+#pragma unroll
+        for (int c = 0; c < 64; ++c) mx = fmaxf(mx, __uint_as_float(sv[c]));
+        mx *= scale2;
       }
       float alpha = 1.f;
       bool need = false;
@@ -320,15 +322,17 @@ fwd_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap
       const bool any = __any_sync(0xffffffffu, need);
       uint32_t pk[32];
       if (att && m_used != -INFINITY) {
-        float sum = 0.f;
+        float sum0 = 0.f, sum1 = 0.f;
+        const float neg_m = -m_used;
 #pragma unroll
         for (int c = 0; c < 32; ++c) {
-          const float p0 = ex2(__uint_as_float(sv[2 * c]) - m_used);
-          const float p1 = ex2(__uint_as_float(sv[2 * c + 1]) - m_used);
-          sum += p0 + p1;
+          const float p0 = ex2(fmaf(__uint_as_float(sv[2 * c]), scale2, neg_m));
+          const float p1 = ex2(fmaf(__uint_as_float(sv[2 * c + 1]), scale2, neg_m));
+          sum0 += p0;
+          sum1 += p1;
           pk[c] = pack2<BF16>(p0, p1);
         }
-        l += sum;
+        l += sum0 + sum1;
       } else {
 #pragma unroll
         for (int c = 0; c < 32; ++c) pk[c] = 0u;
@@ -431,6 +435,7 @@ bool sm100_fwd_supported(const bsa_fwd_params* p, const char** why) {
   if (reinterpret_cast<uintptr_t>(p->o) % 8 || p->o_ss % 4 || p->o_sh % 4 || p->o_sb % 4)
     return no("output rows are not 8-byte aligned");
   if (p->sq == 0 || p->batch == 0) return no("empty problem");
+  if (!(p->sm_scale > 0.f)) return no("sm_scale is not positive");
   return true;
 }
 

@@ -1,7 +1,7 @@
 // Thin wrappers over the sm_100a PTX this library uses: mbarrier, TMA
 // (cp.async.bulk.tensor, each copy addressed to the issuing CTA only), tcgen05 (alloc / mma / commit / ld /
 // st / fences) and the shared-memory / instruction descriptors of tcgen05.mma.
-// Every wait is bounded: after kSpinLimit polls it gives up, records a status
+// Every wait is bounded: after kWaitLimitNs it gives up, records a status
 // word and lets the kernel run to completion (results are then invalid and the
 // host reports the status), so a protocol bug cannot hang the GPU.
 #pragma once
@@ -33,7 +33,6 @@ bool tma_compatible(const void* base, int elem_bytes, int64_t ss, int64_t sh, in
 
 #if defined(__CUDACC__)
 // ---------------------------------------------------------------- device side
-constexpr uint32_t kSpinLimit = 1u << 24;  // ~ a second of polling with backoff
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -64,11 +63,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait.  Returns false (and sets *status to `code`) when it gave up.
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait.  mbarrier.try_wait suspends the thread in hardware for a while
+// before it reports failure, so the loop neither burns issue slots nor adds
+// wake-up latency; the bound is wall-clock time (kWaitLimitNs).  Returns false
+// (and sets *status to `code`) when it gave up.
+constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (i > 64) __nanosleep(32);
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  while (true) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (global_timer_ns() - t0 > kWaitLimitNs) break;
   }
   if (status) atomicCAS(status, 0, code);
   return false;
