@@ -1,0 +1,776 @@
+// Backward on the 5th-generation tensor cores: two kernels after a small
+// pre-pass, no atomics (every gradient tile has exactly one writer).
+//
+//   delta[b,h,i] = sum_d O*dO - dLSE                      (bwd_delta_vec_kernel)
+//   dQ  kernel: one CTA per 128-row query tile (two 64-row halves as in the
+//               forward), walks the union of the halves' CSR rows:
+//                 S = Q K^T, dP = dO V^T, dS = exp2(S c - lse) * (dP - delta),
+//                 dQ += dS K
+//   dKdV kernel: one CTA per pair of adjacent kv blocks of one kv head, walks, for
+//               every q head of the group, the union of the two CSC columns:
+//                 S^T = K Q^T, dP^T = V dO^T, P^T, dS^T,
+//                 dV += P^T dO, dK += dS^T Q
+// All products are tcgen05.mma with fp32 accumulators in TMEM; the transposed
+// formulation of the dK/dV kernel puts the kv rows on the TMEM lanes, so P^T and
+// dS^T are written back by tcgen05.st and consumed as TMEM A operands while Q and
+// dO serve as MN-major B operands straight from their TMA tiles.  S/dP are double
+// buffered in TMEM (512 columns, one CTA per SM) so the MMAs of step e+1 overlap
+// the exponentials of step e.  Math: dkernel/ops/sparse_attn_bwd.py:86-170
+// (dK/dV), :329-419 (dQ), :73-80 (delta); P and dS are rounded to the input
+// type before the second-stage products, like the reference (:144,:166,:413).
+#include "ptx.cuh"
+
+namespace bsa {
+namespace {
+
+constexpr int kD = 128;
+constexpr int kBS = 64;
+constexpr int kBwdThreads = 192;
+constexpr int kMaxBlocks = 1024;   // q or kv blocks per sequence (64K tokens)
+constexpr int kMaxEntries = 2048;  // list entries per CTA
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  if (BF16) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+  } else {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+}
+
+__device__ __forceinline__ void named_bar_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// 128 x 128 fp32 accumulator in TMEM (lane = tile row) -> scaled 16-bit rows in
+// global memory.  Each warp converts its 32 lanes through an 8 KB staging area
+// (XOR-swizzled 16-byte chunks) and then writes whole 256-byte rows.
+// Row r of the tile belongs to half r/64; base[half] points at that half's row 0.
+template <bool BF16>
+__device__ __forceinline__ void store_acc_tile(uint32_t tacc, int warp, int lane, float scale,
+                                               uint8_t* stage, uint8_t* const (&base)[2],
+                                               const int (&valid_rows)[2], int64_t row_stride_bytes) {
+  const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+#pragma unroll
+  for (int ch = 0; ch < 4; ++ch) {
+    uint32_t o[32];
+    tmem_ld32(tacc + lane_off + ch * 32, o);
+    tmem_ld_wait();
+#pragma unroll
+    for (int c4 = 0; c4 < 4; ++c4) {
+      uint4 w;
+      w.x = pack2<BF16>(__uint_as_float(o[c4 * 8 + 0]) * scale, __uint_as_float(o[c4 * 8 + 1]) * scale);
+      w.y = pack2<BF16>(__uint_as_float(o[c4 * 8 + 2]) * scale, __uint_as_float(o[c4 * 8 + 3]) * scale);
+      w.z = pack2<BF16>(__uint_as_float(o[c4 * 8 + 4]) * scale, __uint_as_float(o[c4 * 8 + 5]) * scale);
+      w.w = pack2<BF16>(__uint_as_float(o[c4 * 8 + 6]) * scale, __uint_as_float(o[c4 * 8 + 7]) * scale);
+      const int chunk = ch * 4 + c4;
+      *reinterpret_cast<uint4*>(stage + lane * 256 + ((chunk ^ (lane & 15)) << 4)) = w;
+    }
+  }
+  __syncwarp();
+  for (int i = 0; i < 32; ++i) {
+    const int row = warp * 32 + i;
+    const int ht = row >> 6, rr = row & 63;
+    if (rr < valid_rows[ht]) {
+      const uint2 w = *reinterpret_cast<const uint2*>(stage + i * 256 + (((lane >> 1) ^ (i & 15)) << 4) +
+                                                      (lane & 1) * 8);
+      *reinterpret_cast<uint2*>(base[ht] + (int64_t)rr * row_stride_bytes + lane * 8) = w;
+    }
+  }
+  __syncwarp();
+}
+
+// ------------------------------------------------------------------ delta
+// One warp per (b, h, i) row of 128 elements: each lane reads 8 bytes of O and dO.
+template <bool BF16>
+__global__ void bwd_delta_vec_kernel(bsa_bwd_params bp) {
+  const bsa_fwd_params& p = bp.f;
+  const int lane = threadIdx.x & 31;
+  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long total = (long long)p.batch * p.hq * p.sq;
+  if (w >= total) return;
+  const int i = (int)(w % p.sq);
+  const int h = (int)((w / p.sq) % p.hq);
+  const int b = (int)(w / ((long long)p.sq * p.hq));
+  const uint2 ov = *reinterpret_cast<const uint2*>(
+      reinterpret_cast<const uint8_t*>(p.o) +
+      ((int64_t)b * p.o_sb + (int64_t)h * p.o_sh + (int64_t)i * p.o_ss) * 2 + lane * 8);
+  const uint2 gv = *reinterpret_cast<const uint2*>(
+      reinterpret_cast<const uint8_t*>(bp.d_o) +
+      ((int64_t)b * bp.do_sb + (int64_t)h * bp.do_sh + (int64_t)i * bp.do_ss) * 2 + lane * 8);
+  float s;
+  if (BF16) {
+    const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&ov);
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+    const float2 a0 = __bfloat1622float2(o2[0]), a1 = __bfloat1622float2(o2[1]);
+    const float2 c0 = __bfloat1622float2(g2[0]), c1 = __bfloat1622float2(g2[1]);
+    s = a0.x * c0.x + a0.y * c0.y + a1.x * c1.x + a1.y * c1.y;
+  } else {
+    const __half2* o2 = reinterpret_cast<const __half2*>(&ov);
+    const __half2* g2 = reinterpret_cast<const __half2*>(&gv);
+    const float2 a0 = __half22float2(o2[0]), a1 = __half22float2(o2[1]);
+    const float2 c0 = __half22float2(g2[0]), c1 = __half22float2(g2[1]);
+    s = a0.x * c0.x + a0.y * c0.y + a1.x * c1.x + a1.y * c1.y;
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+  if (lane == 0) {
+    if (bp.d_lse) s -= bp.d_lse[(int64_t)b * p.lse_sb + (int64_t)h * p.lse_sh + i];
+    bp.delta[w] = s;
+  }
+}
+
+// ------------------------------------------------------------------ shared list builder
+// Ordered union of two sets of block indices given as bitmaps; appended to `list`
+// starting at *count.  entry = block | extra | (in set 0) << 24 | (in set 1) << 25.
+__device__ __forceinline__ void append_union(const uint32_t* bits0, const uint32_t* bits1,
+                                             uint32_t* list, int* count, uint32_t extra, int lane,
+                                             int cap) {
+  const uint32_t u0 = bits0[lane], u1 = bits1[lane];
+  uint32_t u = u0 | u1;
+  const int cnt = __popc(u);
+  int incl = cnt;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t;
+  }
+  const int base = *count;
+  int pos = base + incl - cnt;
+  while (u) {
+    const int bit = __ffs(u) - 1;
+    u &= u - 1;
+    if (pos < cap)
+      list[pos] = (uint32_t)(lane * 32 + bit) | extra | (((u0 >> bit) & 1u) << 24) |
+                  (((u1 >> bit) & 1u) << 25);
+    ++pos;
+  }
+  __syncwarp();
+  if (lane == 31) *count = min(base + incl, cap);
+}
+
+// ------------------------------------------------------------------ dK / dV
+constexpr int kQdoStages = 3;
+constexpr int kKVResident = 2 * 128 * kD * 2;      // K and V tiles, 32 KB each
+constexpr int kQdoStageBytes = 2 * kBS * kD * 2;   // Q_r and dO_r, 16 KB each
+
+struct DkdvTail {
+  uint64_t kv_full;
+  uint64_t qdo_full[kQdoStages], qdo_empty[kQdoStages];
+  uint64_t sdp_full[2], p_full[2];
+  uint64_t all_done;
+  uint32_t tmem_base;
+  int n_list;
+  // [buffer][0 = lse*log2e, 1 = delta][row of the q block]; read as float4
+  alignas(16) float ld[2][2][kBS];
+  uint32_t bits[2][kMaxBlocks / 32];
+  uint32_t list[kMaxEntries];
+};
+constexpr size_t kDkdvSmem = 1024 + kKVResident + kQdoStages * kQdoStageBytes + sizeof(DkdvTail);
+
+template <bool BF16>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap4 tmK,
+                      const __grid_constant__ Tmap4 tmV, const __grid_constant__ Tmap4 tmDO,
+                      bsa_bwd_params bp, int* wait_status) {
+  const bsa_fwd_params& p = bp.f;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint8_t* sK = smem;                    // [2 subtiles][128 rows][128 B]
+  uint8_t* sV = smem + 128 * kD * 2;
+  uint8_t* sQdo = smem + kKVResident;    // stage s: Q_r at s*32K, dO_r at s*32K + 16K
+  DkdvTail* tl = reinterpret_cast<DkdvTail*>(smem + kKVResident + kQdoStages * kQdoStageBytes);
+
+  if (*reinterpret_cast<volatile int*>(wait_status) != 0) return;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int c2 = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int G = p.hq / p.hkv;
+  const int past = p.causal ? p.sk - p.sq : 0;
+  const int kblk[2] = {2 * c2, 2 * c2 + 1};
+  const int kvalid[2] = {kblk[0] * kBS < p.sk ? 1 : 0, kblk[1] * kBS < p.sk ? 1 : 0};
+  if (!kvalid[0]) return;
+  const int nqb = min((p.sq + kBS - 1) / kBS, kMaxBlocks);
+
+  if (tid == 0) {
+    mbar_init(&tl->kv_full, 1);
+    for (int s = 0; s < kQdoStages; ++s) {
+      mbar_init(&tl->qdo_full[s], 1);
+      mbar_init(&tl->qdo_empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&tl->sdp_full[s], 1);
+      mbar_init(&tl->p_full[s], 128);
+    }
+    mbar_init(&tl->all_done, 1);
+    mbar_fence_init();
+    tma_prefetch_desc(&tmQ.map);
+    tma_prefetch_desc(&tmK.map);
+    tma_prefetch_desc(&tmV.map);
+    tma_prefetch_desc(&tmDO.map);
+    tl->n_list = 0;
+  }
+  // ---- entry list: for every q head of the group, union of the two CSC columns
+  for (int g = 0; g < G; ++g) {
+    if (tid < 2 * (kMaxBlocks / 32)) (&tl->bits[0][0])[tid] = 0u;
+    __syncthreads();
+    const int h = hk * G + g;
+    const int hp = pattern_head(h, p.h_pat, p.hq, p.hkv);
+    const int32_t* cc = bp.ccol + (int64_t)hp * bp.ccol_sh;
+    const int32_t* rows = bp.row + (int64_t)hp * bp.row_sh;
+    for (int t = 0; t < 2; ++t) {
+      if (!kvalid[t] || kblk[t] >= bp.n_cols) continue;
+      const int r_beg = cc[kblk[t]], r_end = cc[kblk[t] + 1];
+      for (int i = r_beg + tid; i < r_end; i += kBwdThreads) {
+        const int r = rows[i];
+        if (r < 0 || r >= nqb) continue;
+        const int q_pos_last = past + min(r * kBS + kBS, p.sq) - 1;
+        if (p.causal && kblk[t] * kBS > q_pos_last) continue;
+        atomicOr(&tl->bits[t][r >> 5], 1u << (r & 31));
+      }
+    }
+    __syncthreads();
+    if (warp == 0)
+      append_union(tl->bits[0], tl->bits[1], tl->list, &tl->n_list, (uint32_t)g << 16, lane,
+                   kMaxEntries);
+    __syncthreads();
+  }
+  if (warp == 5) {
+    tmem_alloc(&tl->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const int n = tl->n_list;
+  const uint32_t tmem = tl->tmem_base;
+  const uint32_t tST[2] = {tmem, tmem + 64};
+  const uint32_t tDP[2] = {tmem + 128, tmem + 192};
+  const uint32_t tDV = tmem + 256, tDK = tmem + 384;
+
+  if (n > 0 && warp == 4) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      mbar_expect_tx(&tl->kv_full, (uint32_t)(kvalid[0] + kvalid[1]) * 2 * (kBS * kD * 2));
+      for (int t = 0; t < 2; ++t) {
+        if (!kvalid[t]) continue;
+        for (int c = 0; c < 2; ++c) {
+          tma_load_tile(sK + c * 16384 + t * 8192, &tmK, &tl->kv_full, c * 64, kblk[t] * kBS, hk, b);
+          tma_load_tile(sV + c * 16384 + t * 8192, &tmV, &tl->kv_full, c * 64, kblk[t] * kBS, hk, b);
+        }
+      }
+      for (int e = 0; e < n; ++e) {
+        const int s = e % kQdoStages;
+        const uint32_t ent = tl->list[e];
+        const int r = ent & 0xffff, h = hk * G + ((ent >> 16) & 0xff);
+        if (!mbar_wait(&tl->qdo_empty[s], ((e / kQdoStages) & 1) ^ 1, wait_status, 301)) break;
+        mbar_expect_tx(&tl->qdo_full[s], kQdoStageBytes);
+        uint8_t* qd = sQdo + s * kQdoStageBytes;
+        uint8_t* gd = qd + kBS * kD * 2;
+        for (int c = 0; c < 2; ++c) {
+          tma_load_tile(qd + c * 8192, &tmQ, &tl->qdo_full[s], c * 64, r * kBS, h, b);
+          tma_load_tile(gd + c * 8192, &tmDO, &tl->qdo_full[s], c * 64, r * kBS, h, b);
+        }
+      }
+    }
+  } else if (n > 0 && warp == 5) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc_nt = umma_idesc(BF16, 128, kBS, false, false);  // K.Q^T, V.dO^T
+      const uint32_t idesc_acc = umma_idesc(BF16, 128, kD, false, true);   // P^T.dO, dS^T.Q
+      const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), qdo_addr = smem_u32(sQdo);
+      bool ok = mbar_wait(&tl->kv_full, 0, wait_status, 302);
+      auto issue_sdp = [&](int e) {
+        const int s = e % kQdoStages;
+        if (!mbar_wait(&tl->qdo_full[s], (e / kQdoStages) & 1, wait_status, 303)) return false;
+        tc_fence_after();
+        const uint32_t qa = qdo_addr + s * kQdoStageBytes, ga = qa + kBS * kD * 2;
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            tc_mma_ss(tST[e & 1], umma_desc_sw128(k_addr + c * 16384 + kk * 32, 16, 1024),
+                      umma_desc_sw128(qa + c * 8192 + kk * 32, 16, 1024), idesc_nt, (c | kk) ? 1u : 0u);
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            tc_mma_ss(tDP[e & 1], umma_desc_sw128(v_addr + c * 16384 + kk * 32, 16, 1024),
+                      umma_desc_sw128(ga + c * 8192 + kk * 32, 16, 1024), idesc_nt, (c | kk) ? 1u : 0u);
+        tc_commit(&tl->sdp_full[e & 1]);
+        return true;
+      };
+      if (ok) ok = issue_sdp(0);
+      for (int e = 0; e < n && ok; ++e) {
+        if (e + 1 < n) ok = issue_sdp(e + 1);
+        if (!ok) break;
+        const int s = e % kQdoStages;
+        if (!mbar_wait(&tl->p_full[e & 1], (e >> 1) & 1, wait_status, 304)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t qa = qdo_addr + s * kQdoStageBytes, ga = qa + kBS * kD * 2;
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)   // dV += P^T dO   (B = dO_r, MN-major)
+          tc_mma_ts(tDV, tST[e & 1] + kk * 8, umma_desc_sw128(ga + kk * 2048, 8192, 1024), idesc_acc,
+                    (e | kk) ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)   // dK += dS^T Q   (B = Q_r, MN-major)
+          tc_mma_ts(tDK, tDP[e & 1] + kk * 8, umma_desc_sw128(qa + kk * 2048, 8192, 1024), idesc_acc,
+                    (e | kk) ? 1u : 0u);
+        tc_commit(&tl->qdo_empty[s]);
+      }
+      if (ok) tc_commit(&tl->all_done);
+    }
+    __syncwarp();
+  } else if (n > 0) {
+    // ------------------------------------------------------------ P^T / dS^T (warps 0-3)
+    const int r_kv = tid;                 // tile row = TMEM lane
+    const int t = r_kv >> 6;
+    const int kpos = kblk[t] * kBS + (r_kv & 63);
+    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+    const float scale2 = p.sm_scale * kLog2e;
+    // each of the 128 threads fetches one lse or delta value of the next q block
+    const int which = tid >> 6, idx = tid & 63;
+    auto fetch = [&](int e) -> float {
+      const uint32_t ent = tl->list[e];
+      const int r = ent & 0xffff, h = hk * G + ((ent >> 16) & 0xff);
+      const int qi = r * kBS + idx;
+      if (qi >= p.sq) return which == 0 ? INFINITY : 0.f;
+      if (which == 0) {
+        const float l = p.lse[(int64_t)b * p.lse_sb + (int64_t)h * p.lse_sh + qi];
+        return l == -INFINITY ? INFINITY : l * kLog2e;   // empty row: P = 0
+      }
+      return bp.delta[((int64_t)b * p.hq + h) * p.sq + qi];
+    };
+    tl->ld[0][which][idx] = fetch(0);
+    named_bar_sync(1, 128);
+    bool alive = true;
+    for (int e = 0; e < n; ++e) {
+      const float nxt = e + 1 < n ? fetch(e + 1) : 0.f;
+      if (!mbar_wait(&tl->sdp_full[e & 1], (e >> 1) & 1, wait_status, 305)) { alive = false; break; }
+      tc_fence_after();
+      const uint32_t ent = tl->list[e];
+      const int r = ent & 0xffff;
+      const bool att = ((ent >> (24 + t)) & 1u) != 0 && kvalid[t];
+      // causal: q position past + r*64 + c must be >= kpos  ->  c >= c0
+      const int c0 = p.causal ? kpos - past - r * kBS : 0;
+      const float* lse_s = tl->ld[e & 1][0];
+      const float* del_s = tl->ld[e & 1][1];
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        uint32_t sv[32], dv[32];
+        tmem_ld32(tST[e & 1] + lane_off + hh * 32, sv);
+        tmem_ld32(tDP[e & 1] + lane_off + hh * 32, dv);
+        tmem_ld_wait();
+        uint32_t pp[16], ds[16];
+        if (att) {
+#pragma unroll
+          for (int c4 = 0; c4 < 8; ++c4) {
+            const float4 l4 = *reinterpret_cast<const float4*>(lse_s + hh * 32 + c4 * 4);
+            const float4 d4 = *reinterpret_cast<const float4*>(del_s + hh * 32 + c4 * 4);
+            const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
+            const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
+            float pv[4], dsv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int c = hh * 32 + c4 * 4 + i;
+              float x = ex2(fmaf(__uint_as_float(sv[c4 * 4 + i]), scale2, -ls[i]));
+              if (c < c0) x = 0.f;
+              pv[i] = x;
+              dsv[i] = x * (__uint_as_float(dv[c4 * 4 + i]) - dl[i]);
+            }
+            pp[c4 * 2] = pack2<BF16>(pv[0], pv[1]);
+            pp[c4 * 2 + 1] = pack2<BF16>(pv[2], pv[3]);
+            ds[c4 * 2] = pack2<BF16>(dsv[0], dsv[1]);
+            ds[c4 * 2 + 1] = pack2<BF16>(dsv[2], dsv[3]);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) { pp[i] = 0u; ds[i] = 0u; }
+        }
+        // P^T / dS^T overwrite the columns S^T / dP^T were read from (the second
+        // half of S^T/dP^T lives in columns 32..63 and is read before these stores
+        // reach columns 16..31)
+        if (hh == 1) tmem_ld_wait();
+        tmem_st16(tST[e & 1] + lane_off + hh * 16, pp);
+        tmem_st16(tDP[e & 1] + lane_off + hh * 16, ds);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&tl->p_full[e & 1]);
+      if (e + 1 < n) tl->ld[(e + 1) & 1][which][idx] = nxt;
+      named_bar_sync(1, 128);
+    }
+    // ---- epilogue
+    if (alive) alive = mbar_wait(&tl->all_done, 0, wait_status, 306);
+    tc_fence_after();
+    if (alive) {
+      uint8_t* stage = sQdo + warp * 8192;
+      const int vr[2] = {kvalid[0] ? min(kBS, p.sk - kblk[0] * kBS) : 0,
+                         kvalid[1] ? min(kBS, p.sk - kblk[1] * kBS) : 0};
+      uint8_t* const dvb[2] = {
+          reinterpret_cast<uint8_t*>(bp.dv) +
+              ((int64_t)b * bp.dv_sb + (int64_t)hk * bp.dv_sh + (int64_t)kblk[0] * kBS * bp.dv_ss) * 2,
+          reinterpret_cast<uint8_t*>(bp.dv) +
+              ((int64_t)b * bp.dv_sb + (int64_t)hk * bp.dv_sh + (int64_t)kblk[1] * kBS * bp.dv_ss) * 2};
+      uint8_t* const dkb[2] = {
+          reinterpret_cast<uint8_t*>(bp.dk) +
+              ((int64_t)b * bp.dk_sb + (int64_t)hk * bp.dk_sh + (int64_t)kblk[0] * kBS * bp.dk_ss) * 2,
+          reinterpret_cast<uint8_t*>(bp.dk) +
+              ((int64_t)b * bp.dk_sb + (int64_t)hk * bp.dk_sh + (int64_t)kblk[1] * kBS * bp.dk_ss) * 2};
+      store_acc_tile<BF16>(tDV, warp, lane, 1.f, stage, dvb, vr, bp.dv_ss * 2);
+      store_acc_tile<BF16>(tDK, warp, lane, p.sm_scale, stage, dkb, vr, bp.dk_ss * 2);
+    }
+  } else if (warp < 4) {
+    // nothing attends these kv blocks: zero gradients
+    const int t = tid >> 6;
+    const int kv = kblk[t] * kBS + (tid & 63);
+    if (kvalid[t] && kv < p.sk) {
+      uint2* d1 = reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(bp.dk) +
+          ((int64_t)b * bp.dk_sb + (int64_t)hk * bp.dk_sh + (int64_t)kv * bp.dk_ss) * 2);
+      uint2* d2 = reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(bp.dv) +
+          ((int64_t)b * bp.dv_sb + (int64_t)hk * bp.dv_sh + (int64_t)kv * bp.dv_ss) * 2);
+      for (int i = 0; i < 32; ++i) { d1[i] = make_uint2(0u, 0u); d2[i] = make_uint2(0u, 0u); }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) tmem_dealloc(tmem, 512);
+}
+
+// ------------------------------------------------------------------ dQ
+constexpr int kDqKStages = 3, kDqVStages = 2;
+constexpr int kTileKV = kBS * kD * 2;  // 16 KB
+enum { kPairHeads = 0, kPairRows = 1 };
+
+struct DqTail {
+  uint64_t q_full;
+  uint64_t k_full[kDqKStages], k_empty[kDqKStages];
+  uint64_t v_full[kDqVStages], v_empty[kDqVStages];
+  uint64_t sdp_full[2], p_full[2];
+  uint64_t all_done;
+  uint32_t tmem_base;
+  int n_list;
+  uint32_t bits[2][kMaxBlocks / 32];
+  uint32_t list[kMaxBlocks];
+};
+constexpr size_t kDqSmem = 1024 + 2 * 128 * kD * 2 + (kDqKStages + kDqVStages) * kTileKV + sizeof(DqTail);
+
+template <bool BF16>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap4 tmK,
+                    const __grid_constant__ Tmap4 tmV, const __grid_constant__ Tmap4 tmDO,
+                    bsa_bwd_params bp, int mode, int* wait_status) {
+  const bsa_fwd_params& p = bp.f;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint8_t* sQ = smem;                       // [2 subtiles][128 rows][128 B]
+  uint8_t* sDO = smem + 128 * kD * 2;
+  uint8_t* sKs = smem + 2 * 128 * kD * 2;   // K stages
+  uint8_t* sVs = sKs + kDqKStages * kTileKV;
+  DqTail* tl = reinterpret_cast<DqTail*>(sVs + kDqVStages * kTileKV);
+
+  if (*reinterpret_cast<volatile int*>(wait_status) != 0) return;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int G = p.hq / p.hkv;
+  const int b = blockIdx.z;
+  const int tile = gridDim.x - 1 - blockIdx.x;
+  const int past = p.causal ? p.sk - p.sq : 0;
+  int head[2], qblk[2], valid[2], kvh;
+  if (mode == kPairHeads) {
+    const int pairs = G / 2;
+    kvh = blockIdx.y / pairs;
+    head[0] = kvh * G + 2 * (blockIdx.y % pairs);
+    head[1] = head[0] + 1;
+    qblk[0] = qblk[1] = tile;
+    valid[0] = valid[1] = 1;
+  } else {
+    head[0] = head[1] = blockIdx.y;
+    kvh = blockIdx.y / G;
+    qblk[0] = 2 * tile;
+    qblk[1] = 2 * tile + 1;
+    valid[0] = 1;
+    valid[1] = qblk[1] * kBS < p.sq ? 1 : 0;
+  }
+  if (qblk[0] * kBS >= p.sq) return;
+  const int nkb = min((p.sk + kBS - 1) / kBS, kMaxBlocks);
+
+  if (tid == 0) {
+    mbar_init(&tl->q_full, 1);
+    for (int s = 0; s < kDqKStages; ++s) { mbar_init(&tl->k_full[s], 1); mbar_init(&tl->k_empty[s], 1); }
+    for (int s = 0; s < kDqVStages; ++s) { mbar_init(&tl->v_full[s], 1); mbar_init(&tl->v_empty[s], 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&tl->sdp_full[s], 1); mbar_init(&tl->p_full[s], 128); }
+    mbar_init(&tl->all_done, 1);
+    mbar_fence_init();
+    tma_prefetch_desc(&tmQ.map);
+    tma_prefetch_desc(&tmK.map);
+    tma_prefetch_desc(&tmV.map);
+    tma_prefetch_desc(&tmDO.map);
+    tl->n_list = 0;
+  }
+  if (tid < 2 * (kMaxBlocks / 32)) (&tl->bits[0][0])[tid] = 0u;
+  __syncthreads();
+  for (int t = 0; t < 2; ++t) {
+    if (!valid[t] || qblk[t] >= p.n_rows) continue;
+    const int hp = pattern_head(head[t], p.h_pat, p.hq, p.hkv);
+    const int32_t* cr = p.crow + (int64_t)hp * p.crow_sh;
+    const int32_t* cols = p.col + (int64_t)hp * p.col_sh;
+    const int c_beg = cr[qblk[t]], c_end = cr[qblk[t] + 1];
+    const int q_pos_last = past + min(qblk[t] * kBS + kBS, p.sq) - 1;
+    for (int i = c_beg + tid; i < c_end; i += kBwdThreads) {
+      const int blk = cols[i];
+      if (blk >= 0 && blk < nkb && !(p.causal && blk * kBS > q_pos_last))
+        atomicOr(&tl->bits[t][blk >> 5], 1u << (blk & 31));
+    }
+  }
+  __syncthreads();
+  if (warp == 0) append_union(tl->bits[0], tl->bits[1], tl->list, &tl->n_list, 0u, lane, kMaxBlocks);
+  if (warp == 5) {
+    tmem_alloc(&tl->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const int n = tl->n_list;
+  const uint32_t tmem = tl->tmem_base;
+  const uint32_t tS[2] = {tmem, tmem + 64};
+  const uint32_t tDP[2] = {tmem + 128, tmem + 192};
+  const uint32_t tDQ = tmem + 256;
+
+  if (n > 0 && warp == 4) {
+    if (lane == 0) {
+      mbar_expect_tx(&tl->q_full, (uint32_t)(valid[0] + valid[1]) * 2 * (kBS * kD * 2));
+      for (int t = 0; t < 2; ++t) {
+        if (!valid[t]) continue;
+        for (int c = 0; c < 2; ++c) {
+          tma_load_tile(sQ + c * 16384 + t * 8192, &tmQ, &tl->q_full, c * 64, qblk[t] * kBS, head[t], b);
+          tma_load_tile(sDO + c * 16384 + t * 8192, &tmDO, &tl->q_full, c * 64, qblk[t] * kBS, head[t], b);
+        }
+      }
+      for (int e = 0; e < n; ++e) {
+        const int tok = (int)(tl->list[e] & 0xffffu) * kBS;
+        const int sk_ = e % kDqKStages, sv_ = e % kDqVStages;
+        if (!mbar_wait(&tl->k_empty[sk_], ((e / kDqKStages) & 1) ^ 1, wait_status, 311)) break;
+        mbar_expect_tx(&tl->k_full[sk_], kTileKV);
+        tma_load_tile(sKs + sk_ * kTileKV, &tmK, &tl->k_full[sk_], 0, tok, kvh, b);
+        tma_load_tile(sKs + sk_ * kTileKV + 8192, &tmK, &tl->k_full[sk_], 64, tok, kvh, b);
+        if (!mbar_wait(&tl->v_empty[sv_], ((e / kDqVStages) & 1) ^ 1, wait_status, 312)) break;
+        mbar_expect_tx(&tl->v_full[sv_], kTileKV);
+        tma_load_tile(sVs + sv_ * kTileKV, &tmV, &tl->v_full[sv_], 0, tok, kvh, b);
+        tma_load_tile(sVs + sv_ * kTileKV + 8192, &tmV, &tl->v_full[sv_], 64, tok, kvh, b);
+      }
+    }
+  } else if (n > 0 && warp == 5) {
+    if (lane == 0) {
+      const uint32_t idesc_nt = umma_idesc(BF16, 128, kBS, false, false);
+      const uint32_t idesc_acc = umma_idesc(BF16, 128, kD, false, true);
+      const uint32_t q_addr = smem_u32(sQ), do_addr = smem_u32(sDO);
+      const uint32_t k_addr = smem_u32(sKs), v_addr = smem_u32(sVs);
+      bool ok = mbar_wait(&tl->q_full, 0, wait_status, 313);
+      auto issue_sdp = [&](int e) {
+        const int sk_ = e % kDqKStages, sv_ = e % kDqVStages;
+        if (!mbar_wait(&tl->k_full[sk_], (e / kDqKStages) & 1, wait_status, 314)) return false;
+        tc_fence_after();
+        const uint32_t kb = k_addr + sk_ * kTileKV;
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            tc_mma_ss(tS[e & 1], umma_desc_sw128(q_addr + c * 16384 + kk * 32, 16, 1024),
+                      umma_desc_sw128(kb + c * 8192 + kk * 32, 16, 1024), idesc_nt, (c | kk) ? 1u : 0u);
+        if (!mbar_wait(&tl->v_full[sv_], (e / kDqVStages) & 1, wait_status, 315)) return false;
+        tc_fence_after();
+        const uint32_t vb = v_addr + sv_ * kTileKV;
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            tc_mma_ss(tDP[e & 1], umma_desc_sw128(do_addr + c * 16384 + kk * 32, 16, 1024),
+                      umma_desc_sw128(vb + c * 8192 + kk * 32, 16, 1024), idesc_nt, (c | kk) ? 1u : 0u);
+        tc_commit(&tl->v_empty[sv_]);
+        tc_commit(&tl->sdp_full[e & 1]);
+        return true;
+      };
+      if (ok) ok = issue_sdp(0);
+      for (int e = 0; e < n && ok; ++e) {
+        if (e + 1 < n) ok = issue_sdp(e + 1);
+        if (!ok) break;
+        const int sk_ = e % kDqKStages;
+        if (!mbar_wait(&tl->p_full[e & 1], (e >> 1) & 1, wait_status, 316)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t kb = k_addr + sk_ * kTileKV;
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)   // dQ += dS K   (B = K_j, MN-major)
+          tc_mma_ts(tDQ, tDP[e & 1] + kk * 8, umma_desc_sw128(kb + kk * 2048, 8192, 1024), idesc_acc,
+                    (e | kk) ? 1u : 0u);
+        tc_commit(&tl->k_empty[sk_]);
+      }
+      if (ok) tc_commit(&tl->all_done);
+    }
+    __syncwarp();
+  } else if (n > 0) {
+    const int r = tid, t = r >> 6, rr = r & 63;
+    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+    const float scale2 = p.sm_scale * kLog2e;
+    const int q_row = qblk[t] * kBS + rr;
+    const int qpos = past + q_row;
+    float lse2 = INFINITY, delta = 0.f;
+    if (valid[t] && q_row < p.sq) {
+      const float l = p.lse[(int64_t)b * p.lse_sb + (int64_t)head[t] * p.lse_sh + q_row];
+      lse2 = l == -INFINITY ? INFINITY : l * kLog2e;
+      delta = bp.delta[((int64_t)b * p.hq + head[t]) * p.sq + q_row];
+    }
+    bool alive = true;
+    for (int e = 0; e < n; ++e) {
+      if (!mbar_wait(&tl->sdp_full[e & 1], (e >> 1) & 1, wait_status, 317)) { alive = false; break; }
+      tc_fence_after();
+      const uint32_t ent = tl->list[e];
+      const int kbase = (int)(ent & 0xffffu) * kBS;
+      const bool att = ((ent >> (24 + t)) & 1u) != 0 && valid[t];
+      int lim = p.sk - kbase;
+      if (p.causal) lim = min(lim, qpos - kbase + 1);
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        uint32_t sv[32], dv[32];
+        tmem_ld32(tS[e & 1] + lane_off + hh * 32, sv);
+        tmem_ld32(tDP[e & 1] + lane_off + hh * 32, dv);
+        tmem_ld_wait();
+        uint32_t ds[16];
+        if (att) {
+#pragma unroll
+          for (int c2 = 0; c2 < 16; ++c2) {
+            float x0 = ex2(fmaf(__uint_as_float(sv[2 * c2]), scale2, -lse2));
+            float x1 = ex2(fmaf(__uint_as_float(sv[2 * c2 + 1]), scale2, -lse2));
+            if (hh * 32 + 2 * c2 >= lim) x0 = 0.f;
+            if (hh * 32 + 2 * c2 + 1 >= lim) x1 = 0.f;
+            ds[c2] = pack2<BF16>(x0 * (__uint_as_float(dv[2 * c2]) - delta),
+                                 x1 * (__uint_as_float(dv[2 * c2 + 1]) - delta));
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) ds[i] = 0u;
+        }
+        if (hh == 1) tmem_ld_wait();
+        tmem_st16(tDP[e & 1] + lane_off + hh * 16, ds);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&tl->p_full[e & 1]);
+    }
+    if (alive) alive = mbar_wait(&tl->all_done, 0, wait_status, 318);
+    tc_fence_after();
+    if (alive) {
+      uint8_t* stage = sQ + warp * 8192;   // Q is dead once every product has completed
+      const int vr[2] = {valid[0] ? min(kBS, p.sq - qblk[0] * kBS) : 0,
+                         valid[1] ? min(kBS, p.sq - qblk[1] * kBS) : 0};
+      uint8_t* const dqb[2] = {
+          reinterpret_cast<uint8_t*>(bp.dq) + ((int64_t)b * bp.dq_sb + (int64_t)head[0] * bp.dq_sh +
+                                               (int64_t)qblk[0] * kBS * bp.dq_ss) * 2,
+          reinterpret_cast<uint8_t*>(bp.dq) + ((int64_t)b * bp.dq_sb + (int64_t)head[1] * bp.dq_sh +
+                                               (int64_t)qblk[1] * kBS * bp.dq_ss) * 2};
+      store_acc_tile<BF16>(tDQ, warp, lane, p.sm_scale, stage, dqb, vr, bp.dq_ss * 2);
+    }
+  } else if (warp < 4) {
+    const int t = tid >> 6;
+    const int q_row = qblk[t] * kBS + (tid & 63);
+    if (valid[t] && q_row < p.sq) {
+      uint2* d = reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(bp.dq) +
+          ((int64_t)b * bp.dq_sb + (int64_t)head[t] * bp.dq_sh + (int64_t)q_row * bp.dq_ss) * 2);
+      for (int i = 0; i < 32; ++i) d[i] = make_uint2(0u, 0u);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) tmem_dealloc(tmem, 512);
+}
+
+bool rows8(const void* ptr, int64_t ss, int64_t sh, int64_t sb) {
+  return reinterpret_cast<uintptr_t>(ptr) % 8 == 0 && ss % 4 == 0 && sh % 4 == 0 && sb % 4 == 0;
+}
+
+template <bool BF16>
+int launch_bwd(const bsa_bwd_params* bp, cudaStream_t s) {
+  const bsa_fwd_params* p = &bp->f;
+  Tmap4 tmQ, tmK, tmV, tmDO;
+  int rc = make_tmap_4d(&tmQ, p->q, 2, kD, p->sq, p->hq, p->batch, p->q_ss * 2, p->q_sh * 2, p->q_sb * 2,
+                        64, 64, true, BF16);
+  if (rc) return rc;
+  rc = make_tmap_4d(&tmDO, bp->d_o, 2, kD, p->sq, p->hq, p->batch, bp->do_ss * 2, bp->do_sh * 2,
+                    bp->do_sb * 2, 64, 64, true, BF16);
+  if (rc) return rc;
+  rc = make_tmap_4d(&tmK, p->k, 2, kD, p->sk, p->hkv, p->batch, p->k_ss * 2, p->k_sh * 2, p->k_sb * 2,
+                    64, 64, true, BF16);
+  if (rc) return rc;
+  rc = make_tmap_4d(&tmV, p->v, 2, kD, p->sk, p->hkv, p->batch, p->v_ss * 2, p->v_sh * 2, p->v_sb * 2,
+                    64, 64, true, BF16);
+  if (rc) return rc;
+  int* status = wait_status_ptr();
+  if (!status) return BSA_E_CUDA;
+  {
+    const long long rows = (long long)p->batch * p->hq * p->sq;
+    bwd_delta_vec_kernel<BF16><<<(unsigned)((rows + 7) / 8), 256, 0, s>>>(*bp);
+    rc = check_launch("bwd_delta_vec_kernel");
+    if (rc) return rc;
+  }
+  {
+    auto kern = bwd_dkdv_sm100_kernel<BF16>;
+    BSA_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDkdvSmem));
+    dim3 grid(cdiv_i(cdiv_i(p->sk, kBS), 2), p->hkv, p->batch);
+    kern<<<grid, kBwdThreads, kDkdvSmem, s>>>(tmQ, tmK, tmV, tmDO, *bp, status);
+    rc = check_launch("bwd_dkdv_sm100_kernel");
+    if (rc) return rc;
+  }
+  {
+    const int G = p->hq / p->hkv;
+    const int mode = (G % 2 == 0) ? kPairHeads : kPairRows;
+    auto kern = bwd_dq_sm100_kernel<BF16>;
+    BSA_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDqSmem));
+    dim3 grid(cdiv_i(p->sq, mode == kPairHeads ? 64 : 128), mode == kPairHeads ? p->hq / 2 : p->hq,
+              p->batch);
+    kern<<<grid, kBwdThreads, kDqSmem, s>>>(tmQ, tmK, tmV, tmDO, *bp, mode, status);
+    rc = check_launch("bwd_dq_sm100_kernel");
+  }
+  return rc;
+}
+
+}  // namespace
+
+bool sm100_bwd_supported(const bsa_bwd_params* bp, const char** why) {
+  const bsa_fwd_params* p = &bp->f;
+  auto no = [&](const char* w) { *why = w; return false; };
+  if (!(p->dtype == BSA_F16 || p->dtype == BSA_BF16)) return no("dtype is not f16/bf16");
+  if (p->d != kD) return no("head dim is not 128");
+  if (p->block_size != kBS) return no("block size is not 64");
+  if (p->sk > kMaxBlocks * kBS || p->sq > kMaxBlocks * kBS) return no("more than 65536 positions");
+  if ((p->hq / p->hkv) * cdiv_i(p->sq, kBS) > kMaxEntries)
+    return no("group size x q blocks exceeds the per-CTA list capacity");
+  if (p->hq / p->hkv > 255) return no("group size above 255");
+  if (p->q_start || p->k_start || p->row_mode != BSA_ROWS_BY_TILE) return no("padded or packed batch");
+  if (!tma_compatible(p->q, 2, p->q_ss, p->q_sh, p->q_sb) ||
+      !tma_compatible(p->k, 2, p->k_ss, p->k_sh, p->k_sb) ||
+      !tma_compatible(p->v, 2, p->v_ss, p->v_sh, p->v_sb) ||
+      !tma_compatible(bp->d_o, 2, bp->do_ss, bp->do_sh, bp->do_sb))
+    return no("q/k/v/dO need 16-byte aligned bases and strides that are multiples of 16 bytes");
+  if (!rows8(p->o, p->o_ss, p->o_sh, p->o_sb) || !rows8(bp->d_o, bp->do_ss, bp->do_sh, bp->do_sb) ||
+      !rows8(bp->dq, bp->dq_ss, bp->dq_sh, bp->dq_sb) || !rows8(bp->dk, bp->dk_ss, bp->dk_sh, bp->dk_sb) ||
+      !rows8(bp->dv, bp->dv_ss, bp->dv_sh, bp->dv_sb))
+    return no("o/dO/dQ/dK/dV rows are not 8-byte aligned");
+  if (p->sq == 0 || p->sk == 0 || p->batch == 0) return no("empty problem");
+  if (!(p->sm_scale > 0.f)) return no("sm_scale is not positive");
+  return true;
+}
+
+int sm100_bwd(const bsa_bwd_params* bp, cudaStream_t s) {
+  return bp->f.dtype == BSA_BF16 ? launch_bwd<true>(bp, s) : launch_bwd<false>(bp, s);
+}
+
+}  // namespace bsa

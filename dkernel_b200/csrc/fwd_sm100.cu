@@ -474,10 +474,4 @@ int sm100_fwd(const bsa_fwd_params* p, cudaStream_t s) {
   return check_launch("fwd_sm100_kernel");
 }
 
-bool sm100_bwd_supported(const bsa_bwd_params*, const char** why) {
-  *why = "the tcgen05 backward is not built yet";
-  return false;
-}
-int sm100_bwd(const bsa_bwd_params*, cudaStream_t) { return BSA_E_UNSUPPORTED; }
-
 }  // namespace bsa

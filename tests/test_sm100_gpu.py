@@ -109,3 +109,72 @@ def test_sm100_varlen_and_padded_routes():
     _wait_status_clean()
     assert_out_close(out, ref)
     assert_lse_close(lse, ref_lse)
+
+
+BWD_CASES = [
+    # B, Hq, Hkv, Sq, Sk, dtype, seq_dim, pattern kwargs
+    (1, 2, 2, 128, 128, torch.bfloat16, 1, dict(block_size=64, local_blocks=2, vert_stride=2)),
+    (1, 2, 2, 512, 512, torch.bfloat16, 1, dict(block_size=64, local_blocks=2, vert_stride=4)),
+    (2, 4, 2, 320, 320, torch.bfloat16, 2, dict(block_size=64, local_blocks=2, vert_stride=3, num_kv_heads=2)),
+    (1, 3, 3, 200, 200, torch.float16, 1, dict(block_size=64, local_blocks=2, vert_stride=2)),
+    (1, 2, 2, 256, 256, torch.bfloat16, 2, dict(block_size=64, local_blocks=1, vert_stride=3, causal=False)),
+    (1, 2, 2, 256, 640, torch.bfloat16, 1, dict(block_size=64, local_blocks=2, vert_stride=3)),
+    (1, 6, 2, 448, 448, torch.float16, 1, dict(block_size=64, local_blocks=2, vert_stride=4, num_kv_heads=2)),
+    (1, 8, 1, 192, 192, torch.bfloat16, 1, dict(block_size=64, local_blocks=1, vert_stride=2, num_kv_heads=1)),
+]
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,Sq,Sk,dtype,seq_dim,pk", BWD_CASES)
+def test_sm100_backward_vs_oracle(B, Hq, Hkv, Sq, Sk, dtype, seq_dim, pk):
+    from helpers import assert_grad_close
+    D = 128
+    causal = pk.get("causal", True)
+    bs = pk["block_size"]
+    shape = (lambda h, s: (B, h, s, D)) if seq_dim == 2 else (lambda h, s: (B, s, h, D))
+    q, k, v, do = seeded_qkv(21, shape(Hq, Sq), shape(Hkv, Sk), dtype, with_do=True)
+    bm = O.block_mask(Hq, Sk, **pk)
+    qf, kf, vf = (t.detach().clone().float().requires_grad_() for t in (q, k, v))
+    # oracle: q tile rows of the pattern, causal offset Sk - Sq
+    dense = torch.from_numpy(bm[:, :(Sq + bs - 1) // bs]).repeat_interleave(bs, 1).repeat_interleave(bs, 2)
+    dense = dense[:, :Sq, :Sk].bool()
+    if causal:
+        dense = dense & (torch.arange(Sq)[:, None] + (Sk - Sq) >= torch.arange(Sk)[None, :])
+    ref, ref_lse = O.masked_dense_attention(qf, kf, vf, dense[None].to(torch.uint8), None, seq_dim=seq_dim,
+                                            return_lse=True)
+    w = torch.randn(ref_lse.shape, generator=torch.Generator().manual_seed(2))
+    ((ref * do.float()).sum() + (ref_lse * w).sum()).backward()
+    mod = _module(Hq, Sk, pk, seq_dim=seq_dim, impl="sm100", bwd_impl="sm100")
+    qg, kg, vg = (t.cuda().requires_grad_() for t in (q, k, v))
+    out, lse = mod(qg, kg, vg, return_lse=True)
+    ((out.float() * do.cuda().float()).sum() + (lse * w.cuda()).sum()).backward()
+    _wait_status_clean()
+    assert_out_close(out, ref)
+    assert_grad_close(qg.grad, qf.grad, "dq")
+    assert_grad_close(kg.grad, kf.grad, "dk")
+    assert_grad_close(vg.grad, vf.grad, "dv")
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,S,pk", [
+    (1, 4, 4, 2048, dict(block_size=64, local_blocks=8, vert_stride=8)),
+    (1, 8, 2, 2048, dict(block_size=64, local_blocks=4, vert_stride=4, num_kv_heads=2)),
+    (2, 2, 2, 4096, dict(block_size=64, local_blocks=32, vert_stride=8)),
+])
+def test_sm100_backward_matches_generic_on_long_sequences(B, Hq, Hkv, S, pk):
+    from helpers import assert_grad_close
+    q, k, v, do = seeded_qkv(3, (B, S, Hq, 128), (B, S, Hkv, 128), torch.bfloat16, device="cuda", with_do=True)
+    grads = {}
+    for name in ("sm100", "generic"):
+        mod = _module(Hq, S, pk, seq_dim=1, impl=name, bwd_impl=name)
+        qg, kg, vg = (t.clone().requires_grad_() for t in (q, k, v))
+        out = mod(qg, kg, vg)
+        out.backward(do)
+        grads[name] = (qg.grad, kg.grad, vg.grad)
+    _wait_status_clean()
+    for a, b_, n in zip(grads["sm100"], grads["generic"], ("dq", "dk", "dv")):
+        assert_grad_close(a, b_, n, 2e-2)
+    # atomics-free: a second run reproduces the same bits
+    mod = _module(Hq, S, pk, seq_dim=1, impl="sm100", bwd_impl="sm100")
+    qg, kg, vg = (t.clone().requires_grad_() for t in (q, k, v))
+    mod(qg, kg, vg).backward(do)
+    for a, b_ in zip(grads["sm100"], (qg.grad, kg.grad, vg.grad)):
+        assert torch.equal(a, b_)
