@@ -11,7 +11,7 @@ import os
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libbsa_b200.so")
+LIB_PATH = os.environ.get("BSA_B200_LIB") or os.path.join(_HERE, "libbsa_b200.so")
 
 BSA_F16, BSA_BF16, BSA_F32 = 0, 1, 2
 IMPL_AUTO, IMPL_GENERIC, IMPL_SM100 = 0, 1, 2

@@ -15,7 +15,11 @@
 // dS^T are written back by tcgen05.st and consumed as TMEM A operands while Q and
 // dO serve as MN-major B operands straight from their TMA tiles.  S/dP are double
 // buffered in TMEM (512 columns, one CTA per SM) so the MMAs of step e+1 overlap
-// the exponentials of step e.  Math: dkernel/ops/sparse_attn_bwd.py:86-170
+// the exponentials of step e.  352 threads: eight element-wise warps (a TMEM lane
+// quadrant x a 32-column half each, which halves the latency of the element-wise
+// step), one TMA producer warp and two MMA issuer warps (first-stage products
+// S/dP and second-stage accumulations), because the thread that issues a burst
+// of tcgen05.mma is busy until the tensor pipe has accepted it.  Math: dkernel/ops/sparse_attn_bwd.py:86-170
 // (dK/dV), :329-419 (dQ), :73-80 (delta); P and dS are rounded to the input
 // type before the second-stage products, like the reference (:144,:166,:413).
 #include "ptx.cuh"
@@ -25,7 +29,8 @@ namespace {
 
 constexpr int kD = 128;
 constexpr int kBS = 64;
-constexpr int kBwdThreads = 192;
+constexpr int kBwdThreads = 352;
+constexpr int kWarpProducer = 8, kWarpIssueA = 9, kWarpIssueB = 10;
 constexpr int kMaxBlocks = 1024;   // q or kv blocks per sequence (64K tokens)
 constexpr int kMaxEntries = 2048;  // list entries per CTA
 
@@ -46,6 +51,12 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   }
 }
 
+// Packed 16-bit P / dS overwrite the fp32 columns they were computed from: the
+// warp that owns S columns [32h, 32h+32) stores its 16 packed columns at
+// [32h, 32h+16), so no warp writes into columns another warp still has to read.
+// k-step kk (16 rows of the second-stage product) therefore starts at this column.
+__device__ __forceinline__ uint32_t packed_col(int kk) { return (uint32_t)((kk >> 1) * 32 + (kk & 1) * 8); }
+
 __device__ __forceinline__ void named_bar_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
@@ -58,7 +69,7 @@ template <bool BF16>
 __device__ __forceinline__ void store_acc_tile(uint32_t tacc, int warp, int lane, float scale,
                                                uint8_t* stage, uint8_t* const (&base)[2],
                                                const int (&valid_rows)[2], int64_t row_stride_bytes) {
-  const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+  const uint32_t lane_off = (uint32_t)(warp * 32) << 16;   // warp = TMEM lane quadrant (0..3)
 #pragma unroll
   for (int ch = 0; ch < 4; ++ch) {
     uint32_t o[32];
@@ -165,7 +176,7 @@ constexpr int kQdoStageBytes = 2 * kBS * kD * 2;   // Q_r and dO_r, 16 KB each
 struct DkdvTail {
   uint64_t kv_full;
   uint64_t qdo_full[kQdoStages], qdo_empty[kQdoStages];
-  uint64_t sdp_full[2], p_full[2];
+  uint64_t sdp_full[2], p_full[2], acc_done[2];
   uint64_t all_done;
   uint32_t tmem_base;
   int n_list;
@@ -208,7 +219,8 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&tl->sdp_full[s], 1);
-      mbar_init(&tl->p_full[s], 128);
+      mbar_init(&tl->p_full[s], 256);
+      mbar_init(&tl->acc_done[s], 1);
     }
     mbar_init(&tl->all_done, 1);
     mbar_fence_init();
@@ -243,7 +255,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
                    kMaxEntries);
     __syncthreads();
   }
-  if (warp == 5) {
+  if (warp == kWarpIssueA) {
     tmem_alloc(&tl->tmem_base, 512);
     tmem_relinquish();
   }
@@ -256,7 +268,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
   const uint32_t tDP[2] = {tmem + 128, tmem + 192};
   const uint32_t tDV = tmem + 256, tDK = tmem + 384;
 
-  if (n > 0 && warp == 4) {
+  if (n > 0 && warp == kWarpProducer) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       mbar_expect_tx(&tl->kv_full, (uint32_t)(kvalid[0] + kvalid[1]) * 2 * (kBS * kD * 2));
@@ -281,63 +293,72 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
         }
       }
     }
-  } else if (n > 0 && warp == 5) {
-    // ------------------------------------------------------------ MMA issuer
+  } else if (n > 0 && warp == kWarpIssueA) {
+    // ------------------------------------------------------------ S^T = K Q^T, dP^T = V dO^T
     if (lane == 0) {
-      const uint32_t idesc_nt = umma_idesc(BF16, 128, kBS, false, false);  // K.Q^T, V.dO^T
-      const uint32_t idesc_acc = umma_idesc(BF16, 128, kD, false, true);   // P^T.dO, dS^T.Q
-      const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), qdo_addr = smem_u32(sQdo);
+      const uint32_t idesc_nt = umma_idesc(BF16, 128, kBS, false, false);
+      const uint64_t kdesc = umma_desc_sw128(smem_u32(sK), 16, 1024);
+      const uint64_t vdesc = umma_desc_sw128(smem_u32(sV), 16, 1024);
+      const uint64_t qdesc0 = umma_desc_sw128(smem_u32(sQdo), 16, 1024);
       bool ok = mbar_wait(&tl->kv_full, 0, wait_status, 302);
-      auto issue_sdp = [&](int e) {
-        const int s = e % kQdoStages;
-        if (!mbar_wait(&tl->qdo_full[s], (e / kQdoStages) & 1, wait_status, 303)) return false;
-        tc_fence_after();
-        const uint32_t qa = qdo_addr + s * kQdoStageBytes, ga = qa + kBS * kD * 2;
-#pragma unroll
-        for (int c = 0; c < 2; ++c)
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            tc_mma_ss(tST[e & 1], umma_desc_sw128(k_addr + c * 16384 + kk * 32, 16, 1024),
-                      umma_desc_sw128(qa + c * 8192 + kk * 32, 16, 1024), idesc_nt, (c | kk) ? 1u : 0u);
-#pragma unroll
-        for (int c = 0; c < 2; ++c)
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            tc_mma_ss(tDP[e & 1], umma_desc_sw128(v_addr + c * 16384 + kk * 32, 16, 1024),
-                      umma_desc_sw128(ga + c * 8192 + kk * 32, 16, 1024), idesc_nt, (c | kk) ? 1u : 0u);
-        tc_commit(&tl->sdp_full[e & 1]);
-        return true;
-      };
-      if (ok) ok = issue_sdp(0);
       for (int e = 0; e < n && ok; ++e) {
-        if (e + 1 < n) ok = issue_sdp(e + 1);
-        if (!ok) break;
-        const int s = e % kQdoStages;
-        if (!mbar_wait(&tl->p_full[e & 1], (e >> 1) & 1, wait_status, 304)) { ok = false; break; }
+        const int s = e % kQdoStages, bf = e & 1;
+        if (!mbar_wait(&tl->qdo_full[s], (e / kQdoStages) & 1, wait_status, 303)) break;
+        // the buffers still hold P^T / dS^T of entry e-2 until its accumulations finished
+        if (e >= 2 && !mbar_wait(&tl->acc_done[bf], ((e - 2) >> 1) & 1, wait_status, 307)) break;
         tc_fence_after();
-        const uint32_t qa = qdo_addr + s * kQdoStageBytes, ga = qa + kBS * kD * 2;
+        const uint64_t qd = qdesc0 + (uint64_t)((s * kQdoStageBytes) >> 4);
+        const uint64_t gd = qd + (uint64_t)((kBS * kD * 2) >> 4);
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)   // dV += P^T dO   (B = dO_r, MN-major)
-          tc_mma_ts(tDV, tST[e & 1] + kk * 8, umma_desc_sw128(ga + kk * 2048, 8192, 1024), idesc_acc,
+        for (int i = 0; i < 8; ++i)   // i = c * 4 + kk
+          tc_mma_ss(tST[bf], kdesc + (uint64_t)(((i >> 2) * 16384 + (i & 3) * 32) >> 4),
+                    qd + (uint64_t)(((i >> 2) * 8192 + (i & 3) * 32) >> 4), idesc_nt, i ? 1u : 0u);
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          tc_mma_ss(tDP[bf], vdesc + (uint64_t)(((i >> 2) * 16384 + (i & 3) * 32) >> 4),
+                    gd + (uint64_t)(((i >> 2) * 8192 + (i & 3) * 32) >> 4), idesc_nt, i ? 1u : 0u);
+        tc_commit(&tl->sdp_full[bf]);
+      }
+    }
+    __syncwarp();
+  } else if (n > 0 && warp == kWarpIssueB) {
+    // ------------------------------------------------------------ dV += P^T dO, dK += dS^T Q
+    if (lane == 0) {
+      const uint32_t idesc_acc = umma_idesc(BF16, 128, kD, false, true);
+      // B operands are the dO_r / Q_r tiles read MN-major: 16 q rows (2 KB) per k-step,
+      // the two 64-dim halves 8 KB apart
+      const uint64_t qdesc0 = umma_desc_sw128(smem_u32(sQdo), 8192, 1024);
+      bool ok = true;
+      for (int e = 0; e < n; ++e) {
+        const int s = e % kQdoStages, bf = e & 1;
+        if (!mbar_wait(&tl->p_full[bf], (e >> 1) & 1, wait_status, 304)) { ok = false; break; }
+        tc_fence_after();
+        const uint64_t qd = qdesc0 + (uint64_t)((s * kQdoStageBytes) >> 4);
+        const uint64_t gd = qd + (uint64_t)((kBS * kD * 2) >> 4);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          tc_mma_ts(tDV, tST[bf] + packed_col(kk), gd + (uint64_t)((kk * 2048) >> 4), idesc_acc,
                     (e | kk) ? 1u : 0u);
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)   // dK += dS^T Q   (B = Q_r, MN-major)
-          tc_mma_ts(tDK, tDP[e & 1] + kk * 8, umma_desc_sw128(qa + kk * 2048, 8192, 1024), idesc_acc,
+        for (int kk = 0; kk < 4; ++kk)
+          tc_mma_ts(tDK, tDP[bf] + packed_col(kk), qd + (uint64_t)((kk * 2048) >> 4), idesc_acc,
                     (e | kk) ? 1u : 0u);
         tc_commit(&tl->qdo_empty[s]);
+        tc_commit(&tl->acc_done[bf]);
       }
       if (ok) tc_commit(&tl->all_done);
     }
     __syncwarp();
   } else if (n > 0) {
-    // ------------------------------------------------------------ P^T / dS^T (warps 0-3)
-    const int r_kv = tid;                 // tile row = TMEM lane
+    // ------------------------------------------------------------ P^T / dS^T (warps 0-7)
+    const int quad = warp & 3, half = warp >> 2;   // TMEM lane quadrant, 32-column half
+    const int r_kv = quad * 32 + lane;             // tile row = TMEM lane
     const int t = r_kv >> 6;
     const int kpos = kblk[t] * kBS + (r_kv & 63);
-    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
     const float scale2 = p.sm_scale * kLog2e;
-    // each of the 128 threads fetches one lse or delta value of the next q block
-    const int which = tid >> 6, idx = tid & 63;
+    // threads 0..127 fetch one lse or delta value of the next q block each
+    const int which = (tid >> 6) & 1, idx = tid & 63;
     auto fetch = [&](int e) -> float {
       const uint32_t ent = tl->list[e];
       const int r = ent & 0xffff, h = hk * G + ((ent >> 16) & 0xff);
@@ -349,11 +370,11 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
       }
       return bp.delta[((int64_t)b * p.hq + h) * p.sq + qi];
     };
-    tl->ld[0][which][idx] = fetch(0);
-    named_bar_sync(1, 128);
+    if (tid < 128) tl->ld[0][which][idx] = fetch(0);
+    named_bar_sync(1, 256);
     bool alive = true;
     for (int e = 0; e < n; ++e) {
-      const float nxt = e + 1 < n ? fetch(e + 1) : 0.f;
+      const float nxt = (tid < 128 && e + 1 < n) ? fetch(e + 1) : 0.f;
       if (!mbar_wait(&tl->sdp_full[e & 1], (e >> 1) & 1, wait_status, 305)) { alive = false; break; }
       tc_fence_after();
       const uint32_t ent = tl->list[e];
@@ -361,72 +382,69 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
       const bool att = ((ent >> (24 + t)) & 1u) != 0 && kvalid[t];
       // causal: q position past + r*64 + c must be >= kpos  ->  c >= c0
       const int c0 = p.causal ? kpos - past - r * kBS : 0;
-      const float* lse_s = tl->ld[e & 1][0];
-      const float* del_s = tl->ld[e & 1][1];
+      const float* lse_s = tl->ld[e & 1][0] + half * 32;
+      const float* del_s = tl->ld[e & 1][1] + half * 32;
+      uint32_t sv[32], dv[32];
+      tmem_ld32(tST[e & 1] + lane_off + half * 32, sv);
+      tmem_ld32(tDP[e & 1] + lane_off + half * 32, dv);
+      tmem_ld_wait();
+      uint32_t pp[16], ds[16];
+      if (att) {
 #pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {
-        uint32_t sv[32], dv[32];
-        tmem_ld32(tST[e & 1] + lane_off + hh * 32, sv);
-        tmem_ld32(tDP[e & 1] + lane_off + hh * 32, dv);
-        tmem_ld_wait();
-        uint32_t pp[16], ds[16];
-        if (att) {
+        for (int c4 = 0; c4 < 8; ++c4) {
+          const float4 l4 = *reinterpret_cast<const float4*>(lse_s + c4 * 4);
+          const float4 d4 = *reinterpret_cast<const float4*>(del_s + c4 * 4);
+          const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
+          const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
+          float pv[4], dsv[4];
 #pragma unroll
-          for (int c4 = 0; c4 < 8; ++c4) {
-            const float4 l4 = *reinterpret_cast<const float4*>(lse_s + hh * 32 + c4 * 4);
-            const float4 d4 = *reinterpret_cast<const float4*>(del_s + hh * 32 + c4 * 4);
-            const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
-            const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
-            float pv[4], dsv[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int c = hh * 32 + c4 * 4 + i;
-              float x = ex2(fmaf(__uint_as_float(sv[c4 * 4 + i]), scale2, -ls[i]));
-              if (c < c0) x = 0.f;
-              pv[i] = x;
-              dsv[i] = x * (__uint_as_float(dv[c4 * 4 + i]) - dl[i]);
-            }
-            pp[c4 * 2] = pack2<BF16>(pv[0], pv[1]);
-            pp[c4 * 2 + 1] = pack2<BF16>(pv[2], pv[3]);
-            ds[c4 * 2] = pack2<BF16>(dsv[0], dsv[1]);
-            ds[c4 * 2 + 1] = pack2<BF16>(dsv[2], dsv[3]);
+          for (int i = 0; i < 4; ++i) {
+            const int c = half * 32 + c4 * 4 + i;
+            float x = ex2(fmaf(__uint_as_float(sv[c4 * 4 + i]), scale2, -ls[i]));
+            if (c < c0) x = 0.f;
+            pv[i] = x;
+            dsv[i] = x * (__uint_as_float(dv[c4 * 4 + i]) - dl[i]);
           }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) { pp[i] = 0u; ds[i] = 0u; }
+          pp[c4 * 2] = pack2<BF16>(pv[0], pv[1]);
+          pp[c4 * 2 + 1] = pack2<BF16>(pv[2], pv[3]);
+          ds[c4 * 2] = pack2<BF16>(dsv[0], dsv[1]);
+          ds[c4 * 2 + 1] = pack2<BF16>(dsv[2], dsv[3]);
         }
-        // P^T / dS^T overwrite the columns S^T / dP^T were read from (the second
-        // half of S^T/dP^T lives in columns 32..63 and is read before these stores
-        // reach columns 16..31)
-        if (hh == 1) tmem_ld_wait();
-        tmem_st16(tST[e & 1] + lane_off + hh * 16, pp);
-        tmem_st16(tDP[e & 1] + lane_off + hh * 16, ds);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) { pp[i] = 0u; ds[i] = 0u; }
       }
+      // packed results go over the first 16 of the 32 columns this warp has just read
+      tmem_st16(tST[e & 1] + lane_off + half * 32, pp);
+      tmem_st16(tDP[e & 1] + lane_off + half * 32, ds);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&tl->p_full[e & 1]);
-      if (e + 1 < n) tl->ld[(e + 1) & 1][which][idx] = nxt;
-      named_bar_sync(1, 128);
+      if (tid < 128 && e + 1 < n) tl->ld[(e + 1) & 1][which][idx] = nxt;
+      named_bar_sync(1, 256);
     }
-    // ---- epilogue
+    // ---- epilogue: warps 0-3 write dV, warps 4-7 write dK
     if (alive) alive = mbar_wait(&tl->all_done, 0, wait_status, 306);
     tc_fence_after();
     if (alive) {
       uint8_t* stage = sQdo + warp * 8192;
       const int vr[2] = {kvalid[0] ? min(kBS, p.sk - kblk[0] * kBS) : 0,
                          kvalid[1] ? min(kBS, p.sk - kblk[1] * kBS) : 0};
-      uint8_t* const dvb[2] = {
-          reinterpret_cast<uint8_t*>(bp.dv) +
-              ((int64_t)b * bp.dv_sb + (int64_t)hk * bp.dv_sh + (int64_t)kblk[0] * kBS * bp.dv_ss) * 2,
-          reinterpret_cast<uint8_t*>(bp.dv) +
-              ((int64_t)b * bp.dv_sb + (int64_t)hk * bp.dv_sh + (int64_t)kblk[1] * kBS * bp.dv_ss) * 2};
-      uint8_t* const dkb[2] = {
-          reinterpret_cast<uint8_t*>(bp.dk) +
-              ((int64_t)b * bp.dk_sb + (int64_t)hk * bp.dk_sh + (int64_t)kblk[0] * kBS * bp.dk_ss) * 2,
-          reinterpret_cast<uint8_t*>(bp.dk) +
-              ((int64_t)b * bp.dk_sb + (int64_t)hk * bp.dk_sh + (int64_t)kblk[1] * kBS * bp.dk_ss) * 2};
-      store_acc_tile<BF16>(tDV, warp, lane, 1.f, stage, dvb, vr, bp.dv_ss * 2);
-      store_acc_tile<BF16>(tDK, warp, lane, p.sm_scale, stage, dkb, vr, bp.dk_ss * 2);
+      if (half == 0) {
+        uint8_t* const dvb[2] = {
+            reinterpret_cast<uint8_t*>(bp.dv) +
+                ((int64_t)b * bp.dv_sb + (int64_t)hk * bp.dv_sh + (int64_t)kblk[0] * kBS * bp.dv_ss) * 2,
+            reinterpret_cast<uint8_t*>(bp.dv) +
+                ((int64_t)b * bp.dv_sb + (int64_t)hk * bp.dv_sh + (int64_t)kblk[1] * kBS * bp.dv_ss) * 2};
+        store_acc_tile<BF16>(tDV, quad, lane, 1.f, stage, dvb, vr, bp.dv_ss * 2);
+      } else {
+        uint8_t* const dkb[2] = {
+            reinterpret_cast<uint8_t*>(bp.dk) +
+                ((int64_t)b * bp.dk_sb + (int64_t)hk * bp.dk_sh + (int64_t)kblk[0] * kBS * bp.dk_ss) * 2,
+            reinterpret_cast<uint8_t*>(bp.dk) +
+                ((int64_t)b * bp.dk_sb + (int64_t)hk * bp.dk_sh + (int64_t)kblk[1] * kBS * bp.dk_ss) * 2};
+        store_acc_tile<BF16>(tDK, quad, lane, p.sm_scale, stage, dkb, vr, bp.dk_ss * 2);
+      }
     }
   } else if (warp < 4) {
     // nothing attends these kv blocks: zero gradients
@@ -442,7 +460,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) tmem_dealloc(tmem, 512);
+  if (warp == kWarpIssueA) tmem_dealloc(tmem, 512);
 }
 
 // ------------------------------------------------------------------ dQ
@@ -454,7 +472,7 @@ struct DqTail {
   uint64_t q_full;
   uint64_t k_full[kDqKStages], k_empty[kDqKStages];
   uint64_t v_full[kDqVStages], v_empty[kDqVStages];
-  uint64_t sdp_full[2], p_full[2];
+  uint64_t sdp_full[2], p_full[2], acc_done[2];
   uint64_t all_done;
   uint32_t tmem_base;
   int n_list;
@@ -507,7 +525,11 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
     mbar_init(&tl->q_full, 1);
     for (int s = 0; s < kDqKStages; ++s) { mbar_init(&tl->k_full[s], 1); mbar_init(&tl->k_empty[s], 1); }
     for (int s = 0; s < kDqVStages; ++s) { mbar_init(&tl->v_full[s], 1); mbar_init(&tl->v_empty[s], 1); }
-    for (int s = 0; s < 2; ++s) { mbar_init(&tl->sdp_full[s], 1); mbar_init(&tl->p_full[s], 128); }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&tl->sdp_full[s], 1);
+      mbar_init(&tl->p_full[s], 256);
+      mbar_init(&tl->acc_done[s], 1);
+    }
     mbar_init(&tl->all_done, 1);
     mbar_fence_init();
     tma_prefetch_desc(&tmQ.map);
@@ -533,7 +555,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
   }
   __syncthreads();
   if (warp == 0) append_union(tl->bits[0], tl->bits[1], tl->list, &tl->n_list, 0u, lane, kMaxBlocks);
-  if (warp == 5) {
+  if (warp == kWarpIssueA) {
     tmem_alloc(&tl->tmem_base, 512);
     tmem_relinquish();
   }
@@ -546,7 +568,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
   const uint32_t tDP[2] = {tmem + 128, tmem + 192};
   const uint32_t tDQ = tmem + 256;
 
-  if (n > 0 && warp == 4) {
+  if (n > 0 && warp == kWarpProducer) {
     if (lane == 0) {
       mbar_expect_tx(&tl->q_full, (uint32_t)(valid[0] + valid[1]) * 2 * (kBS * kD * 2));
       for (int t = 0; t < 2; ++t) {
@@ -569,57 +591,65 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
         tma_load_tile(sVs + sv_ * kTileKV + 8192, &tmV, &tl->v_full[sv_], 64, tok, kvh, b);
       }
     }
-  } else if (n > 0 && warp == 5) {
+  } else if (n > 0 && warp == kWarpIssueA) {
+    // ------------------------------------------------------------ S = Q K^T, dP = dO V^T
     if (lane == 0) {
       const uint32_t idesc_nt = umma_idesc(BF16, 128, kBS, false, false);
-      const uint32_t idesc_acc = umma_idesc(BF16, 128, kD, false, true);
-      const uint32_t q_addr = smem_u32(sQ), do_addr = smem_u32(sDO);
-      const uint32_t k_addr = smem_u32(sKs), v_addr = smem_u32(sVs);
+      const uint64_t qdesc = umma_desc_sw128(smem_u32(sQ), 16, 1024);
+      const uint64_t gdesc = umma_desc_sw128(smem_u32(sDO), 16, 1024);
+      const uint64_t kdesc0 = umma_desc_sw128(smem_u32(sKs), 16, 1024);
+      const uint64_t vdesc0 = umma_desc_sw128(smem_u32(sVs), 16, 1024);
       bool ok = mbar_wait(&tl->q_full, 0, wait_status, 313);
-      auto issue_sdp = [&](int e) {
-        const int sk_ = e % kDqKStages, sv_ = e % kDqVStages;
-        if (!mbar_wait(&tl->k_full[sk_], (e / kDqKStages) & 1, wait_status, 314)) return false;
-        tc_fence_after();
-        const uint32_t kb = k_addr + sk_ * kTileKV;
-#pragma unroll
-        for (int c = 0; c < 2; ++c)
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            tc_mma_ss(tS[e & 1], umma_desc_sw128(q_addr + c * 16384 + kk * 32, 16, 1024),
-                      umma_desc_sw128(kb + c * 8192 + kk * 32, 16, 1024), idesc_nt, (c | kk) ? 1u : 0u);
-        if (!mbar_wait(&tl->v_full[sv_], (e / kDqVStages) & 1, wait_status, 315)) return false;
-        tc_fence_after();
-        const uint32_t vb = v_addr + sv_ * kTileKV;
-#pragma unroll
-        for (int c = 0; c < 2; ++c)
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            tc_mma_ss(tDP[e & 1], umma_desc_sw128(do_addr + c * 16384 + kk * 32, 16, 1024),
-                      umma_desc_sw128(vb + c * 8192 + kk * 32, 16, 1024), idesc_nt, (c | kk) ? 1u : 0u);
-        tc_commit(&tl->v_empty[sv_]);
-        tc_commit(&tl->sdp_full[e & 1]);
-        return true;
-      };
-      if (ok) ok = issue_sdp(0);
       for (int e = 0; e < n && ok; ++e) {
-        if (e + 1 < n) ok = issue_sdp(e + 1);
-        if (!ok) break;
-        const int sk_ = e % kDqKStages;
-        if (!mbar_wait(&tl->p_full[e & 1], (e >> 1) & 1, wait_status, 316)) { ok = false; break; }
+        const int sk_ = e % kDqKStages, sv_ = e % kDqVStages, bf = e & 1;
+        if (!mbar_wait(&tl->k_full[sk_], (e / kDqKStages) & 1, wait_status, 314)) break;
+        // dP[bf] still holds dS of entry e-2 until dQ += dS K of that entry has finished
+        if (e >= 2 && !mbar_wait(&tl->acc_done[bf], ((e - 2) >> 1) & 1, wait_status, 319)) break;
         tc_fence_after();
-        const uint32_t kb = k_addr + sk_ * kTileKV;
+        const uint64_t kd = kdesc0 + (uint64_t)((sk_ * kTileKV) >> 4);
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)   // dQ += dS K   (B = K_j, MN-major)
-          tc_mma_ts(tDQ, tDP[e & 1] + kk * 8, umma_desc_sw128(kb + kk * 2048, 8192, 1024), idesc_acc,
+        for (int i = 0; i < 8; ++i)   // i = c * 4 + kk
+          tc_mma_ss(tS[bf], qdesc + (uint64_t)(((i >> 2) * 16384 + (i & 3) * 32) >> 4),
+                    kd + (uint64_t)(((i >> 2) * 8192 + (i & 3) * 32) >> 4), idesc_nt, i ? 1u : 0u);
+        if (!mbar_wait(&tl->v_full[sv_], (e / kDqVStages) & 1, wait_status, 315)) break;
+        tc_fence_after();
+        const uint64_t vd = vdesc0 + (uint64_t)((sv_ * kTileKV) >> 4);
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          tc_mma_ss(tDP[bf], gdesc + (uint64_t)(((i >> 2) * 16384 + (i & 3) * 32) >> 4),
+                    vd + (uint64_t)(((i >> 2) * 8192 + (i & 3) * 32) >> 4), idesc_nt, i ? 1u : 0u);
+        tc_commit(&tl->v_empty[sv_]);
+        tc_commit(&tl->sdp_full[bf]);
+      }
+    }
+    __syncwarp();
+  } else if (n > 0 && warp == kWarpIssueB) {
+    // ------------------------------------------------------------ dQ += dS K
+    if (lane == 0) {
+      const uint32_t idesc_acc = umma_idesc(BF16, 128, kD, false, true);
+      // B = K_j read MN-major: 16 kv rows (2 KB) per k-step, 64-dim halves 8 KB apart
+      const uint64_t kdesc0 = umma_desc_sw128(smem_u32(sKs), 8192, 1024);
+      bool ok = true;
+      for (int e = 0; e < n; ++e) {
+        const int sk_ = e % kDqKStages, bf = e & 1;
+        if (!mbar_wait(&tl->p_full[bf], (e >> 1) & 1, wait_status, 316)) { ok = false; break; }
+        tc_fence_after();
+        const uint64_t kd = kdesc0 + (uint64_t)((sk_ * kTileKV) >> 4);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          tc_mma_ts(tDQ, tDP[bf] + packed_col(kk), kd + (uint64_t)((kk * 2048) >> 4), idesc_acc,
                     (e | kk) ? 1u : 0u);
         tc_commit(&tl->k_empty[sk_]);
+        tc_commit(&tl->acc_done[bf]);
       }
       if (ok) tc_commit(&tl->all_done);
     }
     __syncwarp();
   } else if (n > 0) {
-    const int r = tid, t = r >> 6, rr = r & 63;
-    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+    // ------------------------------------------------------------ dS (warps 0-7)
+    const int quad = warp & 3, half = warp >> 2;
+    const int r = quad * 32 + lane, t = r >> 6, rr = r & 63;
+    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
     const float scale2 = p.sm_scale * kLog2e;
     const int q_row = qblk[t] * kBS + rr;
     const int qpos = past + q_row;
@@ -638,38 +668,35 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
       const bool att = ((ent >> (24 + t)) & 1u) != 0 && valid[t];
       int lim = p.sk - kbase;
       if (p.causal) lim = min(lim, qpos - kbase + 1);
+      lim -= half * 32;   // relative to this warp's 32 columns
+      uint32_t sv[32], dv[32];
+      tmem_ld32(tS[e & 1] + lane_off + half * 32, sv);
+      tmem_ld32(tDP[e & 1] + lane_off + half * 32, dv);
+      tmem_ld_wait();
+      uint32_t ds[16];
+      if (att) {
 #pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {
-        uint32_t sv[32], dv[32];
-        tmem_ld32(tS[e & 1] + lane_off + hh * 32, sv);
-        tmem_ld32(tDP[e & 1] + lane_off + hh * 32, dv);
-        tmem_ld_wait();
-        uint32_t ds[16];
-        if (att) {
-#pragma unroll
-          for (int c2 = 0; c2 < 16; ++c2) {
-            float x0 = ex2(fmaf(__uint_as_float(sv[2 * c2]), scale2, -lse2));
-            float x1 = ex2(fmaf(__uint_as_float(sv[2 * c2 + 1]), scale2, -lse2));
-            if (hh * 32 + 2 * c2 >= lim) x0 = 0.f;
-            if (hh * 32 + 2 * c2 + 1 >= lim) x1 = 0.f;
-            ds[c2] = pack2<BF16>(x0 * (__uint_as_float(dv[2 * c2]) - delta),
-                                 x1 * (__uint_as_float(dv[2 * c2 + 1]) - delta));
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) ds[i] = 0u;
+        for (int c2 = 0; c2 < 16; ++c2) {
+          float x0 = ex2(fmaf(__uint_as_float(sv[2 * c2]), scale2, -lse2));
+          float x1 = ex2(fmaf(__uint_as_float(sv[2 * c2 + 1]), scale2, -lse2));
+          if (2 * c2 >= lim) x0 = 0.f;
+          if (2 * c2 + 1 >= lim) x1 = 0.f;
+          ds[c2] = pack2<BF16>(x0 * (__uint_as_float(dv[2 * c2]) - delta),
+                               x1 * (__uint_as_float(dv[2 * c2 + 1]) - delta));
         }
-        if (hh == 1) tmem_ld_wait();
-        tmem_st16(tDP[e & 1] + lane_off + hh * 16, ds);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) ds[i] = 0u;
       }
+      tmem_st16(tDP[e & 1] + lane_off + half * 32, ds);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&tl->p_full[e & 1]);
     }
     if (alive) alive = mbar_wait(&tl->all_done, 0, wait_status, 318);
     tc_fence_after();
-    if (alive) {
-      uint8_t* stage = sQ + warp * 8192;   // Q is dead once every product has completed
+    if (alive && half == 0) {
+      uint8_t* stage = sQ + quad * 8192;   // Q is dead once every product has completed
       const int vr[2] = {valid[0] ? min(kBS, p.sq - qblk[0] * kBS) : 0,
                          valid[1] ? min(kBS, p.sq - qblk[1] * kBS) : 0};
       uint8_t* const dqb[2] = {
@@ -677,7 +704,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
                                                (int64_t)qblk[0] * kBS * bp.dq_ss) * 2,
           reinterpret_cast<uint8_t*>(bp.dq) + ((int64_t)b * bp.dq_sb + (int64_t)head[1] * bp.dq_sh +
                                                (int64_t)qblk[1] * kBS * bp.dq_ss) * 2};
-      store_acc_tile<BF16>(tDQ, warp, lane, p.sm_scale, stage, dqb, vr, bp.dq_ss * 2);
+      store_acc_tile<BF16>(tDQ, quad, lane, p.sm_scale, stage, dqb, vr, bp.dq_ss * 2);
     }
   } else if (warp < 4) {
     const int t = tid >> 6;
@@ -690,7 +717,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) tmem_dealloc(tmem, 512);
+  if (warp == kWarpIssueA) tmem_dealloc(tmem, 512);
 }
 
 bool rows8(const void* ptr, int64_t ss, int64_t sh, int64_t sb) {

@@ -10,9 +10,11 @@
 // The per-head CSR rows of both halves are merged in shared memory (bitmaps ->
 // ordered list) before the pipeline starts.
 //
-// Warp roles (192 threads):  warps 0-3 softmax (thread r owns tile row r = TMEM
-// lane r: no cross-lane reductions at all), warp 4 TMA producer, warp 5 MMA issuer
-// and TMEM owner.  Per kv block j:
+// Warp roles (224 threads):  warps 0-3 softmax (thread r owns tile row r = TMEM
+// lane r: no cross-lane reductions at all), warp 4 TMA producer, warp 5 issues the
+// Q K^T products and owns TMEM, warp 6 issues the P V products (a tcgen05
+// instruction costs its issuing thread 60-75 cycles whatever its size, so one
+// thread cannot keep the tensor pipe fed).  Per kv block j:
 //   S[j&1] = Q K_j^T          tcgen05.mma, A/B from 128B-swizzled smem, fp32 in TMEM
 //   P = exp2(S*c - m)          softmax warps: tcgen05.ld -> registers -> bf16/fp16 ->
 //                              tcgen05.st into the columns S occupied
@@ -30,20 +32,25 @@ namespace {
 
 constexpr int kD = 128;
 constexpr int kBS = 64;
-constexpr int kFwdThreads = 192;
+constexpr int kFwdThreads = 224;
 constexpr int kMaxList = 1024;          // kv blocks per sequence (64K tokens)
 constexpr int kQBytes = 128 * kD * 2;   // 32 KB
 constexpr int kKVBytes = kBS * kD * 2;  // 16 KB per K or V tile
-constexpr int kStagesF = 2;
+#ifndef BSA_FWD_STAGES
+#define BSA_FWD_STAGES 2
+#endif
+constexpr int kStagesF = BSA_FWD_STAGES;     // K and V ring depth
+static_assert(kStagesF == 2, "the S/P double buffer and the K/V rings share their barriers");
 constexpr float kRescaleThreshold = 8.0f;
 
 enum { kPairHeads = 0, kPairRows = 1 };
 
 struct FwdTail {
   uint64_t q_full;
-  uint64_t k_full[kStagesF], v_full[kStagesF], k_empty[kStagesF], v_empty[kStagesF];
-  uint64_t s_full[2], p_full[2];
-  uint64_t pv_done;
+  uint64_t k_full[kStagesF], v_full[kStagesF];
+  // qk_done[j&1]: Q K_j^T has completed -> S[j&1] is readable and the K stage is free.
+  // pv_done[j&1]: P V_j has completed   -> P[j&1] (= S[j&1]) and the V stage are free.
+  uint64_t qk_done[2], pv_done[2], p_full[2];
   uint32_t tmem_base;
   int n_list;
   uint32_t bits[2][kMaxList / 32];
@@ -74,7 +81,7 @@ struct Half {
 };
 
 template <bool BF16>
-__global__ void __launch_bounds__(kFwdThreads, 2)
+__global__ void __launch_bounds__(kFwdThreads, kStagesF <= 2 ? 2 : 1)
 fwd_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap4 tmK,
                  const __grid_constant__ Tmap4 tmV, bsa_fwd_params p, int mode, int* wait_status) {
   extern __shared__ uint8_t smem_raw[];
@@ -133,14 +140,12 @@ fwd_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap
     for (int s = 0; s < kStagesF; ++s) {
       mbar_init(&tl->k_full[s], 1);
       mbar_init(&tl->v_full[s], 1);
-      mbar_init(&tl->k_empty[s], 1);
-      mbar_init(&tl->v_empty[s], 1);
     }
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&tl->s_full[s], 1);
+      mbar_init(&tl->qk_done[s], 1);
+      mbar_init(&tl->pv_done[s], 1);
       mbar_init(&tl->p_full[s], 128);
     }
-    mbar_init(&tl->pv_done, 1);
     mbar_fence_init();
     tma_prefetch_desc(&tmQ.map);
     tma_prefetch_desc(&tmK.map);
@@ -214,59 +219,57 @@ fwd_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap
         const int tok = k_start + (int)(tl->list[j] & 0xffffu) * kBS;
         uint8_t* kdst = sKV + s * 2 * kKVBytes;
         uint8_t* vdst = kdst + kKVBytes;
-        if (!mbar_wait(&tl->k_empty[s], ph, wait_status, 201)) break;
+        if (!mbar_wait(&tl->qk_done[s], ph, wait_status, 201)) break;
         mbar_expect_tx(&tl->k_full[s], kKVBytes);
         tma_load_tile(kdst, &tmK, &tl->k_full[s], 0, tok, kvh, b);
         tma_load_tile(kdst + 8192, &tmK, &tl->k_full[s], 64, tok, kvh, b);
-        if (!mbar_wait(&tl->v_empty[s], ph, wait_status, 202)) break;
+        if (!mbar_wait(&tl->pv_done[s], ph, wait_status, 202)) break;
         mbar_expect_tx(&tl->v_full[s], kKVBytes);
         tma_load_tile(vdst, &tmV, &tl->v_full[s], 0, tok, kvh, b);
         tma_load_tile(vdst + 8192, &tmV, &tl->v_full[s], 64, tok, kvh, b);
       }
     }
   } else if (n > 0 && warp == 5) {
-    // ------------------------------------------------------------ MMA issuer
+    // ------------------------------------------------------------ Q K^T issuer
     if (lane == 0) {
       const uint32_t idesc_qk = umma_idesc(BF16, 128, kBS, false, false);
-      const uint32_t idesc_pv = umma_idesc(BF16, 128, kD, false, true);
-      const uint32_t q_addr = smem_u32(sQ);
-      const uint32_t kv_addr = smem_u32(sKV);
+      // descriptors of the first tile of each operand; the start-address field (bits
+      // 0..13, units of 16 bytes) is advanced by plain additions afterwards
+      const uint64_t qdesc0 = umma_desc_sw128(smem_u32(sQ), 16, 1024);
+      const uint64_t kdesc0 = umma_desc_sw128(smem_u32(sKV), 16, 1024);
       bool ok = mbar_wait(&tl->q_full, 0, wait_status, 203);
-      auto issue_qk = [&](int j) {
-        const int s = j % kStagesF;
-        if (!mbar_wait(&tl->k_full[s], (j / kStagesF) & 1, wait_status, 204)) return false;
-        tc_fence_after();
-        const uint32_t kb = kv_addr + s * 2 * kKVBytes;
-#pragma unroll
-        for (int c = 0; c < 2; ++c)
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
-            const uint64_t da = umma_desc_sw128(q_addr + c * 16384 + kk * 32, 16, 1024);
-            const uint64_t db = umma_desc_sw128(kb + c * 8192 + kk * 32, 16, 1024);
-            tc_mma_ss(tS[j & 1], da, db, idesc_qk, (c | kk) ? 1u : 0u);
-          }
-        tc_commit(&tl->k_empty[s]);
-        tc_commit(&tl->s_full[j & 1]);
-        return true;
-      };
-      if (ok) ok = issue_qk(0);
       for (int j = 0; j < n && ok; ++j) {
-        if (j + 1 < n) ok = issue_qk(j + 1);
-        if (!ok) break;
-        const int s = j % kStagesF;
-        if (!mbar_wait(&tl->p_full[j & 1], (j >> 1) & 1, wait_status, 205)) break;
-        if (!mbar_wait(&tl->v_full[s], (j / kStagesF) & 1, wait_status, 206)) break;
+        const int s = j & 1;
+        if (!mbar_wait(&tl->k_full[s], (j >> 1) & 1, wait_status, 204)) break;
+        // S[s] doubles as P[s]: P V_{j-2} must have consumed it
+        if (j >= 2 && !mbar_wait(&tl->pv_done[s], ((j - 2) >> 1) & 1, wait_status, 210)) break;
         tc_fence_after();
-        const uint32_t vb = kv_addr + s * 2 * kKVBytes + kKVBytes;
+        const uint64_t db0 = kdesc0 + (uint64_t)((s * 2 * kKVBytes) >> 4);
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {
-          // V tile: rows = kv tokens (K of this product), 128 contiguous bytes = 64 head
-          // dims (N); the two 64-dim halves are 8 KB apart
-          const uint64_t db = umma_desc_sw128(vb + kk * 2048, 8192, 1024);
-          tc_mma_ts(tO, tS[j & 1] + kk * 8, db, idesc_pv, (j | kk) ? 1u : 0u);
-        }
-        tc_commit(&tl->v_empty[s]);
-        tc_commit(&tl->pv_done);
+        for (int i = 0; i < 8; ++i)   // i = c * 4 + kk: sub-tile c (8 KB apart for K, 16 KB for Q), k-step kk
+          tc_mma_ss(tS[s], qdesc0 + (uint64_t)(((i >> 2) * 16384 + (i & 3) * 32) >> 4),
+                    db0 + (uint64_t)(((i >> 2) * 8192 + (i & 3) * 32) >> 4), idesc_qk, i ? 1u : 0u);
+        tc_commit(&tl->qk_done[s]);
+      }
+    }
+    __syncwarp();
+  } else if (n > 0 && warp == 6) {
+    // ------------------------------------------------------------ P V issuer
+    if (lane == 0) {
+      const uint32_t idesc_pv = umma_idesc(BF16, 128, kD, false, true);
+      // V tile: rows = kv tokens (K of this product), 128 contiguous bytes = 64 head
+      // dims (N); the two 64-dim halves are 8 KB apart (LBO); 16 tokens per k-step
+      const uint64_t vdesc0 = umma_desc_sw128(smem_u32(sKV) + kKVBytes, 8192, 1024);
+      for (int j = 0; j < n; ++j) {
+        const int s = j & 1;
+        if (!mbar_wait(&tl->p_full[s], (j >> 1) & 1, wait_status, 205)) break;
+        if (!mbar_wait(&tl->v_full[s], (j >> 1) & 1, wait_status, 206)) break;
+        tc_fence_after();
+        const uint64_t dv0 = vdesc0 + (uint64_t)((s * 2 * kKVBytes) >> 4);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          tc_mma_ts(tO, tS[s] + kk * 8, dv0 + (uint64_t)((kk * 2048) >> 4), idesc_pv, (j | kk) ? 1u : 0u);
+        tc_commit(&tl->pv_done[s]);
       }
     }
     __syncwarp();
@@ -282,7 +285,7 @@ fwd_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap
     float m_used = -INFINITY, l = 0.f;
     bool alive = true;
     for (int j = 0; j < n; ++j) {
-      if (!mbar_wait(&tl->s_full[j & 1], (j >> 1) & 1, wait_status, 207)) { alive = false; break; }
+      if (!mbar_wait(&tl->qk_done[j & 1], (j >> 1) & 1, wait_status, 207)) { alive = false; break; }
       tc_fence_after();
       uint32_t sv[64];
       tmem_ld32(tS[j & 1] + lane_off, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
@@ -303,9 +306,15 @@ fwd_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap
           for (int c = 0; c < 64; ++c)
             if (c >= lim) sv[c] = 0xff800000u;  // -inf
         }
+        float m8[8];
 #pragma unroll
-        for (int c = 0; c < 64; ++c) mx = fmaxf(mx, __uint_as_float(sv[c]));
-        mx *= scale2;
+        for (int i = 0; i < 8; ++i) m8[i] = __uint_as_float(sv[i]);
+#pragma unroll
+        for (int c = 8; c < 64; c += 8)
+#pragma unroll
+          for (int i = 0; i < 8; ++i) m8[i] = fmaxf(m8[i], __uint_as_float(sv[c + i]));
+        mx = fmaxf(fmaxf(fmaxf(m8[0], m8[1]), fmaxf(m8[2], m8[3])),
+                   fmaxf(fmaxf(m8[4], m8[5]), fmaxf(m8[6], m8[7]))) * scale2;
       }
       float alpha = 1.f;
       bool need = false;
@@ -322,17 +331,17 @@ fwd_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap
       const bool any = __any_sync(0xffffffffu, need);
       uint32_t pk[32];
       if (att && m_used != -INFINITY) {
-        float sum0 = 0.f, sum1 = 0.f;
+        float sum[4] = {0.f, 0.f, 0.f, 0.f};
         const float neg_m = -m_used;
 #pragma unroll
         for (int c = 0; c < 32; ++c) {
           const float p0 = ex2(fmaf(__uint_as_float(sv[2 * c]), scale2, neg_m));
           const float p1 = ex2(fmaf(__uint_as_float(sv[2 * c + 1]), scale2, neg_m));
-          sum0 += p0;
-          sum1 += p1;
+          sum[(2 * c) & 3] += p0;
+          sum[(2 * c + 1) & 3] += p1;
           pk[c] = pack2<BF16>(p0, p1);
         }
-        l += sum0 + sum1;
+        l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
       } else {
 #pragma unroll
         for (int c = 0; c < 32; ++c) pk[c] = 0u;
@@ -341,7 +350,7 @@ fwd_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap
       if (j > 0) {
         // Every phase of pv_done is observed in order (a parity wait is only
         // meaningful when the waiter is at most one phase behind).
-        if (!mbar_wait(&tl->pv_done, (j - 1) & 1, wait_status, 208)) { alive = false; break; }
+        if (!mbar_wait(&tl->pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, wait_status, 208)) { alive = false; break; }
       }
       if (any && j > 0) {
         // rescale the accumulator rows whose maximum moved (P V_{j-1} has landed)
@@ -361,7 +370,7 @@ fwd_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap
       mbar_arrive(&tl->p_full[j & 1]);
     }
     // ---- epilogue: O / l -> registers -> swizzled smem (the Q tile is dead) -> global
-    if (alive) alive = mbar_wait(&tl->pv_done, (n - 1) & 1, wait_status, 209);
+    if (alive) alive = mbar_wait(&tl->pv_done[(n - 1) & 1], ((n - 1) >> 1) & 1, wait_status, 209);
     tc_fence_after();
     if (alive) {
       const float inv = l > 0.f ? 1.f / l : 0.f;
