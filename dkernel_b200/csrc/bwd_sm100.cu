@@ -567,6 +567,10 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
   const uint32_t tS[2] = {tmem, tmem + 64};
   const uint32_t tDP[2] = {tmem + 128, tmem + 192};
   const uint32_t tDQ = tmem + 256;
+  // Q and dO are the A operands of every first-stage product: they are copied once
+  // from their TMA tiles into TMEM (64 columns each), which takes their 64 KB per
+  // step off the shared-memory read path that the tensor pipe saturates.
+  const uint32_t tQ = tmem + 384, tDO = tmem + 448;
 
   if (n > 0 && warp == kWarpProducer) {
     if (lane == 0) {
@@ -600,6 +604,15 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
       const uint64_t kdesc0 = umma_desc_sw128(smem_u32(sKs), 16, 1024);
       const uint64_t vdesc0 = umma_desc_sw128(smem_u32(sVs), 16, 1024);
       bool ok = mbar_wait(&tl->q_full, 0, wait_status, 313);
+      if (ok) {
+        tc_fence_after();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {   // one k-step (16 head dims = 8 packed columns) per copy
+          const uint64_t off = (uint64_t)(((i >> 2) * 16384 + (i & 3) * 32) >> 4);
+          tc_cp_128x256b(tQ + i * 8, qdesc + off);
+          tc_cp_128x256b(tDO + i * 8, gdesc + off);
+        }
+      }
       for (int e = 0; e < n && ok; ++e) {
         const int sk_ = e % kDqKStages, sv_ = e % kDqVStages, bf = e & 1;
         if (!mbar_wait(&tl->k_full[sk_], (e / kDqKStages) & 1, wait_status, 314)) break;
@@ -609,15 +622,15 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
         const uint64_t kd = kdesc0 + (uint64_t)((sk_ * kTileKV) >> 4);
 #pragma unroll
         for (int i = 0; i < 8; ++i)   // i = c * 4 + kk
-          tc_mma_ss(tS[bf], qdesc + (uint64_t)(((i >> 2) * 16384 + (i & 3) * 32) >> 4),
-                    kd + (uint64_t)(((i >> 2) * 8192 + (i & 3) * 32) >> 4), idesc_nt, i ? 1u : 0u);
+          tc_mma_ts(tS[bf], tQ + i * 8, kd + (uint64_t)(((i >> 2) * 8192 + (i & 3) * 32) >> 4), idesc_nt,
+                    i ? 1u : 0u);
         if (!mbar_wait(&tl->v_full[sv_], (e / kDqVStages) & 1, wait_status, 315)) break;
         tc_fence_after();
         const uint64_t vd = vdesc0 + (uint64_t)((sv_ * kTileKV) >> 4);
 #pragma unroll
         for (int i = 0; i < 8; ++i)
-          tc_mma_ss(tDP[bf], gdesc + (uint64_t)(((i >> 2) * 16384 + (i & 3) * 32) >> 4),
-                    vd + (uint64_t)(((i >> 2) * 8192 + (i & 3) * 32) >> 4), idesc_nt, i ? 1u : 0u);
+          tc_mma_ts(tDP[bf], tDO + i * 8, vd + (uint64_t)(((i >> 2) * 8192 + (i & 3) * 32) >> 4), idesc_nt,
+                    i ? 1u : 0u);
         tc_commit(&tl->v_empty[sv_]);
         tc_commit(&tl->sdp_full[bf]);
       }

@@ -170,6 +170,14 @@ __device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint
       : "memory");
 }
 
+// Copy 128 rows x 32 bytes of a shared-memory matrix (described like an MMA
+// operand) into 8 TMEM columns of all 128 lanes: exactly one k-step of a 16-bit
+// A operand, in the layout tcgen05.mma expects for A in TMEM.  Ordered with the
+// MMAs issued by the same thread.
+__device__ __forceinline__ void tc_cp_128x256b(uint32_t taddr, uint64_t desc) {
+  asm volatile("tcgen05.cp.cta_group::1.128x256b [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+
 // 32 lanes x 32 consecutive 32-bit columns: thread t of the warp gets lane
 // (warp%4)*32 + t, v[i] = column i.
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
