@@ -230,6 +230,22 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
     tma_prefetch_desc(&tmDO.map);
     tl->n_list = 0;
   }
+  __syncthreads();
+  // resident K / V tiles and the TMEM allocation overlap the list construction
+  if (warp == kWarpProducer && lane == 0) {
+    mbar_expect_tx(&tl->kv_full, (uint32_t)(kvalid[0] + kvalid[1]) * 2 * (kBS * kD * 2));
+    for (int t = 0; t < 2; ++t) {
+      if (!kvalid[t]) continue;
+      for (int c = 0; c < 2; ++c) {
+        tma_load_tile(sK + c * 16384 + t * 8192, &tmK, &tl->kv_full, c * 64, kblk[t] * kBS, hk, b);
+        tma_load_tile(sV + c * 16384 + t * 8192, &tmV, &tl->kv_full, c * 64, kblk[t] * kBS, hk, b);
+      }
+    }
+  }
+  if (warp == kWarpIssueA) {
+    tmem_alloc(&tl->tmem_base, 512);
+    tmem_relinquish();
+  }
   // ---- entry list: for every q head of the group, union of the two CSC columns
   for (int g = 0; g < G; ++g) {
     if (tid < 2 * (kMaxBlocks / 32)) (&tl->bits[0][0])[tid] = 0u;
@@ -255,10 +271,6 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
                    kMaxEntries);
     __syncthreads();
   }
-  if (warp == kWarpIssueA) {
-    tmem_alloc(&tl->tmem_base, 512);
-    tmem_relinquish();
-  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -271,14 +283,6 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
   if (n > 0 && warp == kWarpProducer) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      mbar_expect_tx(&tl->kv_full, (uint32_t)(kvalid[0] + kvalid[1]) * 2 * (kBS * kD * 2));
-      for (int t = 0; t < 2; ++t) {
-        if (!kvalid[t]) continue;
-        for (int c = 0; c < 2; ++c) {
-          tma_load_tile(sK + c * 16384 + t * 8192, &tmK, &tl->kv_full, c * 64, kblk[t] * kBS, hk, b);
-          tma_load_tile(sV + c * 16384 + t * 8192, &tmV, &tl->kv_full, c * 64, kblk[t] * kBS, hk, b);
-        }
-      }
       for (int e = 0; e < n; ++e) {
         const int s = e % kQdoStages;
         const uint32_t ent = tl->list[e];
@@ -446,6 +450,8 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
         store_acc_tile<BF16>(tDK, quad, lane, p.sm_scale, stage, dkb, vr, bp.dk_ss * 2);
       }
     }
+  } else if (warp == kWarpProducer) {
+    if (lane == 0) mbar_wait(&tl->kv_full, 0, wait_status, 308);   // let the tiles in flight land
   } else if (warp < 4) {
     // nothing attends these kv blocks: zero gradients
     const int t = tid >> 6;
@@ -540,6 +546,20 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
   }
   if (tid < 2 * (kMaxBlocks / 32)) (&tl->bits[0][0])[tid] = 0u;
   __syncthreads();
+  if (warp == kWarpProducer && lane == 0) {
+    mbar_expect_tx(&tl->q_full, (uint32_t)(valid[0] + valid[1]) * 2 * (kBS * kD * 2));
+    for (int t = 0; t < 2; ++t) {
+      if (!valid[t]) continue;
+      for (int c = 0; c < 2; ++c) {
+        tma_load_tile(sQ + c * 16384 + t * 8192, &tmQ, &tl->q_full, c * 64, qblk[t] * kBS, head[t], b);
+        tma_load_tile(sDO + c * 16384 + t * 8192, &tmDO, &tl->q_full, c * 64, qblk[t] * kBS, head[t], b);
+      }
+    }
+  }
+  if (warp == kWarpIssueA) {
+    tmem_alloc(&tl->tmem_base, 512);
+    tmem_relinquish();
+  }
   for (int t = 0; t < 2; ++t) {
     if (!valid[t] || qblk[t] >= p.n_rows) continue;
     const int hp = pattern_head(head[t], p.h_pat, p.hq, p.hkv);
@@ -555,10 +575,6 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
   }
   __syncthreads();
   if (warp == 0) append_union(tl->bits[0], tl->bits[1], tl->list, &tl->n_list, 0u, lane, kMaxBlocks);
-  if (warp == kWarpIssueA) {
-    tmem_alloc(&tl->tmem_base, 512);
-    tmem_relinquish();
-  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -574,14 +590,6 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
 
   if (n > 0 && warp == kWarpProducer) {
     if (lane == 0) {
-      mbar_expect_tx(&tl->q_full, (uint32_t)(valid[0] + valid[1]) * 2 * (kBS * kD * 2));
-      for (int t = 0; t < 2; ++t) {
-        if (!valid[t]) continue;
-        for (int c = 0; c < 2; ++c) {
-          tma_load_tile(sQ + c * 16384 + t * 8192, &tmQ, &tl->q_full, c * 64, qblk[t] * kBS, head[t], b);
-          tma_load_tile(sDO + c * 16384 + t * 8192, &tmDO, &tl->q_full, c * 64, qblk[t] * kBS, head[t], b);
-        }
-      }
       for (int e = 0; e < n; ++e) {
         const int tok = (int)(tl->list[e] & 0xffffu) * kBS;
         const int sk_ = e % kDqKStages, sv_ = e % kDqVStages;
@@ -719,6 +727,8 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
                                                (int64_t)qblk[1] * kBS * bp.dq_ss) * 2};
       store_acc_tile<BF16>(tDQ, quad, lane, p.sm_scale, stage, dqb, vr, bp.dq_ss * 2);
     }
+  } else if (warp == kWarpProducer) {
+    if (lane == 0) mbar_wait(&tl->q_full, 0, wait_status, 320);   // let the tiles in flight land
   } else if (warp < 4) {
     const int t = tid >> 6;
     const int q_row = qblk[t] * kBS + (tid & 63);

@@ -153,6 +153,21 @@ fwd_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap
   }
   if (tid < 2 * (kMaxList / 32)) (&tl->bits[0][0])[tid] = 0u;
   __syncthreads();
+  // The Q tile and the TMEM allocation do not depend on the block list: start them
+  // now so that their latency overlaps the list construction.
+  if (warp == 4 && lane == 0) {
+    mbar_expect_tx(&tl->q_full, (uint32_t)(hf[0].valid + hf[1].valid) * (kQBytes / 2));
+    for (int t = 0; t < 2; ++t) {
+      if (!hf[t].valid) continue;
+      for (int c = 0; c < 2; ++c)
+        tma_load_tile(sQ + c * 16384 + t * 8192, &tmQ, &tl->q_full, c * 64,
+                      q_start + hf[t].qblk * kBS, hf[t].head, b);
+    }
+  }
+  if (warp == 5) {
+    tmem_alloc(&tl->tmem_base, 256);
+    tmem_relinquish();
+  }
   // union of the two halves' block lists
   for (int t = 0; t < 2; ++t) {
     if (!hf[t].valid) continue;
@@ -190,10 +205,6 @@ fwd_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap
     }
     if (lane == 31) tl->n_list = incl;
   }
-  if (warp == 5) {
-    tmem_alloc(&tl->tmem_base, 256);
-    tmem_relinquish();
-  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -205,14 +216,6 @@ fwd_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap
   if (n > 0 && warp == 4) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      const uint32_t qbytes = (hf[0].valid + hf[1].valid) * (kQBytes / 2);
-      mbar_expect_tx(&tl->q_full, qbytes);
-      for (int t = 0; t < 2; ++t) {
-        if (!hf[t].valid) continue;
-        for (int c = 0; c < 2; ++c)
-          tma_load_tile(sQ + c * 16384 + t * 8192, &tmQ, &tl->q_full, c * 64,
-                        q_start + hf[t].qblk * kBS, hf[t].head, b);
-      }
       for (int j = 0; j < n; ++j) {
         const int s = j % kStagesF;
         const uint32_t ph = ((j / kStagesF) & 1) ^ 1;
@@ -409,6 +412,9 @@ fwd_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap
         p.lse[(int64_t)b * p.lse_sb + (int64_t)hf[t].head * p.lse_sh + q_start + q_row] =
             l > 0.f ? (m_used + log2f(l)) * kLn2 : -INFINITY;
     }
+  } else if (warp == 4) {
+    // nothing to attend: the Q tile is still in flight and must land before the CTA exits
+    if (lane == 0) mbar_wait(&tl->q_full, 0, wait_status, 211);
   } else if (warp < 4) {
     // no attended block at all: zero rows, LSE = -inf
     const int r = tid, t = r >> 6;
