@@ -79,6 +79,8 @@ int generic_fwd(const bsa_fwd_params* p, cudaStream_t s);
 int generic_bwd(const bsa_bwd_params* p, cudaStream_t s);
 bool sm100_fwd_supported(const bsa_fwd_params* p, const char** why);
 int sm100_fwd(const bsa_fwd_params* p, cudaStream_t s);
+bool sm100_fwd_persist_supported(const bsa_fwd_params* p);
+int sm100_fwd_persist(const bsa_fwd_params* p, cudaStream_t s);
 bool sm100_bwd_supported(const bsa_bwd_params* p, const char** why);
 int sm100_bwd(const bsa_bwd_params* p, cudaStream_t s);
 size_t decode_workspace_bytes(const bsa_decode_params* p);
