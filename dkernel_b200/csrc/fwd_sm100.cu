@@ -93,7 +93,10 @@ fwd_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap
   uint8_t* sKV = smem + kQBytes;  // stage s: K at s*32K, V at s*32K + 16K
   FwdTail* tl = reinterpret_cast<FwdTail*>(smem + kQBytes + kStagesF * 2 * kKVBytes);
 
-  if (*reinterpret_cast<volatile int*>(wait_status) != 0) return;
+  // A wait that gave up in an earlier launch makes every later launch return at once.  The
+  // flag is loaded here and tested after the work item is known, so that its latency
+  // overlaps the index arithmetic.
+  const int sticky = *reinterpret_cast<volatile int*>(wait_status);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
   // ---------------------------------------------------------------- work item
@@ -136,29 +139,47 @@ fwd_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap
   }
   const int nkb = min((k_len + kBS - 1) / kBS, kMaxList);
 
-  // ---------------------------------------------------------------- setup
-  if (tid == 0) {
-    mbar_init(&tl->q_full, 1);
-    for (int s = 0; s < kStagesF; ++s) {
-      mbar_init(&tl->k_full[s], 1);
-      mbar_init(&tl->v_full[s], 1);
-    }
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(&tl->qk_done[s], 1);
-      mbar_init(&tl->pv_done[s], 1);
-      mbar_init(&tl->p_full[s], 128);
-    }
-    mbar_fence_init();
-    tma_prefetch_desc(&tmQ.map);
-    tma_prefetch_desc(&tmK.map);
-    tma_prefetch_desc(&tmV.map);
+  // CSR row bounds of both halves: the loads are issued now and consumed after the
+  // barrier setup below.
+  int c_beg[2] = {0, 0}, c_end[2] = {0, 0};
+  const int32_t* cols_of[2] = {nullptr, nullptr};
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    if (!hf[t].valid) continue;
+    const int q_first = hf[t].qblk * kBS;
+    const int row = (p.row_mode == BSA_ROWS_BY_POSITION ? past + q_first : q_first) / kBS;
+    if (row >= p.n_rows) continue;
+    const int hp = pattern_head(hf[t].head, p.h_pat, p.hq, p.hkv);
+    const int32_t* cr = p.crow + (int64_t)hp * p.crow_sh;
+    cols_of[t] = p.col + (int64_t)hp * p.col_sh;
+    c_beg[t] = __ldg(cr + row);
+    c_end[t] = __ldg(cr + row + 1);
   }
-  if (tid < 2 * (kMaxList / 32)) (&tl->bits[0][0])[tid] = 0u;
+  if (sticky != 0) return;
+
+  // ---------------------------------------------------------------- setup
+  if (warp == 0) {
+    // the eleven barriers are contiguous: q_full, k_full[2], v_full[2], qk_done[2],
+    // pv_done[2] (one arrival each) and p_full[2] (all softmax threads)
+    if (lane < 11) {
+      mbar_init(&tl->q_full + lane, lane >= 9 ? 128 : 1);
+      mbar_fence_init();
+    } else if (lane == 11) {
+      tma_prefetch_desc(&tmQ.map);
+    } else if (lane == 12) {
+      tma_prefetch_desc(&tmK.map);
+    } else if (lane == 13) {
+      tma_prefetch_desc(&tmV.map);
+    }
+  } else if (tid - 32 < 2 * (kMaxList / 32)) {
+    (&tl->bits[0][0])[tid - 32] = 0u;
+  }
   __syncthreads();
   // The Q tile and the TMEM allocation do not depend on the block list: start them
   // now so that their latency overlaps the list construction.
   if (warp == 4 && lane == 0) {
     mbar_expect_tx(&tl->q_full, (uint32_t)(hf[0].valid + hf[1].valid) * (kQBytes / 2));
+#pragma unroll
     for (int t = 0; t < 2; ++t) {
       if (!hf[t].valid) continue;
       for (int c = 0; c < 2; ++c)
@@ -171,41 +192,41 @@ fwd_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap
     tmem_relinquish();
   }
   // union of the two halves' block lists
+#pragma unroll
   for (int t = 0; t < 2; ++t) {
-    if (!hf[t].valid) continue;
-    const int q_first = hf[t].qblk * kBS;
-    const int row = (p.row_mode == BSA_ROWS_BY_POSITION ? past + q_first : q_first) / kBS;
-    if (row >= p.n_rows) continue;
-    const int hp = pattern_head(hf[t].head, p.h_pat, p.hq, p.hkv);
-    const int32_t* cr = p.crow + (int64_t)hp * p.crow_sh;
-    const int32_t* cols = p.col + (int64_t)hp * p.col_sh;
-    const int c_beg = cr[row], c_end = cr[row + 1];
-    const int q_pos_last = past + min(q_first + kBS, q_len) - 1;
-    for (int i = c_beg + tid; i < c_end; i += kFwdThreads) {
-      const int blk = cols[i];
+    const int q_pos_last = past + min(hf[t].qblk * kBS + kBS, q_len) - 1;
+    for (int i = c_beg[t] + tid; i < c_end[t]; i += kFwdThreads) {
+      const int blk = __ldg(cols_of[t] + i);
       if (blk >= 0 && blk < nkb && !(p.causal && blk * kBS > q_pos_last))
         atomicOr(&tl->bits[t][blk >> 5], 1u << (blk & 31));
     }
   }
   __syncthreads();
-  if (warp == 0) {
+  {
+    // bitmaps -> ordered list.  Every warp scans the 32 word counts by itself, then the
+    // warps share the words out; in a word each lane owns one bit.
     const uint32_t u0 = tl->bits[0][lane], u1 = tl->bits[1][lane];
-    uint32_t u = u0 | u1;
+    const uint32_t u = u0 | u1;
     const int cnt = __popc(u);
     int incl = cnt;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
-      const int t = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += t;
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
     }
-    int pos = incl - cnt;
-    while (u) {
-      const int bit = __ffs(u) - 1;
-      u &= u - 1;
-      tl->list[pos++] = (uint32_t)(lane * 32 + bit) | (((u0 >> bit) & 1u) << 16) |
-                        (((u1 >> bit) & 1u) << 17);
+    const int base = incl - cnt;
+    const uint32_t nonzero = __ballot_sync(0xffffffffu, u != 0u);
+    for (int w = warp; w < 32; w += kFwdThreads / 32) {
+      if (!((nonzero >> w) & 1u)) continue;
+      const uint32_t uw = __shfl_sync(0xffffffffu, u, w);
+      const uint32_t u0w = __shfl_sync(0xffffffffu, u0, w);
+      const uint32_t u1w = __shfl_sync(0xffffffffu, u1, w);
+      const int bw = __shfl_sync(0xffffffffu, base, w);
+      if ((uw >> lane) & 1u)
+        tl->list[bw + __popc(uw & ((1u << lane) - 1u))] =
+            (uint32_t)(w * 32 + lane) | (((u0w >> lane) & 1u) << 16) | (((u1w >> lane) & 1u) << 17);
     }
-    if (lane == 31) tl->n_list = incl;
+    if (tid == 31) tl->n_list = incl;
   }
   tc_fence_before();
   __syncthreads();
@@ -285,10 +306,23 @@ fwd_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap
     const int rr = r & 63;
     const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
     const float scale2 = p.sm_scale * kLog2e;
-    const int q_row = hf[t].qblk * kBS + rr;   // row inside the sequence
+    const Half my = t ? hf[1] : hf[0];
+    const int q_row = my.qblk * kBS + rr;   // row inside the sequence
     const int qpos = past + q_row;
     float m_used = -INFINITY, l = 0.f;
     bool alive = true;
+    // Completions of P V are observed in order, one phase of a barrier at a time (a parity
+    // wait only means something while the waiter is at most one phase behind).  Q K_j^T was
+    // issued after P V_{j-2} completed, so observing up to j-2 never blocks; P V_{j-1} is
+    // only waited for when the accumulator has to be rescaled.
+    int seen = 0;
+    auto observe_pv = [&](int upto) {   // P V_0 .. P V_upto have completed
+      while (seen <= upto) {
+        if (!mbar_wait(&tl->pv_done[seen & 1], (seen >> 1) & 1, wait_status, 208)) return false;
+        ++seen;
+      }
+      return true;
+    };
     for (int j = 0; j < n; ++j) {
       if (!mbar_wait(&tl->qk_done[j & 1], (j >> 1) & 1, wait_status, 207)) { alive = false; break; }
       tc_fence_after();
@@ -298,7 +332,7 @@ fwd_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap
       tmem_ld_wait();
       const uint32_t ent = tl->list[j];
       const int kbase = (int)(ent & 0xffffu) * kBS;
-      const bool att = ((ent >> (16 + t)) & 1u) != 0 && hf[t].valid;
+      const bool att = ((ent >> (16 + t)) & 1u) != 0 && my.valid;
       // Allowed columns of this block form a prefix: kpos < k_len and, when causal,
       // kpos <= qpos.  Raw logits are compared (sm_scale > 0); the scale is folded
       // into the exponent's FMA.
@@ -352,11 +386,7 @@ fwd_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap
         for (int c = 0; c < 32; ++c) pk[c] = 0u;
       }
       tmem_st32(tS[j & 1] + lane_off, pk);
-      if (j > 0) {
-        // Every phase of pv_done is observed in order (a parity wait is only
-        // meaningful when the waiter is at most one phase behind).
-        if (!mbar_wait(&tl->pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, wait_status, 208)) { alive = false; break; }
-      }
+      if (!observe_pv(any ? j - 1 : j - 2)) { alive = false; break; }
       if (any && j > 0) {
         // rescale the accumulator rows whose maximum moved (P V_{j-1} has landed)
         tc_fence_after();
@@ -375,43 +405,41 @@ fwd_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap
       mbar_arrive(&tl->p_full[j & 1]);
     }
     // ---- epilogue: O / l -> registers -> swizzled smem (the Q tile is dead) -> global
-    if (alive) alive = mbar_wait(&tl->pv_done[(n - 1) & 1], ((n - 1) >> 1) & 1, wait_status, 209);
+    if (alive) alive = observe_pv(n - 1);
     tc_fence_after();
     if (alive) {
+      // ---- epilogue: each thread normalises its own row and stores it straight from
+      // registers, 64 contiguous bytes per 32-column chunk
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      uint8_t* stage = sQ + warp * 8192;  // this warp's 32 rows x 256 B
+      const bool row_ok = my.valid && q_row < q_len;
+      uint8_t* orow = reinterpret_cast<uint8_t*>(p.o) +
+                      ((int64_t)b * p.o_sb + (int64_t)my.head * p.o_sh + (int64_t)(q_start + q_row) * p.o_ss) * 2;
+      const bool wide = reinterpret_cast<uintptr_t>(p.o) % 16 == 0 && p.o_ss % 8 == 0 &&
+                        p.o_sh % 8 == 0 && p.o_sb % 8 == 0;   // rows start on 16-byte boundaries
 #pragma unroll
       for (int ch = 0; ch < 4; ++ch) {
         uint32_t o[32];
         tmem_ld32(tO + lane_off + ch * 32, o);
         tmem_ld_wait();
+        uint32_t w[16];
 #pragma unroll
-        for (int c4 = 0; c4 < 4; ++c4) {   // 4 chunks of 8 values = 16 bytes
-          uint4 w;
-          w.x = pack2<BF16>(__uint_as_float(o[c4 * 8 + 0]) * inv, __uint_as_float(o[c4 * 8 + 1]) * inv);
-          w.y = pack2<BF16>(__uint_as_float(o[c4 * 8 + 2]) * inv, __uint_as_float(o[c4 * 8 + 3]) * inv);
-          w.z = pack2<BF16>(__uint_as_float(o[c4 * 8 + 4]) * inv, __uint_as_float(o[c4 * 8 + 5]) * inv);
-          w.w = pack2<BF16>(__uint_as_float(o[c4 * 8 + 6]) * inv, __uint_as_float(o[c4 * 8 + 7]) * inv);
-          const int chunk = ch * 4 + c4;
-          *reinterpret_cast<uint4*>(stage + lane * 256 + ((chunk ^ (lane & 15)) << 4)) = w;
+        for (int i = 0; i < 16; ++i)
+          w[i] = pack2<BF16>(__uint_as_float(o[2 * i]) * inv, __uint_as_float(o[2 * i + 1]) * inv);
+        if (row_ok) {
+          if (wide) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              *reinterpret_cast<uint4*>(orow + ch * 64 + i * 16) =
+                  make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              *reinterpret_cast<uint2*>(orow + ch * 64 + i * 8) = make_uint2(w[2 * i], w[2 * i + 1]);
+          }
         }
       }
-      __syncwarp();
-      uint8_t* ob = reinterpret_cast<uint8_t*>(p.o);
-      for (int i = 0; i < 32; ++i) {
-        const int row = warp * 32 + i;
-        const int ht = row >> 6;
-        const int qr = hf[ht].qblk * kBS + (row & 63);
-        if (hf[ht].valid && qr < q_len) {
-          const int64_t off = ((int64_t)b * p.o_sb + (int64_t)hf[ht].head * p.o_sh +
-                               (int64_t)(q_start + qr) * p.o_ss) * 2 + lane * 8;
-          const uint2 w = *reinterpret_cast<const uint2*>(
-              stage + i * 256 + (((lane >> 1) ^ (i & 15)) << 4) + (lane & 1) * 8);
-          *reinterpret_cast<uint2*>(ob + off) = w;
-        }
-      }
-      if (p.lse && hf[t].valid && q_row < q_len)
-        p.lse[(int64_t)b * p.lse_sb + (int64_t)hf[t].head * p.lse_sh + q_start + q_row] =
+      if (p.lse && row_ok)
+        p.lse[(int64_t)b * p.lse_sb + (int64_t)my.head * p.lse_sh + q_start + q_row] =
             l > 0.f ? (m_used + log2f(l)) * kLn2 : -INFINITY;
     }
   } else if (warp == 4) {
@@ -420,16 +448,17 @@ fwd_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap
   } else if (warp < 4) {
     // no attended block at all: zero rows, LSE = -inf
     const int r = tid, t = r >> 6;
-    const int q_row = hf[t].qblk * kBS + (r & 63);
-    if (hf[t].valid && q_row < q_len) {
+    const Half my = t ? hf[1] : hf[0];
+    const int q_row = my.qblk * kBS + (r & 63);
+    if (my.valid && q_row < q_len) {
       uint4* dst = reinterpret_cast<uint4*>(
           reinterpret_cast<uint8_t*>(p.o) +
-          ((int64_t)b * p.o_sb + (int64_t)hf[t].head * p.o_sh + (int64_t)(q_start + q_row) * p.o_ss) * 2);
+          ((int64_t)b * p.o_sb + (int64_t)my.head * p.o_sh + (int64_t)(q_start + q_row) * p.o_ss) * 2);
       // rows are only guaranteed 8-byte aligned
       uint2* d2 = reinterpret_cast<uint2*>(dst);
       for (int i = 0; i < 32; ++i) d2[i] = make_uint2(0u, 0u);
       if (p.lse)
-        p.lse[(int64_t)b * p.lse_sb + (int64_t)hf[t].head * p.lse_sh + q_start + q_row] = -INFINITY;
+        p.lse[(int64_t)b * p.lse_sb + (int64_t)my.head * p.lse_sh + q_start + q_row] = -INFINITY;
     }
   }
   tc_fence_before();
@@ -473,7 +502,11 @@ int sm100_fwd(const bsa_fwd_params* p, cudaStream_t s) {
                     p->v_sh * 2, p->v_sb * 2, 64, 64, true, bf16);
   if (rc) return rc;
   const int G = p->hq / p->hkv;
-  const int mode = (G % 2 == 0) ? kPairHeads : kPairRows;
+  // Two heads share a tile only when they share a block list (one pattern for all heads
+  // or one per kv head): with per-head patterns the union of two heads' lists would spend
+  // half of the tensor work of every unshared block on an unattended half.  Two adjacent
+  // row blocks of one head share all but the two ends of their lists.
+  const int mode = (G % 2 == 0 && p->h_pat != p->hq) ? kPairHeads : kPairRows;
   const int tile_rows = mode == kPairHeads ? 64 : 128;
   const int head_items = mode == kPairHeads ? p->hq / 2 : p->hq;
   dim3 grid;

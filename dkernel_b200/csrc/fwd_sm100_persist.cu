@@ -541,7 +541,11 @@ int sm100_fwd_persist(const bsa_fwd_params* p, cudaStream_t s) {
                     true, bf16);
   if (rc) return rc;
   const int G = p->hq / p->hkv;
-  const int mode = (G % 2 == 0) ? kPairHeads : kPairRows;
+  // Two heads share a tile only when they share a block list (one pattern for all heads
+  // or one per kv head): with per-head patterns the union of two heads' lists would spend
+  // half of the tensor work of every unshared block on an unattended half.  Two adjacent
+  // row blocks of one head share all but the two ends of their lists.
+  const int mode = (G % 2 == 0 && p->h_pat != p->hq) ? kPairHeads : kPairRows;
   const int tile_rows = mode == kPairHeads ? 64 : 128;
   const int head_items = mode == kPairHeads ? p->hq / 2 : p->hq;
   const int tiles_x = p->total_q > 0 ? cdiv_i(p->total_q, tile_rows) + p->batch : cdiv_i(p->sq, tile_rows);
