@@ -10,15 +10,16 @@
 // The per-head CSR rows of both halves are merged in shared memory (bitmaps ->
 // ordered list) before the pipeline starts.
 //
-// Warp roles (224 threads):  warps 0-3 softmax (thread r owns tile row r = TMEM
-// lane r: no cross-lane reductions at all), warp 4 TMA producer, warp 5 issues the
-// Q K^T products and owns TMEM, warp 6 issues the P V products (a tcgen05
-// instruction costs its issuing thread 60-75 cycles whatever its size, so one
-// thread cannot keep the tensor pipe fed).  Per kv block j:
+// Warp roles (192 threads):  warps 0-3 softmax (thread r owns tile row r = TMEM
+// lane r: no cross-lane reductions at all), warp 4 TMA producer, warp 5 owns TMEM
+// and issues every product from one thread.  Per kv block j:
 //   S[j&1] = Q K_j^T          tcgen05.mma, A/B from 128B-swizzled smem, fp32 in TMEM
 //   P = exp2(S*c - m)          softmax warps: tcgen05.ld -> registers -> bf16/fp16 ->
 //                              tcgen05.st into the columns S occupied
 //   O += P V_j                 tcgen05.mma, A = P from TMEM, B = V (MN-major) from smem
+// The issue order is Q K_0, Q K_1, then P V_j followed at once by Q K_{j+2}: the
+// tensor pipe runs one thread's products in issue order, so Q K_{j+2} may be queued
+// behind P V_j without waiting for the completion that frees the columns they share.
 // S is double buffered so Q K_{j+1}^T overlaps softmax j; the running maximum is
 // only raised when it grows by more than 2^8 (the accumulator then gets rescaled
 // in TMEM), so the correction step is rare.  Two CTAs fit per SM (about 101 KB of
@@ -34,7 +35,7 @@ namespace {
 
 constexpr int kD = 128;
 constexpr int kBS = 64;
-constexpr int kFwdThreads = 224;
+constexpr int kFwdThreads = 192;
 constexpr int kMaxList = 1024;          // kv blocks per sequence (64K tokens)
 constexpr int kQBytes = 128 * kD * 2;   // 32 KB
 constexpr int kKVBytes = kBS * kD * 2;  // 16 KB per K or V tile
@@ -160,9 +161,9 @@ fwd_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap
   // ---------------------------------------------------------------- setup
   if (warp == 0) {
     // the eleven barriers are contiguous: q_full, k_full[2], v_full[2], qk_done[2],
-    // pv_done[2] (one arrival each) and p_full[2] (all softmax threads)
+    // pv_done[2] (one arrival each) and p_full[2] (one arrival per softmax warp)
     if (lane < 11) {
-      mbar_init(&tl->q_full + lane, lane >= 9 ? 128 : 1);
+      mbar_init(&tl->q_full + lane, lane >= 9 ? 4 : 1);
       mbar_fence_init();
     } else if (lane == 11) {
       tma_prefetch_desc(&tmQ.map);
@@ -256,19 +257,24 @@ fwd_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap
       }
     }
   } else if (n > 0 && warp == 5) {
-    // ------------------------------------------------------------ Q K^T issuer
+    // ------------------------------------------------------------ MMA issuer
+    // One thread issues every product, in the order  Q K_0, Q K_1, then per block j:
+    // P V_j, Q K_{j+2}.  Q K_{j+2} overwrites the columns P_j sits in; it is issued right
+    // behind P V_j without waiting for that product to complete, because the tensor pipe
+    // executes one thread's tcgen05.mma instructions in issue order.
     if (lane == 0) {
       const uint32_t idesc_qk = umma_idesc(BF16, 128, kBS, false, false);
+      const uint32_t idesc_pv = umma_idesc(BF16, 128, kD, false, true);
       // descriptors of the first tile of each operand; the start-address field (bits
       // 0..13, units of 16 bytes) is advanced by plain additions afterwards
       const uint64_t qdesc0 = umma_desc_sw128(smem_u32(sQ), 16, 1024);
       const uint64_t kdesc0 = umma_desc_sw128(smem_u32(sKV), 16, 1024);
-      bool ok = mbar_wait(&tl->q_full, 0, wait_status, 203);
-      for (int j = 0; j < n && ok; ++j) {
+      // V tile: rows = kv tokens (K of this product), 128 contiguous bytes = 64 head
+      // dims (N); the two 64-dim halves are 8 KB apart (LBO); 16 tokens per k-step
+      const uint64_t vdesc0 = umma_desc_sw128(smem_u32(sKV) + kKVBytes, 8192, 1024);
+      auto issue_qk = [&](int j) -> bool {
         const int s = j & 1;
-        if (!mbar_wait(&tl->k_full[s], (j >> 1) & 1, wait_status, 204)) break;
-        // S[s] doubles as P[s]: P V_{j-2} must have consumed it
-        if (j >= 2 && !mbar_wait(&tl->pv_done[s], ((j - 2) >> 1) & 1, wait_status, 210)) break;
+        if (!mbar_wait(&tl->k_full[s], (j >> 1) & 1, wait_status, 204)) return false;
         tc_fence_after();
         const uint64_t db0 = kdesc0 + (uint64_t)((s * 2 * kKVBytes) >> 4);
 #pragma unroll
@@ -276,17 +282,11 @@ fwd_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap
           tc_mma_ss(tS[s], qdesc0 + (uint64_t)(((i >> 2) * 16384 + (i & 3) * 32) >> 4),
                     db0 + (uint64_t)(((i >> 2) * 8192 + (i & 3) * 32) >> 4), idesc_qk, i ? 1u : 0u);
         tc_commit(&tl->qk_done[s]);
-      }
-    }
-    __syncwarp();
-  } else if (n > 0 && warp == 6) {
-    // ------------------------------------------------------------ P V issuer
-    if (lane == 0) {
-      const uint32_t idesc_pv = umma_idesc(BF16, 128, kD, false, true);
-      // V tile: rows = kv tokens (K of this product), 128 contiguous bytes = 64 head
-      // dims (N); the two 64-dim halves are 8 KB apart (LBO); 16 tokens per k-step
-      const uint64_t vdesc0 = umma_desc_sw128(smem_u32(sKV) + kKVBytes, 8192, 1024);
-      for (int j = 0; j < n; ++j) {
+        return true;
+      };
+      bool ok = mbar_wait(&tl->q_full, 0, wait_status, 203);
+      for (int j = 0; j < 2 && j < n && ok; ++j) ok = issue_qk(j);
+      for (int j = 0; j < n && ok; ++j) {
         const int s = j & 1;
         if (!mbar_wait(&tl->p_full[s], (j >> 1) & 1, wait_status, 205)) break;
         if (!mbar_wait(&tl->v_full[s], (j >> 1) & 1, wait_status, 206)) break;
@@ -296,6 +296,7 @@ fwd_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap
         for (int kk = 0; kk < 4; ++kk)
           tc_mma_ts(tO, tS[s] + kk * 8, dv0 + (uint64_t)((kk * 2048) >> 4), idesc_pv, (j | kk) ? 1u : 0u);
         tc_commit(&tl->pv_done[s]);
+        if (j + 2 < n) ok = issue_qk(j + 2);
       }
     }
     __syncwarp();
@@ -400,9 +401,12 @@ fwd_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap
           tmem_st32(tO + lane_off + ch * 32, o);
         }
       }
+      // tcgen05.wait::st is warp-wide: after it every lane's P row is in TMEM, so one
+      // arrival per warp publishes them
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(&tl->p_full[j & 1]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tl->p_full[j & 1]);
     }
     // ---- epilogue: O / l -> registers -> swizzled smem (the Q tile is dead) -> global
     if (alive) alive = observe_pv(n - 1);
