@@ -3,7 +3,8 @@
 // Grid = (split, kv head x head group, sequence).  A CTA owns up to
 // blocks_per_split attended blocks of one (sequence, kv head): a producer warp
 // streams their K and V tiles (64 tokens x D, 128-byte-swizzled TMA boxes) through
-// a 3-stage shared-memory ring, and four consumer warps each take 16 tokens of
+// a 2-stage shared-memory ring (three CTAs fit per SM, so one CTA's prologue and epilogue
+// are covered by the loads of the other two), and four consumer warps each take 16 tokens of
 // every tile.  The q heads of the kv group are stacked into the 16 rows of an
 // m16n8k16 tensor-core tile, so K/V are read from HBM once per group, and the
 // per-token work is a handful of ldmatrix + mma instructions, which keeps the
@@ -23,7 +24,13 @@ __device__ int g_wait_status = 0;  // first bounded wait that gave up (0 = none)
 
 namespace {
 
-constexpr int kStages = 3;
+#ifndef BSA_DEC_STAGES
+#define BSA_DEC_STAGES 2
+#endif
+#ifndef BSA_DEC_MIN_CTAS
+#define BSA_DEC_MIN_CTAS 3
+#endif
+constexpr int kStages = BSA_DEC_STAGES;    // K/V ring depth
 constexpr int kTok = 64;                 // tokens per pipeline stage
 constexpr int kConsumers = 4;            // consumer warps
 constexpr int kDecThreads = 32 * (kConsumers + 1);
@@ -88,7 +95,7 @@ __device__ __forceinline__ uint32_t tile_off(int tok, int chunk) {
 }
 
 template <typename T, int D>
-__global__ void __launch_bounds__(kDecThreads)
+__global__ void __launch_bounds__(kDecThreads, BSA_DEC_MIN_CTAS)
 decode_kernel(const __grid_constant__ Tmap4 tmK, const __grid_constant__ Tmap4 tmV,
               bsa_decode_params p, int nsplit, int* wait_status) {
   constexpr int kTileBytes = kTok * D * 2;
@@ -100,6 +107,8 @@ decode_kernel(const __grid_constant__ Tmap4 tmK, const __grid_constant__ Tmap4 t
   T* Qs = reinterpret_cast<T*>(smem + kStages * kStageBytes);  // [16][D]
   DecodeSmem* sm = reinterpret_cast<DecodeSmem*>(smem + kStages * kStageBytes + 16 * D * 2);
 
+  // the merge kernel behind this one may be made resident as soon as every CTA got here
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (*reinterpret_cast<volatile int*>(wait_status) != 0) return;  // an earlier wait gave up
   const int sp = blockIdx.x, b = blockIdx.z;
   const int G = p.hq / p.hkv;
@@ -109,6 +118,7 @@ decode_kernel(const __grid_constant__ Tmap4 tmK, const __grid_constant__ Tmap4 t
   const int h0 = kvh * G + (blockIdx.y % groups_per_kv) * GH;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bs = p.block_size;
+  const bool q_vec = reinterpret_cast<uintptr_t>(p.q) % 16 == 0 && p.q_sb % 8 == 0 && p.q_sh % 8 == 0;
 
   const int ks = p.k_start ? p.k_start[b] : 0;
   const int ke = p.k_end ? p.k_end[b] : p.sk;
@@ -139,7 +149,7 @@ decode_kernel(const __grid_constant__ Tmap4 tmK, const __grid_constant__ Tmap4 t
       for (int s = 0; s < subs; ++s) {
         const int pos = base + s * kTok;
         if (pos < end_pos && n_units < kMaxUnits) {
-          if (tid == 0) sm->unit_pos[n_units] = pos;
+          if (tid == kConsumers * 32) sm->unit_pos[n_units] = pos;
           ++n_units;
         }
       }
@@ -166,22 +176,44 @@ decode_kernel(const __grid_constant__ Tmap4 tmK, const __grid_constant__ Tmap4 t
     return;
   }
 
-  if (tid == 0) {
+  // The producer thread owns the barriers and the unit list, so its first loads go out
+  // before the rest of the CTA has staged Q.
+  auto issue_unit = [&](int u) {
+    const int s = u % kStages;
+    mbar_expect_tx(&sm->full[s], kStageBytes);
+    const int tok = ks + (sm->unit_pos[u] - pos0);
+    uint8_t* kdst = ring + s * kStageBytes;
+    uint8_t* vdst = kdst + kTileBytes;
+#pragma unroll
+    for (int c = 0; c < D / 64; ++c) {
+      tma_load_tile(kdst + c * (kTok * 128), &tmK, &sm->full[s], c * 64, tok, kvh, b);
+      tma_load_tile(vdst + c * (kTok * 128), &tmV, &sm->full[s], c * 64, tok, kvh, b);
+    }
+  };
+  if (tid == kConsumers * 32) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&sm->full[s], 1);
       mbar_init(&sm->empty[s], kConsumers);
     }
     mbar_fence_init();
-    tma_prefetch_desc(&tmK.map);
-    tma_prefetch_desc(&tmV.map);
+    for (int u = 0; u < n_units && u < kStages; ++u) issue_unit(u);
   }
-  // q heads of the group -> rows of the 16-row A tile (rows >= GH are zero)
-  for (int i = tid; i < 16 * D; i += kDecThreads) {
-    const int r = i / D, d = i % D;
-    T v = Elem<T>::from_f(0.f);
-    if (r < GH)
-      v = reinterpret_cast<const T*>(p.q)[(int64_t)b * p.q_sb + (int64_t)(h0 + r) * p.q_sh + d];
-    Qs[i] = v;
+  // q heads of the group -> rows of the 16-row A tile (rows >= GH are zero), 16 bytes a thread
+  for (int i = tid; i < 16 * D / 8; i += kDecThreads) {
+    const int r = i / (D / 8), c = i % (D / 8);
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (r < GH) {
+      const T* src = reinterpret_cast<const T*>(p.q) + (int64_t)b * p.q_sb + (int64_t)(h0 + r) * p.q_sh + c * 8;
+      if (q_vec) {
+        v = *reinterpret_cast<const uint4*>(src);
+      } else {
+        T tmp[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) tmp[e] = src[e];
+        v = *reinterpret_cast<const uint4*>(tmp);
+      }
+    }
+    reinterpret_cast<uint4*>(Qs)[i] = v;
   }
   __syncthreads();
 
@@ -193,19 +225,11 @@ decode_kernel(const __grid_constant__ Tmap4 tmK, const __grid_constant__ Tmap4 t
   if (warp == kConsumers) {
     // ------------------------------------------------------------ producer
     if (lane == 0) {
-      for (int u = 0; u < n_units; ++u) {
+      for (int u = kStages; u < n_units; ++u) {   // the first kStages units are already in flight
         const int s = u % kStages;
         const uint32_t ph = (u / kStages) & 1;
         if (!mbar_wait(&sm->empty[s], ph ^ 1, wait_status, 101)) break;
-        mbar_expect_tx(&sm->full[s], kStageBytes);
-        const int tok = ks + (sm->unit_pos[u] - pos0);
-        uint8_t* kdst = ring + s * kStageBytes;
-        uint8_t* vdst = kdst + kTileBytes;
-#pragma unroll
-        for (int c = 0; c < D / 64; ++c) {
-          tma_load_tile(kdst + c * (kTok * 128), &tmK, &sm->full[s], c * 64, tok, kvh, b);
-          tma_load_tile(vdst + c * (kTok * 128), &tmV, &sm->full[s], c * 64, tok, kvh, b);
-        }
+        issue_unit(u);
       }
     }
   } else {
@@ -375,6 +399,9 @@ __global__ void merge_kernel(const Tin* __restrict__ o_parts, const float* __res
                              int64_t rsl, Tout* __restrict__ o, int64_t ors,
                              float* __restrict__ lse) {
   const int64_t total = rows * d;
+  // Launched as a programmatic dependent of the decode kernel: the blocks may already be
+  // resident while that grid drains, and wait here until its partials are visible.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
        i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t r = i / d;
@@ -401,14 +428,41 @@ int launch_merge(const void* o_parts, const float* lse_parts, int P, int64_t row
   if (total == 0) return BSA_OK;
   int64_t blocks = (total + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  merge_kernel<Tin, Tout><<<(unsigned)blocks, 256, 0, s>>>(
-      reinterpret_cast<const Tin*>(o_parts), lse_parts, P, rows, d, pso, rso, psl, rsl,
-      reinterpret_cast<Tout*>(o), ors, lse);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)blocks);
+  cfg.blockDim = dim3(256);
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  BSA_CHECK_CUDA(cudaLaunchKernelEx(&cfg, merge_kernel<Tin, Tout>, reinterpret_cast<const Tin*>(o_parts),
+                                    lse_parts, P, rows, d, pso, rso, psl, rsl,
+                                    reinterpret_cast<Tout*>(o), ors, lse));
   return check_launch("merge_kernel");
 }
 
+// Attended blocks per CTA.  A caller's choice is kept; otherwise a CTA gets as many blocks as
+// possible (up to 16: one prologue and one partial per 512 KB of K/V) while the grid still
+// fills the machine about twice over (three resident CTAs per SM).
+int decode_blocks_per_split(const bsa_decode_params* p) {
+  if (p->blocks_per_split > 0) return p->blocks_per_split;
+  const int hpc = p->heads_per_cta > 0 ? p->heads_per_cta : 1;
+  const long long items = (long long)p->batch * p->hkv * ((p->hq / p->hkv) / hpc);
+  const long long want = 2LL * 148 * BSA_DEC_MIN_CTAS;
+  long long splits = items > 0 ? (want + items - 1) / items : 1;
+  if (splits < 1) splits = 1;
+  const int nnz = p->max_row_nnz > 0 ? p->max_row_nnz : 1;
+  long long bps = (nnz + splits - 1) / splits;
+  bps = (bps + 3) / 4 * 4;
+  if (bps < 4) bps = 4;
+  if (bps > 16) bps = 16;
+  return (int)bps;
+}
+
 int decode_nsplit(const bsa_decode_params* p) {
-  const int bps = p->blocks_per_split > 0 ? p->blocks_per_split : 8;
+  const int bps = decode_blocks_per_split(p);
   const int n = (p->max_row_nnz + bps - 1) / bps;
   return n < 1 ? 1 : n;
 }
@@ -430,7 +484,7 @@ int launch_decode(const bsa_decode_params* p, cudaStream_t s) {
   const int G = p->hq / p->hkv;
   dim3 grid(nsplit, p->hkv * (G / p->heads_per_cta), p->batch);
   bsa_decode_params q = *p;
-  if (q.blocks_per_split <= 0) q.blocks_per_split = 8;
+  q.blocks_per_split = decode_blocks_per_split(p);
   int* status = wait_status_ptr();
   if (!status) return BSA_E_CUDA;
   kern<<<grid, kDecThreads, smem, s>>>(tmK, tmV, q, nsplit, status);
@@ -487,7 +541,7 @@ int decode_run(const bsa_decode_params* p, cudaStream_t s) {
     set_error("bsa_decode: K/V need a 16-byte aligned base and strides that are multiples of 16 bytes");
     return BSA_E_UNSUPPORTED;
   }
-  const int bps = p->blocks_per_split > 0 ? p->blocks_per_split : 8;
+  const int bps = decode_blocks_per_split(p);
   if (bps * (p->block_size / kTok) > kMaxUnits) {
     set_error("bsa_decode: blocks_per_split=%d too large (limit %d tiles of 64 tokens per CTA)", bps,
               kMaxUnits);

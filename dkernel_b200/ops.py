@@ -176,7 +176,7 @@ def decode(q: Tensor, k: Tensor, v: Tensor, plan: _Plan, sm_scale: float, *, seq
     _fill_layout(p, plan)
     g = hq // hkv
     p.heads_per_cta = _pick_heads_per_cta(g) if plan.heads_shared_in_group(hq, hkv) else 1
-    p.blocks_per_split = blocks_per_split if blocks_per_split > 0 else 8
+    p.blocks_per_split = blocks_per_split if blocks_per_split > 0 else 0   # 0: the library picks
     p.max_row_nnz = plan.max_row_nnz
     p.dtype = _lib.dtype_code(q.dtype)
     p.sm_scale = float(sm_scale)
@@ -259,10 +259,12 @@ def _padded(q, k, v, sm_scale, plan, left_paddings, seqlens, seq_dim, max_seqlen
     if seqlens is not None:
         k_ends = k_starts + seqlens.to(dev, dtype=torch.int32)
     else:
-        k_ends = torch.full_like(k_starts, k_len)
+        k_ends = None   # every sequence ends at k_len
     if q_len == 1 and _decode_eligible(q, plan, impl):
         o, lse = decode(q, k, v, plan, sm_scale, seq_dim=seq_dim, k_start=k_starts, k_end=k_ends, out=out)
         return o, (lse.unsqueeze(-1) if return_lse else None)
+    if k_ends is None:
+        k_ends = torch.full_like(k_starts, k_len)
     if q_len == 1:
         q_starts = torch.zeros_like(k_starts)
         q_ends = q_starts + 1

@@ -194,7 +194,7 @@ typedef struct {
   int32_t h_pat, n_rows, block_size;
   int32_t heads_per_cta;      /* q heads of one kv group handled together;
                                  they must share one pattern row (1 = safe)     */
-  int32_t blocks_per_split;   /* attended blocks per CTA                        */
+  int32_t blocks_per_split;   /* attended blocks per CTA; <= 0: the library picks 4..16 */
   int32_t max_row_nnz;        /* longest pattern row: bounds the split count    */
   int32_t dtype;
   float sm_scale;
