@@ -299,7 +299,9 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
     }
   } else if (n > 0 && warp == kWarpIssueA) {
     // ------------------------------------------------------------ S^T = K Q^T, dP^T = V dO^T
-    if (lane == 0) {
+    // (the issuer warps run converged so that descriptors stay in uniform registers; only
+    // the tcgen05 instructions sit under the elected lane)
+    {
       const uint32_t idesc_nt = umma_idesc(BF16, 128, kBS, false, false);
       const uint64_t kdesc = umma_desc_sw128(smem_u32(sK), 16, 1024);
       const uint64_t vdesc = umma_desc_sw128(smem_u32(sV), 16, 1024);
@@ -313,21 +315,24 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
         tc_fence_after();
         const uint64_t qd = qdesc0 + (uint64_t)((s * kQdoStageBytes) >> 4);
         const uint64_t gd = qd + (uint64_t)((kBS * kD * 2) >> 4);
+        if (elect_one()) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i)   // i = c * 4 + kk
-          tc_mma_ss(tST[bf], kdesc + (uint64_t)(((i >> 2) * 16384 + (i & 3) * 32) >> 4),
-                    qd + (uint64_t)(((i >> 2) * 8192 + (i & 3) * 32) >> 4), idesc_nt, i ? 1u : 0u);
+          for (int i = 0; i < 8; ++i)   // i = c * 4 + kk
+            tc_mma_ss(tST[bf], kdesc + (uint64_t)(((i >> 2) * 16384 + (i & 3) * 32) >> 4),
+                      qd + (uint64_t)(((i >> 2) * 8192 + (i & 3) * 32) >> 4), idesc_nt, i ? 1u : 0u);
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
-          tc_mma_ss(tDP[bf], vdesc + (uint64_t)(((i >> 2) * 16384 + (i & 3) * 32) >> 4),
-                    gd + (uint64_t)(((i >> 2) * 8192 + (i & 3) * 32) >> 4), idesc_nt, i ? 1u : 0u);
-        tc_commit(&tl->sdp_full[bf]);
+          for (int i = 0; i < 8; ++i)
+            tc_mma_ss(tDP[bf], vdesc + (uint64_t)(((i >> 2) * 16384 + (i & 3) * 32) >> 4),
+                      gd + (uint64_t)(((i >> 2) * 8192 + (i & 3) * 32) >> 4), idesc_nt, i ? 1u : 0u);
+          tc_commit(&tl->sdp_full[bf]);
+        }
+        __syncwarp();
       }
     }
     __syncwarp();
   } else if (n > 0 && warp == kWarpIssueB) {
     // ------------------------------------------------------------ dV += P^T dO, dK += dS^T Q
-    if (lane == 0) {
+    {
       const uint32_t idesc_acc = umma_idesc(BF16, 128, kD, false, true);
       // B operands are the dO_r / Q_r tiles read MN-major: 16 q rows (2 KB) per k-step,
       // the two 64-dim halves 8 KB apart
@@ -339,18 +344,22 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
         tc_fence_after();
         const uint64_t qd = qdesc0 + (uint64_t)((s * kQdoStageBytes) >> 4);
         const uint64_t gd = qd + (uint64_t)((kBS * kD * 2) >> 4);
+        const uint32_t acc0 = e ? 1u : 0u;
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          tc_mma_ts(tDV, tST[bf] + packed_col(kk), gd + (uint64_t)((kk * 2048) >> 4), idesc_acc,
-                    (e | kk) ? 1u : 0u);
+          for (int kk = 0; kk < 4; ++kk)
+            tc_mma_ts(tDV, tST[bf] + packed_col(kk), gd + (uint64_t)((kk * 2048) >> 4), idesc_acc,
+                      kk ? 1u : acc0);
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          tc_mma_ts(tDK, tDP[bf] + packed_col(kk), qd + (uint64_t)((kk * 2048) >> 4), idesc_acc,
-                    (e | kk) ? 1u : 0u);
-        tc_commit(&tl->qdo_empty[s]);
-        tc_commit(&tl->acc_done[bf]);
+          for (int kk = 0; kk < 4; ++kk)
+            tc_mma_ts(tDK, tDP[bf] + packed_col(kk), qd + (uint64_t)((kk * 2048) >> 4), idesc_acc,
+                      kk ? 1u : acc0);
+          tc_commit(&tl->qdo_empty[s]);
+          tc_commit(&tl->acc_done[bf]);
+        }
+        __syncwarp();
       }
-      if (ok) tc_commit(&tl->all_done);
+      if (ok && elect_one()) tc_commit(&tl->all_done);
     }
     __syncwarp();
   } else if (n > 0) {
@@ -605,7 +614,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
     }
   } else if (n > 0 && warp == kWarpIssueA) {
     // ------------------------------------------------------------ S = Q K^T, dP = dO V^T
-    if (lane == 0) {
+    {
       const uint32_t idesc_nt = umma_idesc(BF16, 128, kBS, false, false);
       const uint64_t qdesc = umma_desc_sw128(smem_u32(sQ), 16, 1024);
       const uint64_t gdesc = umma_desc_sw128(smem_u32(sDO), 16, 1024);
@@ -614,12 +623,15 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
       bool ok = mbar_wait(&tl->q_full, 0, wait_status, 313);
       if (ok) {
         tc_fence_after();
+        if (elect_one()) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {   // one k-step (16 head dims = 8 packed columns) per copy
-          const uint64_t off = (uint64_t)(((i >> 2) * 16384 + (i & 3) * 32) >> 4);
-          tc_cp_128x256b(tQ + i * 8, qdesc + off);
-          tc_cp_128x256b(tDO + i * 8, gdesc + off);
+          for (int i = 0; i < 8; ++i) {   // one k-step (16 head dims = 8 packed columns) per copy
+            const uint64_t off = (uint64_t)(((i >> 2) * 16384 + (i & 3) * 32) >> 4);
+            tc_cp_128x256b(tQ + i * 8, qdesc + off);
+            tc_cp_128x256b(tDO + i * 8, gdesc + off);
+          }
         }
+        __syncwarp();
       }
       for (int e = 0; e < n && ok; ++e) {
         const int sk_ = e % kDqKStages, sv_ = e % kDqVStages, bf = e & 1;
@@ -628,25 +640,31 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
         if (e >= 2 && !mbar_wait(&tl->acc_done[bf], ((e - 2) >> 1) & 1, wait_status, 319)) break;
         tc_fence_after();
         const uint64_t kd = kdesc0 + (uint64_t)((sk_ * kTileKV) >> 4);
+        if (elect_one()) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i)   // i = c * 4 + kk
-          tc_mma_ts(tS[bf], tQ + i * 8, kd + (uint64_t)(((i >> 2) * 8192 + (i & 3) * 32) >> 4), idesc_nt,
-                    i ? 1u : 0u);
+          for (int i = 0; i < 8; ++i)   // i = c * 4 + kk
+            tc_mma_ts(tS[bf], tQ + i * 8, kd + (uint64_t)(((i >> 2) * 8192 + (i & 3) * 32) >> 4), idesc_nt,
+                      i ? 1u : 0u);
+        }
+        __syncwarp();
         if (!mbar_wait(&tl->v_full[sv_], (e / kDqVStages) & 1, wait_status, 315)) break;
         tc_fence_after();
         const uint64_t vd = vdesc0 + (uint64_t)((sv_ * kTileKV) >> 4);
+        if (elect_one()) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
-          tc_mma_ts(tDP[bf], tDO + i * 8, vd + (uint64_t)(((i >> 2) * 8192 + (i & 3) * 32) >> 4), idesc_nt,
-                    i ? 1u : 0u);
-        tc_commit(&tl->v_empty[sv_]);
-        tc_commit(&tl->sdp_full[bf]);
+          for (int i = 0; i < 8; ++i)
+            tc_mma_ts(tDP[bf], tDO + i * 8, vd + (uint64_t)(((i >> 2) * 8192 + (i & 3) * 32) >> 4), idesc_nt,
+                      i ? 1u : 0u);
+          tc_commit(&tl->v_empty[sv_]);
+          tc_commit(&tl->sdp_full[bf]);
+        }
+        __syncwarp();
       }
     }
     __syncwarp();
   } else if (n > 0 && warp == kWarpIssueB) {
     // ------------------------------------------------------------ dQ += dS K
-    if (lane == 0) {
+    {
       const uint32_t idesc_acc = umma_idesc(BF16, 128, kD, false, true);
       // B = K_j read MN-major: 16 kv rows (2 KB) per k-step, 64-dim halves 8 KB apart
       const uint64_t kdesc0 = umma_desc_sw128(smem_u32(sKs), 8192, 1024);
@@ -656,14 +674,18 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
         if (!mbar_wait(&tl->p_full[bf], (e >> 1) & 1, wait_status, 316)) { ok = false; break; }
         tc_fence_after();
         const uint64_t kd = kdesc0 + (uint64_t)((sk_ * kTileKV) >> 4);
+        const uint32_t acc0 = e ? 1u : 0u;
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          tc_mma_ts(tDQ, tDP[bf] + packed_col(kk), kd + (uint64_t)((kk * 2048) >> 4), idesc_acc,
-                    (e | kk) ? 1u : 0u);
-        tc_commit(&tl->k_empty[sk_]);
-        tc_commit(&tl->acc_done[bf]);
+          for (int kk = 0; kk < 4; ++kk)
+            tc_mma_ts(tDQ, tDP[bf] + packed_col(kk), kd + (uint64_t)((kk * 2048) >> 4), idesc_acc,
+                      kk ? 1u : acc0);
+          tc_commit(&tl->k_empty[sk_]);
+          tc_commit(&tl->acc_done[bf]);
+        }
+        __syncwarp();
       }
-      if (ok) tc_commit(&tl->all_done);
+      if (ok && elect_one()) tc_commit(&tl->all_done);
     }
     __syncwarp();
   } else if (n > 0) {

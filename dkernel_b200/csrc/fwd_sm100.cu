@@ -262,7 +262,11 @@ fwd_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap
     // P V_j, Q K_{j+2}.  Q K_{j+2} overwrites the columns P_j sits in; it is issued right
     // behind P V_j without waiting for that product to complete, because the tensor pipe
     // executes one thread's tcgen05.mma instructions in issue order.
-    if (lane == 0) {
+    // The whole warp runs this loop converged, so that descriptors and addresses stay in
+    // uniform registers; only the tcgen05 instructions themselves sit under the elected lane.
+    // (A single diverged lane spends about a hundred cycles of dependent scalar work per
+    // product, which is more than the product takes on the tensor pipe.)
+    {
       const uint32_t idesc_qk = umma_idesc(BF16, 128, kBS, false, false);
       const uint32_t idesc_pv = umma_idesc(BF16, 128, kD, false, true);
       // descriptors of the first tile of each operand; the start-address field (bits
@@ -277,11 +281,14 @@ fwd_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap
         if (!mbar_wait(&tl->k_full[s], (j >> 1) & 1, wait_status, 204)) return false;
         tc_fence_after();
         const uint64_t db0 = kdesc0 + (uint64_t)((s * 2 * kKVBytes) >> 4);
+        if (elect_one()) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i)   // i = c * 4 + kk: sub-tile c (8 KB apart for K, 16 KB for Q), k-step kk
-          tc_mma_ss(tS[s], qdesc0 + (uint64_t)(((i >> 2) * 16384 + (i & 3) * 32) >> 4),
-                    db0 + (uint64_t)(((i >> 2) * 8192 + (i & 3) * 32) >> 4), idesc_qk, i ? 1u : 0u);
-        tc_commit(&tl->qk_done[s]);
+          for (int i = 0; i < 8; ++i)   // i = c * 4 + kk: sub-tile c (8 KB apart for K, 16 KB for Q), k-step kk
+            tc_mma_ss(tS[s], qdesc0 + (uint64_t)(((i >> 2) * 16384 + (i & 3) * 32) >> 4),
+                      db0 + (uint64_t)(((i >> 2) * 8192 + (i & 3) * 32) >> 4), idesc_qk, i ? 1u : 0u);
+          tc_commit(&tl->qk_done[s]);
+        }
+        __syncwarp();
         return true;
       };
       bool ok = mbar_wait(&tl->q_full, 0, wait_status, 203);
@@ -292,10 +299,14 @@ fwd_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap
         if (!mbar_wait(&tl->v_full[s], (j >> 1) & 1, wait_status, 206)) break;
         tc_fence_after();
         const uint64_t dv0 = vdesc0 + (uint64_t)((s * 2 * kKVBytes) >> 4);
+        const uint32_t acc0 = j ? 1u : 0u;
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          tc_mma_ts(tO, tS[s] + kk * 8, dv0 + (uint64_t)((kk * 2048) >> 4), idesc_pv, (j | kk) ? 1u : 0u);
-        tc_commit(&tl->pv_done[s]);
+          for (int kk = 0; kk < 4; ++kk)
+            tc_mma_ts(tO, tS[s] + kk * 8, dv0 + (uint64_t)((kk * 2048) >> 4), idesc_pv, kk ? 1u : acc0);
+          tc_commit(&tl->pv_done[s]);
+        }
+        __syncwarp();
         if (j + 2 < n) ok = issue_qk(j + 2);
       }
     }
