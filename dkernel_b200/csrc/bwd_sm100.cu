@@ -57,10 +57,6 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 // k-step kk (16 rows of the second-stage product) therefore starts at this column.
 __device__ __forceinline__ uint32_t packed_col(int kk) { return (uint32_t)((kk >> 1) * 32 + (kk & 1) * 8); }
 
-__device__ __forceinline__ void named_bar_sync(int id, int threads) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
-}
-
 // 128 x 128 fp32 accumulator in TMEM (lane = tile row) -> scaled 16-bit rows in
 // global memory.  Each warp converts its 32 lanes through an 8 KB staging area
 // (XOR-swizzled 16-byte chunks) and then writes whole 256-byte rows.
@@ -100,17 +96,30 @@ __device__ __forceinline__ void store_acc_tile(uint32_t tacc, int warp, int lane
 }
 
 // ------------------------------------------------------------------ delta
+// The workspace holds two arrays of batch x hq rows, each row padded to whole q blocks:
+// delta first, then lse * log2(e) (+inf for an empty row, so that P = 0).  Padding rows get
+// delta = 0 and +inf, which lets the dK/dV kernel copy a block's 64 values with one bulk copy.
+__host__ __device__ inline int padded_sq(int sq) { return (sq + kBS - 1) / kBS * kBS; }
+
 // One warp per (b, h, i) row of 128 elements: each lane reads 8 bytes of O and dO.
 template <bool BF16>
 __global__ void bwd_delta_vec_kernel(bsa_bwd_params bp) {
   const bsa_fwd_params& p = bp.f;
   const int lane = threadIdx.x & 31;
+  const int sp = padded_sq(p.sq);
   const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const long long total = (long long)p.batch * p.hq * p.sq;
+  const long long total = (long long)p.batch * p.hq * sp;
   if (w >= total) return;
-  const int i = (int)(w % p.sq);
-  const int h = (int)((w / p.sq) % p.hq);
-  const int b = (int)(w / ((long long)p.sq * p.hq));
+  const int i = (int)(w % sp);
+  const int h = (int)((w / sp) % p.hq);
+  const int b = (int)(w / ((long long)sp * p.hq));
+  if (i >= p.sq) {
+    if (lane == 0) {
+      bp.delta[w] = 0.f;
+      bp.delta[total + w] = INFINITY;
+    }
+    return;
+  }
   const uint2 ov = *reinterpret_cast<const uint2*>(
       reinterpret_cast<const uint8_t*>(p.o) +
       ((int64_t)b * p.o_sb + (int64_t)h * p.o_sh + (int64_t)i * p.o_ss) * 2 + lane * 8);
@@ -136,6 +145,8 @@ __global__ void bwd_delta_vec_kernel(bsa_bwd_params bp) {
   if (lane == 0) {
     if (bp.d_lse) s -= bp.d_lse[(int64_t)b * p.lse_sb + (int64_t)h * p.lse_sh + i];
     bp.delta[w] = s;
+    const float l = p.lse[(int64_t)b * p.lse_sb + (int64_t)h * p.lse_sh + i];
+    bp.delta[total + w] = l == -INFINITY ? INFINITY : l * kLog2e;
   }
 }
 
@@ -180,8 +191,8 @@ struct DkdvTail {
   uint64_t all_done;
   uint32_t tmem_base;
   int n_list;
-  // [buffer][0 = lse*log2e, 1 = delta][row of the q block]; read as float4
-  alignas(16) float ld[2][2][kBS];
+  // [stage][0 = lse*log2e, 1 = delta][row of the q block]: bulk-copied with the stage's tiles
+  alignas(128) float ld[kQdoStages][2][kBS];
   uint32_t bits[2][kMaxBlocks / 32];
   uint32_t list[kMaxEntries];
 };
@@ -210,6 +221,8 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
   const int kvalid[2] = {kblk[0] * kBS < p.sk ? 1 : 0, kblk[1] * kBS < p.sk ? 1 : 0};
   if (!kvalid[0]) return;
   const int nqb = min((p.sq + kBS - 1) / kBS, kMaxBlocks);
+  const int sq_pad = padded_sq(p.sq);
+  const int64_t ws_half = (int64_t)p.batch * p.hq * sq_pad;
 
   if (tid == 0) {
     mbar_init(&tl->kv_full, 1);
@@ -219,7 +232,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&tl->sdp_full[s], 1);
-      mbar_init(&tl->p_full[s], 256);
+      mbar_init(&tl->p_full[s], 8);   // one arrival per element-wise warp
       mbar_init(&tl->acc_done[s], 1);
     }
     mbar_init(&tl->all_done, 1);
@@ -288,13 +301,16 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
         const uint32_t ent = tl->list[e];
         const int r = ent & 0xffff, h = hk * G + ((ent >> 16) & 0xff);
         if (!mbar_wait(&tl->qdo_empty[s], ((e / kQdoStages) & 1) ^ 1, wait_status, 301)) break;
-        mbar_expect_tx(&tl->qdo_full[s], kQdoStageBytes);
+        mbar_expect_tx(&tl->qdo_full[s], kQdoStageBytes + 2 * kBS * 4);
         uint8_t* qd = sQdo + s * kQdoStageBytes;
         uint8_t* gd = qd + kBS * kD * 2;
         for (int c = 0; c < 2; ++c) {
           tma_load_tile(qd + c * 8192, &tmQ, &tl->qdo_full[s], c * 64, r * kBS, h, b);
           tma_load_tile(gd + c * 8192, &tmDO, &tl->qdo_full[s], c * 64, r * kBS, h, b);
         }
+        const int64_t row0 = ((int64_t)b * p.hq + h) * sq_pad + (int64_t)r * kBS;
+        bulk_load(tl->ld[s][0], bp.delta + ws_half + row0, kBS * 4, &tl->qdo_full[s]);
+        bulk_load(tl->ld[s][1], bp.delta + row0, kBS * 4, &tl->qdo_full[s]);
       }
     }
   } else if (n > 0 && warp == kWarpIssueA) {
@@ -370,24 +386,11 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
     const int kpos = kblk[t] * kBS + (r_kv & 63);
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
     const float scale2 = p.sm_scale * kLog2e;
-    // threads 0..127 fetch one lse or delta value of the next q block each
-    const int which = (tid >> 6) & 1, idx = tid & 63;
-    auto fetch = [&](int e) -> float {
-      const uint32_t ent = tl->list[e];
-      const int r = ent & 0xffff, h = hk * G + ((ent >> 16) & 0xff);
-      const int qi = r * kBS + idx;
-      if (qi >= p.sq) return which == 0 ? INFINITY : 0.f;
-      if (which == 0) {
-        const float l = p.lse[(int64_t)b * p.lse_sb + (int64_t)h * p.lse_sh + qi];
-        return l == -INFINITY ? INFINITY : l * kLog2e;   // empty row: P = 0
-      }
-      return bp.delta[((int64_t)b * p.hq + h) * p.sq + qi];
-    };
-    if (tid < 128) tl->ld[0][which][idx] = fetch(0);
-    named_bar_sync(1, 256);
     bool alive = true;
     for (int e = 0; e < n; ++e) {
-      const float nxt = (tid < 128 && e + 1 < n) ? fetch(e + 1) : 0.f;
+      const int st = e % kQdoStages;
+      // the stage's lse / delta rows arrive with its tiles
+      if (!mbar_wait(&tl->qdo_full[st], (e / kQdoStages) & 1, wait_status, 309)) { alive = false; break; }
       if (!mbar_wait(&tl->sdp_full[e & 1], (e >> 1) & 1, wait_status, 305)) { alive = false; break; }
       tc_fence_after();
       const uint32_t ent = tl->list[e];
@@ -395,8 +398,8 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
       const bool att = ((ent >> (24 + t)) & 1u) != 0 && kvalid[t];
       // causal: q position past + r*64 + c must be >= kpos  ->  c >= c0
       const int c0 = p.causal ? kpos - past - r * kBS : 0;
-      const float* lse_s = tl->ld[e & 1][0] + half * 32;
-      const float* del_s = tl->ld[e & 1][1] + half * 32;
+      const float* lse_s = tl->ld[st][0] + half * 32;
+      const float* del_s = tl->ld[st][1] + half * 32;
       uint32_t sv[32], dv[32];
       tmem_ld32(tST[e & 1] + lane_off + half * 32, sv);
       tmem_ld32(tDP[e & 1] + lane_off + half * 32, dv);
@@ -432,9 +435,8 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
       tmem_st16(tDP[e & 1] + lane_off + half * 32, ds);
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(&tl->p_full[e & 1]);
-      if (tid < 128 && e + 1 < n) tl->ld[(e + 1) & 1][which][idx] = nxt;
-      named_bar_sync(1, 256);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tl->p_full[e & 1]);
     }
     // ---- epilogue: warps 0-3 write dV, warps 4-7 write dK
     if (alive) alive = mbar_wait(&tl->all_done, 0, wait_status, 306);
@@ -700,7 +702,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
     if (valid[t] && q_row < p.sq) {
       const float l = p.lse[(int64_t)b * p.lse_sb + (int64_t)head[t] * p.lse_sh + q_row];
       lse2 = l == -INFINITY ? INFINITY : l * kLog2e;
-      delta = bp.delta[((int64_t)b * p.hq + head[t]) * p.sq + q_row];
+      delta = bp.delta[((int64_t)b * p.hq + head[t]) * padded_sq(p.sq) + q_row];
     }
     bool alive = true;
     for (int e = 0; e < n; ++e) {
@@ -788,7 +790,7 @@ int launch_bwd(const bsa_bwd_params* bp, cudaStream_t s) {
   int* status = wait_status_ptr();
   if (!status) return BSA_E_CUDA;
   {
-    const long long rows = (long long)p->batch * p->hq * p->sq;
+    const long long rows = (long long)p->batch * p->hq * padded_sq(p->sq);
     bwd_delta_vec_kernel<BF16><<<(unsigned)((rows + 7) / 8), 256, 0, s>>>(*bp);
     rc = check_launch("bwd_delta_vec_kernel");
     if (rc) return rc;

@@ -121,6 +121,14 @@ __device__ __forceinline__ void tma_load_tile(void* dst, const Tmap4* tm, uint64
   const int c3 = tm->seq_pos == 3 ? s : (tm->head_pos == 3 ? h : b);
   tma_load_4d(dst, &tm->map, bar, d0, c1, c2, c3);
 }
+// untiled bulk copy global -> shared (both addresses 16-byte aligned, bytes a multiple of 16)
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+          smem_u32(dst)),
+      "l"(src), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }

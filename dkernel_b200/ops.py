@@ -339,7 +339,8 @@ def _backward(ctx, do: Tensor, dlse: Optional[Tensor], dq=None, dk=None, dv=None
     bp.ccol_sh = plan.ccol.stride(0) if plan.ccol.size(0) > 1 else 0
     bp.row_sh = plan.row.stride(0) if plan.row.size(0) > 1 else 0
     bp.n_cols = plan.ccol.size(1) - 1
-    delta = torch.empty(lse.shape, dtype=torch.float32, device=q.device)
+    sq_pad = (q.size(seq_dim) + 63) // 64 * 64
+    delta = torch.empty((2, q.size(0), q.size(3 - seq_dim), sq_pad), dtype=torch.float32, device=q.device)
     bp.delta = _lib.ptr(delta)
     with torch.cuda.device(q.device):
         _lib.check(_lib.lib().bsa_bwd(C.byref(bp), _lib.stream_of(q)), "bsa_bwd")

@@ -160,7 +160,8 @@ typedef struct {
   const int32_t* ccol; const int32_t* row;   /* CSC of the pattern              */
   int64_t ccol_sh, row_sh;
   int32_t n_cols;             /* pattern columns available in ccol              */
-  float* delta;               /* workspace (batch*hq*sq) fp32                   */
+  float* delta;               /* fp32 workspace of 2 * batch * hq * (sq rounded up to a
+                                 multiple of 64) elements, 16-byte aligned          */
 } bsa_bwd_params;
 
 int bsa_bwd(const bsa_bwd_params* p, void* stream);
