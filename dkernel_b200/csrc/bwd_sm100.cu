@@ -29,8 +29,11 @@ namespace {
 
 constexpr int kD = 128;
 constexpr int kBS = 64;
-constexpr int kBwdThreads = 352;
+constexpr int kBwdThreads = 352;      // dQ kernel: 8 element-wise warps, producer, two issuers
 constexpr int kWarpProducer = 8, kWarpIssueA = 9, kWarpIssueB = 10;
+constexpr int kDkdvEwWarps = 16;      // dK/dV kernel: 16 element-wise warps, producer, two issuers
+constexpr int kDkdvThreads = 32 * (kDkdvEwWarps + 3);
+constexpr int kDkdvProducer = kDkdvEwWarps, kDkdvIssuer = kDkdvEwWarps + 1;   // issuers: +1 and +2
 constexpr int kMaxBlocks = 1024;   // q or kv blocks per sequence (64K tokens)
 constexpr int kMaxEntries = 2048;  // list entries per CTA
 
@@ -180,7 +183,7 @@ __device__ __forceinline__ void append_union(const uint32_t* bits0, const uint32
 }
 
 // ------------------------------------------------------------------ dK / dV
-constexpr int kQdoStages = 3;
+constexpr int kQdoStages = 4;
 constexpr int kKVResident = 2 * 128 * kD * 2;      // K and V tiles, 32 KB each
 constexpr int kQdoStageBytes = 2 * kBS * kD * 2;   // Q_r and dO_r, 16 KB each
 
@@ -199,7 +202,7 @@ struct DkdvTail {
 constexpr size_t kDkdvSmem = 1024 + kKVResident + kQdoStages * kQdoStageBytes + sizeof(DkdvTail);
 
 template <bool BF16>
-__global__ void __launch_bounds__(kBwdThreads, 1)
+__global__ void __launch_bounds__(kDkdvThreads, 1)
 bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap4 tmK,
                       const __grid_constant__ Tmap4 tmV, const __grid_constant__ Tmap4 tmDO,
                       bsa_bwd_params bp, int* wait_status) {
@@ -228,14 +231,14 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
     mbar_init(&tl->kv_full, 1);
     for (int s = 0; s < kQdoStages; ++s) {
       mbar_init(&tl->qdo_full[s], 1);
-      mbar_init(&tl->qdo_empty[s], 1);
+      mbar_init(&tl->qdo_empty[s], 2);   // both issuers have finished with the stage
     }
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&tl->sdp_full[s], 1);
-      mbar_init(&tl->p_full[s], 8);   // one arrival per element-wise warp
+      mbar_init(&tl->sdp_full[s], 2);    // S^T and dP^T, one commit each
+      mbar_init(&tl->p_full[s], kDkdvEwWarps);   // one arrival per element-wise warp
       mbar_init(&tl->acc_done[s], 1);
     }
-    mbar_init(&tl->all_done, 1);
+    mbar_init(&tl->all_done, 2);
     mbar_fence_init();
     tma_prefetch_desc(&tmQ.map);
     tma_prefetch_desc(&tmK.map);
@@ -245,7 +248,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
   }
   __syncthreads();
   // resident K / V tiles and the TMEM allocation overlap the list construction
-  if (warp == kWarpProducer && lane == 0) {
+  if (warp == kDkdvProducer && lane == 0) {
     mbar_expect_tx(&tl->kv_full, (uint32_t)(kvalid[0] + kvalid[1]) * 2 * (kBS * kD * 2));
     for (int t = 0; t < 2; ++t) {
       if (!kvalid[t]) continue;
@@ -255,7 +258,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
       }
     }
   }
-  if (warp == kWarpIssueA) {
+  if (warp == kDkdvIssuer) {
     tmem_alloc(&tl->tmem_base, 512);
     tmem_relinquish();
   }
@@ -270,7 +273,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
     for (int t = 0; t < 2; ++t) {
       if (!kvalid[t] || kblk[t] >= bp.n_cols) continue;
       const int r_beg = cc[kblk[t]], r_end = cc[kblk[t] + 1];
-      for (int i = r_beg + tid; i < r_end; i += kBwdThreads) {
+      for (int i = r_beg + tid; i < r_end; i += kDkdvThreads) {
         const int r = rows[i];
         if (r < 0 || r >= nqb) continue;
         const int q_pos_last = past + min(r * kBS + kBS, p.sq) - 1;
@@ -293,7 +296,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
   const uint32_t tDP[2] = {tmem + 128, tmem + 192};
   const uint32_t tDV = tmem + 256, tDK = tmem + 384;
 
-  if (n > 0 && warp == kWarpProducer) {
+  if (n > 0 && warp == kDkdvProducer) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       for (int e = 0; e < n; ++e) {
@@ -313,74 +316,73 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
         bulk_load(tl->ld[s][1], bp.delta + row0, kBS * 4, &tl->qdo_full[s]);
       }
     }
-  } else if (n > 0 && warp == kWarpIssueA) {
-    // ------------------------------------------------------------ S^T = K Q^T, dP^T = V dO^T
-    // (the issuer warps run converged so that descriptors stay in uniform registers; only
-    // the tcgen05 instructions sit under the elected lane)
+  } else if (n > 0 && (warp == kDkdvIssuer || warp == kDkdvIssuer + 1)) {
+    // ------------------------------------------------------------ MMA issuers
+    // A tcgen05.mma costs its issuing thread about as long as a 128x64x16 product takes on
+    // the tensor pipe, so the 24 products of an entry are shared by two warps, split by data
+    // path rather than by stage:
+    //   path 0:  S^T_e = K Q_e^T     ->  P^T_e   ->  dV += P^T_e dO_e
+    //   path 1:  dP^T_e = V dO_e^T   ->  dS^T_e  ->  dK += dS^T_e Q_e
+    // Each warp issues the first stage of entries 0 and 1, then per entry e its second stage
+    // followed at once by the first stage of entry e+2, which overwrites the columns the
+    // second stage reads: the tensor pipe executes one thread's products in issue order, so
+    // no completion has to be waited for in between, and every such hazard stays inside one
+    // warp.  The warps run converged (descriptors stay in uniform registers); only the
+    // tcgen05 instructions sit under the elected lane.
     {
+      const int path = warp - kDkdvIssuer;
       const uint32_t idesc_nt = umma_idesc(BF16, 128, kBS, false, false);
-      const uint64_t kdesc = umma_desc_sw128(smem_u32(sK), 16, 1024);
-      const uint64_t vdesc = umma_desc_sw128(smem_u32(sV), 16, 1024);
-      const uint64_t qdesc0 = umma_desc_sw128(smem_u32(sQdo), 16, 1024);
-      bool ok = mbar_wait(&tl->kv_full, 0, wait_status, 302);
-      for (int e = 0; e < n && ok; ++e) {
+      const uint32_t idesc_acc = umma_idesc(BF16, 128, kD, false, true);
+      // first stage: A = resident K (path 0) or V (path 1); B = Q_e or dO_e, K-major
+      const uint64_t adesc = umma_desc_sw128(smem_u32(path ? sV : sK), 16, 1024);
+      const uint64_t bdesc0 = umma_desc_sw128(smem_u32(sQdo) + (path ? kBS * kD * 2 : 0), 16, 1024);
+      // second stage: B = dO_e (path 0) or Q_e (path 1) read MN-major: 16 q rows (2 KB) per
+      // k-step, the two 64-dim halves 8 KB apart
+      const uint64_t mdesc0 = umma_desc_sw128(smem_u32(sQdo) + (path ? 0 : kBS * kD * 2), 8192, 1024);
+      const uint32_t tFirst[2] = {path ? tDP[0] : tST[0], path ? tDP[1] : tST[1]};
+      const uint32_t tAcc = path ? tDK : tDV;
+      auto first_stage = [&](int e) -> bool {
         const int s = e % kQdoStages, bf = e & 1;
-        if (!mbar_wait(&tl->qdo_full[s], (e / kQdoStages) & 1, wait_status, 303)) break;
-        // the buffers still hold P^T / dS^T of entry e-2 until its accumulations finished
-        if (e >= 2 && !mbar_wait(&tl->acc_done[bf], ((e - 2) >> 1) & 1, wait_status, 307)) break;
+        if (!mbar_wait(&tl->qdo_full[s], (e / kQdoStages) & 1, wait_status, 303)) return false;
         tc_fence_after();
-        const uint64_t qd = qdesc0 + (uint64_t)((s * kQdoStageBytes) >> 4);
-        const uint64_t gd = qd + (uint64_t)((kBS * kD * 2) >> 4);
+        const uint64_t bd = bdesc0 + (uint64_t)((s * kQdoStageBytes) >> 4);
         if (elect_one()) {
 #pragma unroll
           for (int i = 0; i < 8; ++i)   // i = c * 4 + kk
-            tc_mma_ss(tST[bf], kdesc + (uint64_t)(((i >> 2) * 16384 + (i & 3) * 32) >> 4),
-                      qd + (uint64_t)(((i >> 2) * 8192 + (i & 3) * 32) >> 4), idesc_nt, i ? 1u : 0u);
-#pragma unroll
-          for (int i = 0; i < 8; ++i)
-            tc_mma_ss(tDP[bf], vdesc + (uint64_t)(((i >> 2) * 16384 + (i & 3) * 32) >> 4),
-                      gd + (uint64_t)(((i >> 2) * 8192 + (i & 3) * 32) >> 4), idesc_nt, i ? 1u : 0u);
+            tc_mma_ss(tFirst[bf], adesc + (uint64_t)(((i >> 2) * 16384 + (i & 3) * 32) >> 4),
+                      bd + (uint64_t)(((i >> 2) * 8192 + (i & 3) * 32) >> 4), idesc_nt, i ? 1u : 0u);
           tc_commit(&tl->sdp_full[bf]);
         }
         __syncwarp();
-      }
-    }
-    __syncwarp();
-  } else if (n > 0 && warp == kWarpIssueB) {
-    // ------------------------------------------------------------ dV += P^T dO, dK += dS^T Q
-    {
-      const uint32_t idesc_acc = umma_idesc(BF16, 128, kD, false, true);
-      // B operands are the dO_r / Q_r tiles read MN-major: 16 q rows (2 KB) per k-step,
-      // the two 64-dim halves 8 KB apart
-      const uint64_t qdesc0 = umma_desc_sw128(smem_u32(sQdo), 8192, 1024);
-      bool ok = true;
-      for (int e = 0; e < n; ++e) {
+        return true;
+      };
+      bool ok = mbar_wait(&tl->kv_full, 0, wait_status, 302);
+      for (int e = 0; e < 2 && e < n && ok; ++e) ok = first_stage(e);
+      for (int e = 0; e < n && ok; ++e) {
         const int s = e % kQdoStages, bf = e & 1;
         if (!mbar_wait(&tl->p_full[bf], (e >> 1) & 1, wait_status, 304)) { ok = false; break; }
         tc_fence_after();
-        const uint64_t qd = qdesc0 + (uint64_t)((s * kQdoStageBytes) >> 4);
-        const uint64_t gd = qd + (uint64_t)((kBS * kD * 2) >> 4);
+        const uint64_t md = mdesc0 + (uint64_t)((s * kQdoStageBytes) >> 4);
         const uint32_t acc0 = e ? 1u : 0u;
         if (elect_one()) {
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            tc_mma_ts(tDV, tST[bf] + packed_col(kk), gd + (uint64_t)((kk * 2048) >> 4), idesc_acc,
-                      kk ? 1u : acc0);
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            tc_mma_ts(tDK, tDP[bf] + packed_col(kk), qd + (uint64_t)((kk * 2048) >> 4), idesc_acc,
+            tc_mma_ts(tAcc, tFirst[bf] + kk * 16, md + (uint64_t)((kk * 2048) >> 4), idesc_acc,
                       kk ? 1u : acc0);
           tc_commit(&tl->qdo_empty[s]);
-          tc_commit(&tl->acc_done[bf]);
         }
         __syncwarp();
+        if (e + 2 < n) ok = first_stage(e + 2);
       }
       if (ok && elect_one()) tc_commit(&tl->all_done);
     }
     __syncwarp();
-  } else if (n > 0) {
-    // ------------------------------------------------------------ P^T / dS^T (warps 0-7)
-    const int quad = warp & 3, half = warp >> 2;   // TMEM lane quadrant, 32-column half
+  } else if (n > 0 && warp < kDkdvEwWarps) {
+    // ------------------------------------------------------------ P^T / dS^T (warps 0-15)
+    // A warp owns a TMEM lane quadrant (32 kv rows) and 16 of the 64 q columns; its packed
+    // 16-bit results overwrite the first 8 of the 16 fp32 columns it has just read, so the
+    // second-stage k-step kk (16 q rows) starts at column 16 kk.
+    const int quad = warp & 3, qtr = warp >> 2;
     const int r_kv = quad * 32 + lane;             // tile row = TMEM lane
     const int t = r_kv >> 6;
     const int kpos = kblk[t] * kBS + (r_kv & 63);
@@ -397,17 +399,23 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
       const int r = ent & 0xffff;
       const bool att = ((ent >> (24 + t)) & 1u) != 0 && kvalid[t];
       // causal: q position past + r*64 + c must be >= kpos  ->  c >= c0
-      const int c0 = p.causal ? kpos - past - r * kBS : 0;
-      const float* lse_s = tl->ld[st][0] + half * 32;
-      const float* del_s = tl->ld[st][1] + half * 32;
-      uint32_t sv[32], dv[32];
-      tmem_ld32(tST[e & 1] + lane_off + half * 32, sv);
-      tmem_ld32(tDP[e & 1] + lane_off + half * 32, dv);
+      const int c0 = (p.causal ? kpos - past - r * kBS : 0) - qtr * 16;
+      const float* lse_s = tl->ld[st][0] + qtr * 16;
+      const float* del_s = tl->ld[st][1] + qtr * 16;
+      uint32_t sv[16], dv[16];
+      tmem_ld16(tST[e & 1] + lane_off + qtr * 16, sv);
+      tmem_ld16(tDP[e & 1] + lane_off + qtr * 16, dv);
       tmem_ld_wait();
-      uint32_t pp[16], ds[16];
+      uint32_t pp[8], ds[8];
       if (att) {
+        // only a diagonal entry has masked columns: they get S = -inf, hence P = dS = 0
+        if (c0 > 0) {
 #pragma unroll
-        for (int c4 = 0; c4 < 8; ++c4) {
+          for (int c = 0; c < 16; ++c)
+            if (c < c0) sv[c] = 0xff800000u;
+        }
+#pragma unroll
+        for (int c4 = 0; c4 < 4; ++c4) {
           const float4 l4 = *reinterpret_cast<const float4*>(lse_s + c4 * 4);
           const float4 d4 = *reinterpret_cast<const float4*>(del_s + c4 * 4);
           const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
@@ -415,9 +423,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
           float pv[4], dsv[4];
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            const int c = half * 32 + c4 * 4 + i;
-            float x = ex2(fmaf(__uint_as_float(sv[c4 * 4 + i]), scale2, -ls[i]));
-            if (c < c0) x = 0.f;
+            const float x = ex2(fmaf(__uint_as_float(sv[c4 * 4 + i]), scale2, -ls[i]));
             pv[i] = x;
             dsv[i] = x * (__uint_as_float(dv[c4 * 4 + i]) - dl[i]);
           }
@@ -428,40 +434,54 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) { pp[i] = 0u; ds[i] = 0u; }
+        for (int i = 0; i < 8; ++i) { pp[i] = 0u; ds[i] = 0u; }
       }
-      // packed results go over the first 16 of the 32 columns this warp has just read
-      tmem_st16(tST[e & 1] + lane_off + half * 32, pp);
-      tmem_st16(tDP[e & 1] + lane_off + half * 32, ds);
+      tmem_st8(tST[e & 1] + lane_off + qtr * 16, pp);
+      tmem_st8(tDP[e & 1] + lane_off + qtr * 16, ds);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tl->p_full[e & 1]);
     }
-    // ---- epilogue: warps 0-3 write dV, warps 4-7 write dK
+    // ---- epilogue: warp = (lane quadrant, dV or dK, 64-column half); every thread scales
+    // its row and stores 128 contiguous bytes straight from registers
     if (alive) alive = mbar_wait(&tl->all_done, 0, wait_status, 306);
     tc_fence_after();
     if (alive) {
-      uint8_t* stage = sQdo + warp * 8192;
-      const int vr[2] = {kvalid[0] ? min(kBS, p.sk - kblk[0] * kBS) : 0,
-                         kvalid[1] ? min(kBS, p.sk - kblk[1] * kBS) : 0};
-      if (half == 0) {
-        uint8_t* const dvb[2] = {
-            reinterpret_cast<uint8_t*>(bp.dv) +
-                ((int64_t)b * bp.dv_sb + (int64_t)hk * bp.dv_sh + (int64_t)kblk[0] * kBS * bp.dv_ss) * 2,
-            reinterpret_cast<uint8_t*>(bp.dv) +
-                ((int64_t)b * bp.dv_sb + (int64_t)hk * bp.dv_sh + (int64_t)kblk[1] * kBS * bp.dv_ss) * 2};
-        store_acc_tile<BF16>(tDV, quad, lane, 1.f, stage, dvb, vr, bp.dv_ss * 2);
-      } else {
-        uint8_t* const dkb[2] = {
-            reinterpret_cast<uint8_t*>(bp.dk) +
-                ((int64_t)b * bp.dk_sb + (int64_t)hk * bp.dk_sh + (int64_t)kblk[0] * kBS * bp.dk_ss) * 2,
-            reinterpret_cast<uint8_t*>(bp.dk) +
-                ((int64_t)b * bp.dk_sb + (int64_t)hk * bp.dk_sh + (int64_t)kblk[1] * kBS * bp.dk_ss) * 2};
-        store_acc_tile<BF16>(tDK, quad, lane, p.sm_scale, stage, dkb, vr, bp.dk_ss * 2);
+      const int is_dk = (warp >> 2) & 1, ch0 = (warp >> 3) * 2;
+      const int kv = kblk[t] * kBS + (r_kv & 63);
+      const bool row_ok = kvalid[t] && kv < p.sk;
+      void* gbase = is_dk ? bp.dk : bp.dv;
+      const int64_t sb = is_dk ? bp.dk_sb : bp.dv_sb, sh = is_dk ? bp.dk_sh : bp.dv_sh,
+                    ss = is_dk ? bp.dk_ss : bp.dv_ss;
+      uint8_t* grow = reinterpret_cast<uint8_t*>(gbase) + ((int64_t)b * sb + (int64_t)hk * sh + (int64_t)kv * ss) * 2;
+      const bool wide = reinterpret_cast<uintptr_t>(gbase) % 16 == 0 && sb % 8 == 0 && sh % 8 == 0 && ss % 8 == 0;
+      const float scale = is_dk ? p.sm_scale : 1.f;
+      const uint32_t tacc = is_dk ? tDK : tDV;
+#pragma unroll
+      for (int ch = ch0; ch < ch0 + 2; ++ch) {
+        uint32_t o[32];
+        tmem_ld32(tacc + lane_off + ch * 32, o);
+        tmem_ld_wait();
+        uint32_t w[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          w[i] = pack2<BF16>(__uint_as_float(o[2 * i]) * scale, __uint_as_float(o[2 * i + 1]) * scale);
+        if (row_ok) {
+          if (wide) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              *reinterpret_cast<uint4*>(grow + ch * 64 + i * 16) =
+                  make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              *reinterpret_cast<uint2*>(grow + ch * 64 + i * 8) = make_uint2(w[2 * i], w[2 * i + 1]);
+          }
+        }
       }
     }
-  } else if (warp == kWarpProducer) {
+  } else if (warp == kDkdvProducer) {
     if (lane == 0) mbar_wait(&tl->kv_full, 0, wait_status, 308);   // let the tiles in flight land
   } else if (warp < 4) {
     // nothing attends these kv blocks: zero gradients
@@ -477,7 +497,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == kWarpIssueA) tmem_dealloc(tmem, 512);
+  if (warp == kDkdvIssuer) tmem_dealloc(tmem, 512);
 }
 
 // ------------------------------------------------------------------ dQ
@@ -799,7 +819,7 @@ int launch_bwd(const bsa_bwd_params* bp, cudaStream_t s) {
     auto kern = bwd_dkdv_sm100_kernel<BF16>;
     BSA_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDkdvSmem));
     dim3 grid(cdiv_i(cdiv_i(p->sk, kBS), 2), p->hkv, p->batch);
-    kern<<<grid, kBwdThreads, kDkdvSmem, s>>>(tmQ, tmK, tmV, tmDO, *bp, status);
+    kern<<<grid, kDkdvThreads, kDkdvSmem, s>>>(tmQ, tmK, tmV, tmDO, *bp, status);
     rc = check_launch("bwd_dkdv_sm100_kernel");
     if (rc) return rc;
   }
