@@ -15,11 +15,14 @@
 // dS^T are written back by tcgen05.st and consumed as TMEM A operands while Q and
 // dO serve as MN-major B operands straight from their TMA tiles.  S/dP are double
 // buffered in TMEM (512 columns, one CTA per SM) so the MMAs of step e+1 overlap
-// the exponentials of step e.  352 threads: eight element-wise warps (a TMEM lane
-// quadrant x a 32-column half each, which halves the latency of the element-wise
-// step), one TMA producer warp and two MMA issuer warps (first-stage products
-// S/dP and second-stage accumulations), because the thread that issues a burst
-// of tcgen05.mma is busy until the tensor pipe has accepted it.  Math: dkernel/ops/sparse_attn_bwd.py:86-170
+// the exponentials of step e.  Element-wise warps own a TMEM lane quadrant and a slice
+// of the columns (16 warps x 16 columns in the dK/dV kernel, 8 x 32 in the dQ kernel);
+// one TMA producer warp; two MMA issuer warps, because a tcgen05.mma costs its issuing
+// thread about as long as a 128x64x16 product takes on the tensor pipe.  The issuers
+// split the products along the data paths, so that a product overwriting columns an
+// earlier product still reads always follows it in one thread's issue order (the tensor
+// pipe executes one thread's products in order) and never waits for a completion.
+// Math: dkernel/ops/sparse_attn_bwd.py:86-170
 // (dK/dV), :329-419 (dQ), :73-80 (delta); P and dS are rounded to the input
 // type before the second-stage products, like the reference (:144,:166,:413).
 #include "ptx.cuh"
@@ -509,8 +512,8 @@ struct DqTail {
   uint64_t q_full;
   uint64_t k_full[kDqKStages], k_empty[kDqKStages];
   uint64_t v_full[kDqVStages], v_empty[kDqVStages];
-  uint64_t sdp_full[2], p_full[2], acc_done[2];
-  uint64_t all_done;
+  uint64_t sdp_full[2], p_full[2];
+  uint64_t cp_done, all_done;
   uint32_t tmem_base;
   int n_list;
   uint32_t bits[2][kMaxBlocks / 32];
@@ -560,13 +563,14 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
 
   if (tid == 0) {
     mbar_init(&tl->q_full, 1);
-    for (int s = 0; s < kDqKStages; ++s) { mbar_init(&tl->k_full[s], 1); mbar_init(&tl->k_empty[s], 1); }
+    // a K stage is read by both issuers (S and dQ), a V stage by one (dP)
+    for (int s = 0; s < kDqKStages; ++s) { mbar_init(&tl->k_full[s], 1); mbar_init(&tl->k_empty[s], 2); }
     for (int s = 0; s < kDqVStages; ++s) { mbar_init(&tl->v_full[s], 1); mbar_init(&tl->v_empty[s], 1); }
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&tl->sdp_full[s], 1);
-      mbar_init(&tl->p_full[s], 256);
-      mbar_init(&tl->acc_done[s], 1);
+      mbar_init(&tl->sdp_full[s], 2);   // S and dP, one commit each
+      mbar_init(&tl->p_full[s], 8);     // one arrival per element-wise warp
     }
+    mbar_init(&tl->cp_done, 1);
     mbar_init(&tl->all_done, 1);
     mbar_fence_init();
     tma_prefetch_desc(&tmQ.map);
@@ -635,13 +639,17 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
       }
     }
   } else if (n > 0 && warp == kWarpIssueA) {
-    // ------------------------------------------------------------ S = Q K^T, dP = dO V^T
+    // ------------------------------------------------------------ S = Q K^T
+    // The products of an entry are shared by two issuer warps along the data paths: this one
+    // copies Q and dO into TMEM and issues S_e; the other issues dP_e = dO V_e^T and
+    // dQ += dS_e K_e, so that dP_{e+2}, which overwrites the columns dS_e sits in, follows
+    // dQ_e in one thread's issue order and needs no completion wait.  The warps run
+    // converged; only the tcgen05 instructions sit under the elected lane.
     {
       const uint32_t idesc_nt = umma_idesc(BF16, 128, kBS, false, false);
       const uint64_t qdesc = umma_desc_sw128(smem_u32(sQ), 16, 1024);
       const uint64_t gdesc = umma_desc_sw128(smem_u32(sDO), 16, 1024);
       const uint64_t kdesc0 = umma_desc_sw128(smem_u32(sKs), 16, 1024);
-      const uint64_t vdesc0 = umma_desc_sw128(smem_u32(sVs), 16, 1024);
       bool ok = mbar_wait(&tl->q_full, 0, wait_status, 313);
       if (ok) {
         tc_fence_after();
@@ -652,14 +660,15 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
             tc_cp_128x256b(tQ + i * 8, qdesc + off);
             tc_cp_128x256b(tDO + i * 8, gdesc + off);
           }
+          tc_commit(&tl->cp_done);
         }
         __syncwarp();
       }
       for (int e = 0; e < n && ok; ++e) {
-        const int sk_ = e % kDqKStages, sv_ = e % kDqVStages, bf = e & 1;
+        const int sk_ = e % kDqKStages, bf = e & 1;
+        // S[bf] is free once the element-wise warps have consumed entry e-2
+        if (e >= 2 && !mbar_wait(&tl->p_full[bf], ((e - 2) >> 1) & 1, wait_status, 319)) break;
         if (!mbar_wait(&tl->k_full[sk_], (e / kDqKStages) & 1, wait_status, 314)) break;
-        // dP[bf] still holds dS of entry e-2 until dQ += dS K of that entry has finished
-        if (e >= 2 && !mbar_wait(&tl->acc_done[bf], ((e - 2) >> 1) & 1, wait_status, 319)) break;
         tc_fence_after();
         const uint64_t kd = kdesc0 + (uint64_t)((sk_ * kTileKV) >> 4);
         if (elect_one()) {
@@ -667,9 +676,24 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
           for (int i = 0; i < 8; ++i)   // i = c * 4 + kk
             tc_mma_ts(tS[bf], tQ + i * 8, kd + (uint64_t)(((i >> 2) * 8192 + (i & 3) * 32) >> 4), idesc_nt,
                       i ? 1u : 0u);
+          tc_commit(&tl->k_empty[sk_]);
+          tc_commit(&tl->sdp_full[bf]);
         }
         __syncwarp();
-        if (!mbar_wait(&tl->v_full[sv_], (e / kDqVStages) & 1, wait_status, 315)) break;
+      }
+    }
+    __syncwarp();
+  } else if (n > 0 && warp == kWarpIssueB) {
+    // ------------------------------------------------------------ dP = dO V^T, dQ += dS K
+    {
+      const uint32_t idesc_nt = umma_idesc(BF16, 128, kBS, false, false);
+      const uint32_t idesc_acc = umma_idesc(BF16, 128, kD, false, true);
+      const uint64_t vdesc0 = umma_desc_sw128(smem_u32(sVs), 16, 1024);
+      // B = K_j read MN-major: 16 kv rows (2 KB) per k-step, 64-dim halves 8 KB apart
+      const uint64_t kdesc0 = umma_desc_sw128(smem_u32(sKs), 8192, 1024);
+      auto issue_dp = [&](int e) -> bool {
+        const int sv_ = e % kDqVStages, bf = e & 1;
+        if (!mbar_wait(&tl->v_full[sv_], (e / kDqVStages) & 1, wait_status, 315)) return false;
         tc_fence_after();
         const uint64_t vd = vdesc0 + (uint64_t)((sv_ * kTileKV) >> 4);
         if (elect_one()) {
@@ -681,19 +705,14 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
           tc_commit(&tl->sdp_full[bf]);
         }
         __syncwarp();
-      }
-    }
-    __syncwarp();
-  } else if (n > 0 && warp == kWarpIssueB) {
-    // ------------------------------------------------------------ dQ += dS K
-    {
-      const uint32_t idesc_acc = umma_idesc(BF16, 128, kD, false, true);
-      // B = K_j read MN-major: 16 kv rows (2 KB) per k-step, 64-dim halves 8 KB apart
-      const uint64_t kdesc0 = umma_desc_sw128(smem_u32(sKs), 8192, 1024);
-      bool ok = true;
-      for (int e = 0; e < n; ++e) {
+        return true;
+      };
+      bool ok = mbar_wait(&tl->cp_done, 0, wait_status, 318);   // dO is in TMEM
+      for (int e = 0; e < 2 && e < n && ok; ++e) ok = issue_dp(e);
+      for (int e = 0; e < n && ok; ++e) {
         const int sk_ = e % kDqKStages, bf = e & 1;
         if (!mbar_wait(&tl->p_full[bf], (e >> 1) & 1, wait_status, 316)) { ok = false; break; }
+        if (!mbar_wait(&tl->k_full[sk_], (e / kDqKStages) & 1, wait_status, 321)) { ok = false; break; }
         tc_fence_after();
         const uint64_t kd = kdesc0 + (uint64_t)((sk_ * kTileKV) >> 4);
         const uint32_t acc0 = e ? 1u : 0u;
@@ -703,9 +722,9 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
             tc_mma_ts(tDQ, tDP[bf] + packed_col(kk), kd + (uint64_t)((kk * 2048) >> 4), idesc_acc,
                       kk ? 1u : acc0);
           tc_commit(&tl->k_empty[sk_]);
-          tc_commit(&tl->acc_done[bf]);
         }
         __syncwarp();
+        if (e + 2 < n) ok = issue_dp(e + 2);
       }
       if (ok && elect_one()) tc_commit(&tl->all_done);
     }
@@ -756,7 +775,8 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
       tmem_st16(tDP[e & 1] + lane_off + half * 32, ds);
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(&tl->p_full[e & 1]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tl->p_full[e & 1]);
     }
     if (alive) alive = mbar_wait(&tl->all_done, 0, wait_status, 318);
     tc_fence_after();
