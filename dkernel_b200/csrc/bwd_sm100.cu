@@ -107,52 +107,69 @@ __device__ __forceinline__ void store_acc_tile(uint32_t tacc, int warp, int lane
 // delta = 0 and +inf, which lets the dK/dV kernel copy a block's 64 values with one bulk copy.
 __host__ __device__ inline int padded_sq(int sq) { return (sq + kBS - 1) / kBS * kBS; }
 
-// One warp per (b, h, i) row of 128 elements: each lane reads 8 bytes of O and dO.
+// Eight lanes per (b, h, i) row of 128 elements (four rows per warp): a lane reads two
+// 16-byte pieces of O and of dO, so that every thread has four independent loads in flight.
+template <bool BF16>
+__device__ __forceinline__ float dot8(const uint4& a, const uint4& g) {
+  float s = 0.f;
+  const uint32_t av[4] = {a.x, a.y, a.z, a.w}, gv[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 x, y;
+    if (BF16) {
+      x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&av[i]));
+      y = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gv[i]));
+    } else {
+      x = __half22float2(*reinterpret_cast<const __half2*>(&av[i]));
+      y = __half22float2(*reinterpret_cast<const __half2*>(&gv[i]));
+    }
+    s = fmaf(x.x, y.x, fmaf(x.y, y.y, s));
+  }
+  return s;
+}
+__device__ __forceinline__ uint4 load16(const uint8_t* p, bool wide) {
+  if (wide) return *reinterpret_cast<const uint4*>(p);
+  const uint2 a = *reinterpret_cast<const uint2*>(p), b = *reinterpret_cast<const uint2*>(p + 8);
+  return make_uint4(a.x, a.y, b.x, b.y);
+}
+
 template <bool BF16>
 __global__ void bwd_delta_vec_kernel(bsa_bwd_params bp) {
   const bsa_fwd_params& p = bp.f;
-  const int lane = threadIdx.x & 31;
+  const int lane = threadIdx.x & 31, sub = lane & 7;
   const int sp = padded_sq(p.sq);
-  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long w = ((long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * 4 + (lane >> 3);
   const long long total = (long long)p.batch * p.hq * sp;
-  if (w >= total) return;
-  const int i = (int)(w % sp);
-  const int h = (int)((w / sp) % p.hq);
-  const int b = (int)(w / ((long long)sp * p.hq));
-  if (i >= p.sq) {
-    if (lane == 0) {
-      bp.delta[w] = 0.f;
-      bp.delta[total + w] = INFINITY;
-    }
-    return;
-  }
-  const uint2 ov = *reinterpret_cast<const uint2*>(
-      reinterpret_cast<const uint8_t*>(p.o) +
-      ((int64_t)b * p.o_sb + (int64_t)h * p.o_sh + (int64_t)i * p.o_ss) * 2 + lane * 8);
-  const uint2 gv = *reinterpret_cast<const uint2*>(
-      reinterpret_cast<const uint8_t*>(bp.d_o) +
-      ((int64_t)b * bp.do_sb + (int64_t)h * bp.do_sh + (int64_t)i * bp.do_ss) * 2 + lane * 8);
-  float s;
-  if (BF16) {
-    const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&ov);
-    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
-    const float2 a0 = __bfloat1622float2(o2[0]), a1 = __bfloat1622float2(o2[1]);
-    const float2 c0 = __bfloat1622float2(g2[0]), c1 = __bfloat1622float2(g2[1]);
-    s = a0.x * c0.x + a0.y * c0.y + a1.x * c1.x + a1.y * c1.y;
-  } else {
-    const __half2* o2 = reinterpret_cast<const __half2*>(&ov);
-    const __half2* g2 = reinterpret_cast<const __half2*>(&gv);
-    const float2 a0 = __half22float2(o2[0]), a1 = __half22float2(o2[1]);
-    const float2 c0 = __half22float2(g2[0]), c1 = __half22float2(g2[1]);
-    s = a0.x * c0.x + a0.y * c0.y + a1.x * c1.x + a1.y * c1.y;
+  const bool live = w < total;
+  const int i = live ? (int)(w % sp) : 0;
+  const int h = live ? (int)((w / sp) % p.hq) : 0;
+  const int b = live ? (int)(w / ((long long)sp * p.hq)) : 0;
+  const bool real = live && i < p.sq;
+  float s = 0.f;
+  if (real) {
+    const bool wide = reinterpret_cast<uintptr_t>(p.o) % 16 == 0 && p.o_ss % 8 == 0 && p.o_sh % 8 == 0 &&
+                      p.o_sb % 8 == 0 && reinterpret_cast<uintptr_t>(bp.d_o) % 16 == 0 &&
+                      bp.do_ss % 8 == 0 && bp.do_sh % 8 == 0 && bp.do_sb % 8 == 0;
+    const uint8_t* op = reinterpret_cast<const uint8_t*>(p.o) +
+                        ((int64_t)b * p.o_sb + (int64_t)h * p.o_sh + (int64_t)i * p.o_ss) * 2 + sub * 16;
+    const uint8_t* gp = reinterpret_cast<const uint8_t*>(bp.d_o) +
+                        ((int64_t)b * bp.do_sb + (int64_t)h * bp.do_sh + (int64_t)i * bp.do_ss) * 2 + sub * 16;
+    const uint4 o0 = load16(op, wide), o1 = load16(op + 128, wide);
+    const uint4 g0 = load16(gp, wide), g1 = load16(gp + 128, wide);
+    s = dot8<BF16>(o0, g0) + dot8<BF16>(o1, g1);
   }
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-  if (lane == 0) {
-    if (bp.d_lse) s -= bp.d_lse[(int64_t)b * p.lse_sb + (int64_t)h * p.lse_sh + i];
-    bp.delta[w] = s;
-    const float l = p.lse[(int64_t)b * p.lse_sb + (int64_t)h * p.lse_sh + i];
-    bp.delta[total + w] = l == -INFINITY ? INFINITY : l * kLog2e;
+  for (int off = 4; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+  if (live && sub == 0) {
+    if (!real) {
+      bp.delta[w] = 0.f;
+      bp.delta[total + w] = INFINITY;
+    } else {
+      if (bp.d_lse) s -= bp.d_lse[(int64_t)b * p.lse_sb + (int64_t)h * p.lse_sh + i];
+      bp.delta[w] = s;
+      const float l = p.lse[(int64_t)b * p.lse_sb + (int64_t)h * p.lse_sh + i];
+      bp.delta[total + w] = l == -INFINITY ? INFINITY : l * kLog2e;
+    }
   }
 }
 
@@ -831,7 +848,7 @@ int launch_bwd(const bsa_bwd_params* bp, cudaStream_t s) {
   if (!status) return BSA_E_CUDA;
   {
     const long long rows = (long long)p->batch * p->hq * padded_sq(p->sq);
-    bwd_delta_vec_kernel<BF16><<<(unsigned)((rows + 7) / 8), 256, 0, s>>>(*bp);
+    bwd_delta_vec_kernel<BF16><<<(unsigned)((rows + 31) / 32), 256, 0, s>>>(*bp);
     rc = check_launch("bwd_delta_vec_kernel");
     if (rc) return rc;
   }
