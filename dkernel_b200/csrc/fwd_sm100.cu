@@ -501,10 +501,10 @@ bool sm100_fwd_supported(const bsa_fwd_params* p, const char** why) {
 }
 
 int sm100_fwd(const bsa_fwd_params* p, cudaStream_t s) {
-  // BSA_FWD_PERSIST=1 selects the persistent kernel (Q resident in TMEM, one CTA per SM)
-  // for comparison runs; the one-tile-per-CTA kernel below is the faster one and the default.
-  static const bool persist = getenv("BSA_FWD_PERSIST") != nullptr;
-  if (persist && sm100_fwd_persist_supported(p)) return sm100_fwd_persist(p, s);
+  // The persistent kernel (two CTAs per SM walking the tile list) serves every call;
+  // BSA_FWD_TILED=1 selects the one-tile-per-CTA kernel below for comparison runs.
+  static const bool tiled = getenv("BSA_FWD_TILED") != nullptr;
+  if (!tiled && sm100_fwd_persist_supported(p)) return sm100_fwd_persist(p, s);
   const bool bf16 = p->dtype == BSA_BF16;
   Tmap4 tmQ, tmK, tmV;
   int rc = make_tmap_4d(&tmQ, p->q, 2, kD, p->sq, p->hq, p->total_q > 0 ? 1 : p->batch, p->q_ss * 2,

@@ -1,23 +1,21 @@
-// Prefill / training forward, persistent version with the Q tile resident in TMEM.
+// Prefill / training forward, persistent version.
 //
-// Same tiling as the first tcgen05 forward (a 128-row query tile = two 64-row
-// halves that share a kv head, union of the halves' CSR rows), but organised around
-// what the profiles of that kernel showed:
-//   * SS-mode Q K^T re-reads the 32 KB Q tile from shared memory for every kv block,
-//     and the shared-memory read path (128 B/clk) was the busiest unit.  Here Q is
-//     copied once per tile into TMEM (tcgen05.cp, 64 columns) and Q K^T runs in TS
-//     mode, so a kv block costs 16 KB (K) + 16 KB (V) of operand reads.
-//   * a third of the run time was per-CTA fixed cost (barrier set-up, list merge,
-//     TMEM allocation, first loads, epilogue).  Here one CTA per SM is launched and
-//     loops over tiles; a planner/producer warp merges the next tile's block list and
-//     prefetches its Q tile and first K/V blocks while the current tile is computed.
-//   * one hand-off between roles costs a few hundred cycles; S is triple buffered in
-//     TMEM and the K/V ring is four blocks deep so that no role waits on another in
-//     steady state.
-// TMEM (512 columns): Q[2] 2x64 | S[3] 3x64 (P overwrites S) | O 128.
-// Warps: 0-7 softmax (lane quadrant x 32-column half; the two warps of a row pair
-// exchange their partial row maxima through shared memory), 8 planner + TMA
-// producer, 9 Q-copy + Q K^T issuer (owns TMEM), 10 P V issuer.
+// Same tiling and per-block pipeline as fwd_sm100.cu (a 128-row query tile = two 64-row
+// halves that share a kv head; S double buffered in TMEM, P overwrites S, O accumulates in
+// TMEM; one converged issuer warp that queues Q K_{j+2} right behind P V_j), but the CTAs
+// are persistent: two per SM are launched and each walks a strided list of tiles.  In the
+// one-tile-per-CTA kernel a quarter of the run time is per-CTA fixed cost (barrier set-up,
+// TMEM allocation, block-list merge, pipeline fill, epilogue).  Here
+//   * a planner warp merges the next tile's block list while the current tile is computed
+//     (two plan slots),
+//   * the producer loads the next tile's Q as soon as the last Q K^T of the current tile has
+//     completed, and its first K/V blocks as soon as their ring slots are free, i.e. while
+//     the current tile's last softmax, P V and epilogue are still running,
+//   * the issuer queues the next tile's first two Q K^T products right behind the last P V;
+//     only the next tile's first P V (which overwrites O) waits for the epilogue.
+// Block counters run across tiles, so buffer indices and barrier phases never restart.
+// Warps (224 threads): 0-3 softmax + epilogue, 4 TMA producer, 5 MMA issuer (owns TMEM),
+// 6 planner.  TMEM: S[2] 2x64 | O 128 columns.
 // Math: dkernel/ops/sparse_attn_fwd.py:90-165, :351-363.
 #include "ptx.cuh"
 
@@ -26,13 +24,11 @@ namespace {
 
 constexpr int kD = 128;
 constexpr int kBS = 64;
-constexpr int kThreadsP = 352;
-constexpr int kWarpProd = 8, kWarpA = 9, kWarpB = 10;
+constexpr int kThreadsP = 224;
+constexpr int kWarpProd = 4, kWarpIssue = 5, kWarpPlan = 6;
 constexpr int kMaxList = 1024;           // kv blocks per sequence (64K tokens)
 constexpr int kQBytes = 128 * kD * 2;    // 32 KB
 constexpr int kTile = kBS * kD * 2;      // 16 KB: one K or V block
-constexpr int kRing = 4;                 // K/V ring depth
-constexpr int kSBuf = 3;                 // S/P buffers in TMEM
 constexpr float kRescaleThreshold = 8.0f;
 enum { kPairHeads = 0, kPairRows = 1 };
 
@@ -47,17 +43,18 @@ struct Plan {
 
 struct TailP {
   uint64_t plan_full[2], plan_free[2];
-  uint64_t q_full[2], q_stage_free[2];
-  uint64_t k_full[kRing], v_full[kRing], k_free[kRing], v_free[kRing];
-  uint64_t qk_done[kSBuf], p_full[kSBuf], pv_done[kSBuf];
-  uint64_t o_free;
+  uint64_t q_full, q_free;
+  uint64_t k_full[2], v_full[2];
+  // qk_done[g&1]: Q K_g^T has completed -> S[g&1] is readable and the K slot is free.
+  // pv_done[g&1]: P V_g has completed   -> the V slot is free (and O holds block g).
+  uint64_t qk_done[2], p_full[2], pv_done[2];
+  uint64_t o_free;           // the epilogue has read O
   uint32_t tmem_base;
   uint32_t bits[2][kMaxList / 32];
-  float xch[2][2][128];      // [iteration parity][column half][row]: partial row maxima / sums
   Plan plan[2];
 };
 
-constexpr size_t kSmemP = 1024 + 2 * kQBytes + kRing * 2 * kTile + sizeof(TailP);
+constexpr size_t kSmemP = 1024 + kQBytes + 2 * 2 * kTile + sizeof(TailP);
 
 __device__ __forceinline__ float ex2(float x) {
   float y;
@@ -74,19 +71,16 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&h);
   }
 }
-// first TMEM column of the packed P values of k-step kk (see the softmax role)
-__device__ __forceinline__ uint32_t packed_col(int kk) { return (uint32_t)((kk >> 1) * 32 + (kk & 1) * 8); }
-__device__ __forceinline__ void pair_bar(int quad) {
-  asm volatile("bar.sync %0, 64;" ::"r"(quad + 1) : "memory");
-}
 
-// item -> plan (executed by the whole producer warp)
+// item -> plan (executed by the whole planner warp)
 __device__ __forceinline__ void build_plan(const bsa_fwd_params& p, int mode, int item, int tiles_x,
                                            int head_items, Plan* pl, uint32_t (*bits)[kMaxList / 32],
                                            int lane) {
-  const int G = p.hq / p.hkv;
   const int tile_rows = mode == kPairHeads ? 64 : 128;
-  // items are ordered long rows first: the tile index decreases with the item index
+  // Items are ordered long rows first (the tile index decreases with the item index), all
+  // heads and batches of a tile index together: a round of the grid then holds tiles of
+  // nearly equal length, which keeps the CTAs' totals level.
+  const int G = p.hq / p.hkv;
   const int per_tile = head_items * (p.total_q > 0 ? 1 : p.batch);
   const int tx = item / per_tile, rem = item % per_tile;
   const int hy = rem % head_items;
@@ -129,6 +123,7 @@ __device__ __forceinline__ void build_plan(const bsa_fwd_params& p, int mode, in
   bits[0][lane] = 0u;
   bits[1][lane] = 0u;
   __syncwarp();
+#pragma unroll
   for (int t = 0; t < 2; ++t) {
     if (!hvalid[t]) continue;
     const int q_first = qblk[t] * kBS;
@@ -137,17 +132,18 @@ __device__ __forceinline__ void build_plan(const bsa_fwd_params& p, int mode, in
     const int hp = pattern_head(head[t], p.h_pat, p.hq, p.hkv);
     const int32_t* cr = p.crow + (int64_t)hp * p.crow_sh;
     const int32_t* cols = p.col + (int64_t)hp * p.col_sh;
-    const int c_beg = cr[row], c_end = cr[row + 1];
+    const int c_beg = __ldg(cr + row), c_end = __ldg(cr + row + 1);
     const int q_pos_last = past + min(q_first + kBS, q_len) - 1;
     for (int i = c_beg + lane; i < c_end; i += 32) {
-      const int blk = cols[i];
+      const int blk = __ldg(cols + i);
       if (blk >= 0 && blk < nkb && !(p.causal && blk * kBS > q_pos_last))
         atomicOr(&bits[t][blk >> 5], 1u << (blk & 31));
     }
   }
   __syncwarp();
+  // bitmaps -> ordered list: scan the word counts, then every lane owns one bit of a word
   const uint32_t u0 = bits[0][lane], u1 = bits[1][lane];
-  uint32_t u = u0 | u1;
+  const uint32_t u = u0 | u1;
   const int cnt = __popc(u);
   int incl = cnt;
 #pragma unroll
@@ -155,11 +151,18 @@ __device__ __forceinline__ void build_plan(const bsa_fwd_params& p, int mode, in
     const int tt = __shfl_up_sync(0xffffffffu, incl, o);
     if (lane >= o) incl += tt;
   }
-  int pos = incl - cnt;
-  while (u) {
-    const int bit = __ffs(u) - 1;
-    u &= u - 1;
-    pl->list[pos++] = (uint16_t)((lane * 32 + bit) | (((u0 >> bit) & 1u) << 14) | (((u1 >> bit) & 1u) << 15));
+  const int base = incl - cnt;
+  uint32_t nonzero = __ballot_sync(0xffffffffu, u != 0u);
+  while (nonzero) {
+    const int w = __ffs(nonzero) - 1;
+    nonzero &= nonzero - 1;
+    const uint32_t uw = __shfl_sync(0xffffffffu, u, w);
+    const uint32_t u0w = __shfl_sync(0xffffffffu, u0, w);
+    const uint32_t u1w = __shfl_sync(0xffffffffu, u1, w);
+    const int bw = __shfl_sync(0xffffffffu, base, w);
+    if ((uw >> lane) & 1u)
+      pl->list[bw + __popc(uw & ((1u << lane) - 1u))] =
+          (uint16_t)((w * 32 + lane) | (((u0w >> lane) & 1u) << 14) | (((u1w >> lane) & 1u) << 15));
   }
   const int n = __shfl_sync(0xffffffffu, incl, 31);
   if (lane == 0) {
@@ -177,260 +180,266 @@ __device__ __forceinline__ void build_plan(const bsa_fwd_params& p, int mode, in
 }
 
 template <bool BF16>
-__global__ void __launch_bounds__(kThreadsP, 1)
+__global__ void __launch_bounds__(kThreadsP, 2)
 fwd_persist_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap4 tmK,
                    const __grid_constant__ Tmap4 tmV, bsa_fwd_params p, int mode, int n_items,
                    int tiles_x, int head_items, int* wait_status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
-  uint8_t* sQ = smem;                       // two staging tiles, 32 KB each
-  uint8_t* sRing = smem + 2 * kQBytes;      // stage s: K at s*32K, V at s*32K + 16K
-  TailP* tl = reinterpret_cast<TailP*>(smem + 2 * kQBytes + kRing * 2 * kTile);
+  uint8_t* sQ = smem;                   // [2 sub-tiles of 64 head dims][128 rows][128 B]
+  uint8_t* sRing = smem + kQBytes;      // slot s: K at s*32K, V at s*32K + 16K
+  TailP* tl = reinterpret_cast<TailP*>(smem + kQBytes + 2 * 2 * kTile);
 
   if (*reinterpret_cast<volatile int*>(wait_status) != 0) return;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
-  if (tid == 0) {
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&tl->plan_full[i], 1);
-      mbar_init(&tl->plan_free[i], 258);
-      mbar_init(&tl->q_full[i], 1);
-      mbar_init(&tl->q_stage_free[i], 1);
+  if (warp == 0) {
+    // seventeen contiguous barriers (plan_full[2], plan_free[2], q_full, q_free, k_full[2],
+    // v_full[2], qk_done[2], p_full[2], pv_done[2], o_free); arrival counts: plan_free = 4
+    // softmax warps + producer + issuer, p_full and o_free = 4 softmax warps, the rest 1
+    if (lane < 17) {
+      const int cnt = (lane == 2 || lane == 3) ? 6 : (lane == 12 || lane == 13 || lane == 16) ? 4 : 1;
+      mbar_init(&tl->plan_full[0] + lane, cnt);
+      mbar_fence_init();
+    } else if (lane == 17) {
+      tma_prefetch_desc(&tmQ.map);
+    } else if (lane == 18) {
+      tma_prefetch_desc(&tmK.map);
+    } else if (lane == 19) {
+      tma_prefetch_desc(&tmV.map);
     }
-    for (int i = 0; i < kRing; ++i) {
-      mbar_init(&tl->k_full[i], 1);
-      mbar_init(&tl->v_full[i], 1);
-      mbar_init(&tl->k_free[i], 1);
-      mbar_init(&tl->v_free[i], 1);
-    }
-    for (int i = 0; i < kSBuf; ++i) {
-      mbar_init(&tl->qk_done[i], 1);
-      mbar_init(&tl->p_full[i], 256);
-      mbar_init(&tl->pv_done[i], 1);
-    }
-    mbar_init(&tl->o_free, 256);
-    mbar_fence_init();
-    tma_prefetch_desc(&tmQ.map);
-    tma_prefetch_desc(&tmK.map);
-    tma_prefetch_desc(&tmV.map);
   }
-  if (warp == kWarpA) {
-    tmem_alloc(&tl->tmem_base, 512);
+  if (warp == kWarpIssue) {
+    tmem_alloc(&tl->tmem_base, 256);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tl->tmem_base;
-  const uint32_t tQ[2] = {tmem, tmem + 64};
-  const uint32_t tS0 = tmem + 128;          // S buffer i at tS0 + 64 i
-  const uint32_t tO = tmem + 320;
+  const uint32_t tS[2] = {tmem, tmem + 64};
+  const uint32_t tO = tmem + 128;
+  // Round r hands items [r * grid, (r + 1) * grid) to the CTAs.
+  // -2: no more rounds; -1: nothing for this CTA in this round.
+  auto item_of = [&](int r) -> int {
+    const long long base = (long long)r * gridDim.x;
+    if (base >= n_items) return -2;
+    const long long it = base + blockIdx.x;
+    return it < n_items ? (int)it : -1;
+  };
 
-  if (warp == kWarpProd) {
-    // ============================================================ planner + TMA producer
-    uint32_t g = 0;
-    int k = 0, ko = 0;   // items seen / items with work (the Q buffers cycle with the latter)
-    for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++k) {
+  if (warp == kWarpPlan) {
+    // ============================================================ planner
+    int k = 0;
+    for (int r = 0;; ++r) {
+      const int item = item_of(r);
+      if (item == -2) break;
+      if (item < 0) continue;
       const int pb = k & 1;
       if (!mbar_wait(&tl->plan_free[pb], ((k >> 1) & 1) ^ 1, wait_status, 401)) break;
-      Plan* pl = &tl->plan[pb];
-      build_plan(p, mode, item, tiles_x, head_items, pl, tl->bits, lane);
-      const int n = pl->n;
-      if (lane == 0) {
-        mbar_arrive(&tl->plan_full[pb]);
-        if (n > 0) {
-          const int qb = ko & 1;
-          bool ok = mbar_wait(&tl->q_stage_free[qb], ((ko >> 1) & 1) ^ 1, wait_status, 402);
-          if (ok) {
-            mbar_expect_tx(&tl->q_full[qb], (uint32_t)(pl->hvalid[0] + pl->hvalid[1]) * (kQBytes / 2));
-            for (int t = 0; t < 2; ++t) {
-              if (!pl->hvalid[t]) continue;
-              for (int c = 0; c < 2; ++c)
-                tma_load_tile(sQ + qb * kQBytes + c * 16384 + t * 8192, &tmQ, &tl->q_full[qb], c * 64,
-                              pl->q_start + pl->qblk[t] * kBS, pl->head[t], pl->b);
-            }
-          }
-          for (int j = 0; j < n && ok; ++j, ++g) {
-            const int st = g % kRing;
-            const uint32_t ph = ((g / kRing) & 1) ^ 1;
-            const int tok = pl->k_start + (int)(pl->list[j] & 0x3fffu) * kBS;
-            uint8_t* kdst = sRing + st * 2 * kTile;
-            if (!mbar_wait(&tl->k_free[st], ph, wait_status, 403)) { ok = false; break; }
-            mbar_expect_tx(&tl->k_full[st], kTile);
-            tma_load_tile(kdst, &tmK, &tl->k_full[st], 0, tok, pl->kvh, pl->b);
-            tma_load_tile(kdst + 8192, &tmK, &tl->k_full[st], 64, tok, pl->kvh, pl->b);
-            if (!mbar_wait(&tl->v_free[st], ph, wait_status, 404)) { ok = false; break; }
-            mbar_expect_tx(&tl->v_full[st], kTile);
-            tma_load_tile(kdst + kTile, &tmV, &tl->v_full[st], 0, tok, pl->kvh, pl->b);
-            tma_load_tile(kdst + kTile + 8192, &tmV, &tl->v_full[st], 64, tok, pl->kvh, pl->b);
-          }
-        }
-      }
-      if (n > 0) ++ko;
-      // every lane needs the advanced block counter and the go/no-go decision
-      g = __shfl_sync(0xffffffffu, g, 0);
-      if (*reinterpret_cast<volatile int*>(wait_status) != 0) break;
+      build_plan(p, mode, item, tiles_x, head_items, &tl->plan[pb], tl->bits, lane);
+      if (lane == 0) mbar_arrive(&tl->plan_full[pb]);
+      ++k;
     }
-  } else if (warp == kWarpA) {
-    // ============================================================ Q copy + Q K^T issuer
+  } else if (warp == kWarpProd) {
+    // ============================================================ TMA producer
     if (lane == 0) {
-      const uint32_t idesc_qk = umma_idesc(BF16, 128, kBS, false, false);
-      const uint64_t qdesc0 = umma_desc_sw128(smem_u32(sQ), 16, 1024);
-      const uint64_t kdesc0 = umma_desc_sw128(smem_u32(sRing), 16, 1024);
-      uint32_t g = 0;
-      int k = 0, ko = 0;
+      uint32_t g = 0;      // kv blocks issued so far, over all tiles
+      int k = 0, ko = 0;   // tiles seen / tiles with work
       bool ok = true;
-      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++k) {
+      for (int r = 0; ok; ++r) {
+        const int item = item_of(r);
+        if (item == -2) break;
+        if (item < 0) continue;
         const int pb = k & 1;
-        if (!mbar_wait(&tl->plan_full[pb], (k >> 1) & 1, wait_status, 411)) break;
-        const int n = tl->plan[pb].n;
+        if (!mbar_wait(&tl->plan_full[pb], (k >> 1) & 1, wait_status, 402)) break;
+        const Plan* pl = &tl->plan[pb];
+        const int n = pl->n;
         if (n > 0) {
-          const int qb = ko & 1;
-          if (!mbar_wait(&tl->q_full[qb], (ko >> 1) & 1, wait_status, 412)) break;
+          // the Q tile may be replaced once the previous tile's last Q K^T has completed
+          if (ko > 0 && !mbar_wait(&tl->q_free, (ko - 1) & 1, wait_status, 403)) break;
+          mbar_expect_tx(&tl->q_full, (uint32_t)(pl->hvalid[0] + pl->hvalid[1]) * (kQBytes / 2));
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            if (!pl->hvalid[t]) continue;
+            for (int c = 0; c < 2; ++c)
+              tma_load_tile(sQ + c * 16384 + t * 8192, &tmQ, &tl->q_full, c * 64,
+                            pl->q_start + pl->qblk[t] * kBS, pl->head[t], pl->b);
+          }
           ++ko;
-          tc_fence_after();
-          const uint64_t qd = qdesc0 + (uint64_t)((qb * kQBytes) >> 4);
-#pragma unroll
-          for (int i = 0; i < 8; ++i)   // k-step i: 16 head dims = 8 packed TMEM columns
-            tc_cp_128x256b(tQ[qb] + i * 8, qd + (uint64_t)(((i >> 2) * 16384 + (i & 3) * 32) >> 4));
-          tc_commit(&tl->q_stage_free[qb]);
           for (int j = 0; j < n; ++j, ++g) {
-            const int st = g % kRing, sb = g % kSBuf;
-            if (!mbar_wait(&tl->k_full[st], (g / kRing) & 1, wait_status, 413)) { ok = false; break; }
-            // S[sb] is also P[sb]: the P V product that used it three blocks ago must be done
-            if (!mbar_wait(&tl->pv_done[sb], ((g / kSBuf) & 1) ^ 1, wait_status, 414)) { ok = false; break; }
-            tc_fence_after();
-            const uint64_t kd = kdesc0 + (uint64_t)((st * 2 * kTile) >> 4);
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-              tc_mma_ts(tS0 + sb * 64, tQ[qb] + i * 8,
-                        kd + (uint64_t)(((i >> 2) * 8192 + (i & 3) * 32) >> 4), idesc_qk, i ? 1u : 0u);
-            tc_commit(&tl->k_free[st]);
-            tc_commit(&tl->qk_done[sb]);
+            const int s = g & 1;
+            const uint32_t ph = ((g >> 1) & 1) ^ 1;   // completion of the slot's previous user
+            const int tok = pl->k_start + (int)(pl->list[j] & 0x3fffu) * kBS;
+            uint8_t* kdst = sRing + s * 2 * kTile;
+            if (!mbar_wait(&tl->qk_done[s], ph, wait_status, 404)) { ok = false; break; }
+            mbar_expect_tx(&tl->k_full[s], kTile);
+            tma_load_tile(kdst, &tmK, &tl->k_full[s], 0, tok, pl->kvh, pl->b);
+            tma_load_tile(kdst + 8192, &tmK, &tl->k_full[s], 64, tok, pl->kvh, pl->b);
+            if (!mbar_wait(&tl->pv_done[s], ph, wait_status, 405)) { ok = false; break; }
+            mbar_expect_tx(&tl->v_full[s], kTile);
+            tma_load_tile(kdst + kTile, &tmV, &tl->v_full[s], 0, tok, pl->kvh, pl->b);
+            tma_load_tile(kdst + kTile + 8192, &tmV, &tl->v_full[s], 64, tok, pl->kvh, pl->b);
           }
         }
-        mbar_arrive(&tl->plan_free[pb]);
-      }
-    }
-    __syncwarp();
-  } else if (warp == kWarpB) {
-    // ============================================================ P V issuer
-    if (lane == 0) {
-      const uint32_t idesc_pv = umma_idesc(BF16, 128, kD, false, true);
-      // V tile read MN-major: 16 tokens (2 KB) per k-step, the two 64-dim halves 8 KB apart
-      const uint64_t vdesc0 = umma_desc_sw128(smem_u32(sRing) + kTile, 8192, 1024);
-      uint32_t g = 0;
-      int k = 0, ko = 0;
-      bool ok = true;
-      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++k) {
-        const int pb = k & 1;
-        if (!mbar_wait(&tl->plan_full[pb], (k >> 1) & 1, wait_status, 421)) break;
-        const int n = tl->plan[pb].n;
-        for (int j = 0; j < n; ++j, ++g) {
-          const int st = g % kRing, sb = g % kSBuf;
-          if (!mbar_wait(&tl->p_full[sb], (g / kSBuf) & 1, wait_status, 422)) { ok = false; break; }
-          if (!mbar_wait(&tl->v_full[st], (g / kRing) & 1, wait_status, 423)) { ok = false; break; }
-          // the previous tile's epilogue must have read O before it is overwritten
-          if (j == 0 && !mbar_wait(&tl->o_free, (ko & 1) ^ 1, wait_status, 424)) { ok = false; break; }
-          tc_fence_after();
-          const uint64_t vd = vdesc0 + (uint64_t)((st * 2 * kTile) >> 4);
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            tc_mma_ts(tO, tS0 + sb * 64 + packed_col(kk), vd + (uint64_t)((kk * 2048) >> 4), idesc_pv,
-                      (j | kk) ? 1u : 0u);
-          tc_commit(&tl->v_free[st]);
-          tc_commit(&tl->pv_done[sb]);
-        }
-        if (n > 0) ++ko;
         if (ok) mbar_arrive(&tl->plan_free[pb]);
+        ++k;
       }
     }
-    __syncwarp();
-  } else {
-    // ============================================================ softmax (warps 0-7)
-    const int quad = warp & 3, half = warp >> 2;
-    const int r = quad * 32 + lane;       // tile row = TMEM lane
-    const int t = r >> 6, rr = r & 63;
-    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
-    const float scale2 = p.sm_scale * kLog2e;
+  } else if (warp == kWarpIssue) {
+    // ============================================================ MMA issuer
+    // The whole warp runs the loop converged, so that descriptors and addresses stay in
+    // uniform registers; only the tcgen05 instructions sit under the elected lane.  Per
+    // block the order is P V_g, Q K_{g+2}: the tensor pipe runs one thread's products in
+    // issue order, so the product that overwrites P_g's columns needs no completion wait.
+    const uint32_t idesc_qk = umma_idesc(BF16, 128, kBS, false, false);
+    const uint32_t idesc_pv = umma_idesc(BF16, 128, kD, false, true);
+    const uint64_t qdesc0 = umma_desc_sw128(smem_u32(sQ), 16, 1024);
+    const uint64_t kdesc0 = umma_desc_sw128(smem_u32(sRing), 16, 1024);
+    // V tile read MN-major: 16 tokens (2 KB) per k-step, the two 64-dim halves 8 KB apart
+    const uint64_t vdesc0 = umma_desc_sw128(smem_u32(sRing) + kTile, 8192, 1024);
     uint32_t g = 0;
-    uint32_t obs = 0;   // P V products whose completion this thread has observed (in order)
-    // A parity wait tolerates a lag of one phase per barrier, so completions are
-    // observed late (two blocks behind) instead of right before publishing P: the
-    // softmax never stalls on the product it has just enabled.
-    auto observe_pv = [&](uint32_t upto) -> bool {
-      while (obs < upto) {
-        if (!mbar_wait(&tl->pv_done[obs % kSBuf], (obs / kSBuf) & 1, wait_status, 433)) return false;
-        ++obs;
+    int k = 0, ko = 0;
+    bool ok = true;
+    // Q K^T of block gq (gq counts over all tiles); `last` marks the tile's last block
+    auto issue_qk = [&](uint32_t gq, bool last) -> bool {
+      const int s = gq & 1;
+      if (!mbar_wait(&tl->k_full[s], (gq >> 1) & 1, wait_status, 411)) return false;
+      tc_fence_after();
+      const uint64_t db0 = kdesc0 + (uint64_t)((s * 2 * kTile) >> 4);
+      if (elect_one()) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)   // i = c * 4 + kk: sub-tile c (8 KB apart for K, 16 KB for Q), k-step kk
+          tc_mma_ss(tS[s], qdesc0 + (uint64_t)(((i >> 2) * 16384 + (i & 3) * 32) >> 4),
+                    db0 + (uint64_t)(((i >> 2) * 8192 + (i & 3) * 32) >> 4), idesc_qk, i ? 1u : 0u);
+        tc_commit(&tl->qk_done[s]);
+        if (last) tc_commit(&tl->q_free);
+      }
+      __syncwarp();
+      return true;
+    };
+    for (int r = 0; ok; ++r) {
+      const int item = item_of(r);
+      if (item == -2) break;
+      if (item < 0) continue;
+      const int pb = k & 1;
+      if (!mbar_wait(&tl->plan_full[pb], (k >> 1) & 1, wait_status, 412)) break;
+      const int n = tl->plan[pb].n;
+      if (n > 0) {
+        if (!mbar_wait(&tl->q_full, ko & 1, wait_status, 413)) break;
+        for (int j = 0; j < 2 && j < n && ok; ++j) ok = issue_qk(g + j, j == n - 1);
+        for (int j = 0; j < n && ok; ++j, ++g) {
+          const int s = g & 1;
+          if (!mbar_wait(&tl->p_full[s], (g >> 1) & 1, wait_status, 414)) { ok = false; break; }
+          if (!mbar_wait(&tl->v_full[s], (g >> 1) & 1, wait_status, 415)) { ok = false; break; }
+          // the previous tile's epilogue must have read O before it is overwritten
+          if (j == 0 && ko > 0 && !mbar_wait(&tl->o_free, (ko - 1) & 1, wait_status, 416)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t dv0 = vdesc0 + (uint64_t)((s * 2 * kTile) >> 4);
+          const uint32_t acc0 = j ? 1u : 0u;
+          if (elect_one()) {
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)
+              tc_mma_ts(tO, tS[s] + kk * 8, dv0 + (uint64_t)((kk * 2048) >> 4), idesc_pv, kk ? 1u : acc0);
+            tc_commit(&tl->pv_done[s]);
+          }
+          __syncwarp();
+          if (j + 2 < n) ok = issue_qk(g + 2, j + 2 == n - 1);
+        }
+        ++ko;
+      }
+      if (ok && elect_one()) mbar_arrive(&tl->plan_free[pb]);
+      __syncwarp();
+      ++k;
+    }
+  } else if (warp < 4) {
+    // ============================================================ softmax + epilogue (warps 0-3)
+    const int r = tid;            // tile row = TMEM lane
+    const int t = r >> 6;         // half
+    const int rr = r & 63;
+    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+    const float scale2 = p.sm_scale * kLog2e;
+    const bool wide = reinterpret_cast<uintptr_t>(p.o) % 16 == 0 && p.o_ss % 8 == 0 &&
+                      p.o_sh % 8 == 0 && p.o_sb % 8 == 0;   // rows start on 16-byte boundaries
+    uint32_t g = 0;      // kv blocks processed so far, over all tiles
+    uint32_t seen = 0;   // P V completions observed so far (in order, one barrier phase at a time)
+    // A parity wait only means something while the waiter is at most one phase behind, so the
+    // completions are observed in order.  Q K_g^T was issued after P V_{g-2}, so observing up
+    // to g-2 never blocks; P V_{g-1} is only waited for when the accumulator has to be rescaled.
+    auto observe_pv = [&](uint32_t upto) {   // P V_0 .. P V_{upto-1} have completed
+      while (seen < upto) {
+        if (!mbar_wait(&tl->pv_done[seen & 1], (seen >> 1) & 1, wait_status, 421)) return false;
+        ++seen;
       }
       return true;
     };
     int k = 0;
     bool alive = true;
-    for (int item = blockIdx.x; item < n_items && alive; item += gridDim.x, ++k) {
+    for (int r = 0; alive; ++r) {
+      const int item = item_of(r);
+      if (item == -2) break;
+      if (item < 0) continue;
       const int pb = k & 1;
-      if (!mbar_wait(&tl->plan_full[pb], (k >> 1) & 1, wait_status, 431)) break;
+      if (!mbar_wait(&tl->plan_full[pb], (k >> 1) & 1, wait_status, 422)) break;
       const Plan* pl = &tl->plan[pb];
       const int n = pl->n;
       const int hvalid = pl->hvalid[t], head = pl->head[t];
-      const int q_row = pl->qblk[t] * kBS + rr;
+      const int q_row = pl->qblk[t] * kBS + rr;   // row inside the sequence
       const int q_len = pl->q_len, k_len = pl->k_len, b = pl->b;
       const int qpos = pl->past + q_row;
       const bool row_ok = hvalid && q_row < q_len;
       uint8_t* orow = reinterpret_cast<uint8_t*>(p.o) +
-                      ((int64_t)b * p.o_sb + (int64_t)head * p.o_sh + (int64_t)(pl->q_start + q_row) * p.o_ss) * 2 +
-                      half * 128;
+                      ((int64_t)b * p.o_sb + (int64_t)head * p.o_sh + (int64_t)(pl->q_start + q_row) * p.o_ss) * 2;
       float* lse_ptr = p.lse ? p.lse + (int64_t)b * p.lse_sb + (int64_t)head * p.lse_sh + pl->q_start + q_row
                              : nullptr;
       if (n == 0) {
         if (pl->valid && row_ok) {   // a tile that attends nothing: zero rows, LSE = -inf
-#pragma unroll
-          for (int i = 0; i < 8; ++i) reinterpret_cast<uint4*>(orow)[i] = make_uint4(0u, 0u, 0u, 0u);
-          if (half == 0 && lse_ptr) *lse_ptr = -INFINITY;
+          for (int i = 0; i < 32; ++i) reinterpret_cast<uint2*>(orow)[i] = make_uint2(0u, 0u);
+          if (lse_ptr) *lse_ptr = -INFINITY;
         }
-        mbar_arrive(&tl->plan_free[pb]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tl->plan_free[pb]);
+        ++k;
         continue;
       }
       float m_used = -INFINITY, l = 0.f;
       for (int j = 0; j < n; ++j, ++g) {
-        const int sb = g % kSBuf;
-        const uint32_t tS = tS0 + sb * 64;
-        if (!mbar_wait(&tl->qk_done[sb], (g / kSBuf) & 1, wait_status, 432)) { alive = false; break; }
+        const int s = g & 1;
+        if (!mbar_wait(&tl->qk_done[s], (g >> 1) & 1, wait_status, 423)) { alive = false; break; }
         tc_fence_after();
-        uint32_t sv[32];
-        tmem_ld32(tS + lane_off + half * 32, sv);
+        uint32_t sv[64];
+        tmem_ld32(tS[s] + lane_off, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
+        tmem_ld32(tS[s] + lane_off + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
         tmem_ld_wait();
         const uint32_t ent = pl->list[j];
         const int kbase = (int)(ent & 0x3fffu) * kBS;
         const bool att = ((ent >> (14 + t)) & 1u) != 0 && hvalid;
-        // allowed columns form a prefix: kpos < k_len and (causal) kpos <= qpos
+        // Allowed columns of this block form a prefix: kpos < k_len and, when causal,
+        // kpos <= qpos.  Raw logits are compared (sm_scale > 0); the scale is folded
+        // into the exponent's FMA.
         float mx = -INFINITY;
         if (att) {
           int lim = k_len - kbase;
           if (p.causal) lim = min(lim, qpos - kbase + 1);
-          lim -= half * 32;
-          if (lim < 32) {
+          if (lim < kBS) {
 #pragma unroll
-            for (int c = 0; c < 32; ++c)
+            for (int c = 0; c < 64; ++c)
               if (c >= lim) sv[c] = 0xff800000u;  // -inf
           }
-          float m4[4];
+          float m8[8];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) m4[i] = __uint_as_float(sv[i]);
+          for (int i = 0; i < 8; ++i) m8[i] = __uint_as_float(sv[i]);
 #pragma unroll
-          for (int c = 4; c < 32; c += 4)
+          for (int c = 8; c < 64; c += 8)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) m4[i] = fmaxf(m4[i], __uint_as_float(sv[c + i]));
-          mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * scale2;
+            for (int i = 0; i < 8; ++i) m8[i] = fmaxf(m8[i], __uint_as_float(sv[c + i]));
+          mx = fmaxf(fmaxf(fmaxf(m8[0], m8[1]), fmaxf(m8[2], m8[3])),
+                     fmaxf(fmaxf(m8[4], m8[5]), fmaxf(m8[6], m8[7]))) * scale2;
         }
-        // combine with the warp that owns the other 32 columns of the same rows
-        tl->xch[j & 1][half][r] = mx;
-        pair_bar(quad);
-        mx = fmaxf(mx, tl->xch[j & 1][half ^ 1][r]);
         float alpha = 1.f;
         bool need = false;
-        if (mx != -INFINITY) {
+        if (att && mx != -INFINITY) {
           if (m_used == -INFINITY) {
             m_used = mx;   // first attended block of this row: its O row is still exactly 0
           } else if (mx > m_used + kRescaleThreshold) {
@@ -441,12 +450,12 @@ fwd_persist_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tm
           }
         }
         const bool any = __any_sync(0xffffffffu, need);
-        uint32_t pk[16];
+        uint32_t pk[32];
         if (att && m_used != -INFINITY) {
           float sum[4] = {0.f, 0.f, 0.f, 0.f};
           const float neg_m = -m_used;
 #pragma unroll
-          for (int c = 0; c < 16; ++c) {
+          for (int c = 0; c < 32; ++c) {
             const float p0 = ex2(fmaf(__uint_as_float(sv[2 * c]), scale2, neg_m));
             const float p1 = ex2(fmaf(__uint_as_float(sv[2 * c + 1]), scale2, neg_m));
             sum[(2 * c) & 3] += p0;
@@ -456,75 +465,81 @@ fwd_persist_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tm
           l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
         } else {
 #pragma unroll
-          for (int c = 0; c < 16; ++c) pk[c] = 0u;
+          for (int c = 0; c < 32; ++c) pk[c] = 0u;
         }
-        // packed P over the first 16 of the 32 columns this warp has just read
-        tmem_st16(tS + lane_off + half * 32, pk);
-        if (g >= 2 && !observe_pv(g - 1)) { alive = false; break; }
+        tmem_st32(tS[s] + lane_off, pk);
+        // g >= 1: blocks up to g-2 (count g-1); with a rescale also block g-1 (count g)
+        if (!observe_pv(any ? g : (g > 0 ? g - 1 : 0))) { alive = false; break; }
         if (any && j > 0) {
-          // rescale this warp's 64 accumulator columns for the rows whose maximum moved:
-          // the previous block's P V must have landed first
-          if (!observe_pv(g)) { alive = false; break; }
+          // rescale the accumulator rows whose maximum moved (P V_{g-1} has landed)
           tc_fence_after();
 #pragma unroll
-          for (int ch = 0; ch < 2; ++ch) {
+          for (int ch = 0; ch < 4; ++ch) {
             uint32_t o[32];
-            tmem_ld32(tO + lane_off + half * 64 + ch * 32, o);
+            tmem_ld32(tO + lane_off + ch * 32, o);
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_st32(tO + lane_off + half * 64 + ch * 32, o);
+            tmem_st32(tO + lane_off + ch * 32, o);
           }
         }
+        // tcgen05.wait::st is warp-wide: after it every lane's P row is in TMEM, so one
+        // arrival per warp publishes them
         tmem_st_wait();
         tc_fence_before();
-        mbar_arrive(&tl->p_full[sb]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tl->p_full[s]);
       }
       if (!alive) break;
-      // ---- epilogue of the tile: all its P V products must have completed
+      // ---- epilogue of the tile: all its P V products must have completed; each thread
+      // normalises its own row and stores it straight from registers
       if (!observe_pv(g)) { alive = false; break; }
       tc_fence_after();
-      // total row sum = this warp's columns + the partner's
-      tl->xch[n & 1][half][r] = l;
-      pair_bar(quad);
-      const float l_tot = l + tl->xch[n & 1][half ^ 1][r];
-      const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
+      const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
-      for (int ch = 0; ch < 2; ++ch) {
+      for (int ch = 0; ch < 4; ++ch) {
         uint32_t o[32];
-        tmem_ld32(tO + lane_off + half * 64 + ch * 32, o);
+        tmem_ld32(tO + lane_off + ch * 32, o);
         tmem_ld_wait();
-        if (row_ok) {
+        uint32_t w[16];
 #pragma unroll
-          for (int c4 = 0; c4 < 4; ++c4) {
-            uint4 w;
-            w.x = pack2<BF16>(__uint_as_float(o[c4 * 8 + 0]) * inv, __uint_as_float(o[c4 * 8 + 1]) * inv);
-            w.y = pack2<BF16>(__uint_as_float(o[c4 * 8 + 2]) * inv, __uint_as_float(o[c4 * 8 + 3]) * inv);
-            w.z = pack2<BF16>(__uint_as_float(o[c4 * 8 + 4]) * inv, __uint_as_float(o[c4 * 8 + 5]) * inv);
-            w.w = pack2<BF16>(__uint_as_float(o[c4 * 8 + 6]) * inv, __uint_as_float(o[c4 * 8 + 7]) * inv);
-            reinterpret_cast<uint4*>(orow)[ch * 4 + c4] = w;
+        for (int i = 0; i < 16; ++i)
+          w[i] = pack2<BF16>(__uint_as_float(o[2 * i]) * inv, __uint_as_float(o[2 * i + 1]) * inv);
+        if (ch == 3) {
+          // O has been read: the next tile's first P V may overwrite it
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tl->o_free);
+        }
+        if (row_ok) {
+          if (wide) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              *reinterpret_cast<uint4*>(orow + ch * 64 + i * 16) =
+                  make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              *reinterpret_cast<uint2*>(orow + ch * 64 + i * 8) = make_uint2(w[2 * i], w[2 * i + 1]);
           }
         }
       }
-      tc_fence_before();
-      mbar_arrive(&tl->o_free);
-      if (half == 0 && row_ok && lse_ptr) *lse_ptr = l_tot > 0.f ? (m_used + log2f(l_tot)) * kLn2 : -INFINITY;
-      // the exchange slots are reused by the next tile: both partners must have read them
-      pair_bar(quad);
-      mbar_arrive(&tl->plan_free[pb]);
+      if (row_ok && lse_ptr) *lse_ptr = l > 0.f ? (m_used + log2f(l)) * kLn2 : -INFINITY;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tl->plan_free[pb]);
+      ++k;
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == kWarpA) tmem_dealloc(tmem, 512);
+  if (warp == kWarpIssue) tmem_dealloc(tmem, 256);
 }
 
 }  // namespace
 
 bool sm100_fwd_persist_supported(const bsa_fwd_params* p) {
-  // output rows are written with 16-byte stores
-  return reinterpret_cast<uintptr_t>(p->o) % 16 == 0 && p->o_ss % 8 == 0 && p->o_sh % 8 == 0 &&
-         p->o_sb % 8 == 0;
+  (void)p;
+  return true;   // everything the tiled tcgen05 forward accepts
 }
 
 int sm100_fwd_persist(const bsa_fwd_params* p, cudaStream_t s) {
@@ -558,7 +573,7 @@ int sm100_fwd_persist(const bsa_fwd_params* p, cudaStream_t s) {
   int dev = 0, sms = 148;
   BSA_CHECK_CUDA(cudaGetDevice(&dev));
   BSA_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  const int grid = n_items < sms ? n_items : sms;
+  const int grid = n_items < 2 * sms ? n_items : 2 * sms;   // two resident CTAs per SM
   int* status = wait_status_ptr();
   if (!status) return BSA_E_CUDA;
   if (bf16) {
