@@ -280,14 +280,15 @@ def run_prefill(args, world, rank):
                      "traffic": TRAFFIC.get("prefill"), "peak_source": peaks["source"] + " (burst)",
                      "frac_of_sustained": kernel_tflops / peaks["tflops_sustained"] if peaks["tflops_sustained"] else None,
                      "frac_of_nominal_2250": kernel_tflops / NOMINAL_BF16_TFLOPS,
-                     "kernel": "fwd_sm100_kernel<bf16>", "kernel_ms": ms},
+                     "kernel": "fwd_persist_kernel<bf16>", "kernel_ms": ms},
     }
     return line
 
 
-# DRAM bytes per launch of the dominant kernel from the committed ncu captures
-# (profiles/*.md); None = not captured.
-TRAFFIC = {"prefill": None, "train": None, "decode": None, "varlen": None}
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel from
+# the committed ncu captures (profiles/*.md), one GPU, the full workload; None = not captured.
+# train: dK/dV 793.6 MB + dQ 664.9 MB (the roofline line covers both backward kernels).
+TRAFFIC = {"prefill": 682.5e6, "train": 793.6e6 + 664.9e6, "decode": 406.3e6, "varlen": None}
 
 
 def run_train(args, world, rank):
@@ -336,7 +337,7 @@ def run_train(args, world, rank):
         "gpu_launches": args.steps * 4, "clocks": clocks,
         "roofline": {"bound": "tensor", "achieved": bwd_tflops, "peak": peaks["tflops"], "unit": "TFLOP/s",
                      "frac": bwd_tflops / peaks["tflops"], "traffic": TRAFFIC.get("train"),
-                     "peak_source": peaks["source"] + " (burst)", "kernel": "backward (dq + dkdv)"},
+                     "peak_source": peaks["source"] + " (burst)", "kernel": "bwd_dkdv_sm100_kernel + bwd_dq_sm100_kernel (+ delta pre-pass)"},
     }
 
 
@@ -502,7 +503,7 @@ def run_varlen(args, world, rank):
         "gpu_launches": args.steps, "clocks": clocks,
         "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["tflops"], "unit": "TFLOP/s",
                      "frac": tf / peaks["tflops"], "traffic": TRAFFIC.get("varlen"),
-                     "peak_source": peaks["source"] + " (burst)", "kernel": "fwd_sm100_kernel<bf16>"},
+                     "peak_source": peaks["source"] + " (burst)", "kernel": "fwd_persist_kernel<bf16>"},
     }
 
 
