@@ -387,11 +387,31 @@ def run_decode(args, world, rank):
             it[0] += 1
             with torch.no_grad():
                 attn(q, k, v, sm_scale=scale, left_paddings=left, return_lse=True)
-        step, launch_mode = eager_step, "eager module calls"
-        if not args.no_graph and args.steps % nbuf == 0:
-            # A decode step is two short kernels: the module call is captured once (one call per
-            # K/V buffer set) and replayed, as a serving loop would, so that the step is not bound
-            # by the Python launch path.
+        launches = 2
+    else:
+        lo, hi = kv_shard_ranges(lens, rank, world, bs)
+        n = (hi - lo).clamp_min(0)
+        cap = int(((S // world + bs - 1) // bs + 1) * bs)
+        bufs = []
+        for i in range(nbuf):
+            ks = torch.randn((B, cap, Hkv, D), generator=g).to(torch.bfloat16).cuda()
+            vs = torch.randn((B, cap, Hkv, D), generator=g).to(torch.bfloat16).cuda()
+            bufs.append((ks, vs))
+        n_d, lo_d, len_d = (t.to(torch.int32).cuda() for t in (n, lo, lens))
+        it = [0]
+
+        def eager_step():
+            ks, vs = bufs[it[0] % nbuf]
+            it[0] += 1
+            with torch.no_grad():
+                sharded_decode(attn, q, ks, vs, n_d, lo_d, len_d, scale)
+        launches = 4   # decode, split merge, NCCL all-gather, partition merge
+    step, launch_mode = eager_step, "eager calls"
+    if not args.no_graph and args.steps % nbuf == 0:
+        # A decode step is a few short kernels (and, sharded, one small all-gather): the call is
+        # captured once per K/V buffer set and replayed, as a serving loop would, so that the step
+        # is not bound by the Python launch path.
+        try:
             graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
             with torch.cuda.stream(side):
                 for _ in range(nbuf):
@@ -407,26 +427,16 @@ def run_decode(args, world, rank):
                     graph.replay()
                 it[0] += 1
             it[0] = 0
-            launch_mode = f"CUDA graph of {nbuf} module calls (one per K/V buffer set), replayed"
-        launches = 2
-    else:
-        lo, hi = kv_shard_ranges(lens, rank, world, bs)
-        n = (hi - lo).clamp_min(0)
-        cap = int(((S // world + bs - 1) // bs + 1) * bs)
-        bufs = []
-        for i in range(nbuf):
-            ks = torch.randn((B, cap, Hkv, D), generator=g).to(torch.bfloat16).cuda()
-            vs = torch.randn((B, cap, Hkv, D), generator=g).to(torch.bfloat16).cuda()
-            bufs.append((ks, vs))
-        n_d, lo_d, len_d = n.cuda(), lo.cuda(), lens.cuda()
-        it = [0]
-
-        def step():
-            ks, vs = bufs[it[0] % nbuf]
-            it[0] += 1
-            with torch.no_grad():
-                sharded_decode(attn, q, ks, vs, n_d, lo_d, len_d, scale)
-        launches = 4
+            launch_mode = f"CUDA graph of {nbuf} calls (one per K/V buffer set), replayed"
+        except Exception as e:   # capture unsupported in this setup: time the eager calls
+            launch_mode = f"eager calls (graph capture failed: {type(e).__name__})"
+            step = eager_step
+        if world > 1:
+            # every rank must make the same choice, or the collectives would not match up
+            flag = torch.tensor([1.0 if step is not eager_step else 0.0], device="cuda")
+            torch.distributed.all_reduce(flag, op=torch.distributed.ReduceOp.MIN)
+            if flag.item() == 0.0 and step is not eager_step:
+                step, launch_mode = eager_step, "eager calls (graph capture failed on another rank)"
     sampler = ClockSampler(torch.cuda.current_device())
     sampler.start()
     ms = max_over_ranks(time_steps(step, args.steps, args.warmup, world), world)
@@ -443,7 +453,7 @@ def run_decode(args, world, rank):
                    "parallelism": "single GPU" if world == 1 else
                    f"KV sequence sharded over {world} GPUs, one NCCL all-gather of (O,LSE) + fused merge",
                    "algorithmic_bytes_per_step": bytes_alg,
-                   "launch": launch_mode if world == 1 else "eager module calls",
+                   "launch": launch_mode,
                    "l2": f"{nbuf} K/V buffer sets rotated ({nbuf}x{2 * B * S * Hkv * D * 2 / world / 2**20:.0f} MiB)"},
         "gpu_launches": args.steps * launches, "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm"], "unit": "GB/s",

@@ -397,7 +397,7 @@ template <typename Tin, typename Tout>
 __global__ void merge_kernel(const Tin* __restrict__ o_parts, const float* __restrict__ lse_parts,
                              int P, int64_t rows, int d, int64_t pso, int64_t rso, int64_t psl,
                              int64_t rsl, Tout* __restrict__ o, int64_t ors,
-                             float* __restrict__ lse) {
+                             float* __restrict__ lse, int64_t lrs) {
   const int64_t total = rows * d;
   // Launched as a programmatic dependent of the decode kernel: the blocks may already be
   // resident while that grid drains, and wait here until its partials are visible.
@@ -416,14 +416,14 @@ __global__ void merge_kernel(const Tin* __restrict__ o_parts, const float* __res
       if (w != 0.f) acc += w * Elem<Tin>::to_f(o_parts[q * pso + r * rso + c]);
     }
     o[r * ors + c] = Elem<Tout>::from_f(den > 0.f ? acc / den : 0.f);
-    if (c == 0 && lse) lse[r] = den > 0.f ? ms + __logf(den) : -INFINITY;
+    if (c == 0 && lse) lse[r * lrs] = den > 0.f ? ms + __logf(den) : -INFINITY;
   }
 }
 
 template <typename Tin, typename Tout>
 int launch_merge(const void* o_parts, const float* lse_parts, int P, int64_t rows, int d,
                  int64_t pso, int64_t rso, int64_t psl, int64_t rsl, void* o, int64_t ors,
-                 float* lse, cudaStream_t s) {
+                 float* lse, cudaStream_t s, int64_t lrs = 1) {
   const int64_t total = rows * d;
   if (total == 0) return BSA_OK;
   int64_t blocks = (total + 255) / 256;
@@ -439,7 +439,7 @@ int launch_merge(const void* o_parts, const float* lse_parts, int P, int64_t row
   cfg.numAttrs = 1;
   BSA_CHECK_CUDA(cudaLaunchKernelEx(&cfg, merge_kernel<Tin, Tout>, reinterpret_cast<const Tin*>(o_parts),
                                     lse_parts, P, rows, d, pso, rso, psl, rsl,
-                                    reinterpret_cast<Tout*>(o), ors, lse));
+                                    reinterpret_cast<Tout*>(o), ors, lse, lrs));
   return check_launch("merge_kernel");
 }
 
@@ -496,16 +496,17 @@ int launch_decode(const bsa_decode_params* p, cudaStream_t s) {
     // partial o: (rows, nsplit, D) -> partition stride D, row stride nsplit*D
     // the merged rows are written through (o_sb, o_sh): one launch per batch row
     // layout unless o is contiguous over (batch, head)
-    if (p->o_sb == (int64_t)p->hq * p->o_sh && (!p->lse || (p->lse_sb == (int64_t)p->hq * p->lse_sh &&
-                                                             p->lse_sh == 1))) {
+    // rows of o and lse may be strided (e.g. packed side by side in one buffer), but batch
+    // and head must collapse into one row index
+    if (p->o_sb == (int64_t)p->hq * p->o_sh && (!p->lse || p->lse_sb == (int64_t)p->hq * p->lse_sh)) {
       if (bf16)
         return launch_merge<float, __nv_bfloat16>(p->ws, ws_lse, nsplit, rows, D, D,
                                                   (int64_t)nsplit * D, 1, nsplit, p->o, p->o_sh,
-                                                  p->lse, s);
+                                                  p->lse, s, p->lse_sh);
       return launch_merge<float, __half>(p->ws, ws_lse, nsplit, rows, D, D, (int64_t)nsplit * D, 1,
-                                         nsplit, p->o, p->o_sh, p->lse, s);
+                                         nsplit, p->o, p->o_sh, p->lse, s, p->lse_sh);
     }
-    set_error("bsa_decode: o must be contiguous over (batch, head) and lse contiguous");
+    set_error("bsa_decode: with several splits o and lse need batch stride = heads x head stride");
     return BSA_E_UNSUPPORTED;
   }
   return BSA_OK;

@@ -107,6 +107,12 @@ def merge_gathered(o_parts: Tensor, lse_parts: Tensor, out_dtype: torch.dtype
     return res32.to(out_dtype), lse
 
 
+def _as_i32(t: Optional[Tensor], device) -> Optional[Tensor]:
+    if t is None:
+        return None
+    return t.to(device=device, dtype=torch.int32).contiguous()   # no-op for int32 device tensors
+
+
 def sharded_decode(attn, q: Tensor, k_shard: Tensor, v_shard: Tensor, n_local: Tensor,
                    pos0: Tensor, total_len: Tensor, sm_scale: Optional[float] = None,
                    group=None) -> Tuple[Tensor, Tensor]:
@@ -115,16 +121,36 @@ def sharded_decode(attn, q: Tensor, k_shard: Tensor, v_shard: Tensor, n_local: T
     attn: a SparseAttention module (its pattern covers the full sequence).
     q: (B,1,Hq,D) replicated on every rank.  k_shard/v_shard: (B,cap,Hkv,D) this
     rank's left-aligned slice; n_local (B,) stored tokens; pos0 (B,) position of the
-    first stored token (multiple of the block size); total_len (B,) full lengths.
-    Returns the merged (out (B,1,Hq,D), lse (B,Hq)) on every rank."""
+    first stored token (multiple of the block size); total_len (B,) full lengths
+    (int32 device tensors are used as they are).
+    Returns the merged (out (B,1,Hq,D), lse (B,Hq)) on every rank.
+
+    Per step: the decode kernel (+ its split merge) writes this rank's partial O (input
+    dtype) and LSE (fp32) side by side into one byte buffer of (B*Hq) rows of 2*D+4 bytes,
+    ONE all-gather moves it, and the fused merge kernel reads the gathered rows in place."""
     import math
+    from . import _lib
     from .ops import decode
     B, _, Hq, D = q.shape
+    rows, row_bytes = B * Hq, 2 * D + 4
+    assert q.element_size() == 2, "sharded decode packs 16-bit partial outputs"
     scale = sm_scale or 1.0 / math.sqrt(D)
-    i32 = lambda t: t.to(device=q.device, dtype=torch.int32).contiguous()
-    o, lse = decode(q, k_shard, v_shard, attn._plan(), scale, seq_dim=1,
-                    k_start=torch.zeros(B, dtype=torch.int32, device=q.device),
-                    k_end=i32(n_local), k_pos0=i32(pos0), k_total=i32(total_len))
-    o_parts, lse_parts = gather_partials(o.reshape(B * Hq, D), lse.reshape(B * Hq), group)
-    merged, mlse = merge_gathered(o_parts, lse_parts, q.dtype)
-    return merged.view(B, 1, Hq, D), mlse.view(B, Hq)
+    world = dist.get_world_size(group)
+    packed = torch.empty((rows, row_bytes), dtype=torch.uint8, device=q.device)
+    o_view = packed[:, :2 * D].view(q.dtype)                 # (rows, D), row stride D + 2 elements
+    lse_view = packed[:, 2 * D:].view(torch.float32)[:, 0]   # (rows,), row stride (2*D+4)/4 floats
+    decode(q, k_shard, v_shard, attn._plan(), scale, seq_dim=1, k_start=None,
+           k_end=_as_i32(n_local, q.device), k_pos0=_as_i32(pos0, q.device),
+           k_total=_as_i32(total_len, q.device), out=o_view, lse_out=lse_view)
+    gathered = torch.empty((world * rows, row_bytes), dtype=torch.uint8, device=q.device)
+    dist.all_gather_into_tensor(gathered, packed, group=group)
+    merged = torch.empty((B, 1, Hq, D), dtype=q.dtype, device=q.device)
+    mlse = torch.empty((B, Hq), dtype=torch.float32, device=q.device)
+    elems, floats = row_bytes // 2, row_bytes // 4
+    lse_parts = gathered.view(torch.float32)      # (world*rows, floats); the LSE is the last float of a row
+    with torch.cuda.device(q.device):
+        _lib.check(_lib.lib().bsa_merge_partials(
+            _lib.ptr(gathered), lse_parts.data_ptr() + 2 * D, world, rows, D, rows * elems, elems,
+            rows * floats, floats, _lib.ptr(merged), D, _lib.ptr(mlse), _lib.dtype_code(q.dtype),
+            _lib.stream_of(q)), "bsa_merge_partials")
+    return merged, mlse

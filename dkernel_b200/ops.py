@@ -137,7 +137,8 @@ def decode(q: Tensor, k: Tensor, v: Tensor, plan: _Plan, sm_scale: float, *, seq
            k_start: Optional[Tensor] = None, k_end: Optional[Tensor] = None,
            k_pos0: Optional[Tensor] = None, k_total: Optional[Tensor] = None,
            out: Optional[Tensor] = None, blocks_per_split: int = 0,
-           workspace: Optional[Tensor] = None) -> Tuple[Tensor, Tensor]:
+           workspace: Optional[Tensor] = None, lse_out: Optional[Tensor] = None
+           ) -> Tuple[Tensor, Tensor]:
     """One query token per sequence (split-KV decode kernel).
 
     q: (B,1,Hq,D)/(B,Hq,1,D) or packed (B,Hq,D); k, v: 4-D with the module's
@@ -153,9 +154,19 @@ def decode(q: Tensor, k: Tensor, v: Tensor, plan: _Plan, sm_scale: float, *, seq
     else:
         B, hq, d = q.shape
         q_sb, q_sh = q.stride(0), q.stride(1)
-    o = out if out is not None else torch.empty(q.shape, dtype=q.dtype, device=q.device)
-    assert o.is_contiguous(), "decode output must be contiguous"
-    lse = torch.empty((B, hq), dtype=torch.float32, device=q.device)
+    if out is not None and out.dim() == 2:
+        # rows = (batch, head) with a row stride, e.g. packed next to the LSE for one all-gather
+        assert out.shape == (B * hq, d) and out.stride(1) == 1 and out.dtype == q.dtype
+        o, o_sh = out, out.stride(0)
+    else:
+        o = out if out is not None else torch.empty(q.shape, dtype=q.dtype, device=q.device)
+        assert o.is_contiguous(), "decode output must be contiguous"
+        o_sh = d
+    if lse_out is not None:
+        assert lse_out.dtype == torch.float32 and lse_out.numel() == B * hq and lse_out.dim() == 1
+        lse, lse_sh = lse_out, lse_out.stride(0)
+    else:
+        lse, lse_sh = torch.empty((B, hq), dtype=torch.float32, device=q.device), 1
     p = _lib.DecodeParams()
     k = _tma_friendly(k)
     v = _tma_friendly(v)
@@ -164,8 +175,8 @@ def decode(q: Tensor, k: Tensor, v: Tensor, plan: _Plan, sm_scale: float, *, seq
     p.q_sb, p.q_sh = q_sb, q_sh
     p.k_sb, p.k_ss, p.k_sh = _strides_bsh(k, seq_dim)
     p.v_sb, p.v_ss, p.v_sh = _strides_bsh(v, seq_dim)
-    p.o_sb, p.o_sh = hq * d, d
-    p.lse_sb, p.lse_sh = hq, 1
+    p.o_sb, p.o_sh = hq * o_sh, o_sh
+    p.lse_sb, p.lse_sh = hq * lse_sh, lse_sh
     if k.dim() == 3:
         hkv, sk = k.size(1), k.size(0)
     else:

@@ -160,6 +160,32 @@ def test_kv_sharded_decode_merges_to_whole():
     assert_lse_close(mlse, ref_lse)
 
 
+def test_sharded_decode_single_rank_group(tmp_path):
+    """sharded_decode end to end (packed (O, LSE) rows -> all-gather -> fused merge) with a
+    one-rank NCCL group: the whole sequence is the only shard."""
+    import torch.distributed as dist
+    from dkernel_b200.dist import sharded_decode
+    B, Hq, Hkv, S, D, bs = 3, 8, 2, 1024, 128, 64
+    pk = dict(block_size=bs, local_blocks=4, vert_stride=4, num_kv_heads=Hkv)
+    q, k, v = seeded_qkv(23, (B, 1, Hq, D), (B, S, Hkv, D), torch.bfloat16)
+    lens = torch.tensor([1024, 513, 64])
+    bm = O.block_mask(Hq, S, **pk)
+    # left-aligned storage: sequence b occupies rows [0, lens[b])
+    ref, ref_lse = O.decode_attention(q.float(), k.float(), v.float(), bm, bs, seqlens=lens)
+    mod = _module(Hq, S, pk, seq_dim=1)
+    store = dist.FileStore(str(tmp_path / "pg"), 1)
+    dist.init_process_group("nccl", store=store, rank=0, world_size=1)
+    try:
+        out, lse = sharded_decode(mod, q.cuda(), k.cuda(), v.cuda(), lens.to(torch.int32).cuda(),
+                                  torch.zeros(B, dtype=torch.int32).cuda(), lens.to(torch.int32).cuda(),
+                                  1 / math.sqrt(D))
+        torch.cuda.synchronize()
+    finally:
+        dist.destroy_process_group()
+    assert_out_close(out, ref)
+    assert_lse_close(lse.unsqueeze(-1), ref_lse)
+
+
 def test_combine_attn_partitions_matches_reference_fixture(golden_dir):
     from dkernel_b200 import combine_attn_partitions
     C = np.load(f"{golden_dir}/combine.npz")
