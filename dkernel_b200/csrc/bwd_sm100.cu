@@ -210,7 +210,7 @@ constexpr int kQdoStageBytes = 2 * kBS * kD * 2;   // Q_r and dO_r, 16 KB each
 struct DkdvTail {
   uint64_t kv_full;
   uint64_t qdo_full[kQdoStages], qdo_empty[kQdoStages];
-  uint64_t sdp_full[2], p_full[2], acc_done[2];
+  uint64_t sdp_full[2], p_full[2];
   uint64_t all_done;
   uint32_t tmem_base;
   int n_list;
@@ -256,7 +256,6 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
     for (int s = 0; s < 2; ++s) {
       mbar_init(&tl->sdp_full[s], 2);    // S^T and dP^T, one commit each
       mbar_init(&tl->p_full[s], kDkdvEwWarps);   // one arrival per element-wise warp
-      mbar_init(&tl->acc_done[s], 1);
     }
     mbar_init(&tl->all_done, 2);
     mbar_fence_init();

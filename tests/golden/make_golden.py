@@ -1,9 +1,9 @@
 """Generate the golden vectors under tests/golden/ from the reference package.
 
-Run once, in a container that has a read-only checkout of the reference
-(default /root/reference, override with DKERNEL_REF):
+Run once, where a read-only checkout of the reference (linxihui/dkernel) is available; its
+path comes from the command line or from the environment variable DKERNEL_REF:
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py <path to the dkernel checkout>
 
 It imports the reference's own ``dkernel.utils`` / ``dkernel.interface`` and the
 ``torch_attention`` oracle of its test-suite on the CPU (the Triton kernels are
@@ -27,7 +27,9 @@ import sys
 import numpy as np
 import torch
 
-REF = os.environ.get("DKERNEL_REF", "/root/reference")
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("DKERNEL_REF")
+if not REF or not os.path.isdir(os.path.join(REF, "dkernel")):
+    raise SystemExit("usage: make_golden.py <path to the dkernel checkout>   (or set DKERNEL_REF)")
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 _orig_version = md.version
