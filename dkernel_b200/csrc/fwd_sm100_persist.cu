@@ -363,16 +363,13 @@ fwd_persist_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tm
     const bool wide = reinterpret_cast<uintptr_t>(p.o) % 16 == 0 && p.o_ss % 8 == 0 &&
                       p.o_sh % 8 == 0 && p.o_sb % 8 == 0;   // rows start on 16-byte boundaries
     uint32_t g = 0;      // kv blocks processed so far, over all tiles
-    uint32_t seen = 0;   // P V completions observed so far (in order, one barrier phase at a time)
-    // A parity wait only means something while the waiter is at most one phase behind, so the
-    // completions are observed in order.  Q K_g^T was issued after P V_{g-2}, so observing up
-    // to g-2 never blocks; P V_{g-1} is only waited for when the accumulator has to be rescaled.
-    auto observe_pv = [&](uint32_t upto) {   // P V_0 .. P V_{upto-1} have completed
-      while (seen < upto) {
-        if (!mbar_wait(&tl->pv_done[seen & 1], (seen >> 1) & 1, wait_status, 421)) return false;
-        ++seen;
-      }
-      return true;
+    // Completion of P V_x.  A parity wait is unambiguous while the barrier can be at most one
+    // phase past the awaited one: that holds for x = g-1 while block g is being processed (the
+    // barrier's next phase, P V_{g+1}, needs this warp's P_{g+1}) and for the last block of a
+    // tile in its epilogue.  P V_{g-2} needs no wait at all: Q K_g^T was queued behind it and
+    // the tensor pipe runs in order, so S_g being readable implies it has completed.
+    auto wait_pv = [&](uint32_t x) {
+      return mbar_wait(&tl->pv_done[x & 1], (x >> 1) & 1, wait_status, 421);
     };
     int k = 0;
     bool alive = true;
@@ -468,10 +465,9 @@ fwd_persist_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tm
           for (int c = 0; c < 32; ++c) pk[c] = 0u;
         }
         tmem_st32(tS[s] + lane_off, pk);
-        // g >= 1: blocks up to g-2 (count g-1); with a rescale also block g-1 (count g)
-        if (!observe_pv(any ? g : (g > 0 ? g - 1 : 0))) { alive = false; break; }
         if (any && j > 0) {
-          // rescale the accumulator rows whose maximum moved (P V_{g-1} has landed)
+          // rescale the accumulator rows whose maximum moved, once P V_{g-1} has landed
+          if (!wait_pv(g - 1)) { alive = false; break; }
           tc_fence_after();
 #pragma unroll
           for (int ch = 0; ch < 4; ++ch) {
@@ -493,7 +489,7 @@ fwd_persist_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tm
       if (!alive) break;
       // ---- epilogue of the tile: all its P V products must have completed; each thread
       // normalises its own row and stores it straight from registers
-      if (!observe_pv(g)) { alive = false; break; }
+      if (!wait_pv(g - 1)) { alive = false; break; }
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
