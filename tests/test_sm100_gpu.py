@@ -178,3 +178,19 @@ def test_sm100_backward_matches_generic_on_long_sequences(B, Hq, Hkv, S, pk):
     mod(qg, kg, vg).backward(do)
     for a, b_ in zip(grads["sm100"], (qg.grad, kg.grad, vg.grad)):
         assert torch.equal(a, b_)
+
+
+def test_one_tile_per_cta_forward_kernel_in_a_subprocess():
+    """The persistent forward kernel is the default; BSA_FWD_TILED=1 (read once per process)
+    selects the one-tile-per-CTA kernel.  Its parity cases run in a child process."""
+    import os
+    import subprocess
+    import sys
+    env = dict(os.environ, BSA_FWD_TILED="1")
+    here = os.path.dirname(os.path.abspath(__file__))
+    res = subprocess.run(
+        [sys.executable, "-m", "pytest", "-x", "-q", "-m", "gpu",
+         os.path.join(here, "test_sm100_gpu.py") + "::test_sm100_forward_vs_oracle",
+         os.path.join(here, "test_sm100_gpu.py") + "::test_sm100_varlen_and_padded_routes"],
+        env=env, cwd=os.path.dirname(here), capture_output=True, text=True, timeout=900)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
