@@ -447,24 +447,30 @@ fwd_persist_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tm
           }
         }
         const bool any = __any_sync(0xffffffffu, need);
-        uint32_t pk[32];
-        if (att && m_used != -INFINITY) {
-          float sum[4] = {0.f, 0.f, 0.f, 0.f};
-          const float neg_m = -m_used;
+        // P is produced and stored in two halves, so that the first store's latency is covered
+        // by the second half's exponentials and fewer packed values are live at a time
+        const bool live = att && m_used != -INFINITY;
+        const float neg_m = -m_used;
+        float sum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-          for (int c = 0; c < 32; ++c) {
-            const float p0 = ex2(fmaf(__uint_as_float(sv[2 * c]), scale2, neg_m));
-            const float p1 = ex2(fmaf(__uint_as_float(sv[2 * c + 1]), scale2, neg_m));
-            sum[(2 * c) & 3] += p0;
-            sum[(2 * c + 1) & 3] += p1;
-            pk[c] = pack2<BF16>(p0, p1);
+        for (int hlf = 0; hlf < 2; ++hlf) {
+          uint32_t pk[16];
+          if (live) {
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+              const float p0 = ex2(fmaf(__uint_as_float(sv[hlf * 32 + 2 * c]), scale2, neg_m));
+              const float p1 = ex2(fmaf(__uint_as_float(sv[hlf * 32 + 2 * c + 1]), scale2, neg_m));
+              sum[(2 * c) & 3] += p0;
+              sum[(2 * c + 1) & 3] += p1;
+              pk[c] = pack2<BF16>(p0, p1);
+            }
+          } else {
+#pragma unroll
+            for (int c = 0; c < 16; ++c) pk[c] = 0u;
           }
-          l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
-        } else {
-#pragma unroll
-          for (int c = 0; c < 32; ++c) pk[c] = 0u;
+          tmem_st16(tS[s] + lane_off + hlf * 16, pk);
         }
-        tmem_st32(tS[s] + lane_off, pk);
+        l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
         if (any && j > 0) {
           // rescale the accumulator rows whose maximum moved, once P V_{g-1} has landed
           if (!wait_pv(g - 1)) { alive = false; break; }
