@@ -180,7 +180,7 @@ __device__ __forceinline__ void append_union(const uint32_t* bits0, const uint32
                                              uint32_t* list, int* count, uint32_t extra, int lane,
                                              int cap) {
   const uint32_t u0 = bits0[lane], u1 = bits1[lane];
-  uint32_t u = u0 | u1;
+  const uint32_t u = u0 | u1;
   const int cnt = __popc(u);
   int incl = cnt;
 #pragma unroll
@@ -189,14 +189,19 @@ __device__ __forceinline__ void append_union(const uint32_t* bits0, const uint32
     if (lane >= o) incl += t;
   }
   const int base = *count;
-  int pos = base + incl - cnt;
-  while (u) {
-    const int bit = __ffs(u) - 1;
-    u &= u - 1;
-    if (pos < cap)
-      list[pos] = (uint32_t)(lane * 32 + bit) | extra | (((u0 >> bit) & 1u) << 24) |
-                  (((u1 >> bit) & 1u) << 25);
-    ++pos;
+  const int first = base + incl - cnt;   // list position of this lane's word
+  // one word at a time; within a word every lane owns one bit
+  uint32_t nonzero = __ballot_sync(0xffffffffu, u != 0u);
+  while (nonzero) {
+    const int w = __ffs(nonzero) - 1;
+    nonzero &= nonzero - 1;
+    const uint32_t uw = __shfl_sync(0xffffffffu, u, w);
+    const uint32_t u0w = __shfl_sync(0xffffffffu, u0, w);
+    const uint32_t u1w = __shfl_sync(0xffffffffu, u1, w);
+    const int pos = __shfl_sync(0xffffffffu, first, w) + __popc(uw & ((1u << lane) - 1u));
+    if (((uw >> lane) & 1u) && pos < cap)
+      list[pos] = (uint32_t)(w * 32 + lane) | extra | (((u0w >> lane) & 1u) << 24) |
+                  (((u1w >> lane) & 1u) << 25);
   }
   __syncwarp();
   if (lane == 31) *count = min(base + incl, cap);
