@@ -61,3 +61,28 @@ def test_argument_validation_needs_no_device():
     assert lib.bsa_merge_partials(None, None, 2, 4, 8, 0, 0, 0, 0, None, 0, None, 1, None) == -1
     with pytest.raises(_lib.BsaError):
         _lib.check(-1, "x")
+
+
+def test_decode_split_choice_needs_no_device():
+    """bsa_decode_workspace_bytes reflects the blocks-per-CTA choice: the caller's value, or
+    (<= 0) the library's: as many blocks per CTA as keep the grid about two waves deep."""
+    import ctypes as C
+    from dkernel_b200 import _lib
+    lib = _lib.lib()
+    p = _lib.DecodeParams()
+    p.batch, p.hq, p.hkv, p.d, p.sk = 64, 32, 8, 128, 8192
+    p.block_size, p.heads_per_cta, p.max_row_nnz = 64, 4, 30
+
+    def splits():
+        return lib.bsa_decode_workspace_bytes(C.byref(p)) // (4 * p.batch * p.hq * (p.d + 1))
+
+    p.blocks_per_split = 8
+    assert splits() == 4                      # ceil(30 / 8)
+    p.blocks_per_split = 0
+    assert splits() == 2                      # 512 (sequence, kv head) items -> 16 blocks per CTA
+    p.batch = 1
+    assert splits() == 8                      # few items: 4 blocks per CTA (the minimum)
+    p.batch, p.max_row_nnz = 4096, 30
+    assert lib.bsa_decode_workspace_bytes(C.byref(p)) // (4 * p.batch * p.hq * (p.d + 1)) == 2
+    p.max_row_nnz = 12
+    assert lib.bsa_decode_workspace_bytes(C.byref(p)) == 0   # one split: no workspace
