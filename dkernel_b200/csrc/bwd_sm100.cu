@@ -32,8 +32,9 @@ namespace {
 
 constexpr int kD = 128;
 constexpr int kBS = 64;
-constexpr int kBwdThreads = 352;      // dQ kernel: 8 element-wise warps, producer, two issuers
-constexpr int kWarpProducer = 8, kWarpIssueA = 9, kWarpIssueB = 10;
+constexpr int kDqEwWarps = 16;        // dQ kernel: 16 element-wise warps, producer, two issuers
+constexpr int kBwdThreads = 32 * (kDqEwWarps + 3);
+constexpr int kWarpProducer = kDqEwWarps, kWarpIssueA = kDqEwWarps + 1, kWarpIssueB = kDqEwWarps + 2;
 constexpr int kDkdvEwWarps = 16;      // dK/dV kernel: 16 element-wise warps, producer, two issuers
 constexpr int kDkdvThreads = 32 * (kDkdvEwWarps + 3);
 constexpr int kDkdvProducer = kDkdvEwWarps, kDkdvIssuer = kDkdvEwWarps + 1;   // issuers: +1 and +2
@@ -55,50 +56,6 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     __half2 h = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&h);
   }
-}
-
-// Packed 16-bit P / dS overwrite the fp32 columns they were computed from: the
-// warp that owns S columns [32h, 32h+32) stores its 16 packed columns at
-// [32h, 32h+16), so no warp writes into columns another warp still has to read.
-// k-step kk (16 rows of the second-stage product) therefore starts at this column.
-__device__ __forceinline__ uint32_t packed_col(int kk) { return (uint32_t)((kk >> 1) * 32 + (kk & 1) * 8); }
-
-// 128 x 128 fp32 accumulator in TMEM (lane = tile row) -> scaled 16-bit rows in
-// global memory.  Each warp converts its 32 lanes through an 8 KB staging area
-// (XOR-swizzled 16-byte chunks) and then writes whole 256-byte rows.
-// Row r of the tile belongs to half r/64; base[half] points at that half's row 0.
-template <bool BF16>
-__device__ __forceinline__ void store_acc_tile(uint32_t tacc, int warp, int lane, float scale,
-                                               uint8_t* stage, uint8_t* const (&base)[2],
-                                               const int (&valid_rows)[2], int64_t row_stride_bytes) {
-  const uint32_t lane_off = (uint32_t)(warp * 32) << 16;   // warp = TMEM lane quadrant (0..3)
-#pragma unroll
-  for (int ch = 0; ch < 4; ++ch) {
-    uint32_t o[32];
-    tmem_ld32(tacc + lane_off + ch * 32, o);
-    tmem_ld_wait();
-#pragma unroll
-    for (int c4 = 0; c4 < 4; ++c4) {
-      uint4 w;
-      w.x = pack2<BF16>(__uint_as_float(o[c4 * 8 + 0]) * scale, __uint_as_float(o[c4 * 8 + 1]) * scale);
-      w.y = pack2<BF16>(__uint_as_float(o[c4 * 8 + 2]) * scale, __uint_as_float(o[c4 * 8 + 3]) * scale);
-      w.z = pack2<BF16>(__uint_as_float(o[c4 * 8 + 4]) * scale, __uint_as_float(o[c4 * 8 + 5]) * scale);
-      w.w = pack2<BF16>(__uint_as_float(o[c4 * 8 + 6]) * scale, __uint_as_float(o[c4 * 8 + 7]) * scale);
-      const int chunk = ch * 4 + c4;
-      *reinterpret_cast<uint4*>(stage + lane * 256 + ((chunk ^ (lane & 15)) << 4)) = w;
-    }
-  }
-  __syncwarp();
-  for (int i = 0; i < 32; ++i) {
-    const int row = warp * 32 + i;
-    const int ht = row >> 6, rr = row & 63;
-    if (rr < valid_rows[ht]) {
-      const uint2 w = *reinterpret_cast<const uint2*>(stage + i * 256 + (((lane >> 1) ^ (i & 15)) << 4) +
-                                                      (lane & 1) * 8);
-      *reinterpret_cast<uint2*>(base[ht] + (int64_t)rr * row_stride_bytes + lane * 8) = w;
-    }
-  }
-  __syncwarp();
 }
 
 // ------------------------------------------------------------------ delta
@@ -589,7 +546,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
     for (int s = 0; s < kDqVStages; ++s) { mbar_init(&tl->v_full[s], 1); mbar_init(&tl->v_empty[s], 1); }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&tl->sdp_full[s], 2);   // S and dP, one commit each
-      mbar_init(&tl->p_full[s], 8);     // one arrival per element-wise warp
+      mbar_init(&tl->p_full[s], kDqEwWarps);   // one arrival per element-wise warp
     }
     mbar_init(&tl->cp_done, 1);
     mbar_init(&tl->all_done, 1);
@@ -740,7 +697,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
         if (elect_one()) {
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            tc_mma_ts(tDQ, tDP[bf] + packed_col(kk), kd + (uint64_t)((kk * 2048) >> 4), idesc_acc,
+            tc_mma_ts(tDQ, tDP[bf] + kk * 16, kd + (uint64_t)((kk * 2048) >> 4), idesc_acc,
                       kk ? 1u : acc0);
           tc_commit(&tl->k_empty[sk_]);
         }
@@ -750,9 +707,12 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
       if (ok && elect_one()) tc_commit(&tl->all_done);
     }
     __syncwarp();
-  } else if (n > 0) {
-    // ------------------------------------------------------------ dS (warps 0-7)
-    const int quad = warp & 3, half = warp >> 2;
+  } else if (n > 0 && warp < kDqEwWarps) {
+    // ------------------------------------------------------------ dS (warps 0-15)
+    // A warp owns a TMEM lane quadrant (32 q rows) and 16 of the 64 kv columns; its packed dS
+    // overwrites the first 8 of the 16 dP columns it has read, so k-step kk of dQ += dS K
+    // starts at column 16 kk.
+    const int quad = warp & 3, qtr = warp >> 2;
     const int r = quad * 32 + lane, t = r >> 6, rr = r & 63;
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
     const float scale2 = p.sm_scale * kLog2e;
@@ -764,6 +724,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
       lse2 = l == -INFINITY ? INFINITY : l * kLog2e;
       delta = bp.delta[((int64_t)b * p.hq + head[t]) * padded_sq(p.sq) + q_row];
     }
+    const float neg_lse = -lse2;
     bool alive = true;
     for (int e = 0; e < n; ++e) {
       if (!mbar_wait(&tl->sdp_full[e & 1], (e >> 1) & 1, wait_status, 317)) { alive = false; break; }
@@ -773,44 +734,66 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
       const bool att = ((ent >> (24 + t)) & 1u) != 0 && valid[t];
       int lim = p.sk - kbase;
       if (p.causal) lim = min(lim, qpos - kbase + 1);
-      lim -= half * 32;   // relative to this warp's 32 columns
-      uint32_t sv[32], dv[32];
-      tmem_ld32(tS[e & 1] + lane_off + half * 32, sv);
-      tmem_ld32(tDP[e & 1] + lane_off + half * 32, dv);
+      lim -= qtr * 16;   // relative to this warp's 16 columns
+      uint32_t sv[16], dv[16];
+      tmem_ld16(tS[e & 1] + lane_off + qtr * 16, sv);
+      tmem_ld16(tDP[e & 1] + lane_off + qtr * 16, dv);
       tmem_ld_wait();
-      uint32_t ds[16];
+      uint32_t ds[8];
       if (att) {
+        // only blocks on the diagonal or at the end of the keys have masked columns:
+        // they get S = -inf, hence P = dS = 0
+        if (lim < 16) {
 #pragma unroll
-        for (int c2 = 0; c2 < 16; ++c2) {
-          float x0 = ex2(fmaf(__uint_as_float(sv[2 * c2]), scale2, -lse2));
-          float x1 = ex2(fmaf(__uint_as_float(sv[2 * c2 + 1]), scale2, -lse2));
-          if (2 * c2 >= lim) x0 = 0.f;
-          if (2 * c2 + 1 >= lim) x1 = 0.f;
+          for (int c = 0; c < 16; ++c)
+            if (c >= lim) sv[c] = 0xff800000u;
+        }
+#pragma unroll
+        for (int c2 = 0; c2 < 8; ++c2) {
+          const float x0 = ex2(fmaf(__uint_as_float(sv[2 * c2]), scale2, neg_lse));
+          const float x1 = ex2(fmaf(__uint_as_float(sv[2 * c2 + 1]), scale2, neg_lse));
           ds[c2] = pack2<BF16>(x0 * (__uint_as_float(dv[2 * c2]) - delta),
                                x1 * (__uint_as_float(dv[2 * c2 + 1]) - delta));
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) ds[i] = 0u;
+        for (int i = 0; i < 8; ++i) ds[i] = 0u;
       }
-      tmem_st16(tDP[e & 1] + lane_off + half * 32, ds);
+      tmem_st8(tDP[e & 1] + lane_off + qtr * 16, ds);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tl->p_full[e & 1]);
     }
+    // ---- epilogue: warp = (lane quadrant, 32-column chunk); every thread scales its row and
+    // stores 64 contiguous bytes straight from registers
     if (alive) alive = mbar_wait(&tl->all_done, 0, wait_status, 318);
     tc_fence_after();
-    if (alive && half == 0) {
-      uint8_t* stage = sQ + quad * 8192;   // Q is dead once every product has completed
-      const int vr[2] = {valid[0] ? min(kBS, p.sq - qblk[0] * kBS) : 0,
-                         valid[1] ? min(kBS, p.sq - qblk[1] * kBS) : 0};
-      uint8_t* const dqb[2] = {
-          reinterpret_cast<uint8_t*>(bp.dq) + ((int64_t)b * bp.dq_sb + (int64_t)head[0] * bp.dq_sh +
-                                               (int64_t)qblk[0] * kBS * bp.dq_ss) * 2,
-          reinterpret_cast<uint8_t*>(bp.dq) + ((int64_t)b * bp.dq_sb + (int64_t)head[1] * bp.dq_sh +
-                                               (int64_t)qblk[1] * kBS * bp.dq_ss) * 2};
-      store_acc_tile<BF16>(tDQ, quad, lane, p.sm_scale, stage, dqb, vr, bp.dq_ss * 2);
+    if (alive) {
+      const bool row_ok = valid[t] && q_row < p.sq;
+      uint8_t* grow = reinterpret_cast<uint8_t*>(bp.dq) +
+                      ((int64_t)b * bp.dq_sb + (int64_t)head[t] * bp.dq_sh + (int64_t)q_row * bp.dq_ss) * 2 +
+                      qtr * 64;
+      const bool wide = reinterpret_cast<uintptr_t>(bp.dq) % 16 == 0 && bp.dq_sb % 8 == 0 &&
+                        bp.dq_sh % 8 == 0 && bp.dq_ss % 8 == 0;
+      uint32_t o[32];
+      tmem_ld32(tDQ + lane_off + qtr * 32, o);
+      tmem_ld_wait();
+      uint32_t w[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i)
+        w[i] = pack2<BF16>(__uint_as_float(o[2 * i]) * p.sm_scale, __uint_as_float(o[2 * i + 1]) * p.sm_scale);
+      if (row_ok) {
+        if (wide) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            *reinterpret_cast<uint4*>(grow + i * 16) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            *reinterpret_cast<uint2*>(grow + i * 8) = make_uint2(w[2 * i], w[2 * i + 1]);
+        }
+      }
     }
   } else if (warp == kWarpProducer) {
     if (lane == 0) mbar_wait(&tl->q_full, 0, wait_status, 320);   // let the tiles in flight land
