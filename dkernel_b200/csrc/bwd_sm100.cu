@@ -16,7 +16,7 @@
 // dO serve as MN-major B operands straight from their TMA tiles.  S/dP are double
 // buffered in TMEM (512 columns, one CTA per SM) so the MMAs of step e+1 overlap
 // the exponentials of step e.  Element-wise warps own a TMEM lane quadrant and a slice
-// of the columns (16 warps x 16 columns in the dK/dV kernel, 8 x 32 in the dQ kernel);
+// of the columns (16 warps x 16 columns in both kernels);
 // one TMA producer warp; two MMA issuer warps, because a tcgen05.mma costs its issuing
 // thread about as long as a 128x64x16 product takes on the tensor pipe.  The issuers
 // split the products along the data paths, so that a product overwriting columns an

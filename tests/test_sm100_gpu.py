@@ -61,6 +61,8 @@ def test_sm100_forward_vs_oracle(B, Hq, Hkv, Sq, Sk, dtype, seq_dim, pk):
     (1, 8, 2, 4096, dict(block_size=64, local_blocks=16, vert_stride=8, num_kv_heads=2)),
     (1, 4, 4, 4096, dict(block_size=64, local_blocks=32, vert_stride=8)),
     (2, 2, 2, 8192, dict(block_size=64, local_blocks=4, vert_stride=16)),
+    # several tiles per persistent CTA (1024 tiles for 296 CTAs)
+    (4, 16, 16, 2048, dict(block_size=64, local_blocks=2, vert_stride=4)),
 ])
 def test_sm100_matches_generic_on_long_sequences(B, Hq, Hkv, S, pk):
     q, k, v = seeded_qkv(1, (B, S, Hq, 128), (B, S, Hkv, 128), torch.bfloat16, device="cuda")
@@ -76,6 +78,23 @@ def test_sm100_matches_generic_on_long_sequences(B, Hq, Hkv, S, pk):
     with torch.no_grad():
         o3 = fast(q, k, v)
     assert torch.equal(o1, o3)
+
+
+def test_sm100_shared_pattern_pairs_heads_over_many_tiles():
+    """One pattern for all heads + GQA: a tile is two q heads of a kv group (1536 tiles for 296
+    persistent CTAs); checked against the generic kernel on the same device."""
+    from dkernel_b200 import SparseAttention
+    B, Hq, Hkv, S, bs = 3, 16, 4, 4096, 64
+    pat = torch.from_numpy(O.block_mask(1, S, block_size=bs, local_blocks=3, vert_stride=8)).bool()
+    q, k, v = seeded_qkv(3, (B, S, Hq, 128), (B, S, Hkv, 128), torch.bfloat16, device="cuda")
+    fast = SparseAttention(bs, pat.cuda(), seq_dim=1, impl="sm100")
+    slow = SparseAttention(bs, pat.cuda(), seq_dim=1, impl="generic")
+    with torch.no_grad():
+        o1, l1 = fast(q, k, v, return_lse=True)
+        o2, l2 = slow(q, k, v, return_lse=True)
+    _wait_status_clean()
+    assert_out_close(o1, o2, max_abs=2e-2, mean_abs=1e-3)
+    assert_lse_close(l1, l2)
 
 
 def test_sm100_varlen_and_padded_routes():
