@@ -49,6 +49,15 @@ int make_tmap_4d(Tmap4* out, const void* base, int elem_bytes, uint64_t d, uint6
     set_error("cuTensorMapEncodeTiled is not available from the CUDA driver");
     return BSA_E_CUDA;
   }
+  // The encoder is a driver entry point and wants a context current on the calling thread.  A
+  // thread that has not made a runtime call yet (an autograd worker entering the backward, a
+  // host's worker thread) has none: binding the device's primary context once per thread costs
+  // nothing afterwards.
+  thread_local bool context_bound = false;
+  if (!context_bound) {
+    BSA_CHECK_CUDA(cudaFree(nullptr));
+    context_bound = true;
+  }
   // The three outer dimensions are placed in order of increasing stride, so the
   // map looks like an ordinary padded row-major tensor whatever the caller's
   // layout ((B,S,H,D), (B,H,S,D), packed (T,H,D), views of larger tensors).
