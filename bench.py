@@ -358,7 +358,9 @@ def run_train(args, world, rank):
         "gpu_launches": args.steps * 4, "clocks": clocks,
         "roofline": {"bound": "tensor", "achieved": bwd_tflops, "peak": peaks["tflops"], "unit": "TFLOP/s",
                      "frac": bwd_tflops / peaks["tflops"], "traffic": TRAFFIC.get("train"),
-                     "peak_source": peaks["source"] + " (burst)", "kernel": "bwd_dkdv_sm100_kernel + bwd_dq_sm100_kernel (+ delta pre-pass)"},
+                     "peak_source": peaks["source"] + " (burst)",
+                     "frac_of_sustained": bwd_tflops / peaks["tflops_sustained"] if peaks["tflops_sustained"] else None,
+                     "kernel": "bwd_dkdv_sm100_kernel + bwd_dq_sm100_kernel (+ delta pre-pass)"},
     }
 
 
