@@ -202,9 +202,16 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
   const int c2 = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
   const int G = p.hq / p.hkv;
   const int past = p.causal ? p.sk - p.sq : 0;
-  const int kblk[2] = {2 * c2, 2 * c2 + 1};
-  const int kvalid[2] = {kblk[0] * kBS < p.sk ? 1 : 0, kblk[1] * kBS < p.sk ? 1 : 0};
-  if (!kvalid[0]) return;
+  // the two kv blocks of this tile: adjacent ones, or the caller's pairing
+  int kblk[2] = {2 * c2, 2 * c2 + 1};
+  if (bp.kv_pairs) {
+    const int32_t* pr = bp.kv_pairs + (int64_t)hk * bp.kv_pairs_sh + 2 * c2;
+    kblk[0] = pr[0];
+    kblk[1] = pr[1];
+  }
+  const int kvalid[2] = {kblk[0] >= 0 && kblk[0] * kBS < p.sk ? 1 : 0,
+                         kblk[1] >= 0 && kblk[1] * kBS < p.sk ? 1 : 0};
+  if (!kvalid[0] && !kvalid[1]) return;
   const int nqb = min((p.sq + kBS - 1) / kBS, kMaxBlocks);
   const int sq_pad = padded_sq(p.sq);
   const int64_t ws_half = (int64_t)p.batch * p.hq * sq_pad;
@@ -842,7 +849,7 @@ int launch_bwd(const bsa_bwd_params* bp, cudaStream_t s) {
   {
     auto kern = bwd_dkdv_sm100_kernel<BF16>;
     BSA_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDkdvSmem));
-    dim3 grid(cdiv_i(cdiv_i(p->sk, kBS), 2), p->hkv, p->batch);
+    dim3 grid(bp->kv_pairs ? bp->n_pairs : cdiv_i(cdiv_i(p->sk, kBS), 2), p->hkv, p->batch);
     kern<<<grid, kDkdvThreads, kDkdvSmem, s>>>(tmQ, tmK, tmV, tmDO, *bp, status);
     rc = check_launch("bwd_dkdv_sm100_kernel");
     if (rc) return rc;

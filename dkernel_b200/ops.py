@@ -52,6 +52,7 @@ class _Plan:
         self.block_size = block_size
         self.max_row_nnz = max_row_nnz
         self._group_shared: Dict[int, bool] = {}
+        self._kv_pairs: Dict[Tuple[int, int, int], Optional[Tensor]] = {}
 
     def heads_shared_in_group(self, hq: int, hkv: int) -> bool:
         """True when all q heads of a kv group use the same pattern rows (then the
@@ -66,6 +67,52 @@ class _Plan:
             same = bool((cr == cr[:, :1]).all().item()) and bool((cc == cc[:, :1]).all().item())
             self._group_shared[hkv] = same
         return self._group_shared[hkv]
+
+
+    def kv_pairs(self, hq: int, hkv: int, n_kv_blocks: int) -> Optional[Tensor]:
+        """Pairing of kv blocks for the tensor-core dK/dV kernel, which computes two kv blocks
+        (128 rows) per tile and walks the union of their CSC columns: int32 (1 or hkv,
+        ceil(n/2), 2), -1 = no partner, or None when pairing neighbours is at least as good.
+
+        Candidate: blocks ordered by how many q blocks attend them (ties in index order),
+        neighbours in that order paired.  For a local + vertical-stride pattern this puts
+        vertical columns (attended by every later row) with vertical columns, where a
+        neighbour pair would pad a short local column up to a long vertical one.  The
+        candidate is kept only if it shrinks the total length of the unions."""
+        key = (hq, hkv, n_kv_blocks)
+        if key in self._kv_pairs:
+            return self._kv_pairs[key]
+        from .utils import ccol_row_to_dense
+        hp = self.ccol.size(0)
+        n = min(n_kv_blocks, self.ccol.size(1) - 1)
+        result = None
+        if n >= 4 and (hp == 1 or hp == hkv or hp == hq):
+            dense = ccol_row_to_dense(self.ccol, self.row, torch.float32)[:, :, :n]   # (hp, M, N)
+            if dense.size(2) < n:
+                dense = torch.nn.functional.pad(dense, (0, n - dense.size(2)))
+            if hp == hq and hq != hkv:
+                # the CTA of a kv head walks all q heads of its group: stack their rows
+                m = dense.reshape(hkv, (hq // hkv) * dense.size(1), n)
+            else:
+                m = dense
+            count = m.sum(1)                                               # (heads, n)
+            order = torch.argsort(count, dim=1, stable=True)
+            if n % 2:
+                order = torch.cat([order, order.new_full((order.size(0), 1), -1)], 1)
+            cand = order.reshape(order.size(0), -1, 2)
+            a_idx, b_idx = cand[..., 0], cand[..., 1].clamp_min(0)
+            has_b = (cand[..., 1] >= 0).float()
+            ma = torch.gather(m, 2, a_idx[:, None, :].expand(-1, m.size(1), -1))
+            mb = torch.gather(m, 2, b_idx[:, None, :].expand(-1, m.size(1), -1)) * has_b[:, None, :]
+            cost_cand = torch.maximum(ma, mb).sum().item()
+            even, odd = m[:, :, 0::2], m[:, :, 1::2]
+            if odd.size(2) < even.size(2):
+                odd = torch.nn.functional.pad(odd, (0, 1))
+            cost_adj = torch.maximum(even, odd).sum().item()
+            if cost_cand < 0.97 * cost_adj:
+                result = cand.to(torch.int32).contiguous()
+        self._kv_pairs[key] = result
+        return result
 
 
 def _fill_layout(p, plan: _Plan) -> None:
@@ -350,6 +397,12 @@ def _backward(ctx, do: Tensor, dlse: Optional[Tensor], dq=None, dk=None, dv=None
     bp.ccol_sh = plan.ccol.stride(0) if plan.ccol.size(0) > 1 else 0
     bp.row_sh = plan.row.stride(0) if plan.row.size(0) > 1 else 0
     bp.n_cols = plan.ccol.size(1) - 1
+    hdim = 3 - seq_dim
+    pairs = plan.kv_pairs(q.size(hdim), k.size(hdim), (k.size(seq_dim) + plan.block_size - 1) // plan.block_size)
+    if pairs is not None:
+        bp.kv_pairs = _lib.ptr(pairs)
+        bp.kv_pairs_sh = pairs.stride(0) if pairs.size(0) > 1 else 0
+        bp.n_pairs = pairs.size(1)
     sq_pad = (q.size(seq_dim) + 63) // 64 * 64
     delta = torch.empty((2, q.size(0), q.size(3 - seq_dim), sq_pad), dtype=torch.float32, device=q.device)
     bp.delta = _lib.ptr(delta)

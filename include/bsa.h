@@ -162,6 +162,14 @@ typedef struct {
   int32_t n_cols;             /* pattern columns available in ccol              */
   float* delta;               /* fp32 workspace of 2 * batch * hq * (sq rounded up to a
                                  multiple of 64) elements, 16-byte aligned          */
+  /* Optional: which two kv blocks share a dK/dV tile of the tensor-core kernel (it computes
+   * 128 kv rows at a time and walks the union of the two blocks' CSC columns, so blocks with
+   * similar columns should be paired).  int32 (pairs heads, n_pairs, 2), -1 = no partner;
+   * every kv block of a head appears exactly once; one table per kv head (kv_pairs_sh =
+   * elements between heads) or one for all (kv_pairs_sh = 0).  NULL: blocks 2i and 2i+1. */
+  const int32_t* kv_pairs;
+  int64_t kv_pairs_sh;
+  int32_t n_pairs;
 } bsa_bwd_params;
 
 int bsa_bwd(const bsa_bwd_params* p, void* stream);

@@ -139,3 +139,32 @@ def test_host_logic_without_gpu():
             dkernel_b200.get_sparse_attn_mask(2, 128)
         with pytest.raises(RuntimeError, match="no CPU path|CUDA"):
             dkernel_b200.SparseAttention(64, torch.ones(2, 2))
+
+
+def test_kv_block_pairing_table_for_the_dkdv_kernel():
+    """Host-side planning: the pairing of kv blocks handed to the tensor-core dK/dV kernel covers
+    every block once, shortens the unions for a local + vertical-stride pattern and is not
+    produced where pairing neighbours is as good."""
+    import numpy as np
+    from oracle import dkernel_oracle as O
+    from dkernel_b200.ops import _Plan
+    H, S, bs = 4, 4096, 64
+    bm = np.tril(np.ones((S // bs, S // bs), bool))[None] & O.block_mask(H, S, block_size=bs, local_blocks=8,
+                                                                         vert_stride=8).astype(bool)
+    as_i32 = lambda arrs: [torch.from_numpy(np.ascontiguousarray(a)).int() for a in arrs]
+    plan = _Plan(*as_i32(O.dense_to_crow_col(bm)), *as_i32(O.dense_to_ccol_row(bm)), bs, 0)
+    pairs = plan.kv_pairs(H, H, S // bs)
+    assert pairs is not None and pairs.shape == (H, S // bs // 2, 2) and pairs.dtype == torch.int32
+    for h in range(H):
+        assert sorted(pairs[h].flatten().tolist()) == list(range(S // bs))
+        union = sum(int((bm[h, :, a] | bm[h, :, b]).sum()) for a, b in pairs[h].tolist())
+        adjacent = sum(int((bm[h, :, c] | bm[h, :, c + 1]).sum()) for c in range(0, S // bs, 2))
+        assert union < 0.97 * adjacent
+    assert plan.kv_pairs(H, H, S // bs) is pairs                       # cached
+    # fewer key blocks than the pattern has: only those are paired, odd count leaves one alone
+    p5 = plan.kv_pairs(H, H, 31)
+    assert p5 is None or (p5.shape[1] == 16 and sorted(x for x in p5[0].flatten().tolist() if x >= 0) == list(range(31)))
+    # a dense causal pattern gains nothing: neighbours stay paired
+    dense = np.tril(np.ones((16, 16), bool))[None]
+    plan2 = _Plan(*as_i32(O.dense_to_crow_col(dense)), *as_i32(O.dense_to_ccol_row(dense)), bs, 0)
+    assert plan2.kv_pairs(1, 1, 16) is None
