@@ -55,8 +55,8 @@ int make_tmap_4d(Tmap4* out, const void* base, int elem_bytes, uint64_t d, uint6
   // nothing afterwards.
   thread_local bool context_bound = false;
   if (!context_bound) {
-    BSA_CHECK_CUDA(cudaFree(nullptr));
-    context_bound = true;
+    if (cudaFree(nullptr) == cudaSuccess) context_bound = true;
+    else (void)cudaGetLastError();   // e.g. refused during stream capture: the encode below decides
   }
   // The three outer dimensions are placed in order of increasing stride, so the
   // map looks like an ordinary padded row-major tensor whatever the caller's
