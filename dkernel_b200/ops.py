@@ -53,6 +53,31 @@ class _Plan:
         self.max_row_nnz = max_row_nnz
         self._group_shared: Dict[int, bool] = {}
         self._kv_pairs: Dict[Tuple[int, int, int], Optional[Tensor]] = {}
+        self._fine: Optional["_Plan"] = None
+
+    def for_kernels(self, q: Tensor) -> "_Plan":
+        """The layouts the prefill / backward kernels should read.  The tensor-core kernels work
+        on 64 x 64 blocks; a pattern with blocks of 128, 256, ... tokens is the same attention
+        as its refinement to 64-token blocks (every block becomes a square of sub-blocks; the
+        kernels mask the diagonal per element anyway), so such patterns get refined layouts
+        instead of falling back to the CUDA-core kernels."""
+        bs = self.block_size
+        if not (bs > 64 and bs % 64 == 0 and q.dtype in (torch.float16, torch.bfloat16) and q.size(-1) == 128):
+            return self
+        if self._fine is None:
+            from .utils import crow_col_to_dense, dense_to_crow_col, dense_to_ccol_row, zero_stride
+            f = bs // 64
+            n_cols = self.ccol.size(1) - 1
+            dense = crow_col_to_dense(self.crow, self.col, torch.uint8)
+            if dense.size(2) < n_cols:
+                dense = torch.nn.functional.pad(dense, (0, n_cols - dense.size(2)))
+            dense = dense.repeat_interleave(f, 1).repeat_interleave(f, 2).contiguous()
+            lay = list(dense_to_crow_col(dense)) + list(dense_to_ccol_row(dense, include_values=False))
+            lay = [x.to(torch.int32) for x in lay]
+            if lay[0].size(0) == 1:
+                lay = [zero_stride(x) for x in lay]
+            self._fine = _Plan(lay[0], lay[1], lay[2], lay[3], 64, self.max_row_nnz * f)
+        return self._fine
 
     def heads_shared_in_group(self, hq: int, hkv: int) -> bool:
         """True when all q heads of a kv group use the same pattern rows (then the
@@ -127,6 +152,8 @@ def _fill_layout(p, plan: _Plan) -> None:
 def _fwd_params(q, k, v, o, lse, seq_dim, plan: _Plan, sm_scale, causal, row_mode,
                 q_start=None, q_end=None, k_start=None, k_end=None, total_q=0, impl=0):
     p = _lib.FwdParams()
+    if impl != _lib.IMPL_GENERIC:
+        plan = plan.for_kernels(q)
     p.q, p.k, p.v, p.o, p.lse = _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(lse)
     p.q_sb, p.q_ss, p.q_sh = _strides_bsh(q, seq_dim)
     p.k_sb, p.k_ss, p.k_sh = _strides_bsh(k, seq_dim)
@@ -371,6 +398,8 @@ def _backward(ctx, do: Tensor, dlse: Optional[Tensor], dq=None, dk=None, dv=None
     """dQ / dK / dV of the un-padded forward (dkernel/ops/sparse_attn_bwd.py:724-852)."""
     q, k, v, o, lse = ctx.saved_tensors
     seq_dim, plan = ctx.seq_dim, ctx.plan
+    if ctx.bwd_impl != _lib.IMPL_GENERIC:
+        plan = plan.for_kernels(q)
     do = _tma_friendly(do)
     if dq is None:
         dq = torch.empty_like(q, memory_format=torch.contiguous_format)

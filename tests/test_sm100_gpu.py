@@ -36,6 +36,9 @@ CASES = [
     (1, 2, 2, 256, 640, torch.bfloat16, 1, dict(block_size=64, local_blocks=2, vert_stride=3)),
     (1, 6, 2, 448, 448, torch.float16, 1, dict(block_size=64, local_blocks=2, vert_stride=4, num_kv_heads=2)),
     (1, 4, 4, 512, 512, torch.bfloat16, 1, dict(block_size=64, local_blocks=8, vert_stride=1)),
+    # coarser pattern blocks are refined to 64-token blocks for the tensor-core kernels
+    (1, 4, 2, 1024, 1024, torch.bfloat16, 1, dict(block_size=128, local_blocks=2, vert_stride=3, num_kv_heads=2)),
+    (2, 2, 2, 700, 700, torch.float16, 2, dict(block_size=256, local_blocks=1, vert_stride=2)),
 ]
 
 
@@ -140,6 +143,7 @@ BWD_CASES = [
     (1, 2, 2, 256, 640, torch.bfloat16, 1, dict(block_size=64, local_blocks=2, vert_stride=3)),
     (1, 6, 2, 448, 448, torch.float16, 1, dict(block_size=64, local_blocks=2, vert_stride=4, num_kv_heads=2)),
     (1, 8, 1, 192, 192, torch.bfloat16, 1, dict(block_size=64, local_blocks=1, vert_stride=2, num_kv_heads=1)),
+    (1, 4, 2, 512, 512, torch.bfloat16, 1, dict(block_size=128, local_blocks=1, vert_stride=2, num_kv_heads=2)),
 ]
 
 
