@@ -38,7 +38,7 @@ CASES = [
     (1, 4, 4, 512, 512, torch.bfloat16, 1, dict(block_size=64, local_blocks=8, vert_stride=1)),
     # coarser pattern blocks are refined to 64-token blocks for the tensor-core kernels
     (1, 4, 2, 1024, 1024, torch.bfloat16, 1, dict(block_size=128, local_blocks=2, vert_stride=3, num_kv_heads=2)),
-    (2, 2, 2, 700, 700, torch.float16, 2, dict(block_size=256, local_blocks=1, vert_stride=2)),
+    (2, 2, 2, 700, 700, torch.float16, 2, dict(block_size=128, local_blocks=1, vert_stride=2)),
 ]
 
 
