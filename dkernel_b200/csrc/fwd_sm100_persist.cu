@@ -61,6 +61,11 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float y;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
+  return y;
+}
 template <bool BF16>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   if (BF16) {
@@ -331,8 +336,9 @@ fwd_persist_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tm
         for (int j = 0; j < 2 && j < n && ok; ++j) ok = issue_qk(g + j, j == n - 1);
         for (int j = 0; j < n && ok; ++j, ++g) {
           const int s = g & 1;
-          if (!mbar_wait(&tl->p_full[s], (g >> 1) & 1, wait_status, 414)) { ok = false; break; }
+          // V first: its probe is then off the path between the softmax publishing P and P V
           if (!mbar_wait(&tl->v_full[s], (g >> 1) & 1, wait_status, 415)) { ok = false; break; }
+          if (!mbar_wait(&tl->p_full[s], (g >> 1) & 1, wait_status, 414)) { ok = false; break; }
           // the previous tile's epilogue must have read O before it is overwritten
           if (j == 0 && ko > 0 && !mbar_wait(&tl->o_free, (ko - 1) & 1, wait_status, 416)) { ok = false; break; }
           tc_fence_after();
@@ -403,36 +409,39 @@ fwd_persist_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tm
       float m_used = -INFINITY, l = 0.f;
       for (int j = 0; j < n; ++j, ++g) {
         const int s = g & 1;
+        // everything that only depends on the block list is done before the barrier probe
+        const uint32_t ent = pl->list[j];
+        const int kbase = (int)(ent & 0x3fffu) * kBS;
+        const bool att = ((ent >> (14 + t)) & 1u) != 0 && hvalid;
+        int lim = k_len - kbase;
+        if (p.causal) lim = min(lim, qpos - kbase + 1);
         if (!mbar_wait(&tl->qk_done[s], (g >> 1) & 1, wait_status, 423)) { alive = false; break; }
         tc_fence_after();
         uint32_t sv[64];
         tmem_ld32(tS[s] + lane_off, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
         tmem_ld32(tS[s] + lane_off + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
         tmem_ld_wait();
-        const uint32_t ent = pl->list[j];
-        const int kbase = (int)(ent & 0x3fffu) * kBS;
-        const bool att = ((ent >> (14 + t)) & 1u) != 0 && hvalid;
         // Allowed columns of this block form a prefix: kpos < k_len and, when causal,
         // kpos <= qpos.  Raw logits are compared (sm_scale > 0); the scale is folded
         // into the exponent's FMA.
         float mx = -INFINITY;
         if (att) {
-          int lim = k_len - kbase;
-          if (p.causal) lim = min(lim, qpos - kbase + 1);
           if (lim < kBS) {
 #pragma unroll
             for (int c = 0; c < 64; ++c)
               if (c >= lim) sv[c] = 0xff800000u;  // -inf
           }
-          float m8[8];
+          float m4[4];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) m8[i] = __uint_as_float(sv[i]);
+          for (int i = 0; i < 4; ++i) m4[i] = max3(__uint_as_float(sv[3 * i]), __uint_as_float(sv[3 * i + 1]),
+                                                   __uint_as_float(sv[3 * i + 2]));
 #pragma unroll
-          for (int c = 8; c < 64; c += 8)
+          for (int c = 12; c < 60; c += 8)
 #pragma unroll
-            for (int i = 0; i < 8; ++i) m8[i] = fmaxf(m8[i], __uint_as_float(sv[c + i]));
-          mx = fmaxf(fmaxf(fmaxf(m8[0], m8[1]), fmaxf(m8[2], m8[3])),
-                     fmaxf(fmaxf(m8[4], m8[5]), fmaxf(m8[6], m8[7]))) * scale2;
+            for (int i = 0; i < 4; ++i)
+              m4[i] = max3(m4[i], __uint_as_float(sv[c + 2 * i]), __uint_as_float(sv[c + 2 * i + 1]));
+          mx = max3(max3(m4[0], m4[1], m4[2]), max3(m4[3], __uint_as_float(sv[60]), __uint_as_float(sv[61])),
+                    fmaxf(__uint_as_float(sv[62]), __uint_as_float(sv[63]))) * scale2;
         }
         float alpha = 1.f;
         bool need = false;
