@@ -37,6 +37,7 @@ sys.path.insert(0, ROOT)
 METRIC = "sparse_attn_attended_tflops"
 NOMINAL_BF16_TFLOPS = 2250.0
 NOMINAL_HBM_GBS = 8000.0
+E2E_CHUNK = 4096   # query rows per pipelined chunk of the end-to-end prefill step
 
 WORKLOADS = {
     # BASELINE.json configs[1..4]
@@ -241,11 +242,26 @@ def run_prefill(args, world, rank):
     out_host = torch.empty((B, S, hq_l, D), dtype=torch.bfloat16).pin_memory()
     lse_host = torch.empty((B, hq_l, S), dtype=torch.float32).pin_memory()
 
-    # The batch elements are independent, so the step is pipelined per element over three streams:
-    # host->device copy of element b+1, the module call on element b and the device->host copy of
-    # element b-1 overlap (PCIe is full duplex); the timed stream waits for the last copy out.
+    # The step is pipelined over three streams in chunks of E2E_CHUNK query rows: causal attention
+    # of rows [s0, s1) needs keys [0, s1) only, so chunk c is computed (q shorter than k, the
+    # module's chunked-prefill case) while the host->device copy of chunk c+1 and the device->host
+    # copy of chunk c-1 run (PCIe is full duplex); the timed stream waits for the last copy out.
+    # All chunk copies are contiguous; the LSE rows go out once per batch element.
     qd, kd, vd = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    lse_dev = torch.empty((B, hq_l, S), dtype=torch.float32, device="cuda")
     s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    chunk = max(cfg["block"], min(args.e2e_chunk, S))
+    # one module per chunk offset: the pattern rows of query rows [s0, s1) over keys [0, s1)
+    # (the reference's recipe for sequence partitions: get_sparse_attn_mask with
+    # q_start_position / kv_seqlen, then SparseAttention on the block mask)
+    from dkernel_b200 import SparseAttention, get_sparse_attn_mask
+    chunk_attn = {}
+    for s0 in range(0, S, chunk):
+        s1 = min(s0 + chunk, S)
+        bmask = get_sparse_attn_mask(Hq, s1 - s0, cfg["block"], cfg["local"], cfg["stride"], dtype=torch.uint8,
+                                     num_kv_heads=Hkv, q_start_position=s0, kv_start_position=0,
+                                     kv_seqlen=s1)[1]
+        chunk_attn[s0] = SparseAttention(cfg["block"], bmask[h0:h1].contiguous(), seq_dim=1, causal=True)
 
     def step_e2e():
         main = torch.cuda.current_stream()
@@ -253,23 +269,36 @@ def run_prefill(args, world, rank):
         s_out.wait_stream(main)
         with torch.no_grad():
             for b in range(B):
-                with torch.cuda.stream(s_in):
-                    qd[b].copy_(hq_host[b], non_blocking=True)
-                    kd[b].copy_(hk_host[b], non_blocking=True)
-                    vd[b].copy_(hv_host[b], non_blocking=True)
-                    ev_in = torch.cuda.Event()
-                    ev_in.record(s_in)
-                main.wait_event(ev_in)
-                o, l = attn(qd[b:b + 1], kd[b:b + 1], vd[b:b + 1], sm_scale=scale, return_lse=True)
-                ev_c = torch.cuda.Event()
-                ev_c.record(main)
-                with torch.cuda.stream(s_out):
-                    s_out.wait_event(ev_c)
-                    out_host[b:b + 1].copy_(o, non_blocking=True)
-                    lse_host[b:b + 1].copy_(l, non_blocking=True)
-                    o.record_stream(s_out)
-                    l.record_stream(s_out)
+                for s0 in range(0, S, chunk):
+                    s1 = min(s0 + chunk, S)
+                    with torch.cuda.stream(s_in):
+                        qd[b, s0:s1].copy_(hq_host[b, s0:s1], non_blocking=True)
+                        kd[b, s0:s1].copy_(hk_host[b, s0:s1], non_blocking=True)
+                        vd[b, s0:s1].copy_(hv_host[b, s0:s1], non_blocking=True)
+                        ev_in = torch.cuda.Event()
+                        ev_in.record(s_in)
+                    main.wait_event(ev_in)
+                    o, l = chunk_attn[s0](qd[b:b + 1, s0:s1], kd[b:b + 1, :s1], vd[b:b + 1, :s1],
+                                          sm_scale=scale, return_lse=True)
+                    lse_dev[b, :, s0:s1].copy_(l[0])
+                    ev_c = torch.cuda.Event()
+                    ev_c.record(main)
+                    with torch.cuda.stream(s_out):
+                        s_out.wait_event(ev_c)
+                        out_host[b, s0:s1].copy_(o[0], non_blocking=True)
+                        o.record_stream(s_out)
+                        if s1 == S:
+                            lse_host[b].copy_(lse_dev[b], non_blocking=True)
         main.wait_stream(s_out)
+
+    # the chunked step must reproduce the one-call result
+    with torch.no_grad():
+        o_full, l_full = attn(q, k, v, sm_scale=scale, return_lse=True)
+    step_e2e()
+    torch.cuda.synchronize()
+    assert (out_host.float() - o_full.cpu().float()).abs().max().item() <= 2e-2, "chunked e2e output differs"
+    assert (lse_host - l_full.cpu()).abs().max().item() <= 1e-3, "chunked e2e LSE differs"
+    del o_full, l_full
 
     e2e_steps = max(1, min(args.steps, 5))
     ms_e2e = time_steps(step_e2e, e2e_steps, 3, world)
@@ -292,6 +321,7 @@ def run_prefill(args, world, rank):
                    "l2": "inputs (q 256 MiB + k,v 64 MiB each per GPU) exceed the 126 MB L2"},
         "e2e": {"value": flops_all / (ms_e2e_max * 1e-3) / 1e12, "unit": "TFLOP/s",
                 "ms_per_step": ms_e2e_max,
+                "pipeline": f"chunked prefill, {chunk} query rows per module call, copies overlapped",
                 "h2d_bytes_per_step": (hq_host.numel() + hk_host.numel() + hv_host.numel()) * 2,
                 "d2h_bytes_per_step": out_host.numel() * 2 + lse_host.numel() * 4},
         "gpu_launches": args.steps,
@@ -594,6 +624,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="prefill", choices=list(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--e2e-chunk", type=int, default=E2E_CHUNK,
+                    help="prefill: query rows per pipelined chunk of the end-to-end step")
     ap.add_argument("--no-graph", action="store_true", help="decode: time eager module calls, not a CUDA graph")
     args = ap.parse_args()
     if args.impl == "reference":
