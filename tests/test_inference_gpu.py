@@ -69,6 +69,34 @@ def test_varlen_prefill_user_pattern(Hq, Hkv, D, dtype, bs, lens):
     assert_lse_close(lse, ref_lse)
 
 
+@pytest.mark.parametrize("impl", ["sm100", "generic"])
+def test_varlen_batched_chunked_prefill(impl):
+    """A packed batch that mixes whole prompts, decode tokens and prompt chunks whose earlier
+    part is already in the KV cache (q_len not in {1, k_len}; the chunk starts on a block
+    boundary).  The reference's kernel computes this case (pattern row from past_len + q
+    offset, dkernel/ops/sparse_attn_inference.py:507-514) but its host code refuses it
+    (:211-212); here the host does not look at the lengths, so it is served."""
+    from dkernel_b200 import SparseAttention
+    Hq, Hkv, D, bs, nb = 8, 2, 128, 64, 16
+    g = torch.Generator().manual_seed(3)
+    pat = torch.rand(Hq, nb, nb, generator=g) < 0.35
+    pat |= torch.eye(nb, dtype=torch.bool)[None]
+    pat &= torch.tril(torch.ones(nb, nb, dtype=torch.bool))[None]
+    q_lens = [64, 1, 130, 72, 300]
+    k_lens = [192, 300, 130, 200, 940]          # pasts 128, 299, 0, 128, 640
+    cu_q = torch.tensor([0] + list(np.cumsum(q_lens)), dtype=torch.int32)
+    cu_k = torch.tensor([0] + list(np.cumsum(k_lens)), dtype=torch.int32)
+    q, k, v = seeded_qkv(31, (sum(q_lens), Hq, D), (sum(k_lens), Hkv, D), torch.bfloat16)
+    ref, ref_lse = O.varlen_attention(q.float(), k.float(), v.float(), cu_k, pat.numpy().astype(np.uint8), bs,
+                                      cu_seqlens_q=cu_q)
+    with pytest.warns(UserWarning):
+        mod = SparseAttention(bs, pat.cuda(), impl=impl)
+    out, lse = mod(q.cuda(), k.cuda(), v.cuda(), cu_seqlen_k=cu_k.cuda(), cu_seqlen_q=cu_q.cuda(),
+                   return_lse=True)
+    assert_out_close(out, ref)
+    assert_lse_close(lse, ref_lse)
+
+
 @pytest.mark.parametrize("B,Hq,Hkv,S,D,dtype,seq_dim,pk,bps", [
     (5, 8, 2, 1024, 128, torch.bfloat16, 1, dict(block_size=64, local_blocks=4, vert_stride=4, num_kv_heads=2), 0),
     (3, 4, 4, 640, 64, torch.float16, 2, dict(block_size=64, local_blocks=2, vert_stride=3), 2),
