@@ -60,8 +60,9 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 
 // ------------------------------------------------------------------ delta
 // The workspace holds two arrays of batch x hq rows, each row padded to whole q blocks:
-// delta first, then lse * log2(e) (+inf for an empty row, so that P = 0).  Padding rows get
-// delta = 0 and +inf, which lets the dK/dV kernel copy a block's 64 values with one bulk copy.
+// -delta first, then -lse * log2(e) (-inf for an empty row, so that P = 0): both enter the
+// kernels as addends of packed fp32 operations.  Padding rows get 0 and -inf, which lets the
+// dK/dV kernel copy a block's 64 values with one bulk copy.
 __host__ __device__ inline int padded_sq(int sq) { return (sq + kBS - 1) / kBS * kBS; }
 
 // Eight lanes per (b, h, i) row of 128 elements (four rows per warp): a lane reads two
@@ -120,12 +121,12 @@ __global__ void bwd_delta_vec_kernel(bsa_bwd_params bp) {
   if (live && sub == 0) {
     if (!real) {
       bp.delta[w] = 0.f;
-      bp.delta[total + w] = INFINITY;
+      bp.delta[total + w] = -INFINITY;
     } else {
       if (bp.d_lse) s -= bp.d_lse[(int64_t)b * p.lse_sb + (int64_t)h * p.lse_sh + i];
-      bp.delta[w] = s;
+      bp.delta[w] = -s;
       const float l = p.lse[(int64_t)b * p.lse_sb + (int64_t)h * p.lse_sh + i];
-      bp.delta[total + w] = l == -INFINITY ? INFINITY : l * kLog2e;
+      bp.delta[total + w] = l == -INFINITY ? -INFINITY : -l * kLog2e;
     }
   }
 }
@@ -176,7 +177,7 @@ struct DkdvTail {
   uint64_t all_done;
   uint32_t tmem_base;
   int n_list;
-  // [stage][0 = lse*log2e, 1 = delta][row of the q block]: bulk-copied with the stage's tiles
+  // [stage][0 = -lse*log2e, 1 = -delta][row of the q block]: bulk-copied with the stage's tiles
   alignas(128) float ld[kQdoStages][2][kBS];
   uint32_t bits[2][kMaxBlocks / 32];
   uint32_t list[kMaxEntries];
@@ -376,6 +377,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
     const int kpos = kblk[t] * kBS + (r_kv & 63);
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
     const float scale2 = p.sm_scale * kLog2e;
+    const uint64_t scale_2 = f32x2(scale2, scale2);
     bool alive = true;
     for (int e = 0; e < n; ++e) {
       const int st = e % kQdoStages;
@@ -406,14 +408,19 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
         for (int c4 = 0; c4 < 4; ++c4) {
           const float4 l4 = *reinterpret_cast<const float4*>(lse_s + c4 * 4);
           const float4 d4 = *reinterpret_cast<const float4*>(del_s + c4 * 4);
-          const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
-          const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
+          // two columns per instruction: P = exp2(S c - lse), dS = P (dP - delta)
+          const uint64_t nl[2] = {f32x2(l4.x, l4.y), f32x2(l4.z, l4.w)};
+          const uint64_t nd[2] = {f32x2(d4.x, d4.y), f32x2(d4.z, d4.w)};
           float pv[4], dsv[4];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float x = ex2(fmaf(__uint_as_float(sv[c4 * 4 + i]), scale2, -ls[i]));
-            pv[i] = x;
-            dsv[i] = x * (__uint_as_float(dv[c4 * 4 + i]) - dl[i]);
+          for (int i = 0; i < 2; ++i) {
+            float x0, x1;
+            f32x2_split(fma_f32x2(f32x2(sv[c4 * 4 + 2 * i], sv[c4 * 4 + 2 * i + 1]), scale_2, nl[i]), x0, x1);
+            pv[2 * i] = ex2(x0);
+            pv[2 * i + 1] = ex2(x1);
+            f32x2_split(mul_f32x2(f32x2(pv[2 * i], pv[2 * i + 1]),
+                                  add_f32x2(f32x2(dv[c4 * 4 + 2 * i], dv[c4 * 4 + 2 * i + 1]), nd[i])),
+                        dsv[2 * i], dsv[2 * i + 1]);
           }
           pp[c4 * 2] = pack2<BF16>(pv[0], pv[1]);
           pp[c4 * 2 + 1] = pack2<BF16>(pv[2], pv[3]);
@@ -725,13 +732,14 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
     const float scale2 = p.sm_scale * kLog2e;
     const int q_row = qblk[t] * kBS + rr;
     const int qpos = past + q_row;
-    float lse2 = INFINITY, delta = 0.f;
+    float neg_lse = -INFINITY, neg_delta = 0.f;
     if (valid[t] && q_row < p.sq) {
       const float l = p.lse[(int64_t)b * p.lse_sb + (int64_t)head[t] * p.lse_sh + q_row];
-      lse2 = l == -INFINITY ? INFINITY : l * kLog2e;
-      delta = bp.delta[((int64_t)b * p.hq + head[t]) * padded_sq(p.sq) + q_row];
+      neg_lse = l == -INFINITY ? -INFINITY : -l * kLog2e;
+      neg_delta = bp.delta[((int64_t)b * p.hq + head[t]) * padded_sq(p.sq) + q_row];   // holds -delta
     }
-    const float neg_lse = -lse2;
+    const uint64_t scale_2 = f32x2(scale2, scale2), neg_lse2 = f32x2(neg_lse, neg_lse),
+                   neg_delta2 = f32x2(neg_delta, neg_delta);
     bool alive = true;
     for (int e = 0; e < n; ++e) {
       if (!mbar_wait(&tl->sdp_full[e & 1], (e >> 1) & 1, wait_status, 317)) { alive = false; break; }
@@ -757,10 +765,12 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
         }
 #pragma unroll
         for (int c2 = 0; c2 < 8; ++c2) {
-          const float x0 = ex2(fmaf(__uint_as_float(sv[2 * c2]), scale2, neg_lse));
-          const float x1 = ex2(fmaf(__uint_as_float(sv[2 * c2 + 1]), scale2, neg_lse));
-          ds[c2] = pack2<BF16>(x0 * (__uint_as_float(dv[2 * c2]) - delta),
-                               x1 * (__uint_as_float(dv[2 * c2 + 1]) - delta));
+          // two columns per instruction: P = exp2(S c - lse), dS = P (dP - delta)
+          float x0, x1, d0, d1;
+          f32x2_split(fma_f32x2(f32x2(sv[2 * c2], sv[2 * c2 + 1]), scale_2, neg_lse2), x0, x1);
+          f32x2_split(mul_f32x2(f32x2(ex2(x0), ex2(x1)),
+                                add_f32x2(f32x2(dv[2 * c2], dv[2 * c2 + 1]), neg_delta2)), d0, d1);
+          ds[c2] = pack2<BF16>(d0, d1);
         }
       } else {
 #pragma unroll

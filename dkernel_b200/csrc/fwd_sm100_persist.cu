@@ -460,17 +460,20 @@ fwd_persist_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tm
         // by the second half's exponentials and fewer packed values are live at a time
         const bool live = att && m_used != -INFINITY;
         const float neg_m = -m_used;
-        float sum[4] = {0.f, 0.f, 0.f, 0.f};
+        // two columns per fused multiply-add and per addition (packed fp32 pairs): the softmax
+        // warps are bound by instruction issue as much as by the exponential unit
+        const uint64_t scale_2 = f32x2(scale2, scale2), neg_m2 = f32x2(neg_m, neg_m);
+        uint64_t sum2[2] = {0ull, 0ull};
 #pragma unroll
         for (int hlf = 0; hlf < 2; ++hlf) {
           uint32_t pk[16];
           if (live) {
 #pragma unroll
             for (int c = 0; c < 16; ++c) {
-              const float p0 = ex2(fmaf(__uint_as_float(sv[hlf * 32 + 2 * c]), scale2, neg_m));
-              const float p1 = ex2(fmaf(__uint_as_float(sv[hlf * 32 + 2 * c + 1]), scale2, neg_m));
-              sum[(2 * c) & 3] += p0;
-              sum[(2 * c + 1) & 3] += p1;
+              float x0, x1;
+              f32x2_split(fma_f32x2(f32x2(sv[hlf * 32 + 2 * c], sv[hlf * 32 + 2 * c + 1]), scale_2, neg_m2), x0, x1);
+              const float p0 = ex2(x0), p1 = ex2(x1);
+              sum2[c & 1] = add_f32x2(sum2[c & 1], f32x2(p0, p1));
               pk[c] = pack2<BF16>(p0, p1);
             }
           } else {
@@ -479,6 +482,9 @@ fwd_persist_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tm
           }
           tmem_st16(tS[s] + lane_off + hlf * 16, pk);
         }
+        float sum[4];
+        f32x2_split(sum2[0], sum[0], sum[1]);
+        f32x2_split(sum2[1], sum[2], sum[3]);
         l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
         if (any && j > 0) {
           // rescale the accumulator rows whose maximum moved, once P V_{g-1} has landed
