@@ -338,8 +338,8 @@ def run_prefill(args, world, rank):
 
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel from
 # the committed ncu captures (profiles/*.md), one GPU, the full workload; None = not captured.
-# train: dK/dV 793.6 MB + dQ 664.9 MB (the roofline line covers both backward kernels).
-TRAFFIC = {"prefill": 688.9e6, "train": 793.6e6 + 664.9e6, "decode": 406.3e6, "varlen": None}
+# train: dK/dV 796.7 MB + dQ 664.6 MB (the roofline line covers both backward kernels).
+TRAFFIC = {"prefill": 684.5e6, "train": 796.7e6 + 664.6e6, "decode": 406.3e6, "varlen": None}
 
 
 def run_train(args, world, rank):
