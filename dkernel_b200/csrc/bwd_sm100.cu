@@ -198,6 +198,10 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
   uint8_t* sQdo = smem + kKVResident;    // stage s: Q_r at s*32K, dO_r at s*32K + 16K
   DkdvTail* tl = reinterpret_cast<DkdvTail*>(smem + kKVResident + kQdoStages * kQdoStageBytes);
 
+  // The dQ kernel is launched behind this one as a programmatic dependent and reads nothing
+  // this kernel writes: its CTAs may become resident as soon as every CTA of this grid has
+  // started, and fill the SMs that the last, uneven wave of this grid leaves idle.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (*reinterpret_cast<volatile int*>(wait_status) != 0) return;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int c2 = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
@@ -528,7 +532,11 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
   uint8_t* sVs = sKs + kDqKStages * kTileKV;
   DqTail* tl = reinterpret_cast<DqTail*>(sVs + kDqVStages * kTileKV);
 
-  if (*reinterpret_cast<volatile int*>(wait_status) != 0) return;
+  // Launched as a programmatic dependent of the dK/dV kernel, whose results it does not read
+  // (a no-op after a plain launch).  No CTA leaves before that grid has completed, so that
+  // whatever follows this kernel in the stream also follows the dK/dV kernel.
+  auto wait_for_dkdv = [] { asm volatile("griddepcontrol.wait;" ::: "memory"); };
+  if (*reinterpret_cast<volatile int*>(wait_status) != 0) { wait_for_dkdv(); return; }
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int G = p.hq / p.hkv;
   const int b = blockIdx.z;
@@ -550,7 +558,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
     valid[0] = 1;
     valid[1] = qblk[1] * kBS < p.sq ? 1 : 0;
   }
-  if (qblk[0] * kBS >= p.sq) return;
+  if (qblk[0] * kBS >= p.sq) { wait_for_dkdv(); return; }
   const int nkb = min((p.sk + kBS - 1) / kBS, kMaxBlocks);
 
   if (tid == 0) {
@@ -826,6 +834,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
   tc_fence_before();
   __syncthreads();
   if (warp == kWarpIssueA) tmem_dealloc(tmem, 512);
+  wait_for_dkdv();
 }
 
 bool rows8(const void* ptr, int64_t ss, int64_t sh, int64_t sb) {
@@ -871,7 +880,18 @@ int launch_bwd(const bsa_bwd_params* bp, cudaStream_t s) {
     BSA_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDqSmem));
     dim3 grid(cdiv_i(p->sq, mode == kPairHeads ? 64 : 128), mode == kPairHeads ? p->hq / 2 : p->hq,
               p->batch);
-    kern<<<grid, kBwdThreads, kDqSmem, s>>>(tmQ, tmK, tmV, tmDO, *bp, mode, status);
+    // programmatic dependent of the dK/dV kernel (see the kernels' first lines)
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kBwdThreads);
+    cfg.dynamicSmemBytes = kDqSmem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    BSA_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, tmQ, tmK, tmV, tmDO, *bp, mode, status));
     rc = check_launch("bwd_dq_sm100_kernel");
   }
   return rc;
