@@ -5,17 +5,26 @@
     torchrun --nproc-per-node N ... bench.py --gpus N --steps K --warmup W
     python bench.py --impl reference ...      # CPU restatement of the reference path
 
-One JSON line on stdout (rank 0).  The default workload is BASELINE config 2
+One JSON line on stdout (rank 0).  The headline is BASELINE config 2
 (Phi-3-small-shape local-stride prefill forward): a step is one forward pass
 over one synthetic batch; ``value`` = attended-block TFLOP/s of the whole job
 with inputs resident in HBM; ``e2e`` = the same through the module API with
-pinned host inputs copied in and the output copied back every step.
+pinned host inputs copied in and the output copied back every step.  Every
+timed region is exactly K steps between CUDA events; it is repeated (5 times by
+default) and the median is reported with the spread.
+
+The default run (``--workload all``) also times the rest of the metric and puts
+compact numeric sub-records under ``config.sub`` (and their roofline fractions
+under ``roofline.sub``): at one GPU the training step of config 3 (forward,
+backward), the decode step of config 4 (CUDA-graph replay and eager calls), the
+packed varlen prefill of config 5 and a head-dim-64 prefill; at N > 1 the
+KV-sharded decode step (peer-store exchange kernel and NCCL all-gather route,
+both checked against the one-GPU decode of the same cache before timing), and
+configs 2 and 5 at fixed total size with heads sharded ("strong").
 
 Multi-GPU (one process per GPU): q heads are sharded over the ranks through
 ``active_head_range`` (no collective on the data path) and the batch grows with
-the world size, so per-GPU work is constant ("weak").  ``--workload decode`` at
-N > 1 shards the KV sequence and merges partial (O, LSE) after one NCCL
-all-gather.
+the world size, so per-GPU work of the headline is constant ("weak").
 """
 from __future__ import annotations
 
@@ -58,31 +67,75 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi SM clock / throttle reasons sampled while the timed region runs."""
+    """SM clock and throttle reasons sampled while a timed region runs: NVML polled from a thread
+    every few milliseconds (a timed region lasts tens of milliseconds), nvidia-smi as fallback."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown",
+               0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown"}
 
-    def __init__(self, gpu_index: int):
-        self.gpu = gpu_index
-        self.proc = None
-        self.lines = []
+    def __init__(self, gpu_index: int, period_s: float = 0.004):
+        self.gpu, self.period = gpu_index, period_s
+        self.proc = self.thread = self.handle = None
+        self.lines, self.sm, self.bits, self.power = [], [], 0, []
+        self.stop_flag = threading.Event()
+        self.max_mhz = None
+
+    def _physical_index(self):
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            try:
+                return int(vis.split(",")[self.gpu])
+            except (ValueError, IndexError):
+                return self.gpu
+        return self.gpu
 
     def start(self):
         try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(self._physical_index())
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self.thread = threading.Thread(target=self._poll, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.handle = None
+        try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
-                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.t = threading.Thread(target=self._read, daemon=True)
-            self.t.start()
+                 "-i", str(self._physical_index())], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
         except OSError:
             self.proc = None
+
+    def _poll(self):
+        nv = self.nv
+        while not self.stop_flag.is_set():
+            try:
+                self.sm.append(float(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)))
+                self.bits |= int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle))
+                self.power.append(nv.nvmlDeviceGetPowerUsage(self.handle) / 1000.0)
+            except Exception:
+                pass
+            time.sleep(self.period)
 
     def _read(self):
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
     def stop(self):
+        if self.handle is not None:
+            self.stop_flag.set()
+            self.thread.join(timeout=1)
+            reasons = sorted(name for bit, name in self.REASONS.items() if self.bits & bit)
+            return {"sm_mhz": float(np.median(self.sm)) if self.sm else None,
+                    "sm_min_mhz": float(min(self.sm)) if self.sm else None, "sm_max_mhz": self.max_mhz,
+                    "reasons": reasons, "samples": len(self.sm),
+                    "power_w_max": float(max(self.power)) if self.power else None, "source": "nvml"}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.15)
@@ -106,7 +159,7 @@ class ClockSampler:
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "source": "nvidia-smi"}
 
 
 # --------------------------------------------------------------------------- work accounting
@@ -169,59 +222,117 @@ def sum_over_ranks(x: float, world: int) -> float:
     return float(t.item())
 
 
-def time_steps(fn, steps, warmup, world):
-    """W warm-up steps, then exactly K steps between CUDA events on the launching
-    stream, bracketed by barrier + synchronize; returns ms per step (this rank)."""
+REPEATS = 5
+
+
+def time_steps(fn, steps, warmup, world, repeats=None):
+    """W warm-up steps, then `repeats` timed regions of exactly K steps each, every region
+    between CUDA events on the launching stream and bracketed by barrier + synchronize.
+    Returns (median ms per step of this rank, [ms per step of every region])."""
+    repeats = repeats or REPEATS
     for _ in range(warmup):
         fn()
-    barrier_sync(world)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps):
-        fn()
-    e1.record()
-    barrier_sync(world)
-    return e0.elapsed_time(e1) / steps
+    regions = []
+    for _ in range(repeats):
+        barrier_sync(world)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier_sync(world)
+        regions.append(e0.elapsed_time(e1) / steps)
+    return float(np.median(regions)), regions
 
 
-def cpu_baseline_c1(max_seconds=20.0):
+def timed(fn, steps, warmup, world, repeats=None):
+    """time_steps with the clocks sampled over all regions and the max over ranks taken.
+    Returns (ms median max-over-ranks, spread dict, clocks dict, ms of this rank)."""
+    sampler = ClockSampler(torch.cuda.current_device())
+    sampler.start()
+    ms, regions = time_steps(fn, steps, warmup, world, repeats)
+    clocks = sampler.stop()
+    ms_max = max_over_ranks(ms, world)
+    spread = {"ms_min": min(regions), "ms_max": max(regions), "repeats": len(regions)}
+    return ms_max, spread, clocks, ms
+
+
+def cpu_baseline_c1(max_seconds=12.0):
     """BASELINE config 1 on the host cores: the masked-dense torch path of the
-    reference (restated in oracle/), fp32, all threads.  Returns the dict for the
-    JSON line; value is attended-block TFLOP/s (620 tiles of 64x64x64)."""
+    reference (restated in oracle/), fp32, with all threads and with one.  Returns the dict for
+    the JSON line; value is attended-block TFLOP/s (620 tiles of 64x64x64)."""
     from oracle import dkernel_oracle as O
     torch.manual_seed(0)
     q, k, v = (torch.randn(1, 1024, 8, 64) for _ in range(3))
     bm = O.block_mask(8, 1024, 64, 4, 4)
     dense = O.token_mask(bm, 64, 1024, 1024)
     cores = torch.get_num_threads()
-    O.masked_dense_attention(q, k, v, dense, 0.125, seq_dim=1)
-    best, t_start, n = float("inf"), time.time(), 0
-    while n < 5 or (time.time() - t_start < 2.0 and n < 50):
-        t0 = time.perf_counter()
-        O.masked_dense_attention(q, k, v, dense, 0.125, seq_dim=1)
-        best = min(best, time.perf_counter() - t0)
-        n += 1
-        if time.time() - t_start > max_seconds:
-            break
     flops = int(bm.sum()) * 4.0 * 64 * 64 * 64
+
+    def best_of(budget):
+        O.masked_dense_attention(q, k, v, dense, 0.125, seq_dim=1)
+        best, t_start, n = float("inf"), time.time(), 0
+        while n < 5 or (time.time() - t_start < 2.0 and n < 50):
+            t0 = time.perf_counter()
+            O.masked_dense_attention(q, k, v, dense, 0.125, seq_dim=1)
+            best = min(best, time.perf_counter() - t0)
+            n += 1
+            if time.time() - t_start > budget:
+                break
+        return best, n
+
+    best, n = best_of(max_seconds * 0.6)
+    torch.set_num_threads(1)
+    best1, n1 = best_of(max_seconds * 0.4)
+    torch.set_num_threads(cores)
     return {"value": flops / best / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+            "value_1thread": flops / best1 / 1e12,
             "sample": f"BASELINE config 1 (B1,S1024,H8,D64,fp32, block 64, local 4, stride 4), "
-                      f"masked-dense oracle, best of {n} runs = {best * 1e3:.2f} ms"}
+                      f"masked-dense oracle, best of {n} runs = {best * 1e3:.2f} ms on {cores} threads, "
+                      f"best of {n1} = {best1 * 1e3:.2f} ms on 1 thread"}
 
 
-def run_prefill(args, world, rank):
+def _free():
+    import gc
+    gc.collect()
+    torch.cuda.empty_cache()
+
+
+def tensor_roofline(tflops, kernel, traffic=None, source=None):
+    peaks = measured_peaks()
+    r = {"bound": "tensor", "achieved": tflops, "peak": peaks["tflops"], "unit": "TFLOP/s",
+         "frac": tflops / peaks["tflops"], "traffic": traffic,
+         "peak_source": peaks["source"] + " (burst)",
+         "frac_of_sustained": tflops / peaks["tflops_sustained"] if peaks["tflops_sustained"] else None,
+         "frac_of_nominal_2250": tflops / NOMINAL_BF16_TFLOPS, "kernel": kernel}
+    if traffic is not None:
+        r["traffic_source"] = source or "ncu capture of the same workload (profiles/), not measured in this run"
+    return r
+
+
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel, taken
+# from ncu captures of the same full-size workloads on one GPU; None = not captured.
+# train: dK/dV 796.7 MB + dQ 664.6 MB (the roofline line covers both backward kernels).
+TRAFFIC = {"prefill": 684.5e6, "train": 796.7e6 + 664.6e6, "decode": 406.3e6, "varlen": None}
+
+
+def run_prefill(args, world, rank, strong=False, with_e2e=True):
+    """BASELINE config 2.  strong=False: 4 sequences per GPU, heads sharded (weak scaling, the
+    headline); strong=True: the one-GPU problem (B=4) with its heads split over the ranks."""
     from dkernel_b200 import LocalStrideSparseAttention, _lib
     from dkernel_b200.dist import head_shard
     cfg = WORKLOADS["prefill"]
-    B, S, Hq, Hkv, D = cfg["B"] * world, cfg["S"], cfg["Hq"], cfg["Hkv"], cfg["D"]
+    B, S, Hq, Hkv, D = cfg["B"] * (1 if strong else world), cfg["S"], cfg["Hq"], cfg["Hkv"], cfg["D"]
     (h0, h1), (kv0, kv1) = head_shard(Hq, Hkv, rank, world)
     hq_l, hkv_l = h1 - h0, kv1 - kv0
     attn = LocalStrideSparseAttention(Hq, S, cfg["block"], cfg["local"], cfg["stride"], num_kv_heads=Hkv,
                                       active_head_range=(h0, h1) if world > 1 else None, seq_dim=1)
     g = torch.Generator().manual_seed(1234 + rank)
-    hq_host = torch.randn((B, S, hq_l, D), generator=g).to(torch.bfloat16).pin_memory()
-    hk_host = torch.randn((B, S, hkv_l, D), generator=g).to(torch.bfloat16).pin_memory()
-    hv_host = torch.randn((B, S, hkv_l, D), generator=g).to(torch.bfloat16).pin_memory()
+    hq_host = torch.randn((B, S, hq_l, D), generator=g).to(torch.bfloat16)
+    hk_host = torch.randn((B, S, hkv_l, D), generator=g).to(torch.bfloat16)
+    hv_host = torch.randn((B, S, hkv_l, D), generator=g).to(torch.bfloat16)
+    if with_e2e:
+        hq_host, hk_host, hv_host = hq_host.pin_memory(), hk_host.pin_memory(), hv_host.pin_memory()
     q, k, v = hq_host.cuda(), hk_host.cuda(), hv_host.cuda()
     scale = 1.0 / math.sqrt(D)
     mask = local_stride_mask_np(Hq, S, cfg["block"], cfg["local"], cfg["stride"], Hkv)[h0:h1]
@@ -232,11 +343,35 @@ def run_prefill(args, world, rank):
         with torch.no_grad():
             attn(q, k, v, sm_scale=scale, return_lse=True)
 
-    sampler = ClockSampler(torch.cuda.current_device())
-    sampler.start()
-    ms = time_steps(step, args.steps, args.warmup, world)
-    clocks = sampler.stop()
+    ms_max, spread, clocks, ms = timed(step, args.steps, args.warmup, world)
     assert _lib.wait_status() == 0, "a device-side wait gave up: results invalid"
+    flops_all = sum_over_ranks(flops, world)
+    kernel_tflops = flops / (ms * 1e-3) / 1e12
+    if strong:
+        return {"ms": ms_max, "tflops": flops_all / (ms_max * 1e-3) / 1e12, "B": B, "scaling": "strong",
+                "tiles": int(round(flops_all / tile_flops(cfg["block"], D))), **spread,
+                "sm_mhz": clocks.get("sm_mhz"), "reasons": clocks.get("reasons")}
+
+    line = {
+        "metric": METRIC, "value": flops_all / (ms_max * 1e-3) / 1e12, "unit": "TFLOP/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_max,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": "prefill_fwd: BASELINE config 2 (Phi-3-small shape), B=%d (4 per GPU), S=8192, "
+                               "Hq=32, Hkv=8, D=128, block 64, local 16, stride 8, causal, return_lse" % B,
+                   "parallelism": f"heads sharded over {world} GPU(s) via active_head_range, no collective",
+                   "attended_tiles_per_step": int(round(flops_all / tile_flops(cfg["block"], D))),
+                   "flops_convention": "4*64*64*128 per attended block, diagonal blocks counted full",
+                   "l2": "inputs (q 256 MiB + k,v 64 MiB each per GPU) exceed the 126 MB L2",
+                   "timing": f"median of {spread['repeats']} regions of {args.steps} steps",
+                   **spread},
+        "gpu_launches": args.steps,
+        "clocks": clocks,
+        "roofline": {**tensor_roofline(kernel_tflops, "fwd_persist_kernel<bf16,128>", TRAFFIC.get("prefill")),
+                     "kernel_ms": ms},
+    }
+    if not with_e2e:
+        return line
 
     # e2e: pinned host -> device, forward through the public API, output -> pinned host
     out_host = torch.empty((B, S, hq_l, D), dtype=torch.bfloat16).pin_memory()
@@ -301,45 +436,14 @@ def run_prefill(args, world, rank):
     del o_full, l_full
 
     e2e_steps = max(1, min(args.steps, 5))
-    ms_e2e = time_steps(step_e2e, e2e_steps, 3, world)
-
-    ms_max = max_over_ranks(ms, world)
+    ms_e2e, _ = time_steps(step_e2e, e2e_steps, 3, world, repeats=3)
     ms_e2e_max = max_over_ranks(ms_e2e, world)
-    flops_all = sum_over_ranks(flops, world)
-    peaks = measured_peaks()
-    kernel_tflops = flops / (ms * 1e-3) / 1e12
-    line = {
-        "metric": METRIC, "value": flops_all / (ms_max * 1e-3) / 1e12, "unit": "TFLOP/s",
-        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_max,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-        "data": "synthetic",
-        "config": {"workload": "prefill_fwd: BASELINE config 2 (Phi-3-small shape), B=%d (4 per GPU), S=8192, "
-                               "Hq=32, Hkv=8, D=128, block 64, local 16, stride 8, causal, return_lse" % B,
-                   "parallelism": f"heads sharded over {world} GPU(s) via active_head_range, no collective",
-                   "attended_tiles_per_step": int(round(flops_all / tile_flops(cfg["block"], D))),
-                   "flops_convention": "4*64*64*128 per attended block, diagonal blocks counted full",
-                   "l2": "inputs (q 256 MiB + k,v 64 MiB each per GPU) exceed the 126 MB L2"},
-        "e2e": {"value": flops_all / (ms_e2e_max * 1e-3) / 1e12, "unit": "TFLOP/s",
-                "ms_per_step": ms_e2e_max,
-                "pipeline": f"chunked prefill, {chunk} query rows per module call, copies overlapped",
-                "h2d_bytes_per_step": (hq_host.numel() + hk_host.numel() + hv_host.numel()) * 2,
-                "d2h_bytes_per_step": out_host.numel() * 2 + lse_host.numel() * 4},
-        "gpu_launches": args.steps,
-        "clocks": clocks,
-        "roofline": {"bound": "tensor", "achieved": kernel_tflops, "peak": peaks["tflops"],
-                     "unit": "TFLOP/s", "frac": kernel_tflops / peaks["tflops"],
-                     "traffic": TRAFFIC.get("prefill"), "peak_source": peaks["source"] + " (burst)",
-                     "frac_of_sustained": kernel_tflops / peaks["tflops_sustained"] if peaks["tflops_sustained"] else None,
-                     "frac_of_nominal_2250": kernel_tflops / NOMINAL_BF16_TFLOPS,
-                     "kernel": "fwd_persist_kernel<bf16>", "kernel_ms": ms},
-    }
+    line["e2e"] = {"value": flops_all / (ms_e2e_max * 1e-3) / 1e12, "unit": "TFLOP/s",
+                   "ms_per_step": ms_e2e_max, "steps_per_region": e2e_steps,
+                   "pipeline": f"chunked prefill, {chunk} query rows per module call, copies overlapped",
+                   "h2d_bytes_per_step": (hq_host.numel() + hk_host.numel() + hv_host.numel()) * 2,
+                   "d2h_bytes_per_step": out_host.numel() * 2 + lse_host.numel() * 4}
     return line
-
-
-# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel from
-# the committed ncu captures (profiles/*.md), one GPU, the full workload; None = not captured.
-# train: dK/dV 796.7 MB + dQ 664.6 MB (the roofline line covers both backward kernels).
-TRAFFIC = {"prefill": 684.5e6, "train": 796.7e6 + 664.6e6, "decode": 406.3e6, "varlen": None}
 
 
 def run_train(args, world, rank):
@@ -351,8 +455,8 @@ def run_train(args, world, rank):
     hl = h1 - h0
     attn = LocalStrideSparseAttention(Hq, S, cfg["block"], cfg["local"], cfg["stride"],
                                       active_head_range=(h0, h1) if world > 1 else None, seq_dim=1)
-    g = torch.Generator().manual_seed(99 + rank)
-    q, k, v, do = (torch.randn((B, S, hl, D), generator=g).to(torch.bfloat16).cuda() for _ in range(4))
+    g = torch.Generator(device="cuda").manual_seed(99 + rank)
+    q, k, v, do = (torch.randn((B, S, hl, D), generator=g, device="cuda").to(torch.bfloat16) for _ in range(4))
     q.requires_grad_(), k.requires_grad_(), v.requires_grad_()
     mask = local_stride_mask_np(Hq, S, cfg["block"], cfg["local"], cfg["stride"], Hq)[h0:h1]
     tiles = int(mask.sum()) * B
@@ -367,14 +471,10 @@ def run_train(args, world, rank):
         with torch.no_grad():
             attn(q, k, v, return_lse=True)
 
-    ms_fwd = max_over_ranks(time_steps(step_fwd, args.steps, args.warmup, world), world)
-    sampler = ClockSampler(torch.cuda.current_device())
-    sampler.start()
-    ms = max_over_ranks(time_steps(step, args.steps, args.warmup, world), world)
-    clocks = sampler.stop()
+    ms_fwd, _, _, _ = timed(step_fwd, args.steps, args.warmup, world)
+    ms, spread, clocks, _ = timed(step, args.steps, args.warmup, world)
     assert _lib.wait_status() == 0
     total = sum_over_ranks(fwd_flops * 3.5, world)
-    peaks = measured_peaks()
     bwd_ms = ms - ms_fwd
     bwd_tflops = sum_over_ranks(fwd_flops * 2.5, world) / world / (bwd_ms * 1e-3) / 1e12
     return {
@@ -384,21 +484,18 @@ def run_train(args, world, rank):
         "config": {"workload": "train fwd+bwd: BASELINE config 3, B=%d (2 per GPU), S=8192, H=32, D=128, "
                                "block 64, local 32, stride 8; FLOPs = 3.5 x forward (5 backward GEMMs, "
                                "recomputation not counted)" % B,
-                   "fwd_ms": ms_fwd, "bwd_ms": bwd_ms},
+                   "fwd_ms": ms_fwd, "bwd_ms": bwd_ms, **spread,
+                   "fwd_tflops": sum_over_ranks(fwd_flops, world) / world / (ms_fwd * 1e-3) / 1e12,
+                   "executed_products_per_block": 7, "algorithmic_products_per_block": 5},
         "gpu_launches": args.steps * 4, "clocks": clocks,
-        "roofline": {"bound": "tensor", "achieved": bwd_tflops, "peak": peaks["tflops"], "unit": "TFLOP/s",
-                     "frac": bwd_tflops / peaks["tflops"], "traffic": TRAFFIC.get("train"),
-                     "peak_source": peaks["source"] + " (burst)",
-                     "frac_of_sustained": bwd_tflops / peaks["tflops_sustained"] if peaks["tflops_sustained"] else None,
-                     "kernel": "bwd_dkdv_sm100_kernel + bwd_dq_sm100_kernel (+ delta pre-pass)"},
+        "roofline": tensor_roofline(bwd_tflops, "bwd_dkdv_sm100_kernel + bwd_dq_sm100_kernel (+ delta pre-pass)",
+                                    TRAFFIC.get("train")),
     }
 
 
-def decode_inputs(cfg, rank_seed=0):
-    B, S, Hq, Hkv, D = cfg["B"], cfg["S"], cfg["Hq"], cfg["Hkv"], cfg["D"]
+def decode_lens(cfg):
     g = torch.Generator().manual_seed(0)
-    lens = torch.randint(1024, 8193, (B,), generator=g)
-    return lens
+    return torch.randint(1024, 8193, (cfg["B"],), generator=g)
 
 
 def attended_kv_tokens(lens, mask_kv, block):
@@ -412,27 +509,49 @@ def attended_kv_tokens(lens, mask_kv, block):
     return total
 
 
+def _graph_of(calls, n):
+    """Capture `n` consecutive calls of `calls()` in one CUDA graph (after running them once)."""
+    graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for _ in range(n):
+            calls()
+        torch.cuda.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            for _ in range(n):
+                calls()
+    torch.cuda.synchronize()
+    return graph
+
+
 def run_decode(args, world, rank):
+    """BASELINE config 4.  One GPU: the module call (decode kernel + split merge), timed as a
+    replayed CUDA graph and as eager calls.  N > 1: every sequence's KV sharded over the ranks;
+    the merged result of both exchange routes is checked against the one-GPU decode of the same
+    cache on every rank before anything is timed."""
     from dkernel_b200 import LocalStrideSparseAttention, _lib
-    from dkernel_b200.dist import kv_shard_ranges, sharded_decode
+    from dkernel_b200.dist import ShardedDecoder, kv_shard_ranges, pack_kv_shard, sharded_decode
     cfg = WORKLOADS["decode"]
     B, S, Hq, Hkv, D, bs = cfg["B"], cfg["S"], cfg["Hq"], cfg["Hkv"], cfg["D"], cfg["block"]
-    lens = decode_inputs(cfg)
+    lens = decode_lens(cfg)
     attn = LocalStrideSparseAttention(Hq, S, bs, cfg["local"], cfg["stride"], num_kv_heads=Hkv, seq_dim=1)
-    g = torch.Generator().manual_seed(7)
-    q = torch.randn((B, 1, Hq, D), generator=g).to(torch.bfloat16).cuda()
+    g = torch.Generator(device="cuda").manual_seed(7)      # the same stream of numbers on every rank
+    q = torch.randn((B, 1, Hq, D), generator=g, device="cuda").to(torch.bfloat16)
     mask_kv = local_stride_mask_np(Hq, S, bs, cfg["local"], cfg["stride"], Hkv)[::Hq // Hkv]
     tokens = attended_kv_tokens(lens, mask_kv, bs)
     bytes_alg = tokens * D * 2 * 2 + 2 * B * Hq * D * 2
     scale = 1.0 / math.sqrt(D)
-    nbuf = 4 if world == 1 else 2            # rotate K/V buffers so the L2 never holds the next step's data
+    left = (S - lens).to(torch.int32).cuda()
+    steps = max(4, args.steps // 4 * 4)
+    rec = {"algorithmic_bytes_per_step": bytes_alg, "steps": steps}
+    peaks = measured_peaks()
+
+    def make_kv():
+        return (torch.randn((B, S, Hkv, D), generator=g, device="cuda").to(torch.bfloat16),
+                torch.randn((B, S, Hkv, D), generator=g, device="cuda").to(torch.bfloat16))
+
     if world == 1:
-        left = (S - lens).to(torch.int32).cuda()
-        bufs = []
-        for i in range(nbuf):
-            k = torch.randn((B, S, Hkv, D), generator=g).to(torch.bfloat16).cuda()
-            v = torch.randn((B, S, Hkv, D), generator=g).to(torch.bfloat16).cuda()
-            bufs.append((k, v))
+        nbuf = 4                               # rotate K/V buffers so the L2 never holds the next step's data
+        bufs = [make_kv() for _ in range(nbuf)]
         it = [0]
 
         def eager_step():
@@ -440,121 +559,181 @@ def run_decode(args, world, rank):
             it[0] += 1
             with torch.no_grad():
                 attn(q, k, v, sm_scale=scale, left_paddings=left, return_lse=True)
-        launches = 2
-    else:
-        lo, hi = kv_shard_ranges(lens, rank, world, bs)
-        n = (hi - lo).clamp_min(0)
-        cap = int(((S // world + bs - 1) // bs + 1) * bs)
-        bufs = []
-        for i in range(nbuf):
-            ks = torch.randn((B, cap, Hkv, D), generator=g).to(torch.bfloat16).cuda()
-            vs = torch.randn((B, cap, Hkv, D), generator=g).to(torch.bfloat16).cuda()
-            bufs.append((ks, vs))
-        n_d, lo_d, len_d = (t.to(torch.int32).cuda() for t in (n, lo, lens))
-        it = [0]
 
-        def eager_step():
-            ks, vs = bufs[it[0] % nbuf]
+        ms_eager, _, _, _ = timed(eager_step, steps, args.warmup, world)
+        it[0] = 0
+        graph = _graph_of(eager_step, nbuf)
+
+        def graph_step():
+            if it[0] % nbuf == 0:
+                graph.replay()
             it[0] += 1
-            with torch.no_grad():
-                sharded_decode(attn, q, ks, vs, n_d, lo_d, len_d, scale)
-        launches = 4   # decode, split merge, NCCL all-gather, partition merge
-    step, launch_mode = eager_step, "eager calls"
-    if not args.no_graph and args.steps % nbuf == 0:
-        # A decode step is a few short kernels (and, sharded, one small all-gather): the call is
-        # captured once per K/V buffer set and replayed, as a serving loop would, so that the step
-        # is not bound by the Python launch path.
-        try:
-            graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
-            with torch.cuda.stream(side):
-                for _ in range(nbuf):
-                    eager_step()
-                torch.cuda.synchronize()
-                with torch.cuda.graph(graph, stream=side):
-                    for _ in range(nbuf):
-                        eager_step()
-            torch.cuda.synchronize()
+        it[0] = 0
+        ms, spread, clocks, _ = timed(graph_step, steps, args.warmup, world)
+        assert _lib.wait_status() == 0
+        gbs = bytes_alg / (ms * 1e-3) / 1e9
+        rec.update({"us_graph": ms * 1e3, "us_eager": ms_eager * 1e3, "gbs": gbs, "hbm_frac": gbs / peaks["hbm"],
+                    "hbm_frac_of_nominal_8000": gbs / NOMINAL_HBM_GBS, **spread,
+                    "launch": f"CUDA graph of {nbuf} module calls (one per K/V buffer set) replayed; "
+                              "us_eager = the same calls made from Python",
+                    "l2": f"{nbuf} K/V buffer sets rotated ({nbuf}x{2 * B * S * Hkv * D * 2 / 2**20:.0f} MiB)",
+                    "sm_mhz": clocks.get("sm_mhz"), "reasons": clocks.get("reasons"), "launches_per_step": 2})
+        return rec, ms, clocks, gbs
 
-            def step():
+    # ---- N > 1: shards of ONE seeded cache (identical on every rank), checked, then timed
+    k_full, v_full = make_kv()
+    with torch.no_grad():
+        ref_o, ref_lse = attn(q, k_full, v_full, sm_scale=scale, left_paddings=left, return_lse=True)
+    lo, hi = kv_shard_ranges(lens, rank, world, bs)
+    cap = int(((S // world + bs - 1) // bs + 1) * bs)
+    ks, vs, n = pack_kv_shard(k_full, v_full, left.cpu(), lo, hi, capacity=cap)
+    del k_full, v_full
+    n_d, lo_d, len_d = (t.to(torch.int32).cuda() for t in (n, lo, lens))
+    dec, dec_err = None, ""
+    try:
+        dec = ShardedDecoder(attn, B, Hq, D, torch.bfloat16, torch.device("cuda", torch.cuda.current_device()))
+    except Exception as e:      # no symmetric memory in this setup: only the all-gather route is timed
+        dec_err = f"{type(e).__name__}: {e}"[:200]
+    flag = torch.tensor([1.0 if dec is not None else 0.0], device="cuda")
+    torch.distributed.all_reduce(flag, op=torch.distributed.ReduceOp.MIN)
+    if flag.item() == 0.0:
+        dec = None
+        rec["xchg_unavailable"] = dec_err or "failed on another rank"
+    routes = []
+    with torch.no_grad():
+        if dec is not None:
+            routes.append(("xchg",) + tuple(dec.step(q, ks, vs, n_d, lo_d, len_d, scale)))
+        routes.append(("nccl",) + tuple(sharded_decode(attn, q, ks, vs, n_d, lo_d, len_d, scale)))
+    torch.cuda.synchronize()
+    assert _lib.wait_status() == 0, "a bounded wait gave up"
+    errs = {}
+    for name, o, l in routes:
+        e_o = (o.float() - ref_o.float()).abs().max().item()
+        e_l = (l - ref_lse.reshape(B, Hq)).abs().max().item()
+        assert e_o <= 2e-2 and e_l <= 1e-3, f"KV-sharded decode ({name}) differs from the one-GPU decode: {e_o} {e_l}"
+        errs[name] = (e_o, e_l)
+    rec.update({"check_max_abs_out": max(e[0] for e in errs.values()),
+                "check_max_abs_lse": max(e[1] for e in errs.values()), "check": "vs one-GPU decode of the same cache"})
+    # the second buffer set holds other random shards of the same geometry
+    bufs = [(ks, vs), (torch.randn(ks.shape, generator=g, device="cuda").to(torch.bfloat16),
+                       torch.randn(vs.shape, generator=g, device="cuda").to(torch.bfloat16))]
+    nbuf = len(bufs)
+    it = [0]
+
+    def step_xchg():
+        a, b_ = bufs[it[0] % nbuf]
+        it[0] += 1
+        with torch.no_grad():
+            dec.step(q, a, b_, n_d, lo_d, len_d, scale)
+
+    def step_nccl():
+        a, b_ = bufs[it[0] % nbuf]
+        it[0] += 1
+        with torch.no_grad():
+            sharded_decode(attn, q, a, b_, n_d, lo_d, len_d, scale)
+
+    results = {}
+    for name, fn in ((("xchg", step_xchg),) if dec is not None else ()) + (("nccl", step_nccl),):
+        it[0] = 0
+        mode = "graph"
+        try:
+            graph = _graph_of(fn, nbuf)
+
+            def gstep(graph=graph):
                 if it[0] % nbuf == 0:
                     graph.replay()
                 it[0] += 1
-            it[0] = 0
-            launch_mode = f"CUDA graph of {nbuf} calls (one per K/V buffer set), replayed"
-        except Exception as e:   # capture unsupported in this setup: time the eager calls
-            launch_mode = f"eager calls (graph capture failed: {type(e).__name__})"
-            step = eager_step
-        if world > 1:
-            # every rank must make the same choice, or the collectives would not match up
-            flag = torch.tensor([1.0 if step is not eager_step else 0.0], device="cuda")
-            torch.distributed.all_reduce(flag, op=torch.distributed.ReduceOp.MIN)
-            if flag.item() == 0.0 and step is not eager_step:
-                step, launch_mode = eager_step, "eager calls (graph capture failed on another rank)"
-    sampler = ClockSampler(torch.cuda.current_device())
-    sampler.start()
-    ms = max_over_ranks(time_steps(step, args.steps, args.warmup, world), world)
-    clocks = sampler.stop()
+            run = gstep
+        except Exception as e:     # capture unsupported in this setup: time the eager calls
+            mode, run = f"eager ({type(e).__name__})", fn
+        flag = torch.tensor([1.0 if mode == "graph" else 0.0], device="cuda")
+        torch.distributed.all_reduce(flag, op=torch.distributed.ReduceOp.MIN)
+        if flag.item() == 0.0 and mode == "graph":
+            mode, run = "eager (capture failed on another rank)", fn
+        it[0] = 0
+        ms, spread, clocks, _ = timed(run, steps, args.warmup, world)
+        results[name] = (ms, spread, clocks, mode)
     assert _lib.wait_status() == 0
-    peaks = measured_peaks()
+    ms, spread, clocks, mode = results["xchg" if dec is not None else "nccl"]
     gbs = bytes_alg / world / (ms * 1e-3) / 1e9
+    rec.update({"us_xchg": ms * 1e3 if dec is not None else None, "us_nccl": results["nccl"][0] * 1e3,
+                "mode_xchg": mode if dec is not None else None,
+                "mode_nccl": results["nccl"][3], "gbs_per_gpu": gbs, **spread,
+                "exchange": "xchg = peer-store exchange + merge kernel (bsa_xchg_merge); "
+                            "nccl = one all-gather + merge kernel",
+                "sm_mhz": clocks.get("sm_mhz"), "reasons": clocks.get("reasons"), "launches_per_step": 3})
+    return rec, ms, clocks, gbs
+
+
+def decode_line(args, world, rank):
+    rec, ms, clocks, gbs = run_decode(args, world, rank)
+    peaks = measured_peaks()
     return {
         "metric": "sparse_attn_decode_us_per_step", "value": ms * 1e3, "unit": "us", "n_gpus": world,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False,
+        "steps": rec["steps"], "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": "decode: BASELINE config 4, B=64, one query token, Hq=32, Hkv=8, D=128, KV lengths "
                                "U[1024,8192] left-padded to 8192, block 64, local 16, stride 8",
                    "parallelism": "single GPU" if world == 1 else
-                   f"KV sequence sharded over {world} GPUs, one NCCL all-gather of (O,LSE) + fused merge",
-                   "algorithmic_bytes_per_step": bytes_alg,
-                   "launch": launch_mode,
-                   "l2": f"{nbuf} K/V buffer sets rotated ({nbuf}x{2 * B * S * Hkv * D * 2 / world / 2**20:.0f} MiB)"},
-        "gpu_launches": args.steps * launches, "clocks": clocks,
+                   f"KV sequence sharded over {world} GPUs, peer-store exchange + merge kernel", **rec},
+        "gpu_launches": rec["steps"] * rec["launches_per_step"], "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm"], "unit": "GB/s",
                      "frac": gbs / peaks["hbm"], "traffic": TRAFFIC.get("decode"),
+                     "traffic_source": "ncu capture of the same workload (profiles/), not measured in this run",
                      "peak_source": peaks["source"], "frac_of_nominal_8000": gbs / NOMINAL_HBM_GBS,
                      "kernel": "decode_kernel<bf16,128> (+ merge_kernel)", "per_gpu": True},
     }
 
 
-def run_varlen(args, world, rank):
-    from dkernel_b200 import SparseAttention, _lib
-    from dkernel_b200.dist import head_shard
-    import warnings
-    cfg = WORKLOADS["varlen"]
-    H, D, bs = cfg["H"], cfg["D"], cfg["block"]
+def varlen_problem(cfg):
+    H, bs = cfg["H"], cfg["block"]
     nb = cfg["max_seq"] // bs
     g = torch.Generator().manual_seed(0)
     pat = torch.rand((H, nb, nb), generator=g) < cfg["p"]
     pat |= torch.eye(nb, dtype=torch.bool)[None]
     pat &= torch.tril(torch.ones(nb, nb, dtype=torch.bool))[None]
     lens = torch.randint(cfg["lo"], cfg["hi"] + 1, (cfg["nseq"],), generator=g)
+    return pat, lens
+
+
+def run_varlen(args, world, rank):
+    """BASELINE config 5 (fixed problem; at N > 1 its 32 heads are split over the ranks)."""
+    from dkernel_b200 import SparseAttention, _lib
+    from dkernel_b200.dist import head_shard
+    import warnings
+    cfg = WORKLOADS["varlen"]
+    H, D, bs = cfg["H"], cfg["D"], cfg["block"]
+    pat, lens = varlen_problem(cfg)
     (h0, h1), _ = head_shard(H, H, rank, world)
     with warnings.catch_warnings():
         warnings.simplefilter("ignore")
         attn = SparseAttention(bs, pat[h0:h1].cuda())
     T = int(lens.sum())
-    q, k, v = (torch.randn((T, h1 - h0, D), generator=g).to(torch.bfloat16).cuda() for _ in range(3))
+    g = torch.Generator(device="cuda").manual_seed(3 + rank)
+    q, k, v = (torch.randn((T, h1 - h0, D), generator=g, device="cuda").to(torch.bfloat16) for _ in range(3))
     cu = torch.cat([torch.zeros(1, dtype=torch.int64), lens.cumsum(0)]).to(torch.int32).cuda()
-    tiles = 0
+    tiles = executed = 0
     pn = pat[h0:h1].numpy()
     for L in lens.tolist():
         n = (L + bs - 1) // bs
-        tiles += int(pn[:, :n, :n].sum())
+        sub = pn[:, :n, :n]
+        tiles += int(sub.sum())
+        # a 128-row tile = two adjacent row blocks walking the union of their lists
+        even, odd = sub[:, 0::2], sub[:, 1::2]
+        if odd.shape[1] < even.shape[1]:
+            odd = np.concatenate([odd, np.zeros_like(even[:, :1])], 1)
+        executed += 2 * int((even | odd).sum())
     flops = tiles * tile_flops(bs, D)
 
     def step():
         with torch.no_grad():
             attn(q, k, v, cu_seqlen_k=cu)
 
-    sampler = ClockSampler(torch.cuda.current_device())
-    sampler.start()
-    ms = time_steps(step, args.steps, args.warmup, world)
-    clocks = sampler.stop()
+    ms_max, spread, clocks, ms = timed(step, args.steps, args.warmup, world)
     assert _lib.wait_status() == 0
-    ms_max = max_over_ranks(ms, world)
     total = sum_over_ranks(flops, world)
-    peaks = measured_peaks()
     tf = flops / (ms * 1e-3) / 1e12
+    ratio = sum_over_ranks(executed, world) / max(sum_over_ranks(tiles, world), 1)
     return {
         "metric": METRIC, "value": total / (ms_max * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_max, "higher_is_better": True,
@@ -562,12 +741,103 @@ def run_varlen(args, world, rank):
         "config": {"workload": "varlen prefill, user pattern: BASELINE config 5, H=32, D=128, block 64, "
                                "Bernoulli(0.2) lower-triangular 256x256 pattern, 16 packed sequences "
                                f"U[512,4096] (sum {T} tokens)",
-                   "parallelism": f"heads sharded over {world} GPU(s)", "attended_tiles": int(total / tile_flops(bs, D))},
+                   "parallelism": f"heads sharded over {world} GPU(s)", "attended_tiles": int(total / tile_flops(bs, D)),
+                   "executed_over_attended": ratio, **spread},
         "gpu_launches": args.steps, "clocks": clocks,
-        "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["tflops"], "unit": "TFLOP/s",
-                     "frac": tf / peaks["tflops"], "traffic": TRAFFIC.get("varlen"),
-                     "peak_source": peaks["source"] + " (burst)", "kernel": "fwd_persist_kernel<bf16>"},
+        "roofline": tensor_roofline(tf, "fwd_persist_kernel<bf16,128>", TRAFFIC.get("varlen")),
     }
+
+
+def run_fwd_d64(args, world, rank):
+    """Head dim 64 on the tensor-core forward: config 2's pattern and sizes with D = 64."""
+    from dkernel_b200 import LocalStrideSparseAttention, _lib
+    cfg = WORKLOADS["prefill"]
+    B, S, Hq, Hkv, D = cfg["B"], cfg["S"], cfg["Hq"], cfg["Hkv"], 64
+    attn = LocalStrideSparseAttention(Hq, S, cfg["block"], cfg["local"], cfg["stride"], num_kv_heads=Hkv, seq_dim=1)
+    g = torch.Generator(device="cuda").manual_seed(5)
+    q = torch.randn((B, S, Hq, D), generator=g, device="cuda").to(torch.bfloat16)
+    k, v = (torch.randn((B, S, Hkv, D), generator=g, device="cuda").to(torch.bfloat16) for _ in range(2))
+    tiles = int(local_stride_mask_np(Hq, S, cfg["block"], cfg["local"], cfg["stride"], Hkv).sum()) * B
+    flops = tiles * tile_flops(cfg["block"], D)
+
+    def step():
+        with torch.no_grad():
+            attn(q, k, v, return_lse=True)
+
+    ms_max, spread, clocks, ms = timed(step, args.steps, args.warmup, 1)
+    assert _lib.wait_status() == 0
+    tf = flops / (ms * 1e-3) / 1e12
+    return {"ms": ms, "tflops": tf, "frac": tf / measured_peaks()["tflops"], **spread,
+            "shape": "B4 S8192 Hq32 Hkv8 D64 bf16, config 2's pattern", "sm_mhz": clocks.get("sm_mhz")}
+
+
+def compact(line, keys=()):
+    """A sub-record of the combined line: numbers only, no prose."""
+    c = line["config"]
+    rec = {"ms": line["ms_per_step"], "value": line["value"], "unit": line["unit"],
+           "frac": line["roofline"]["frac"], "achieved": line["roofline"]["achieved"],
+           "sm_mhz": line["clocks"].get("sm_mhz"), "reasons": line["clocks"].get("reasons"),
+           "clock_samples": line["clocks"].get("samples")}
+    for k in ("fwd_ms", "bwd_ms", "fwd_tflops", "ms_min", "ms_max", "repeats", "executed_over_attended",
+              "attended_tiles", "executed_products_per_block", "algorithmic_products_per_block") + tuple(keys):
+        if k in c:
+            rec[k] = c[k]
+    return rec
+
+
+def run_all(args, world, rank):
+    """The headline (config 2 prefill) plus the rest of the metric as sub-records.  A sub-workload
+    that fails is reported as {"error": ...} in its place; the headline still prints."""
+    line = run_prefill(args, world, rank)
+    sub, rsub = {}, {}
+
+    def guarded(name, fn):
+        _free()
+        try:
+            fn()
+        except Exception as e:      # keep the line; the failure is visible in the record
+            sub[name] = {"error": f"{type(e).__name__}: {e}"[:300]}
+
+    def train():
+        t = run_train(args, world, rank)
+        sub["train_c3"] = compact(t)
+        rsub["train_bwd"] = {"achieved": t["roofline"]["achieved"], "frac": t["roofline"]["frac"],
+                             "frac_of_sustained": t["roofline"]["frac_of_sustained"], "unit": "TFLOP/s"}
+
+    def decode():
+        rec, ms, clocks, gbs = run_decode(args, world, rank)
+        name = "decode_c4" if world == 1 else "decode_c4_kv_sharded"
+        sub[name] = {k: v for k, v in rec.items() if not isinstance(v, str)}
+        if world == 1:
+            rsub["decode"] = {"achieved": gbs, "frac": rec["hbm_frac"], "unit": "GB/s", "bound": "hbm"}
+
+    def varlen():
+        vl = run_varlen(args, world, rank)
+        sub["varlen_c5" if world == 1 else "varlen_c5_strong"] = compact(vl)
+        if world == 1:
+            rsub["varlen"] = {"achieved": vl["roofline"]["achieved"], "frac": vl["roofline"]["frac"],
+                              "unit": "TFLOP/s"}
+
+    def d64():
+        r = run_fwd_d64(args, world, rank)
+        sub["prefill_d64"] = {k: v for k, v in r.items() if not isinstance(v, str)}
+        rsub["prefill_d64"] = {"achieved": r["tflops"], "frac": r["frac"], "unit": "TFLOP/s"}
+
+    def prefill_strong():
+        r = run_prefill(args, world, rank, strong=True, with_e2e=False)
+        sub["prefill_c2_strong"] = {k: v for k, v in r.items() if not isinstance(v, (str, list))}
+
+    if world == 1:
+        for name, fn in (("train_c3", train), ("decode_c4", decode), ("varlen_c5", varlen), ("prefill_d64", d64)):
+            guarded(name, fn)
+    else:
+        for name, fn in (("decode_c4_kv_sharded", decode), ("varlen_c5_strong", varlen),
+                         ("prefill_c2_strong", prefill_strong)):
+            guarded(name, fn)
+    _free()
+    line["config"]["sub"] = sub
+    line["roofline"]["sub"] = rsub
+    return line
 
 
 # --------------------------------------------------------------------------- reference arm
@@ -605,7 +875,7 @@ def run_reference(args):
     val = flops / dt / 1e12
     sample = ("1 of the %d (batch, head) pairs of BASELINE config 2 per step (B=1, Hq=1 slice, S=8192, D=128), "
               "masked-dense fp32 on CPU" % (cfg["B"] * cfg["Hq"]))
-    return {
+    line = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": "TFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
@@ -614,22 +884,28 @@ def run_reference(args):
         "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
+    if getattr(args, "steps_requested", args.steps) != args.steps:
+        line["config"]["steps_clamped_from"] = args.steps_requested
+    return line
 
 
 def main():
+    global REPEATS
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=40)
-    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="prefill", choices=list(WORKLOADS))
+    ap.add_argument("--workload", default="all", choices=["all"] + list(WORKLOADS))
+    ap.add_argument("--repeats", type=int, default=REPEATS, help="timed regions of K steps each (median reported)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--e2e-chunk", type=int, default=E2E_CHUNK,
                     help="prefill: query rows per pipelined chunk of the end-to-end step")
-    ap.add_argument("--no-graph", action="store_true", help="decode: time eager module calls, not a CUDA graph")
     args = ap.parse_args()
     if args.impl == "reference":
-        args.steps = min(args.steps, 5)
+        # a step takes ~0.2 s of host time: bound the run to a few minutes, and say so in the line
+        args.steps_requested = args.steps
+        args.steps = min(args.steps, 200)
         line = run_reference(args)
         if line is not None:
             print(json.dumps(line), flush=True)
@@ -637,11 +913,12 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (the product has no CPU path); "
                          "use --impl reference for the CPU restatement")
+    REPEATS = max(1, args.repeats)
     args.warmup = max(args.warmup, 3)
     world, rank, _ = setup_dist(args)
     if args.gpus != world and rank == 0:
         print(f"note: --gpus {args.gpus} but WORLD_SIZE={world}; using {world}", file=sys.stderr)
-    line = {"prefill": run_prefill, "train": run_train, "decode": run_decode,
+    line = {"all": run_all, "prefill": run_prefill, "train": run_train, "decode": decode_line,
             "varlen": run_varlen}[args.workload](args, world, rank)
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:

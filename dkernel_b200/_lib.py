@@ -66,6 +66,12 @@ class DecodeParams(C.Structure):
     )
 
 
+class XchgParams(C.Structure):
+    _fields_ = ([(n, _vp) for n in ("stage_o", "stage_lse", "out", "out_lse")]
+                + [("xbuf", _vp * 8), ("rows", _i64)]
+                + [(n, _i32) for n in ("world", "rank", "d", "dtype")])
+
+
 EXPORTS = {
     # name: (restype, argtypes)
     "bsa_abi_version": (_i32, []),
@@ -82,7 +88,12 @@ EXPORTS = {
     "bsa_decode_static_capacity": (C.c_size_t, []),
     "bsa_merge_partials": (_i32, [_vp, _vp, _i32, _i64, _i32, _i64, _i64, _i64, _i64, _vp, _i64, _vp,
                                   _i32, _vp]),
+    "bsa_xchg_buffer_bytes": (C.c_size_t, [_i32, _i64, _i32]),
+    "bsa_xchg_merge": (_i32, [C.POINTER(XchgParams), _vp]),
     "bsa_wait_status": (_i32, [C.POINTER(_i32), _i32]),
+    "bsa_set_wait_status_mirror": (_i32, [_vp]),
+    "bsa_selftest_wait_timeout": (_i32, [C.c_uint32, _vp]),
+    "bsa_fwd_why_not_sm100": (C.c_char_p, [C.POINTER(FwdParams)]),
 }
 
 _lib = None
@@ -110,10 +121,42 @@ def lib() -> C.CDLL:
     return _lib
 
 
+# Host-visible copy of the device wait-status word (one pinned int32 shared by all devices):
+# the kernels store the code of the first bounded wait that gave up there, so every later
+# call can raise without synchronising with the device.
+_mirror = None          # the pinned tensor (kept alive here)
+_mirror_addr = None     # its address; tests may point this at any int32
+_armed = set()          # device indices whose status block knows the mirror
+
+
+def _arm_mirror(device_index: int) -> None:
+    global _mirror, _mirror_addr
+    if device_index in _armed:
+        return
+    if _mirror is None:
+        _mirror = torch.zeros(1, dtype=torch.int32).pin_memory()
+        _mirror_addr = _mirror.data_ptr()
+    with torch.cuda.device(device_index):
+        rc = lib().bsa_set_wait_status_mirror(_mirror.data_ptr())
+    if rc != 0:
+        msg = lib().bsa_last_error()
+        raise BsaError(f"bsa_set_wait_status_mirror failed ({rc}): {msg.decode() if msg else ''}")
+    _armed.add(device_index)
+
+
 def check(rc: int, what: str) -> None:
+    """Raise on a failed call, or when a device-side wait has given up since the last
+    ``wait_status()``: from then on the kernels are no-ops and outputs are undefined."""
     if rc != 0:
         msg = lib().bsa_last_error()
         raise BsaError(f"{what} failed ({rc}): {msg.decode() if msg else ''}")
+    if _mirror_addr is not None:
+        code = C.c_int32.from_address(_mirror_addr).value
+        if code != 0:
+            raise BsaError(
+                f"{what}: a bounded device-side wait gave up earlier (code {code}); kernels launched "
+                "since then did nothing and their outputs are undefined. Call "
+                "dkernel_b200._lib.wait_status() to read and clear the status.")
 
 
 def dtype_code(dt: torch.dtype) -> int:
@@ -131,6 +174,7 @@ def ptr(t) -> int:
 
 
 def stream_of(t: torch.Tensor) -> int:
+    _arm_mirror(t.device.index if t.device.index is not None else torch.cuda.current_device())
     return torch.cuda.current_stream(t.device).cuda_stream
 
 

@@ -121,6 +121,27 @@ int bsa_merge_partials(const void* o_parts, const float* lse_parts, int32_t P, i
                         static_cast<cudaStream_t>(stream));
 }
 
+size_t bsa_xchg_buffer_bytes(int32_t world, int64_t rows, int32_t d) {
+  return xchg_buffer_bytes(world, rows, d);
+}
+
+int bsa_xchg_merge(const bsa_xchg_params* p, void* stream) {
+  return xchg_merge(p, static_cast<cudaStream_t>(stream));
+}
+
 int bsa_wait_status(int32_t* status, int32_t reset) { return read_wait_status(status, reset); }
+
+int bsa_set_wait_status_mirror(int32_t* host_word) { return set_wait_status_mirror(host_word); }
+
+int bsa_selftest_wait_timeout(uint32_t limit_us, void* stream) {
+  return selftest_wait_timeout(limit_us, static_cast<cudaStream_t>(stream));
+}
+
+const char* bsa_fwd_why_not_sm100(const bsa_fwd_params* p) {
+  if (validate_fwd(p, "bsa_fwd_why_not_sm100")) return last_error();
+  const char* why = nullptr;
+  if (sm100_fwd_supported(p, &why)) return nullptr;
+  return why ? why : "unsupported";
+}
 
 }  // extern "C"

@@ -875,7 +875,8 @@ int launch_bwd(const bsa_bwd_params* bp, cudaStream_t s) {
   }
   {
     const int G = p->hq / p->hkv;
-    const int mode = (G % 2 == 0) ? kPairHeads : kPairRows;
+    // as in the forward: two q heads share a tile only when they share a block list
+    const int mode = (G % 2 == 0 && p->h_pat != p->hq) ? kPairHeads : kPairRows;
     auto kern = bwd_dq_sm100_kernel<BF16>;
     BSA_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDqSmem));
     dim3 grid(cdiv_i(p->sq, mode == kPairHeads ? 64 : 128), mode == kPairHeads ? p->hq / 2 : p->hq,

@@ -79,8 +79,6 @@ int generic_fwd(const bsa_fwd_params* p, cudaStream_t s);
 int generic_bwd(const bsa_bwd_params* p, cudaStream_t s);
 bool sm100_fwd_supported(const bsa_fwd_params* p, const char** why);
 int sm100_fwd(const bsa_fwd_params* p, cudaStream_t s);
-bool sm100_fwd_persist_supported(const bsa_fwd_params* p);
-int sm100_fwd_persist(const bsa_fwd_params* p, cudaStream_t s);
 bool sm100_bwd_supported(const bsa_bwd_params* p, const char** why);
 int sm100_bwd(const bsa_bwd_params* p, cudaStream_t s);
 size_t decode_workspace_bytes(const bsa_decode_params* p);
@@ -90,7 +88,11 @@ size_t decode_static_capacity();
 int merge_partials(const void* o_parts, const float* lse_parts, int P, int64_t rows, int d,
                    int64_t pso, int64_t rso, int64_t psl, int64_t rsl, void* o, int64_t ors,
                    float* lse, int dtype, cudaStream_t s);
+size_t xchg_buffer_bytes(int world, int64_t rows, int d);
+int xchg_merge(const bsa_xchg_params* p, cudaStream_t s);
 int read_wait_status(int* out, int reset);
+int set_wait_status_mirror(int* host_word);
+int selftest_wait_timeout(uint32_t limit_us, cudaStream_t s);
 int* wait_status_ptr();
 
 }  // namespace bsa

@@ -16,21 +16,20 @@
 // dkernel/ops/sparse_attn_inference.py:503-514: positions are re-based to the
 // first real token, the pattern row is (len - 1) / block_size, every real token
 // of an attended block is visible.
+#include <mutex>
+
 #include "ptx.cuh"
 
 namespace bsa {
 
-__device__ int g_wait_status = 0;  // first bounded wait that gave up (0 = none)
+// Status block of the bounded waits: [0] code of the first wait that gave up (0 = none),
+// [2..3] device-visible address of the host's mirror word (or null).
+__device__ __align__(16) int g_wait_status[4] = {0, 0, 0, 0};
 
 namespace {
 
-#ifndef BSA_DEC_STAGES
-#define BSA_DEC_STAGES 2
-#endif
-#ifndef BSA_DEC_MIN_CTAS
-#define BSA_DEC_MIN_CTAS 3
-#endif
-constexpr int kStages = BSA_DEC_STAGES;    // K/V ring depth
+constexpr int kStages = 2;               // K/V ring depth
+constexpr int kMinCtas = 3;              // resident CTAs per SM the kernel is built for
 constexpr int kTok = 64;                 // tokens per pipeline stage
 constexpr int kConsumers = 4;            // consumer warps
 constexpr int kDecThreads = 32 * (kConsumers + 1);
@@ -95,7 +94,7 @@ __device__ __forceinline__ uint32_t tile_off(int tok, int chunk) {
 }
 
 template <typename T, int D>
-__global__ void __launch_bounds__(kDecThreads, BSA_DEC_MIN_CTAS)
+__global__ void __launch_bounds__(kDecThreads, kMinCtas)
 decode_kernel(const __grid_constant__ Tmap4 tmK, const __grid_constant__ Tmap4 tmV,
               bsa_decode_params p, int nsplit, int* wait_status) {
   constexpr int kTileBytes = kTok * D * 2;
@@ -443,6 +442,21 @@ int launch_merge(const void* o_parts, const float* lse_parts, int P, int64_t row
   return check_launch("merge_kernel");
 }
 
+// Checks that must hold before any arithmetic on the head counts (the split planning divides by
+// them): shared by bsa_decode, bsa_decode_static and bsa_decode_workspace_bytes.
+int decode_validate_heads(const bsa_decode_params* p, const char* who) {
+  BSA_CHECK_ARG(p, "%s: null params", who);
+  BSA_CHECK_ARG(p->batch >= 0 && p->hq >= 1 && p->hkv >= 1 && p->hq % p->hkv == 0,
+                "%s: bad head counts hq=%d hkv=%d", who, p->hq, p->hkv);
+  const int G = p->hq / p->hkv;
+  BSA_CHECK_ARG(p->heads_per_cta >= 1 && p->heads_per_cta <= 16 && G % p->heads_per_cta == 0,
+                "%s: heads_per_cta=%d must divide the group size %d and be <= 16", who,
+                p->heads_per_cta, G);
+  BSA_CHECK_ARG(p->d >= 1 && p->max_row_nnz >= 0, "%s: bad sizes d=%d max_row_nnz=%d", who, p->d,
+                p->max_row_nnz);
+  return BSA_OK;
+}
+
 // Attended blocks per CTA.  A caller's choice is kept; otherwise a CTA gets as many blocks as
 // possible (up to 16: one prologue and one partial per 512 KB of K/V) while the grid still
 // fills the machine about twice over (three resident CTAs per SM).
@@ -450,7 +464,7 @@ int decode_blocks_per_split(const bsa_decode_params* p) {
   if (p->blocks_per_split > 0) return p->blocks_per_split;
   const int hpc = p->heads_per_cta > 0 ? p->heads_per_cta : 1;
   const long long items = (long long)p->batch * p->hkv * ((p->hq / p->hkv) / hpc);
-  const long long want = 2LL * 148 * BSA_DEC_MIN_CTAS;
+  const long long want = 2LL * 148 * kMinCtas;
   long long splits = items > 0 ? (want + items - 1) / items : 1;
   if (splits < 1) splits = 1;
   const int nnz = p->max_row_nnz > 0 ? p->max_row_nnz : 1;
@@ -515,19 +529,16 @@ int launch_decode(const bsa_decode_params* p, cudaStream_t s) {
 }  // namespace
 
 size_t decode_workspace_bytes(const bsa_decode_params* p) {
+  if (decode_validate_heads(p, "bsa_decode_workspace_bytes") != BSA_OK) return 0;
   const int nsplit = decode_nsplit(p);
   if (nsplit <= 1) return 0;
   return sizeof(float) * (size_t)p->batch * p->hq * nsplit * (p->d + 1);
 }
 
 int decode_run(const bsa_decode_params* p, cudaStream_t s) {
-  BSA_CHECK_ARG(p && p->q && p->k && p->v && p->o && p->crow && p->col, "bsa_decode: null pointer");
-  BSA_CHECK_ARG(p->batch >= 0 && p->hq >= 1 && p->hkv >= 1 && p->hq % p->hkv == 0,
-                "bsa_decode: bad head counts hq=%d hkv=%d", p->hq, p->hkv);
-  const int G = p->hq / p->hkv;
-  BSA_CHECK_ARG(p->heads_per_cta >= 1 && p->heads_per_cta <= 16 && G % p->heads_per_cta == 0,
-                "bsa_decode: heads_per_cta=%d must divide the group size %d and be <= 16",
-                p->heads_per_cta, G);
+  int vrc = decode_validate_heads(p, "bsa_decode");
+  if (vrc) return vrc;
+  BSA_CHECK_ARG(p->q && p->k && p->v && p->o && p->crow && p->col, "bsa_decode: null pointer");
   BSA_CHECK_ARG(p->h_pat == 1 || p->h_pat == p->hkv || p->h_pat == p->hq,
                 "bsa_decode: pattern has %d heads, expected 1, %d or %d", p->h_pat, p->hkv, p->hq);
   if (p->batch == 0) return BSA_OK;
@@ -576,6 +587,8 @@ namespace bsa {
 // only a host-side handle; kernels get the real address as an argument).
 int* wait_status_ptr() {
   static int* cache[64] = {nullptr};
+  static std::mutex mu;   // entry points may be called from several host threads
+  std::lock_guard<std::mutex> lock(mu);
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
     set_error("cudaGetDevice failed or device index out of range");
@@ -593,6 +606,8 @@ int* wait_status_ptr() {
   return cache[dev];
 }
 
+static int* g_mirror_host[64] = {nullptr};   // the registered mirror word of each device
+
 int read_wait_status(int* out, int reset) {
   BSA_CHECK_ARG(out, "bsa_wait_status: null pointer");
   BSA_CHECK_CUDA(cudaDeviceSynchronize());
@@ -600,8 +615,50 @@ int read_wait_status(int* out, int reset) {
   if (reset && *out != 0) {
     const int zero = 0;
     BSA_CHECK_CUDA(cudaMemcpyToSymbol(g_wait_status, &zero, sizeof(int)));
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64 && g_mirror_host[dev])
+      *reinterpret_cast<volatile int*>(g_mirror_host[dev]) = 0;
   }
   return BSA_OK;
+}
+
+int set_wait_status_mirror(int* host_word) {
+  int dev = 0;
+  BSA_CHECK_CUDA(cudaGetDevice(&dev));
+  BSA_CHECK_ARG(dev >= 0 && dev < 64, "bsa_set_wait_status_mirror: device index out of range");
+  int* dptr = nullptr;
+  if (host_word) {
+    cudaError_t e = cudaHostGetDevicePointer(reinterpret_cast<void**>(&dptr), host_word, 0);
+    if (e != cudaSuccess || !dptr) {
+      (void)cudaGetLastError();
+      set_error("bsa_set_wait_status_mirror: the word must be page-locked host memory that the device "
+                "can address (%s)", cudaGetErrorString(e));
+      return BSA_E_BADARG;
+    }
+  }
+  BSA_CHECK_CUDA(cudaMemcpyToSymbol(g_wait_status, &dptr, sizeof(dptr), 2 * sizeof(int)));
+  g_mirror_host[dev] = host_word;
+  return BSA_OK;
+}
+
+// A wait that nothing will ever satisfy, with a short limit: exercises the give-up path
+// (status block, mirror word, no-op behaviour of later launches) without faulting the GPU.
+__global__ void wait_timeout_selftest_kernel(int* status, uint64_t limit_ns) {
+  __shared__ uint64_t bar;
+  if (*reinterpret_cast<volatile int*>(status) != 0) return;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    mbar_fence_init();
+    mbar_wait(&bar, 0, status, 900, limit_ns);   // nobody arrives
+  }
+}
+
+int selftest_wait_timeout(uint32_t limit_us, cudaStream_t s) {
+  BSA_CHECK_ARG(limit_us >= 1 && limit_us <= 100000, "bsa_selftest_wait_timeout: limit must be 1..100000 us");
+  int* status = wait_status_ptr();
+  if (!status) return BSA_E_CUDA;
+  wait_timeout_selftest_kernel<<<1, 32, 0, s>>>(status, (uint64_t)limit_us * 1000ull);
+  return check_launch("wait_timeout_selftest_kernel");
 }
 }  // namespace bsa
 
@@ -627,6 +684,8 @@ static __device__ __align__(256) float g_decode_scratch[kStaticScratchBytes / si
 // and handed to the kernels as an ordinary pointer.
 static float* static_scratch_ptr() {
   static float* cache[64] = {nullptr};
+  static std::mutex mu;   // entry points may be called from several host threads
+  std::lock_guard<std::mutex> lock(mu);
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
     set_error("bsa_decode_static: cudaGetDevice failed or device index out of range");
@@ -647,7 +706,8 @@ static float* static_scratch_ptr() {
 size_t decode_static_capacity() { return kStaticScratchBytes; }
 
 int decode_run_static(const bsa_decode_params* p, cudaStream_t s) {
-  BSA_CHECK_ARG(p, "bsa_decode_static: null params");
+  int vrc = decode_validate_heads(p, "bsa_decode_static");
+  if (vrc) return vrc;
   const size_t need = decode_workspace_bytes(p);
   if (need > kStaticScratchBytes) {
     set_error("bsa_decode_static: this call needs %zu bytes of split-KV scratch but the built-in "

@@ -1,73 +1,74 @@
-// Prefill / training forward on the 5th-generation tensor cores.
+// Prefill / training forward on the tcgen05 tensor cores (head dim 64 or 128, 64-token blocks).
 //
-// One CTA = one 128-row query tile made of two 64-row halves that share a kv
-// head, so every K/V block fetched by TMA feeds a full M=128 tcgen05.mma:
-//   * PAIR_HEADS (GQA, even group size): the halves are two q heads of one kv
-//     group at the same q block -- identical block lists, no wasted work;
-//   * PAIR_ROWS (otherwise): the halves are two adjacent q blocks of one head;
-//     the CTA walks the union of their block lists and a half that does not
-//     attend a block contributes P = 0 for it.
-// The per-head CSR rows of both halves are merged in shared memory (bitmaps ->
-// ordered list) before the pipeline starts.
-//
-// Warp roles (192 threads):  warps 0-3 softmax (thread r owns tile row r = TMEM
-// lane r: no cross-lane reductions at all), warp 4 TMA producer, warp 5 owns TMEM
-// and issues every product from one thread.  Per kv block j:
-//   S[j&1] = Q K_j^T          tcgen05.mma, A/B from 128B-swizzled smem, fp32 in TMEM
-//   P = exp2(S*c - m)          softmax warps: tcgen05.ld -> registers -> bf16/fp16 ->
-//                              tcgen05.st into the columns S occupied
-//   O += P V_j                 tcgen05.mma, A = P from TMEM, B = V (MN-major) from smem
-// The issue order is Q K_0, Q K_1, then P V_j followed at once by Q K_{j+2}: the
-// tensor pipe runs one thread's products in issue order, so Q K_{j+2} may be queued
-// behind P V_j without waiting for the completion that frees the columns they share.
-// S is double buffered so Q K_{j+1}^T overlaps softmax j; the running maximum is
-// only raised when it grows by more than 2^8 (the accumulator then gets rescaled
-// in TMEM), so the correction step is rare.  Two CTAs fit per SM (about 101 KB of
-// shared memory and 256 TMEM columns each), which lets one CTA's tensor-core
-// work hide the other's softmax.  Math follows
-// dkernel/ops/sparse_attn_fwd.py:90-165, :351-363 (base-2 online softmax, LSE).
-#include <cstdlib>
-
+// A 128-row query tile = two 64-row halves that share a kv head; S double buffered in TMEM,
+// P overwrites S, O accumulates in TMEM; one converged issuer warp queues Q K_{j+2} right
+// behind P V_j.  The CTAs are persistent: two per SM are launched and each walks a strided
+// list of tiles, so that the per-tile fixed cost (block-list merge, pipeline fill, epilogue)
+// overlaps the neighbouring tiles:
+//   * a planner warp merges the next tile's block list while the current tile is computed
+//     (two plan slots),
+//   * the producer loads the next tile's Q as soon as the last Q K^T of the current tile has
+//     completed, and its first K/V blocks as soon as their ring slots are free, i.e. while
+//     the current tile's last softmax, P V and epilogue are still running,
+//   * the issuer queues the next tile's first two Q K^T products right behind the last P V;
+//     only the next tile's first P V (which overwrites O) waits for the epilogue.
+// Block counters run across tiles, so buffer indices and barrier phases never restart.
+// Warps (224 threads): 0-3 softmax + epilogue, 4 TMA producer, 5 MMA issuer (owns TMEM),
+// 6 planner.  TMEM: S[2] 2x64 | O D columns.
+// Math: dkernel/ops/sparse_attn_fwd.py:90-165, :351-363.
 #include "ptx.cuh"
 
 namespace bsa {
 namespace {
 
-constexpr int kD = 128;
 constexpr int kBS = 64;
-constexpr int kFwdThreads = 192;
-constexpr int kMaxList = 1024;          // kv blocks per sequence (64K tokens)
-constexpr int kQBytes = 128 * kD * 2;   // 32 KB
-constexpr int kKVBytes = kBS * kD * 2;  // 16 KB per K or V tile
-#ifndef BSA_FWD_STAGES
-#define BSA_FWD_STAGES 2
-#endif
-constexpr int kStagesF = BSA_FWD_STAGES;     // K and V ring depth
-static_assert(kStagesF == 2, "the S/P double buffer and the K/V rings share their barriers");
+constexpr int kThreadsP = 224;
+constexpr int kWarpProd = 4, kWarpIssue = 5, kWarpPlan = 6;
+constexpr int kMaxList = 1024;           // kv blocks per sequence (64K tokens)
+// Shared-memory tiles are stored as D/64 sub-tiles of [rows][128 bytes] (one TMA box each,
+// 128-byte swizzled): Q 128 rows (16 KB per sub-tile), K and V 64 rows (8 KB per sub-tile).
+template <int D> struct Geo {
+  static constexpr int kSub = D / 64;
+  static constexpr int kQBytes = 128 * D * 2;
+  static constexpr int kTile = kBS * D * 2;           // one K or V block
+  static constexpr size_t kSmem = 1024 + kQBytes + 2 * 2 * kTile;   // + sizeof(TailP)
+};
 constexpr float kRescaleThreshold = 8.0f;
-
 enum { kPairHeads = 0, kPairRows = 1 };
 
-struct FwdTail {
-  uint64_t q_full;
-  uint64_t k_full[kStagesF], v_full[kStagesF];
-  // qk_done[j&1]: Q K_j^T has completed -> S[j&1] is readable and the K stage is free.
-  // pv_done[j&1]: P V_j has completed   -> P[j&1] (= S[j&1]) and the V stage are free.
-  uint64_t qk_done[2], pv_done[2], p_full[2];
-  uint32_t tmem_base;
-  int n_list;
-  uint32_t bits[2][kMaxList / 32];
-  uint32_t list[kMaxList];
+struct Plan {
+  int valid;                 // 0: nothing to do for this item (packed batches over-enumerate)
+  int n;                     // number of kv blocks in list
+  int b, kvh;
+  int head[2], qblk[2], hvalid[2];
+  int q_start, q_len, k_start, k_len, past;
+  uint16_t list[kMaxList];   // block | attended-by-half-0 << 14 | attended-by-half-1 << 15
 };
 
-constexpr size_t kFwdSmem = 1024 + kQBytes + kStagesF * 2 * kKVBytes + sizeof(FwdTail);
+struct TailP {
+  uint64_t plan_full[2], plan_free[2];
+  uint64_t q_full, q_free;
+  uint64_t k_full[2], v_full[2];
+  // qk_done[g&1]: Q K_g^T has completed -> S[g&1] is readable and the K slot is free.
+  // pv_done[g&1]: P V_g has completed   -> the V slot is free (and O holds block g).
+  uint64_t qk_done[2], p_full[2], pv_done[2];
+  uint64_t o_free;           // the epilogue has read O
+  uint32_t tmem_base;
+  uint32_t bits[2][kMaxList / 32];
+  Plan plan[2];
+};
+
 
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float y;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
+  return y;
+}
 template <bool BF16>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   if (BF16) {
@@ -79,360 +80,460 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   }
 }
 
-struct Half {
-  int head, qblk, valid;
-};
+// item -> plan (executed by the whole planner warp)
+__device__ __forceinline__ void build_plan(const bsa_fwd_params& p, int mode, int item, int tiles_x,
+                                           int head_items, Plan* pl, uint32_t (*bits)[kMaxList / 32],
+                                           int lane) {
+  const int tile_rows = mode == kPairHeads ? 64 : 128;
+  // Items are ordered long rows first (the tile index decreases with the item index), all
+  // heads and batches of a tile index together: a round of the grid then holds tiles of
+  // nearly equal length, which keeps the CTAs' totals level.
+  const int G = p.hq / p.hkv;
+  const int per_tile = head_items * (p.total_q > 0 ? 1 : p.batch);
+  const int tx = item / per_tile, rem = item % per_tile;
+  const int hy = rem % head_items;
+  int b = rem / head_items, tile = 0, valid = 1;
+  if (p.total_q > 0) {
+    int acc = 0;
+    valid = 0;
+    for (int i = 0; i < p.batch; ++i) {
+      const int len = p.q_end[i] - p.q_start[i];
+      const int nt = len > 0 ? (len + tile_rows - 1) / tile_rows : 0;
+      if (tx < acc + nt) { b = i; tile = tx - acc; valid = 1; break; }
+      acc += nt;
+    }
+  } else {
+    tile = tiles_x - 1 - tx;
+  }
+  const int q_start = valid && p.q_start ? p.q_start[b] : 0;
+  const int q_len = valid ? (p.q_end ? p.q_end[b] : p.sq) - q_start : 0;
+  const int k_start = valid && p.k_start ? p.k_start[b] : 0;
+  const int k_len = valid ? (p.k_end ? p.k_end[b] : p.sk) - k_start : 0;
+  if (tile * tile_rows >= q_len) valid = 0;
+  const int past = (p.causal || p.row_mode == BSA_ROWS_BY_POSITION) ? k_len - q_len : 0;
+  int head[2], qblk[2], hvalid[2], kvh;
+  if (mode == kPairHeads) {
+    const int pairs = G / 2;
+    kvh = hy / pairs;
+    head[0] = kvh * G + 2 * (hy % pairs);
+    head[1] = head[0] + 1;
+    qblk[0] = qblk[1] = tile;
+    hvalid[0] = hvalid[1] = valid;
+  } else {
+    head[0] = head[1] = hy;
+    kvh = hy / G;
+    qblk[0] = 2 * tile;
+    qblk[1] = 2 * tile + 1;
+    hvalid[0] = valid;
+    hvalid[1] = valid && qblk[1] * kBS < q_len;
+  }
+  const int nkb = min((k_len + kBS - 1) / kBS, kMaxList);
+  bits[0][lane] = 0u;
+  bits[1][lane] = 0u;
+  __syncwarp();
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    if (!hvalid[t]) continue;
+    const int q_first = qblk[t] * kBS;
+    const int row = (p.row_mode == BSA_ROWS_BY_POSITION ? past + q_first : q_first) / kBS;
+    if (row >= p.n_rows) continue;
+    const int hp = pattern_head(head[t], p.h_pat, p.hq, p.hkv);
+    const int32_t* cr = p.crow + (int64_t)hp * p.crow_sh;
+    const int32_t* cols = p.col + (int64_t)hp * p.col_sh;
+    const int c_beg = __ldg(cr + row), c_end = __ldg(cr + row + 1);
+    const int q_pos_last = past + min(q_first + kBS, q_len) - 1;
+    for (int i = c_beg + lane; i < c_end; i += 32) {
+      const int blk = __ldg(cols + i);
+      if (blk >= 0 && blk < nkb && !(p.causal && blk * kBS > q_pos_last))
+        atomicOr(&bits[t][blk >> 5], 1u << (blk & 31));
+    }
+  }
+  __syncwarp();
+  // bitmaps -> ordered list: scan the word counts, then every lane owns one bit of a word
+  const uint32_t u0 = bits[0][lane], u1 = bits[1][lane];
+  const uint32_t u = u0 | u1;
+  const int cnt = __popc(u);
+  int incl = cnt;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int tt = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += tt;
+  }
+  const int base = incl - cnt;
+  uint32_t nonzero = __ballot_sync(0xffffffffu, u != 0u);
+  while (nonzero) {
+    const int w = __ffs(nonzero) - 1;
+    nonzero &= nonzero - 1;
+    const uint32_t uw = __shfl_sync(0xffffffffu, u, w);
+    const uint32_t u0w = __shfl_sync(0xffffffffu, u0, w);
+    const uint32_t u1w = __shfl_sync(0xffffffffu, u1, w);
+    const int bw = __shfl_sync(0xffffffffu, base, w);
+    if ((uw >> lane) & 1u)
+      pl->list[bw + __popc(uw & ((1u << lane) - 1u))] =
+          (uint16_t)((w * 32 + lane) | (((u0w >> lane) & 1u) << 14) | (((u1w >> lane) & 1u) << 15));
+  }
+  const int n = __shfl_sync(0xffffffffu, incl, 31);
+  if (lane == 0) {
+    pl->valid = valid;
+    pl->n = valid ? n : 0;
+    pl->b = b;
+    pl->kvh = kvh;
+    pl->head[0] = head[0]; pl->head[1] = head[1];
+    pl->qblk[0] = qblk[0]; pl->qblk[1] = qblk[1];
+    pl->hvalid[0] = hvalid[0]; pl->hvalid[1] = hvalid[1];
+    pl->q_start = q_start; pl->q_len = q_len; pl->k_start = k_start; pl->k_len = k_len;
+    pl->past = past;
+  }
+  __syncwarp();
+}
 
-template <bool BF16>
-__global__ void __launch_bounds__(kFwdThreads, kStagesF <= 2 ? 2 : 1)
-fwd_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap4 tmK,
-                 const __grid_constant__ Tmap4 tmV, bsa_fwd_params p, int mode, int* wait_status) {
+template <bool BF16, int D>
+__global__ void __launch_bounds__(kThreadsP, 2)
+fwd_persist_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap4 tmK,
+                   const __grid_constant__ Tmap4 tmV, bsa_fwd_params p, int mode, int n_items,
+                   int tiles_x, int head_items, int* wait_status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
-  uint8_t* sQ = smem;
-  uint8_t* sKV = smem + kQBytes;  // stage s: K at s*32K, V at s*32K + 16K
-  FwdTail* tl = reinterpret_cast<FwdTail*>(smem + kQBytes + kStagesF * 2 * kKVBytes);
+  constexpr int kSub = Geo<D>::kSub, kQBytes = Geo<D>::kQBytes, kTile = Geo<D>::kTile;
+  uint8_t* sQ = smem;                   // [kSub sub-tiles of 64 head dims][128 rows][128 B]
+  uint8_t* sRing = smem + kQBytes;      // slot s: K at s * 2 * kTile, V one kTile behind it
+  TailP* tl = reinterpret_cast<TailP*>(smem + kQBytes + 2 * 2 * kTile);
 
-  // A wait that gave up in an earlier launch makes every later launch return at once.  The
-  // flag is loaded here and tested after the work item is known, so that its latency
-  // overlaps the index arithmetic.
-  const int sticky = *reinterpret_cast<volatile int*>(wait_status);
+  if (*reinterpret_cast<volatile int*>(wait_status) != 0) return;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
-  // ---------------------------------------------------------------- work item
-  const int G = p.hq / p.hkv;
-  const int tile_rows = mode == kPairHeads ? 64 : 128;
-  int b = blockIdx.z, tile;
-  if (p.total_q > 0) {
-    int acc = 0, found = 0;
-    tile = 0;
-    for (int i = 0; i < p.batch; ++i) {
-      const int len = p.q_end[i] - p.q_start[i];
-      const int n = len > 0 ? (len + tile_rows - 1) / tile_rows : 0;
-      if ((int)blockIdx.x < acc + n) { b = i; tile = blockIdx.x - acc; found = 1; break; }
-      acc += n;
-    }
-    if (!found) return;
-  } else {
-    tile = gridDim.x - 1 - blockIdx.x;  // long rows first
-  }
-  const int q_start = p.q_start ? p.q_start[b] : 0;
-  const int q_len = (p.q_end ? p.q_end[b] : p.sq) - q_start;
-  const int k_start = p.k_start ? p.k_start[b] : 0;
-  const int k_len = (p.k_end ? p.k_end[b] : p.sk) - k_start;
-  if (tile * tile_rows >= q_len) return;
-  const int past = (p.causal || p.row_mode == BSA_ROWS_BY_POSITION) ? k_len - q_len : 0;
-
-  Half hf[2];
-  int kvh;
-  if (mode == kPairHeads) {
-    const int pairs = G / 2;
-    kvh = blockIdx.y / pairs;
-    const int h0 = kvh * G + 2 * (blockIdx.y % pairs);
-    hf[0] = {h0, tile, 1};
-    hf[1] = {h0 + 1, tile, 1};
-  } else {
-    const int h = blockIdx.y;
-    kvh = h / G;
-    hf[0] = {h, 2 * tile, 1};
-    hf[1] = {h, 2 * tile + 1, (2 * tile + 1) * kBS < q_len ? 1 : 0};
-  }
-  const int nkb = min((k_len + kBS - 1) / kBS, kMaxList);
-
-  // CSR row bounds of both halves: the loads are issued now and consumed after the
-  // barrier setup below.
-  int c_beg[2] = {0, 0}, c_end[2] = {0, 0};
-  const int32_t* cols_of[2] = {nullptr, nullptr};
-#pragma unroll
-  for (int t = 0; t < 2; ++t) {
-    if (!hf[t].valid) continue;
-    const int q_first = hf[t].qblk * kBS;
-    const int row = (p.row_mode == BSA_ROWS_BY_POSITION ? past + q_first : q_first) / kBS;
-    if (row >= p.n_rows) continue;
-    const int hp = pattern_head(hf[t].head, p.h_pat, p.hq, p.hkv);
-    const int32_t* cr = p.crow + (int64_t)hp * p.crow_sh;
-    cols_of[t] = p.col + (int64_t)hp * p.col_sh;
-    c_beg[t] = __ldg(cr + row);
-    c_end[t] = __ldg(cr + row + 1);
-  }
-  if (sticky != 0) return;
-
-  // ---------------------------------------------------------------- setup
   if (warp == 0) {
-    // the eleven barriers are contiguous: q_full, k_full[2], v_full[2], qk_done[2],
-    // pv_done[2] (one arrival each) and p_full[2] (one arrival per softmax warp)
-    if (lane < 11) {
-      mbar_init(&tl->q_full + lane, lane >= 9 ? 4 : 1);
+    // seventeen contiguous barriers (plan_full[2], plan_free[2], q_full, q_free, k_full[2],
+    // v_full[2], qk_done[2], p_full[2], pv_done[2], o_free); arrival counts: plan_free = 4
+    // softmax warps + producer + issuer, p_full and o_free = 4 softmax warps, the rest 1
+    if (lane < 17) {
+      const int cnt = (lane == 2 || lane == 3) ? 6 : (lane == 12 || lane == 13 || lane == 16) ? 4 : 1;
+      mbar_init(&tl->plan_full[0] + lane, cnt);
       mbar_fence_init();
-    } else if (lane == 11) {
+    } else if (lane == 17) {
       tma_prefetch_desc(&tmQ.map);
-    } else if (lane == 12) {
+    } else if (lane == 18) {
       tma_prefetch_desc(&tmK.map);
-    } else if (lane == 13) {
+    } else if (lane == 19) {
       tma_prefetch_desc(&tmV.map);
     }
-  } else if (tid - 32 < 2 * (kMaxList / 32)) {
-    (&tl->bits[0][0])[tid - 32] = 0u;
   }
-  __syncthreads();
-  // The Q tile and the TMEM allocation do not depend on the block list: start them
-  // now so that their latency overlaps the list construction.
-  if (warp == 4 && lane == 0) {
-    mbar_expect_tx(&tl->q_full, (uint32_t)(hf[0].valid + hf[1].valid) * (kQBytes / 2));
-#pragma unroll
-    for (int t = 0; t < 2; ++t) {
-      if (!hf[t].valid) continue;
-      for (int c = 0; c < 2; ++c)
-        tma_load_tile(sQ + c * 16384 + t * 8192, &tmQ, &tl->q_full, c * 64,
-                      q_start + hf[t].qblk * kBS, hf[t].head, b);
-    }
-  }
-  if (warp == 5) {
+  if (warp == kWarpIssue) {
     tmem_alloc(&tl->tmem_base, 256);
     tmem_relinquish();
-  }
-  // union of the two halves' block lists
-#pragma unroll
-  for (int t = 0; t < 2; ++t) {
-    const int q_pos_last = past + min(hf[t].qblk * kBS + kBS, q_len) - 1;
-    for (int i = c_beg[t] + tid; i < c_end[t]; i += kFwdThreads) {
-      const int blk = __ldg(cols_of[t] + i);
-      if (blk >= 0 && blk < nkb && !(p.causal && blk * kBS > q_pos_last))
-        atomicOr(&tl->bits[t][blk >> 5], 1u << (blk & 31));
-    }
-  }
-  __syncthreads();
-  {
-    // bitmaps -> ordered list.  Every warp scans the 32 word counts by itself, then the
-    // warps share the words out; in a word each lane owns one bit.
-    const uint32_t u0 = tl->bits[0][lane], u1 = tl->bits[1][lane];
-    const uint32_t u = u0 | u1;
-    const int cnt = __popc(u);
-    int incl = cnt;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const int v = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += v;
-    }
-    const int base = incl - cnt;
-    const uint32_t nonzero = __ballot_sync(0xffffffffu, u != 0u);
-    for (int w = warp; w < 32; w += kFwdThreads / 32) {
-      if (!((nonzero >> w) & 1u)) continue;
-      const uint32_t uw = __shfl_sync(0xffffffffu, u, w);
-      const uint32_t u0w = __shfl_sync(0xffffffffu, u0, w);
-      const uint32_t u1w = __shfl_sync(0xffffffffu, u1, w);
-      const int bw = __shfl_sync(0xffffffffu, base, w);
-      if ((uw >> lane) & 1u)
-        tl->list[bw + __popc(uw & ((1u << lane) - 1u))] =
-            (uint32_t)(w * 32 + lane) | (((u0w >> lane) & 1u) << 16) | (((u1w >> lane) & 1u) << 17);
-    }
-    if (tid == 31) tl->n_list = incl;
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const int n = tl->n_list;
   const uint32_t tmem = tl->tmem_base;
   const uint32_t tS[2] = {tmem, tmem + 64};
   const uint32_t tO = tmem + 128;
+  // Round r hands items [r * grid, (r + 1) * grid) to the CTAs.
+  // -2: no more rounds; -1: nothing for this CTA in this round.
+  auto item_of = [&](int r) -> int {
+    const long long base = (long long)r * gridDim.x;
+    if (base >= n_items) return -2;
+    const long long it = base + blockIdx.x;
+    return it < n_items ? (int)it : -1;
+  };
 
-  if (n > 0 && warp == 4) {
-    // ------------------------------------------------------------ TMA producer
+  if (warp == kWarpPlan) {
+    // ============================================================ planner
+    int k = 0;
+    for (int r = 0;; ++r) {
+      const int item = item_of(r);
+      if (item == -2) break;
+      if (item < 0) continue;
+      const int pb = k & 1;
+      if (!mbar_wait(&tl->plan_free[pb], ((k >> 1) & 1) ^ 1, wait_status, 401)) break;
+      build_plan(p, mode, item, tiles_x, head_items, &tl->plan[pb], tl->bits, lane);
+      if (lane == 0) mbar_arrive(&tl->plan_full[pb]);
+      ++k;
+    }
+  } else if (warp == kWarpProd) {
+    // ============================================================ TMA producer
     if (lane == 0) {
-      for (int j = 0; j < n; ++j) {
-        const int s = j % kStagesF;
-        const uint32_t ph = ((j / kStagesF) & 1) ^ 1;
-        const int tok = k_start + (int)(tl->list[j] & 0xffffu) * kBS;
-        uint8_t* kdst = sKV + s * 2 * kKVBytes;
-        uint8_t* vdst = kdst + kKVBytes;
-        if (!mbar_wait(&tl->qk_done[s], ph, wait_status, 201)) break;
-        mbar_expect_tx(&tl->k_full[s], kKVBytes);
-        tma_load_tile(kdst, &tmK, &tl->k_full[s], 0, tok, kvh, b);
-        tma_load_tile(kdst + 8192, &tmK, &tl->k_full[s], 64, tok, kvh, b);
-        if (!mbar_wait(&tl->pv_done[s], ph, wait_status, 202)) break;
-        mbar_expect_tx(&tl->v_full[s], kKVBytes);
-        tma_load_tile(vdst, &tmV, &tl->v_full[s], 0, tok, kvh, b);
-        tma_load_tile(vdst + 8192, &tmV, &tl->v_full[s], 64, tok, kvh, b);
+      uint32_t g = 0;      // kv blocks issued so far, over all tiles
+      int k = 0, ko = 0;   // tiles seen / tiles with work
+      bool ok = true;
+      for (int r = 0; ok; ++r) {
+        const int item = item_of(r);
+        if (item == -2) break;
+        if (item < 0) continue;
+        const int pb = k & 1;
+        if (!mbar_wait(&tl->plan_full[pb], (k >> 1) & 1, wait_status, 402)) break;
+        const Plan* pl = &tl->plan[pb];
+        const int n = pl->n;
+        if (n > 0) {
+          // the Q tile may be replaced once the previous tile's last Q K^T has completed
+          if (ko > 0 && !mbar_wait(&tl->q_free, (ko - 1) & 1, wait_status, 403)) break;
+          mbar_expect_tx(&tl->q_full, (uint32_t)(pl->hvalid[0] + pl->hvalid[1]) * (kQBytes / 2));
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            if (!pl->hvalid[t]) continue;
+            for (int c = 0; c < kSub; ++c)
+              tma_load_tile(sQ + c * 16384 + t * 8192, &tmQ, &tl->q_full, c * 64,
+                            pl->q_start + pl->qblk[t] * kBS, pl->head[t], pl->b);
+          }
+          ++ko;
+          for (int j = 0; j < n; ++j, ++g) {
+            const int s = g & 1;
+            const uint32_t ph = ((g >> 1) & 1) ^ 1;   // completion of the slot's previous user
+            const int tok = pl->k_start + (int)(pl->list[j] & 0x3fffu) * kBS;
+            uint8_t* kdst = sRing + s * 2 * kTile;
+            if (!mbar_wait(&tl->qk_done[s], ph, wait_status, 404)) { ok = false; break; }
+            mbar_expect_tx(&tl->k_full[s], kTile);
+#pragma unroll
+            for (int c = 0; c < kSub; ++c)
+              tma_load_tile(kdst + c * 8192, &tmK, &tl->k_full[s], c * 64, tok, pl->kvh, pl->b);
+            if (!mbar_wait(&tl->pv_done[s], ph, wait_status, 405)) { ok = false; break; }
+            mbar_expect_tx(&tl->v_full[s], kTile);
+#pragma unroll
+            for (int c = 0; c < kSub; ++c)
+              tma_load_tile(kdst + kTile + c * 8192, &tmV, &tl->v_full[s], c * 64, tok, pl->kvh, pl->b);
+          }
+        }
+        if (ok) mbar_arrive(&tl->plan_free[pb]);
+        ++k;
       }
     }
-  } else if (n > 0 && warp == 5) {
-    // ------------------------------------------------------------ MMA issuer
-    // One thread issues every product, in the order  Q K_0, Q K_1, then per block j:
-    // P V_j, Q K_{j+2}.  Q K_{j+2} overwrites the columns P_j sits in; it is issued right
-    // behind P V_j without waiting for that product to complete, because the tensor pipe
-    // executes one thread's tcgen05.mma instructions in issue order.
-    // The whole warp runs this loop converged, so that descriptors and addresses stay in
-    // uniform registers; only the tcgen05 instructions themselves sit under the elected lane.
-    // (A single diverged lane spends about a hundred cycles of dependent scalar work per
-    // product, which is more than the product takes on the tensor pipe.)
-    {
-      const uint32_t idesc_qk = umma_idesc(BF16, 128, kBS, false, false);
-      const uint32_t idesc_pv = umma_idesc(BF16, 128, kD, false, true);
-      // descriptors of the first tile of each operand; the start-address field (bits
-      // 0..13, units of 16 bytes) is advanced by plain additions afterwards
-      const uint64_t qdesc0 = umma_desc_sw128(smem_u32(sQ), 16, 1024);
-      const uint64_t kdesc0 = umma_desc_sw128(smem_u32(sKV), 16, 1024);
-      // V tile: rows = kv tokens (K of this product), 128 contiguous bytes = 64 head
-      // dims (N); the two 64-dim halves are 8 KB apart (LBO); 16 tokens per k-step
-      const uint64_t vdesc0 = umma_desc_sw128(smem_u32(sKV) + kKVBytes, 8192, 1024);
-      auto issue_qk = [&](int j) -> bool {
-        const int s = j & 1;
-        if (!mbar_wait(&tl->k_full[s], (j >> 1) & 1, wait_status, 204)) return false;
-        tc_fence_after();
-        const uint64_t db0 = kdesc0 + (uint64_t)((s * 2 * kKVBytes) >> 4);
-        if (elect_one()) {
+  } else if (warp == kWarpIssue) {
+    // ============================================================ MMA issuer
+    // The whole warp runs the loop converged, so that descriptors and addresses stay in
+    // uniform registers; only the tcgen05 instructions sit under the elected lane.  Per
+    // block the order is P V_g, Q K_{g+2}: the tensor pipe runs one thread's products in
+    // issue order, so the product that overwrites P_g's columns needs no completion wait.
+    const uint32_t idesc_qk = umma_idesc(BF16, 128, kBS, false, false);
+    const uint32_t idesc_pv = umma_idesc(BF16, 128, D, false, true);
+    const uint64_t qdesc0 = umma_desc_sw128(smem_u32(sQ), 16, 1024);
+    const uint64_t kdesc0 = umma_desc_sw128(smem_u32(sRing), 16, 1024);
+    // V tile read MN-major: 16 tokens (2 KB) per k-step, the two 64-dim halves 8 KB apart
+    const uint64_t vdesc0 = umma_desc_sw128(smem_u32(sRing) + kTile, 8192, 1024);
+    uint32_t g = 0;
+    int k = 0, ko = 0;
+    bool ok = true;
+    // Q K^T of block gq (gq counts over all tiles); `last` marks the tile's last block
+    auto issue_qk = [&](uint32_t gq, bool last) -> bool {
+      const int s = gq & 1;
+      if (!mbar_wait(&tl->k_full[s], (gq >> 1) & 1, wait_status, 411)) return false;
+      tc_fence_after();
+      const uint64_t db0 = kdesc0 + (uint64_t)((s * 2 * kTile) >> 4);
+      if (elect_one()) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i)   // i = c * 4 + kk: sub-tile c (8 KB apart for K, 16 KB for Q), k-step kk
-            tc_mma_ss(tS[s], qdesc0 + (uint64_t)(((i >> 2) * 16384 + (i & 3) * 32) >> 4),
-                      db0 + (uint64_t)(((i >> 2) * 8192 + (i & 3) * 32) >> 4), idesc_qk, i ? 1u : 0u);
-          tc_commit(&tl->qk_done[s]);
-        }
-        __syncwarp();
-        return true;
-      };
-      bool ok = mbar_wait(&tl->q_full, 0, wait_status, 203);
-      for (int j = 0; j < 2 && j < n && ok; ++j) ok = issue_qk(j);
-      for (int j = 0; j < n && ok; ++j) {
-        const int s = j & 1;
-        if (!mbar_wait(&tl->p_full[s], (j >> 1) & 1, wait_status, 205)) break;
-        if (!mbar_wait(&tl->v_full[s], (j >> 1) & 1, wait_status, 206)) break;
-        tc_fence_after();
-        const uint64_t dv0 = vdesc0 + (uint64_t)((s * 2 * kKVBytes) >> 4);
-        const uint32_t acc0 = j ? 1u : 0u;
-        if (elect_one()) {
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            tc_mma_ts(tO, tS[s] + kk * 8, dv0 + (uint64_t)((kk * 2048) >> 4), idesc_pv, kk ? 1u : acc0);
-          tc_commit(&tl->pv_done[s]);
-        }
-        __syncwarp();
-        if (j + 2 < n) ok = issue_qk(j + 2);
+        for (int i = 0; i < D / 16; ++i)   // i = c * 4 + kk: sub-tile c (8 KB apart for K, 16 KB for Q), k-step kk
+          tc_mma_ss(tS[s], qdesc0 + (uint64_t)(((i >> 2) * 16384 + (i & 3) * 32) >> 4),
+                    db0 + (uint64_t)(((i >> 2) * 8192 + (i & 3) * 32) >> 4), idesc_qk, i ? 1u : 0u);
+        tc_commit(&tl->qk_done[s]);
+        if (last) tc_commit(&tl->q_free);
       }
+      __syncwarp();
+      return true;
+    };
+    for (int r = 0; ok; ++r) {
+      const int item = item_of(r);
+      if (item == -2) break;
+      if (item < 0) continue;
+      const int pb = k & 1;
+      if (!mbar_wait(&tl->plan_full[pb], (k >> 1) & 1, wait_status, 412)) break;
+      const int n = tl->plan[pb].n;
+      if (n > 0) {
+        if (!mbar_wait(&tl->q_full, ko & 1, wait_status, 413)) break;
+        for (int j = 0; j < 2 && j < n && ok; ++j) ok = issue_qk(g + j, j == n - 1);
+        for (int j = 0; j < n && ok; ++j, ++g) {
+          const int s = g & 1;
+          // V first: its probe is then off the path between the softmax publishing P and P V
+          if (!mbar_wait(&tl->v_full[s], (g >> 1) & 1, wait_status, 415)) { ok = false; break; }
+          if (!mbar_wait(&tl->p_full[s], (g >> 1) & 1, wait_status, 414)) { ok = false; break; }
+          // the previous tile's epilogue must have read O before it is overwritten
+          if (j == 0 && ko > 0 && !mbar_wait(&tl->o_free, (ko - 1) & 1, wait_status, 416)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t dv0 = vdesc0 + (uint64_t)((s * 2 * kTile) >> 4);
+          const uint32_t acc0 = j ? 1u : 0u;
+          if (elect_one()) {
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)
+              tc_mma_ts(tO, tS[s] + kk * 8, dv0 + (uint64_t)((kk * 2048) >> 4), idesc_pv, kk ? 1u : acc0);
+            tc_commit(&tl->pv_done[s]);
+          }
+          __syncwarp();
+          if (j + 2 < n) ok = issue_qk(g + 2, j + 2 == n - 1);
+        }
+        ++ko;
+      }
+      if (ok && elect_one()) mbar_arrive(&tl->plan_free[pb]);
+      __syncwarp();
+      ++k;
     }
-    __syncwarp();
-  } else if (n > 0) {
-    // ------------------------------------------------------------ softmax (warps 0-3)
+  } else if (warp < 4) {
+    // ============================================================ softmax + epilogue (warps 0-3)
     const int r = tid;            // tile row = TMEM lane
     const int t = r >> 6;         // half
     const int rr = r & 63;
     const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
     const float scale2 = p.sm_scale * kLog2e;
-    const Half my = t ? hf[1] : hf[0];
-    const int q_row = my.qblk * kBS + rr;   // row inside the sequence
-    const int qpos = past + q_row;
-    float m_used = -INFINITY, l = 0.f;
-    bool alive = true;
-    // Completions of P V are observed in order, one phase of a barrier at a time (a parity
-    // wait only means something while the waiter is at most one phase behind).  Q K_j^T was
-    // issued after P V_{j-2} completed, so observing up to j-2 never blocks; P V_{j-1} is
-    // only waited for when the accumulator has to be rescaled.
-    int seen = 0;
-    auto observe_pv = [&](int upto) {   // P V_0 .. P V_upto have completed
-      while (seen <= upto) {
-        if (!mbar_wait(&tl->pv_done[seen & 1], (seen >> 1) & 1, wait_status, 208)) return false;
-        ++seen;
-      }
-      return true;
+    const bool wide = reinterpret_cast<uintptr_t>(p.o) % 16 == 0 && p.o_ss % 8 == 0 &&
+                      p.o_sh % 8 == 0 && p.o_sb % 8 == 0;   // rows start on 16-byte boundaries
+    uint32_t g = 0;      // kv blocks processed so far, over all tiles
+    // Completion of P V_x.  A parity wait is unambiguous while the barrier can be at most one
+    // phase past the awaited one: that holds for x = g-1 while block g is being processed (the
+    // barrier's next phase, P V_{g+1}, needs this warp's P_{g+1}) and for the last block of a
+    // tile in its epilogue.  P V_{g-2} needs no wait at all: Q K_g^T was queued behind it and
+    // the tensor pipe runs in order, so S_g being readable implies it has completed.
+    auto wait_pv = [&](uint32_t x) {
+      return mbar_wait(&tl->pv_done[x & 1], (x >> 1) & 1, wait_status, 421);
     };
-    for (int j = 0; j < n; ++j) {
-      if (!mbar_wait(&tl->qk_done[j & 1], (j >> 1) & 1, wait_status, 207)) { alive = false; break; }
-      tc_fence_after();
-      uint32_t sv[64];
-      tmem_ld32(tS[j & 1] + lane_off, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
-      tmem_ld32(tS[j & 1] + lane_off + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
-      tmem_ld_wait();
-      const uint32_t ent = tl->list[j];
-      const int kbase = (int)(ent & 0xffffu) * kBS;
-      const bool att = ((ent >> (16 + t)) & 1u) != 0 && my.valid;
-      // Allowed columns of this block form a prefix: kpos < k_len and, when causal,
-      // kpos <= qpos.  Raw logits are compared (sm_scale > 0); the scale is folded
-      // into the exponent's FMA.
-      float mx = -INFINITY;
-      if (att) {
+    int k = 0;
+    bool alive = true;
+    for (int r = 0; alive; ++r) {
+      const int item = item_of(r);
+      if (item == -2) break;
+      if (item < 0) continue;
+      const int pb = k & 1;
+      if (!mbar_wait(&tl->plan_full[pb], (k >> 1) & 1, wait_status, 422)) break;
+      const Plan* pl = &tl->plan[pb];
+      const int n = pl->n;
+      const int hvalid = pl->hvalid[t], head = pl->head[t];
+      const int q_row = pl->qblk[t] * kBS + rr;   // row inside the sequence
+      const int q_len = pl->q_len, k_len = pl->k_len, b = pl->b;
+      const int qpos = pl->past + q_row;
+      const bool row_ok = hvalid && q_row < q_len;
+      uint8_t* orow = reinterpret_cast<uint8_t*>(p.o) +
+                      ((int64_t)b * p.o_sb + (int64_t)head * p.o_sh + (int64_t)(pl->q_start + q_row) * p.o_ss) * 2;
+      float* lse_ptr = p.lse ? p.lse + (int64_t)b * p.lse_sb + (int64_t)head * p.lse_sh + pl->q_start + q_row
+                             : nullptr;
+      if (n == 0) {
+        if (pl->valid && row_ok) {   // a tile that attends nothing: zero rows, LSE = -inf
+          for (int i = 0; i < D / 4; ++i) reinterpret_cast<uint2*>(orow)[i] = make_uint2(0u, 0u);
+          if (lse_ptr) *lse_ptr = -INFINITY;
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tl->plan_free[pb]);
+        ++k;
+        continue;
+      }
+      float m_used = -INFINITY, l = 0.f;
+      for (int j = 0; j < n; ++j, ++g) {
+        const int s = g & 1;
+        // everything that only depends on the block list is done before the barrier probe
+        const uint32_t ent = pl->list[j];
+        const int kbase = (int)(ent & 0x3fffu) * kBS;
+        const bool att = ((ent >> (14 + t)) & 1u) != 0 && hvalid;
         int lim = k_len - kbase;
         if (p.causal) lim = min(lim, qpos - kbase + 1);
-        if (lim < kBS) {
-#pragma unroll
-          for (int c = 0; c < 64; ++c)
-            if (c >= lim) sv[c] = 0xff800000u;  // -inf
-        }
-        float m8[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) m8[i] = __uint_as_float(sv[i]);
-#pragma unroll
-        for (int c = 8; c < 64; c += 8)
-#pragma unroll
-          for (int i = 0; i < 8; ++i) m8[i] = fmaxf(m8[i], __uint_as_float(sv[c + i]));
-        mx = fmaxf(fmaxf(fmaxf(m8[0], m8[1]), fmaxf(m8[2], m8[3])),
-                   fmaxf(fmaxf(m8[4], m8[5]), fmaxf(m8[6], m8[7]))) * scale2;
-      }
-      float alpha = 1.f;
-      bool need = false;
-      if (att && mx != -INFINITY) {
-        if (m_used == -INFINITY) {
-          m_used = mx;   // first attended block of this row: O row is still exactly 0
-        } else if (mx > m_used + kRescaleThreshold) {
-          alpha = ex2(m_used - mx);
-          m_used = mx;
-          l *= alpha;
-          need = true;
-        }
-      }
-      const bool any = __any_sync(0xffffffffu, need);
-      uint32_t pk[32];
-      if (att && m_used != -INFINITY) {
-        float sum[4] = {0.f, 0.f, 0.f, 0.f};
-        const float neg_m = -m_used;
-#pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          const float p0 = ex2(fmaf(__uint_as_float(sv[2 * c]), scale2, neg_m));
-          const float p1 = ex2(fmaf(__uint_as_float(sv[2 * c + 1]), scale2, neg_m));
-          sum[(2 * c) & 3] += p0;
-          sum[(2 * c + 1) & 3] += p1;
-          pk[c] = pack2<BF16>(p0, p1);
-        }
-        l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
-      } else {
-#pragma unroll
-        for (int c = 0; c < 32; ++c) pk[c] = 0u;
-      }
-      tmem_st32(tS[j & 1] + lane_off, pk);
-      if (!observe_pv(any ? j - 1 : j - 2)) { alive = false; break; }
-      if (any && j > 0) {
-        // rescale the accumulator rows whose maximum moved (P V_{j-1} has landed)
+        if (!mbar_wait(&tl->qk_done[s], (g >> 1) & 1, wait_status, 423)) { alive = false; break; }
         tc_fence_after();
+        uint32_t sv[64];
+        tmem_ld32(tS[s] + lane_off, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
+        tmem_ld32(tS[s] + lane_off + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
+        tmem_ld_wait();
+        // Allowed columns of this block form a prefix: kpos < k_len and, when causal,
+        // kpos <= qpos.  Raw logits are compared (sm_scale > 0); the scale is folded
+        // into the exponent's FMA.
+        float mx = -INFINITY;
+        if (att) {
+          if (lim < kBS) {
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          uint32_t o[32];
-          tmem_ld32(tO + lane_off + ch * 32, o);
-          tmem_ld_wait();
+            for (int c = 0; c < 64; ++c)
+              if (c >= lim) sv[c] = 0xff800000u;  // -inf
+          }
+          float m4[4];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tmem_st32(tO + lane_off + ch * 32, o);
+          for (int i = 0; i < 4; ++i) m4[i] = max3(__uint_as_float(sv[3 * i]), __uint_as_float(sv[3 * i + 1]),
+                                                   __uint_as_float(sv[3 * i + 2]));
+#pragma unroll
+          for (int c = 12; c < 60; c += 8)
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              m4[i] = max3(m4[i], __uint_as_float(sv[c + 2 * i]), __uint_as_float(sv[c + 2 * i + 1]));
+          mx = max3(max3(m4[0], m4[1], m4[2]), max3(m4[3], __uint_as_float(sv[60]), __uint_as_float(sv[61])),
+                    fmaxf(__uint_as_float(sv[62]), __uint_as_float(sv[63]))) * scale2;
         }
-      }
-      // tcgen05.wait::st is warp-wide: after it every lane's P row is in TMEM, so one
-      // arrival per warp publishes them
-      tmem_st_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&tl->p_full[j & 1]);
-    }
-    // ---- epilogue: O / l -> registers -> swizzled smem (the Q tile is dead) -> global
-    if (alive) alive = observe_pv(n - 1);
-    tc_fence_after();
-    if (alive) {
-      // ---- epilogue: each thread normalises its own row and stores it straight from
-      // registers, 64 contiguous bytes per 32-column chunk
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      const bool row_ok = my.valid && q_row < q_len;
-      uint8_t* orow = reinterpret_cast<uint8_t*>(p.o) +
-                      ((int64_t)b * p.o_sb + (int64_t)my.head * p.o_sh + (int64_t)(q_start + q_row) * p.o_ss) * 2;
-      const bool wide = reinterpret_cast<uintptr_t>(p.o) % 16 == 0 && p.o_ss % 8 == 0 &&
-                        p.o_sh % 8 == 0 && p.o_sb % 8 == 0;   // rows start on 16-byte boundaries
+        float alpha = 1.f;
+        bool need = false;
+        if (att && mx != -INFINITY) {
+          if (m_used == -INFINITY) {
+            m_used = mx;   // first attended block of this row: its O row is still exactly 0
+          } else if (mx > m_used + kRescaleThreshold) {
+            alpha = ex2(m_used - mx);
+            m_used = mx;
+            l *= alpha;
+            need = true;
+          }
+        }
+        const bool any = __any_sync(0xffffffffu, need);
+        // P is produced and stored in two halves, so that the first store's latency is covered
+        // by the second half's exponentials and fewer packed values are live at a time
+        const bool live = att && m_used != -INFINITY;
+        const float neg_m = -m_used;
+        // two columns per fused multiply-add and per addition (packed fp32 pairs): the softmax
+        // warps are bound by instruction issue as much as by the exponential unit
+        const uint64_t scale_2 = f32x2(scale2, scale2), neg_m2 = f32x2(neg_m, neg_m);
+        uint64_t sum2[2] = {0ull, 0ull};
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
+        for (int hlf = 0; hlf < 2; ++hlf) {
+          uint32_t pk[16];
+          if (live) {
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+              float x0, x1;
+              f32x2_split(fma_f32x2(f32x2(sv[hlf * 32 + 2 * c], sv[hlf * 32 + 2 * c + 1]), scale_2, neg_m2), x0, x1);
+              const float p0 = ex2(x0), p1 = ex2(x1);
+              sum2[c & 1] = add_f32x2(sum2[c & 1], f32x2(p0, p1));
+              pk[c] = pack2<BF16>(p0, p1);
+            }
+          } else {
+#pragma unroll
+            for (int c = 0; c < 16; ++c) pk[c] = 0u;
+          }
+          tmem_st16(tS[s] + lane_off + hlf * 16, pk);
+        }
+        float sum[4];
+        f32x2_split(sum2[0], sum[0], sum[1]);
+        f32x2_split(sum2[1], sum[2], sum[3]);
+        l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
+        if (any && j > 0) {
+          // rescale the accumulator rows whose maximum moved, once P V_{g-1} has landed
+          if (!wait_pv(g - 1)) { alive = false; break; }
+          tc_fence_after();
+#pragma unroll
+          for (int ch = 0; ch < D / 32; ++ch) {
+            uint32_t o[32];
+            tmem_ld32(tO + lane_off + ch * 32, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st32(tO + lane_off + ch * 32, o);
+          }
+        }
+        if (k_len - kbase < kBS) {
+          // The block reaches past the end of the sequence.  Its logits are masked above, but the
+          // P V product still reads the whole V tile, and rows past the end hold whatever the
+          // caller's buffer holds there (0 * NaN = NaN): clear them in shared memory.
+          if (!mbar_wait(&tl->v_full[s], (g >> 1) & 1, wait_status, 424)) { alive = false; break; }
+          uint8_t* vt = sRing + s * 2 * kTile + kTile;
+          const int first = k_len - kbase;   // >= 1: blocks that start at or past the end are not listed
+          for (int idx = tid; idx < (kBS - first) * kSub * 8; idx += 128) {
+            const int row = first + idx / (kSub * 8), c = (idx / 8) % kSub, ch = idx & 7;
+            *reinterpret_cast<uint4*>(vt + c * 8192 + row * 128 + ch * 16) = make_uint4(0u, 0u, 0u, 0u);
+          }
+          fence_proxy_async();   // generic-proxy writes -> visible to the tensor core's reads
+        }
+        // tcgen05.wait::st is warp-wide: after it every lane's P row is in TMEM, so one
+        // arrival per warp publishes them
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tl->p_full[s]);
+      }
+      if (!alive) break;
+      // ---- epilogue of the tile: all its P V products must have completed; each thread
+      // normalises its own row and stores it straight from registers
+      if (!wait_pv(g - 1)) { alive = false; break; }
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+      for (int ch = 0; ch < D / 32; ++ch) {
         uint32_t o[32];
         tmem_ld32(tO + lane_off + ch * 32, o);
         tmem_ld_wait();
@@ -440,6 +541,12 @@ fwd_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap
 #pragma unroll
         for (int i = 0; i < 16; ++i)
           w[i] = pack2<BF16>(__uint_as_float(o[2 * i]) * inv, __uint_as_float(o[2 * i + 1]) * inv);
+        if (ch == D / 32 - 1) {
+          // O has been read: the next tile's first P V may overwrite it
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tl->o_free);
+        }
         if (row_ok) {
           if (wide) {
 #pragma unroll
@@ -453,32 +560,15 @@ fwd_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap
           }
         }
       }
-      if (p.lse && row_ok)
-        p.lse[(int64_t)b * p.lse_sb + (int64_t)my.head * p.lse_sh + q_start + q_row] =
-            l > 0.f ? (m_used + log2f(l)) * kLn2 : -INFINITY;
-    }
-  } else if (warp == 4) {
-    // nothing to attend: the Q tile is still in flight and must land before the CTA exits
-    if (lane == 0) mbar_wait(&tl->q_full, 0, wait_status, 211);
-  } else if (warp < 4) {
-    // no attended block at all: zero rows, LSE = -inf
-    const int r = tid, t = r >> 6;
-    const Half my = t ? hf[1] : hf[0];
-    const int q_row = my.qblk * kBS + (r & 63);
-    if (my.valid && q_row < q_len) {
-      uint4* dst = reinterpret_cast<uint4*>(
-          reinterpret_cast<uint8_t*>(p.o) +
-          ((int64_t)b * p.o_sb + (int64_t)my.head * p.o_sh + (int64_t)(q_start + q_row) * p.o_ss) * 2);
-      // rows are only guaranteed 8-byte aligned
-      uint2* d2 = reinterpret_cast<uint2*>(dst);
-      for (int i = 0; i < 32; ++i) d2[i] = make_uint2(0u, 0u);
-      if (p.lse)
-        p.lse[(int64_t)b * p.lse_sb + (int64_t)my.head * p.lse_sh + q_start + q_row] = -INFINITY;
+      if (row_ok && lse_ptr) *lse_ptr = l > 0.f ? (m_used + log2f(l)) * kLn2 : -INFINITY;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tl->plan_free[pb]);
+      ++k;
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) tmem_dealloc(tmem, 256);
+  if (warp == kWarpIssue) tmem_dealloc(tmem, 256);
 }
 
 }  // namespace
@@ -486,7 +576,7 @@ fwd_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap
 bool sm100_fwd_supported(const bsa_fwd_params* p, const char** why) {
   auto no = [&](const char* w) { *why = w; return false; };
   if (!(p->dtype == BSA_F16 || p->dtype == BSA_BF16)) return no("dtype is not f16/bf16");
-  if (p->d != kD) return no("head dim is not 128");
+  if (p->d != 128 && p->d != 64) return no("head dim is not 64 or 128");
   if (p->block_size != kBS) return no("block size is not 64");
   if (p->sk > kMaxList * kBS) return no("more than 65536 key positions");
   if (!tma_compatible(p->q, 2, p->q_ss, p->q_sh, p->q_sb) ||
@@ -500,21 +590,19 @@ bool sm100_fwd_supported(const bsa_fwd_params* p, const char** why) {
   return true;
 }
 
-int sm100_fwd(const bsa_fwd_params* p, cudaStream_t s) {
-  // The persistent kernel (two CTAs per SM walking the tile list) serves every call;
-  // BSA_FWD_TILED=1 selects the one-tile-per-CTA kernel below for comparison runs.
-  static const bool tiled = getenv("BSA_FWD_TILED") != nullptr;
-  if (!tiled && sm100_fwd_persist_supported(p)) return sm100_fwd_persist(p, s);
-  const bool bf16 = p->dtype == BSA_BF16;
+namespace {
+template <bool BF16, int D>
+int launch_fwd(const bsa_fwd_params* p, cudaStream_t s) {
   Tmap4 tmQ, tmK, tmV;
-  int rc = make_tmap_4d(&tmQ, p->q, 2, kD, p->sq, p->hq, p->total_q > 0 ? 1 : p->batch, p->q_ss * 2,
-                        p->q_sh * 2, p->q_sb * 2, 64, 64, true, bf16);
+  const uint64_t nb = p->total_q > 0 ? 1 : p->batch;
+  int rc = make_tmap_4d(&tmQ, p->q, 2, D, p->sq, p->hq, nb, p->q_ss * 2, p->q_sh * 2, p->q_sb * 2, 64, 64,
+                        true, BF16);
   if (rc) return rc;
-  rc = make_tmap_4d(&tmK, p->k, 2, kD, p->sk, p->hkv, p->total_q > 0 ? 1 : p->batch, p->k_ss * 2,
-                    p->k_sh * 2, p->k_sb * 2, 64, 64, true, bf16);
+  rc = make_tmap_4d(&tmK, p->k, 2, D, p->sk, p->hkv, nb, p->k_ss * 2, p->k_sh * 2, p->k_sb * 2, 64, 64,
+                    true, BF16);
   if (rc) return rc;
-  rc = make_tmap_4d(&tmV, p->v, 2, kD, p->sk, p->hkv, p->total_q > 0 ? 1 : p->batch, p->v_ss * 2,
-                    p->v_sh * 2, p->v_sb * 2, 64, 64, true, bf16);
+  rc = make_tmap_4d(&tmV, p->v, 2, D, p->sk, p->hkv, nb, p->v_ss * 2, p->v_sh * 2, p->v_sb * 2, 64, 64,
+                    true, BF16);
   if (rc) return rc;
   const int G = p->hq / p->hkv;
   // Two heads share a tile only when they share a block list (one pattern for all heads
@@ -524,23 +612,31 @@ int sm100_fwd(const bsa_fwd_params* p, cudaStream_t s) {
   const int mode = (G % 2 == 0 && p->h_pat != p->hq) ? kPairHeads : kPairRows;
   const int tile_rows = mode == kPairHeads ? 64 : 128;
   const int head_items = mode == kPairHeads ? p->hq / 2 : p->hq;
-  dim3 grid;
-  if (p->total_q > 0)
-    grid = dim3(cdiv_i(p->total_q, tile_rows) + p->batch, head_items, 1);
-  else
-    grid = dim3(cdiv_i(p->sq, tile_rows), head_items, p->batch);
+  const int tiles_x = p->total_q > 0 ? cdiv_i(p->total_q, tile_rows) + p->batch : cdiv_i(p->sq, tile_rows);
+  const long long n_items_ll = (long long)tiles_x * head_items * (p->total_q > 0 ? 1 : p->batch);
+  if (n_items_ll > 0x7fffffffLL) {
+    set_error("bsa_fwd: too many tiles for one launch");
+    return BSA_E_TOOBIG;
+  }
+  const int n_items = (int)n_items_ll;
+  int dev = 0, sms = 148;
+  BSA_CHECK_CUDA(cudaGetDevice(&dev));
+  BSA_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  const int grid = n_items < 2 * sms ? n_items : 2 * sms;   // two resident CTAs per SM
   int* status = wait_status_ptr();
   if (!status) return BSA_E_CUDA;
-  if (bf16) {
-    auto kern = fwd_sm100_kernel<true>;
-    BSA_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFwdSmem));
-    kern<<<grid, kFwdThreads, kFwdSmem, s>>>(tmQ, tmK, tmV, *p, mode, status);
-  } else {
-    auto kern = fwd_sm100_kernel<false>;
-    BSA_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFwdSmem));
-    kern<<<grid, kFwdThreads, kFwdSmem, s>>>(tmQ, tmK, tmV, *p, mode, status);
-  }
-  return check_launch("fwd_sm100_kernel");
+  constexpr size_t smem = Geo<D>::kSmem + sizeof(TailP);
+  auto kern = fwd_persist_kernel<BF16, D>;
+  BSA_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<grid, kThreadsP, smem, s>>>(tmQ, tmK, tmV, *p, mode, n_items, tiles_x, head_items, status);
+  return check_launch("fwd_persist_kernel");
+}
+}  // namespace
+
+int sm100_fwd(const bsa_fwd_params* p, cudaStream_t s) {
+  const bool bf16 = p->dtype == BSA_BF16;
+  if (p->d == 128) return bf16 ? launch_fwd<true, 128>(p, s) : launch_fwd<false, 128>(p, s);
+  return bf16 ? launch_fwd<true, 64>(p, s) : launch_fwd<false, 64>(p, s);
 }
 
 }  // namespace bsa

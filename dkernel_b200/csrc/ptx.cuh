@@ -70,19 +70,34 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 }
 // Bounded wait.  mbarrier.try_wait suspends the thread in hardware for a while
 // before it reports failure, so the loop neither burns issue slots nor adds
-// wake-up latency; the bound is wall-clock time (kWaitLimitNs).  Returns false
-// (and sets *status to `code`) when it gave up.
+// wake-up latency; the bound is wall-clock time (kWaitLimitNs unless the caller
+// gives its own).  Returns false when it gave up, after recording `code`:
+// `status` points at the device status block {int code; int pad; int* mirror}.
+// The first wait that gives up stores its code in the block and, when the host
+// has registered one, in the host-visible mirror word, so that the host can
+// notice without synchronising.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
+static __device__ __noinline__ void record_wait_failure(int* status, int code) {
+  if (!status) return;
+  if (atomicCAS(status, 0, code) == 0) {
+    int* mirror = *reinterpret_cast<int* volatile*>(status + 2);
+    if (mirror) {
+      *reinterpret_cast<volatile int*>(mirror) = code;
+      __threadfence_system();
+    }
+  }
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code,
+                                          uint64_t limit_ns = kWaitLimitNs) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
   while (true) {
 #pragma unroll 1
     for (int i = 0; i < 64; ++i)
       if (mbar_try_wait(bar, parity)) return true;
-    if (global_timer_ns() - t0 > kWaitLimitNs) break;
+    if (global_timer_ns() - t0 > limit_ns) break;
   }
-  if (status) atomicCAS(status, 0, code);
+  record_wait_failure(status, code);
   return false;
 }
 

@@ -1,28 +1,39 @@
 """Single-node multi-GPU partitioning (one process per GPU, torch.distributed).
 
-Two schemes, matching what the attention path allows:
+Three schemes, matching what the attention path allows:
 
 * **Head sharding** -- heads are independent, so a rank owns a contiguous range of
   q heads (whole kv groups) and builds its module with ``active_head_range``
   (dkernel/interface.py:293-298).  No collective is involved.
 * **KV-sequence sharding for decode** -- every rank holds a block-aligned slice
   of each sequence's keys/values, computes a partial (O, LSE) with the decode
-  kernel and the partials are merged after ONE all-gather (NCCL over NVLink on
-  GPUs) with the semantics of ``combine_attn_partitions``
-  (dkernel/interface.py:319-324).
+  kernel, and the partials are merged with the semantics of
+  ``combine_attn_partitions`` (dkernel/interface.py:319-324).  Two exchange
+  routes: ``ShardedDecoder`` (one fused kernel per rank that stores the partial
+  rows straight into every peer's buffer over NVLink and merges as soon as the
+  peers' rows have landed; no collective library on the data path) and
+  ``sharded_decode`` (one NCCL all-gather + the fused merge kernel).
+* **Context-parallel (ring) prefill / training** -- the sequence is cut into one
+  chunk per rank; K/V chunks travel round the ring while every rank attends its
+  q chunk to the chunk it currently holds, partial results are merged by LSE and
+  gradients travel back the same way.  This is the multi-GPU form of what the
+  reference simulates on one GPU in tests/test_seq_partition.py:83-139.
 
-The planning functions are pure Python / CPU torch so that they can be tested
-with the gloo backend; only ``sharded_decode`` touches the GPU.
+The planning functions and the ring schedule are pure Python / torch so that they
+run under the gloo backend on CPU; only the compute callbacks touch the GPU.
 """
 from __future__ import annotations
 
-from typing import List, Optional, Tuple
+import ctypes as C
+import math
+from typing import Callable, Dict, List, Optional, Tuple
 
 import torch
 import torch.distributed as dist
 from torch import Tensor
 
 
+# --------------------------------------------------------------------------- head sharding
 def head_shard(num_heads: int, num_kv_heads: Optional[int], rank: int, world: int
                ) -> Tuple[Tuple[int, int], Tuple[int, int]]:
     """((q_head_start, q_head_end), (kv_head_start, kv_head_end)) of ``rank``.
@@ -37,6 +48,7 @@ def head_shard(num_heads: int, num_kv_heads: Optional[int], rank: int, world: in
     return (kv0 * g, kv1 * g), (kv0, kv1)
 
 
+# --------------------------------------------------------------------------- KV-sharded decode
 def kv_shard_ranges(lens: Tensor, rank: int, world: int, block_size: int) -> Tuple[Tensor, Tensor]:
     """Position range [lo, hi) of every sequence owned by ``rank``: the blocks of
     each sequence are dealt out proportionally, so all ranks hold about 1/world
@@ -70,53 +82,43 @@ def pack_kv_shard(k: Tensor, v: Tensor, left_paddings: Tensor, lo: Tensor, hi: T
     return ks, vs, n
 
 
-def gather_partials(o: Tensor, lse: Tensor, group=None) -> Tuple[Tensor, Tensor]:
-    """All-gather one rank's partial (o: (rows, D) any float dtype, lse: (rows,)
-    fp32) into (world, rows, D) / (world, rows).  O and LSE travel in ONE message:
-    they are packed into a single fp32 buffer (rows, D+1) so that a decode step
-    costs one collective."""
+def partial_row_bytes(d: int, elem_size: int = 2) -> int:
+    """Bytes of one packed partial row: d 16-bit outputs followed by the fp32 LSE."""
+    return d * elem_size + 4
+
+
+def packed_partial_views(packed: Tensor, d: int, dtype: torch.dtype) -> Tuple[Tensor, Tensor]:
+    """Views into a (rows, partial_row_bytes) uint8 buffer: the (rows, d) outputs in ``dtype``
+    (row stride d + 2 elements) and the (rows,) fp32 LSE column.  The decode kernel writes its
+    results straight through these views, so that ONE message carries both."""
+    assert packed.dtype == torch.uint8 and packed.dim() == 2 and packed.size(1) == partial_row_bytes(d)
+    o_view = packed[:, :2 * d].view(dtype)
+    lse_view = packed[:, 2 * d:].view(torch.float32)[:, 0]
+    return o_view, lse_view
+
+
+def gather_packed_partials(packed: Tensor, group=None) -> Tensor:
+    """All-gather of every rank's packed partial rows: (world * rows, row_bytes) uint8, rank-major."""
     world = dist.get_world_size(group)
-    rows, D = o.shape
-    packed = torch.empty((rows, D + 1), dtype=torch.float32, device=o.device)
-    packed[:, :D] = o
-    packed[:, D] = lse
-    out = torch.empty((world * rows, D + 1), dtype=torch.float32, device=o.device)
-    dist.all_gather_into_tensor(out, packed, group=group)
-    out = out.view(world, rows, D + 1)
-    return out[:, :, :D], out[:, :, D]
+    gathered = torch.empty((world * packed.size(0), packed.size(1)), dtype=torch.uint8, device=packed.device)
+    dist.all_gather_into_tensor(gathered, packed, group=group)
+    return gathered
 
 
-def merge_gathered(o_parts: Tensor, lse_parts: Tensor, out_dtype: torch.dtype
-                   ) -> Tuple[Tensor, Tensor]:
-    """Merge gathered partials ((P, rows, D) fp32 strided views and (P, rows)) with
-    the fused CUDA kernel (bsa_merge_partials).  Returns (o (rows, D) in
-    ``out_dtype``, lse (rows,))."""
-    import ctypes as C  # noqa: F401
-    from . import _lib
-    P, rows, D = o_parts.shape
-    _lib.require_cuda(o_parts, "gathered partials")
-    assert o_parts.dtype == torch.float32 and o_parts.stride(2) == 1
-    lse_c = lse_parts.contiguous()
-    res32 = torch.empty((rows, D), dtype=torch.float32, device=o_parts.device)
-    lse = torch.empty((rows,), dtype=torch.float32, device=o_parts.device)
-    with torch.cuda.device(o_parts.device):
-        _lib.check(_lib.lib().bsa_merge_partials(
-            _lib.ptr(o_parts), _lib.ptr(lse_c), P, rows, D, o_parts.stride(0), o_parts.stride(1),
-            lse_c.stride(0), 1, _lib.ptr(res32), D, _lib.ptr(lse), _lib.BSA_F32,
-            _lib.stream_of(o_parts)), "bsa_merge_partials")
-    return res32.to(out_dtype), lse
-
-
-def _as_i32(t: Optional[Tensor], device) -> Optional[Tensor]:
-    if t is None:
-        return None
-    return t.to(device=device, dtype=torch.int32).contiguous()   # no-op for int32 device tensors
+def split_gathered_partials(gathered: Tensor, world: int, d: int, dtype: torch.dtype
+                            ) -> Tuple[Tensor, Tensor]:
+    """(o_parts (world, rows, d) in ``dtype``, lse_parts (world, rows) fp32) as strided views of a
+    gathered packed buffer (no copy)."""
+    rows = gathered.size(0) // world
+    o, lse = packed_partial_views(gathered, d, dtype)
+    return o.unflatten(0, (world, rows)), lse.unflatten(0, (world, rows))
 
 
 def sharded_decode(attn, q: Tensor, k_shard: Tensor, v_shard: Tensor, n_local: Tensor,
                    pos0: Tensor, total_len: Tensor, sm_scale: Optional[float] = None,
                    group=None) -> Tuple[Tensor, Tensor]:
-    """One decode step with the KV sequence sharded over the ranks of ``group``.
+    """One decode step with the KV sequence sharded over the ranks of ``group``, exchanged by
+    ONE NCCL all-gather (the portable route; ``ShardedDecoder`` is the faster one).
 
     attn: a SparseAttention module (its pattern covers the full sequence).
     q: (B,1,Hq,D) replicated on every rank.  k_shard/v_shard: (B,cap,Hkv,D) this
@@ -127,30 +129,277 @@ def sharded_decode(attn, q: Tensor, k_shard: Tensor, v_shard: Tensor, n_local: T
 
     Per step: the decode kernel (+ its split merge) writes this rank's partial O (input
     dtype) and LSE (fp32) side by side into one byte buffer of (B*Hq) rows of 2*D+4 bytes,
-    ONE all-gather moves it, and the fused merge kernel reads the gathered rows in place."""
-    import math
+    one all-gather moves it, and the fused merge kernel reads the gathered rows in place."""
     from . import _lib
     from .ops import decode
     B, _, Hq, D = q.shape
-    rows, row_bytes = B * Hq, 2 * D + 4
+    rows, row_bytes = B * Hq, partial_row_bytes(D)
     assert q.element_size() == 2, "sharded decode packs 16-bit partial outputs"
     scale = sm_scale or 1.0 / math.sqrt(D)
     world = dist.get_world_size(group)
     packed = torch.empty((rows, row_bytes), dtype=torch.uint8, device=q.device)
-    o_view = packed[:, :2 * D].view(q.dtype)                 # (rows, D), row stride D + 2 elements
-    lse_view = packed[:, 2 * D:].view(torch.float32)[:, 0]   # (rows,), row stride (2*D+4)/4 floats
+    o_view, lse_view = packed_partial_views(packed, D, q.dtype)
     decode(q, k_shard, v_shard, attn._plan(), scale, seq_dim=1, k_start=None,
            k_end=_as_i32(n_local, q.device), k_pos0=_as_i32(pos0, q.device),
            k_total=_as_i32(total_len, q.device), out=o_view, lse_out=lse_view)
-    gathered = torch.empty((world * rows, row_bytes), dtype=torch.uint8, device=q.device)
-    dist.all_gather_into_tensor(gathered, packed, group=group)
+    gathered = gather_packed_partials(packed, group)
     merged = torch.empty((B, 1, Hq, D), dtype=q.dtype, device=q.device)
     mlse = torch.empty((B, Hq), dtype=torch.float32, device=q.device)
     elems, floats = row_bytes // 2, row_bytes // 4
-    lse_parts = gathered.view(torch.float32)      # (world*rows, floats); the LSE is the last float of a row
     with torch.cuda.device(q.device):
         _lib.check(_lib.lib().bsa_merge_partials(
-            _lib.ptr(gathered), lse_parts.data_ptr() + 2 * D, world, rows, D, rows * elems, elems,
+            _lib.ptr(gathered), gathered.data_ptr() + 2 * D, world, rows, D, rows * elems, elems,
             rows * floats, floats, _lib.ptr(merged), D, _lib.ptr(mlse), _lib.dtype_code(q.dtype),
             _lib.stream_of(q)), "bsa_merge_partials")
     return merged, mlse
+
+
+def _as_i32(t: Optional[Tensor], device) -> Optional[Tensor]:
+    if t is None:
+        return None
+    return t.to(device=device, dtype=torch.int32).contiguous()   # no-op for int32 device tensors
+
+
+class ShardedDecoder:
+    """KV-sharded decode whose exchange step is the library's own kernel over peer memory.
+
+    Construction (collective over ``group``, once): every rank allocates an exchange buffer in
+    torch's symmetric memory and maps the buffers of all ranks of the node.  A step is then
+    three launches on the caller's stream and no host synchronisation: the decode kernel and its
+    split merge write this rank's partial (O, LSE) rows into a local staging buffer, and
+    ``bsa_xchg_merge`` stores them into every rank's exchange buffer over NVLink, waits (bounded)
+    for the peers' rows to land in the local buffer and merges them.  All ranks must call
+    ``step`` the same number of times.  The call can be captured in a CUDA graph and replayed."""
+
+    def __init__(self, attn, batch: int, num_heads: int, head_dim: int, dtype: torch.dtype,
+                 device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        from . import _lib
+        assert dtype in (torch.float16, torch.bfloat16), "sharded decode exchanges 16-bit partial outputs"
+        self.attn, self.group = attn, group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.B, self.Hq, self.D, self.dtype = batch, num_heads, head_dim, dtype
+        self.rows = batch * num_heads
+        nbytes = _lib.lib().bsa_xchg_buffer_bytes(self.world, self.rows, head_dim)
+        assert nbytes > 0, "unsupported exchange geometry (at most 8 ranks, head dim a multiple of 8)"
+        self.xbuf = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
+        self.xbuf.zero_()
+        torch.cuda.synchronize(device)
+        grp = group if group is not None else dist.group.WORLD
+        self.handle = symm_mem.rendezvous(self.xbuf, grp)
+        self.peer_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        assert len(self.peer_ptrs) == self.world and self.peer_ptrs[self.rank] == self.xbuf.data_ptr()
+        dist.barrier(group)      # every buffer is zeroed before anyone's first push can arrive
+        self.stage_o = torch.empty((self.rows, head_dim), dtype=dtype, device=device)
+        self.stage_lse = torch.empty((self.rows,), dtype=torch.float32, device=device)
+
+    def step(self, q: Tensor, k_shard: Tensor, v_shard: Tensor, n_local: Tensor, pos0: Tensor,
+             total_len: Tensor, sm_scale: Optional[float] = None,
+             out: Optional[Tensor] = None, lse: Optional[Tensor] = None) -> Tuple[Tensor, Tensor]:
+        """Arguments as for ``sharded_decode``; returns the merged (out (B,1,Hq,D), lse (B,Hq))."""
+        from . import _lib
+        from .ops import decode
+        B, _, Hq, D = q.shape
+        assert (B, Hq, D) == (self.B, self.Hq, self.D) and q.dtype == self.dtype
+        scale = sm_scale or 1.0 / math.sqrt(D)
+        decode(q, k_shard, v_shard, self.attn._plan(), scale, seq_dim=1, k_start=None,
+               k_end=_as_i32(n_local, q.device), k_pos0=_as_i32(pos0, q.device),
+               k_total=_as_i32(total_len, q.device), out=self.stage_o, lse_out=self.stage_lse)
+        merged = out if out is not None else torch.empty((B, 1, Hq, D), dtype=q.dtype, device=q.device)
+        mlse = lse if lse is not None else torch.empty((B, Hq), dtype=torch.float32, device=q.device)
+        assert merged.is_contiguous() and mlse.is_contiguous()
+        p = _lib.XchgParams()
+        p.stage_o, p.stage_lse = _lib.ptr(self.stage_o), _lib.ptr(self.stage_lse)
+        p.out, p.out_lse = _lib.ptr(merged), _lib.ptr(mlse)
+        for w in range(self.world):
+            p.xbuf[w] = self.peer_ptrs[w]
+        p.rows, p.world, p.rank, p.d = self.rows, self.world, self.rank, D
+        p.dtype = _lib.dtype_code(q.dtype)
+        with torch.cuda.device(q.device):
+            _lib.check(_lib.lib().bsa_xchg_merge(C.byref(p), _lib.stream_of(q)), "bsa_xchg_merge")
+        return merged, mlse
+
+
+# --------------------------------------------------------------------------- context parallelism
+def chunk_bounds(seq_len: int, world: int, block_size: int) -> List[Tuple[int, int]]:
+    """Contiguous position ranges, one per rank: equal chunks, multiples of the block size."""
+    assert seq_len % world == 0 and (seq_len // world) % block_size == 0, \
+        f"sequence length {seq_len} must split into {world} chunks that are multiples of {block_size}"
+    c = seq_len // world
+    return [(r * c, (r + 1) * c) for r in range(world)]
+
+
+def ring_steps(rank: int, world: int, causal: bool = True) -> List[Tuple[int, int, bool]]:
+    """The ring schedule of one rank: [(step, kv_chunk, active)].  At step t the rank holds kv
+    chunk (rank - t) mod world (its own at t = 0; chunks arrive from the previous rank); with a
+    causal mask only chunks at or before the rank's own q chunk are computed."""
+    return [(t, (rank - t) % world, (not causal) or ((rank - t) % world) <= rank) for t in range(world)]
+
+
+def _ring_exchange(send: Tensor, recv: Tensor, group) -> list:
+    """Post "send to the next rank, receive from the previous one"; returns the requests."""
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    nxt = dist.get_global_rank(group, (rank + 1) % world) if group is not None else (rank + 1) % world
+    prv = dist.get_global_rank(group, (rank - 1) % world) if group is not None else (rank - 1) % world
+    ops = [dist.P2POp(dist.isend, send, nxt, group), dist.P2POp(dist.irecv, recv, prv, group)]
+    return dist.batch_isend_irecv(ops)
+
+
+def ring_forward(q: Tensor, k: Tensor, v: Tensor, forward_chunk: Callable, merge: Callable,
+                 group=None, causal: bool = True):
+    """Forward pass of ring attention for this rank's q chunk.
+
+    forward_chunk(q, k_s, v_s, r, s) -> (o, lse) attends q (chunk r) to kv chunk s;
+    merge(list of (o, lse)) -> (out, lse) combines the partial results.
+    The K/V chunk for the next step is received while the current one is computed."""
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    kv = torch.stack([k, v]).contiguous()
+    parts = []
+    for t, s, active in ring_steps(rank, world, causal):
+        reqs, nxt = [], None
+        if t < world - 1:
+            nxt = torch.empty_like(kv)
+            reqs = _ring_exchange(kv, nxt, group)
+        if active:
+            parts.append(forward_chunk(q, kv[0], kv[1], rank, s))
+        for r_ in reqs:
+            r_.wait()
+        if nxt is not None:
+            kv = nxt
+    return merge(parts)
+
+
+def ring_backward(q: Tensor, k: Tensor, v: Tensor, o: Tensor, lse: Tensor, do: Tensor,
+                  dlse: Optional[Tensor], backward_chunk: Callable, group=None, causal: bool = True):
+    """Backward pass of ring attention.  backward_chunk(q, k_s, v_s, o, lse, do, dlse, r, s) ->
+    (dq, dk_s, dv_s) evaluates the gradients of the (r, s) chunk pair from the MERGED output and
+    LSE of the forward pass (the probabilities exp(S - lse) are then already globally normalised,
+    so the pair's contributions simply add up).  dQ accumulates locally in fp32; the dK/dV
+    accumulator travels round the ring with its K/V chunk and is home after ``world`` hops."""
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    kv = torch.stack([k, v]).contiguous()
+    dkv = torch.zeros(kv.shape, dtype=torch.float32, device=kv.device)
+    dq = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
+    for t, s, active in ring_steps(rank, world, causal):
+        reqs, nxt = [], None
+        if t < world - 1:
+            nxt = torch.empty_like(kv)
+            reqs = _ring_exchange(kv, nxt, group)
+        if active:
+            dq_p, dk_p, dv_p = backward_chunk(q, kv[0], kv[1], o, lse, do, dlse, rank, s)
+            dq += dq_p
+            dkv[0] += dk_p
+            dkv[1] += dv_p
+        for r_ in reqs:
+            r_.wait()
+        # the gradient accumulator follows its chunk (one hop more than the chunk itself)
+        dnxt = torch.empty_like(dkv)
+        for r_ in _ring_exchange(dkv, dnxt, group):
+            r_.wait()
+        dkv = dnxt
+        if nxt is not None:
+            kv = nxt
+    return dq.to(q.dtype), dkv[0].to(k.dtype), dkv[1].to(v.dtype)
+
+
+class _RingAttention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, owner):
+        out, lse = ring_forward(q, k, v, owner._forward_chunk, owner._merge, owner.group, owner.causal)
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.owner = owner
+        return out, lse
+
+    @staticmethod
+    def backward(ctx, do, dlse):
+        q, k, v, out, lse = ctx.saved_tensors
+        owner = ctx.owner
+        if dlse is not None and not bool((dlse != 0).any()):
+            dlse = None
+        dq, dk, dv = ring_backward(q, k, v, out, lse, do.contiguous(), dlse, owner._backward_chunk,
+                                   owner.group, owner.causal)
+        return dq, dk, dv, None
+
+
+class ContextParallelSparseAttention(torch.nn.Module):
+    """Local-stride block-sparse attention over a sequence that is split across the ranks of a
+    process group (one contiguous chunk of q, k and v per rank), forward and backward.
+
+    Rank r attends its q chunk to kv chunk s through a ``SparseAttention`` built on the block mask
+    of that chunk pair (``get_sparse_attn_mask`` with ``q_start_position`` / ``kv_start_position``,
+    dkernel/utils.py:161-169,185-191), causal only on the diagonal pair; the K/V chunks travel
+    round the ring over NCCL send/recv while the previous pair is computed, partial results are
+    merged by LSE, and the backward pass sends the dK/dV accumulators round the same ring.
+
+    forward(q, k, v, sm_scale=None, return_lse=False): tensors are this rank's chunk,
+    (B, S/world, H, D) for ``seq_dim=1`` or (B, H, S/world, D) for ``seq_dim=2``."""
+
+    def __init__(self, num_heads: int, seq_len: int, block_size: int, local_blocks: int,
+                 vert_stride: int, *, num_kv_heads: Optional[int] = None, homo_head: bool = False,
+                 head_sliding_offset: int = 0, seq_dim: int = 1, causal: bool = True, group=None,
+                 **kwargs):
+        super().__init__()
+        self.group = group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.bounds = chunk_bounds(seq_len, self.world, block_size)
+        self.mask_args = dict(num_heads=num_heads, block_size=block_size, local_blocks=local_blocks,
+                              vert_stride=vert_stride, homo_head=homo_head, num_kv_heads=num_kv_heads,
+                              head_sliding_offset=head_sliding_offset, causal=causal)
+        self.block_size, self.seq_dim, self.causal, self.kwargs = block_size, seq_dim, causal, kwargs
+        self._chunks: Dict[int, object] = {}
+        self._scale = None
+
+    def _module(self, s: int):
+        """SparseAttention of the (own q chunk, kv chunk s) pair, built on first use."""
+        if s not in self._chunks:
+            from .interface import SparseAttention
+            from .utils import get_sparse_attn_mask
+            a = self.mask_args
+            (q0, q1), (k0, k1) = self.bounds[self.rank], self.bounds[s]
+            bmask = get_sparse_attn_mask(a["num_heads"], q1 - q0, a["block_size"], a["local_blocks"],
+                                         a["vert_stride"], homo_head=a["homo_head"], dtype=torch.uint8,
+                                         num_kv_heads=a["num_kv_heads"],
+                                         head_sliding_offset=a["head_sliding_offset"], causal=a["causal"],
+                                         q_start_position=q0, kv_start_position=k0, kv_seqlen=k1 - k0)[1]
+            self._chunks[s] = SparseAttention(self.block_size, bmask, seq_dim=self.seq_dim,
+                                              causal=self.causal and s == self.rank, **self.kwargs)
+        return self._chunks[s]
+
+    def _forward_chunk(self, q, k, v, r, s):
+        from . import ops
+        mod = self._module(s)
+        impl = ops._IMPL_NAMES[mod.kwargs.get("impl", None)]
+        return ops._train_forward(None, q, k, v, self._scale, mod._plan(), self.seq_dim,
+                                  mod.kwargs["causal"], None, impl, need_lse=True, inference=True)
+
+    def _backward_chunk(self, q, k, v, o, lse, do, dlse, r, s):
+        from types import SimpleNamespace
+        from . import ops
+        mod = self._module(s)
+        name = mod.kwargs.get("bwd_impl", "generic" if mod.kwargs.get("impl") == "generic" else None)
+        ctx = SimpleNamespace(saved_tensors=(q, k, v, o, lse), sm_scale=self._scale, seq_dim=self.seq_dim,
+                              causal=mod.kwargs["causal"], plan=mod._plan(), bwd_impl=ops._IMPL_NAMES[name])
+        return ops._backward(ctx, do, dlse)
+
+    def _merge(self, parts):
+        from .interface import combine_attn_partitions
+        if len(parts) == 1:
+            return parts[0]
+        return combine_attn_partitions(*parts, hdim=3 - self.seq_dim, return_lse=True)
+
+    def forward(self, q: Tensor, k: Tensor, v: Tensor, sm_scale: Optional[float] = None,
+                return_lse: bool = False):
+        from . import ops
+        ops._check_inputs(q, k, v)
+        self._scale = sm_scale or 1.0 / math.sqrt(float(q.size(-1)))
+        q, k, v = (ops._tma_friendly(t.contiguous()) for t in (q, k, v))
+        if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad):
+            out, lse = _RingAttention.apply(q, k, v, self)
+        else:
+            out, lse = ring_forward(q, k, v, self._forward_chunk, self._merge, self.group, self.causal)
+        return (out, lse) if return_lse else out
+
+
+__all__ = ["head_shard", "kv_shard_ranges", "pack_kv_shard", "sharded_decode", "ShardedDecoder",
+           "chunk_bounds", "ring_steps", "ring_forward", "ring_backward",
+           "ContextParallelSparseAttention"]

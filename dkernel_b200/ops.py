@@ -62,7 +62,8 @@ class _Plan:
         kernels mask the diagonal per element anyway), so such patterns get refined layouts
         instead of falling back to the CUDA-core kernels."""
         bs = self.block_size
-        if not (bs > 64 and bs % 64 == 0 and q.dtype in (torch.float16, torch.bfloat16) and q.size(-1) == 128):
+        if not (bs > 64 and bs % 64 == 0 and q.dtype in (torch.float16, torch.bfloat16)
+                and q.size(-1) in (64, 128)):
             return self
         if self._fine is None:
             from .utils import crow_col_to_dense, dense_to_crow_col, dense_to_ccol_row, zero_stride
@@ -183,6 +184,26 @@ def _fwd_params(q, k, v, o, lse, seq_dim, plan: _Plan, sm_scale, causal, row_mod
     return p
 
 
+_warned_fallback = set()
+
+
+def _launch_fwd(p, q: Tensor) -> None:
+    """bsa_fwd on q's device and stream.  A call whose shape the tensor-core kernel handles but
+    which would still run on the CUDA-core kernel (an unaligned output view, for instance) is
+    reported once per reason: that path is tens of times slower."""
+    lib = _lib.lib()
+    if (p.impl == _lib.IMPL_AUTO and p.dtype != _lib.BSA_F32 and p.d in (64, 128)
+            and p.block_size == 64):
+        why = lib.bsa_fwd_why_not_sm100(C.byref(p))
+        if why and why not in _warned_fallback:
+            _warned_fallback.add(why)
+            import warnings
+            warnings.warn("dkernel_b200: this attention call runs on the CUDA-core fallback kernel, "
+                          f"not on the tensor cores: {why.decode()}", RuntimeWarning, stacklevel=3)
+    with torch.cuda.device(q.device):
+        _lib.check(lib.bsa_fwd(C.byref(p), _lib.stream_of(q)), "bsa_fwd")
+
+
 def _check_inputs(q: Tensor, k: Tensor, v: Tensor) -> None:
     for n, t in (("q", q), ("k", k), ("v", v)):
         _lib.require_cuda(t, n)
@@ -220,6 +241,7 @@ def decode(q: Tensor, k: Tensor, v: Tensor, plan: _Plan, sm_scale: float, *, seq
     ``k_pos0``/``k_total`` describe a KV shard (see include/bsa.h).
     Returns (out shaped like q, lse fp32 (B,Hq))."""
     lib = _lib.lib()
+    q = _last_dim_contig(q)     # before the strides are read: a copy has its own
     if q.dim() == 4:
         B = q.size(0)
         hdim = 3 - seq_dim
@@ -244,7 +266,6 @@ def decode(q: Tensor, k: Tensor, v: Tensor, plan: _Plan, sm_scale: float, *, seq
     p = _lib.DecodeParams()
     k = _tma_friendly(k)
     v = _tma_friendly(v)
-    q = _last_dim_contig(q)
     p.q, p.k, p.v, p.o, p.lse = _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(lse)
     p.q_sb, p.q_sh = q_sb, q_sh
     p.k_sb, p.k_ss, p.k_sh = _strides_bsh(k, seq_dim)
@@ -313,8 +334,7 @@ def _varlen(q, k, v, cu_seqlens_k, cu_seqlens_q, sm_scale, plan, causal, out, im
         if return_lse else None
     p = _fwd_params(q, k, v, o, lse, None, plan, sm_scale, causal, _lib.ROWS_BY_POSITION,
                     cu_q[:-1], cu_q[1:], cu_k[:-1], cu_k[1:], total_q=q.size(0), impl=impl)
-    with torch.cuda.device(q.device):
-        _lib.check(_lib.lib().bsa_fwd(C.byref(p), _lib.stream_of(q)), "bsa_fwd")
+    _launch_fwd(p, q)
     return o, lse
 
 
@@ -361,8 +381,7 @@ def _padded(q, k, v, sm_scale, plan, left_paddings, seqlens, seq_dim, max_seqlen
         if return_lse else None
     p = _fwd_params(q, k, v, o, lse, seq_dim, plan, sm_scale, causal, _lib.ROWS_BY_POSITION,
                     q_starts, q_ends, k_starts, k_ends, impl=impl)
-    with torch.cuda.device(dev):
-        _lib.check(_lib.lib().bsa_fwd(C.byref(p), _lib.stream_of(q)), "bsa_fwd")
+    _launch_fwd(p, q)
     return o, lse
 
 
@@ -381,13 +400,16 @@ def _train_forward(ctx, q, k, v, sm_scale, plan, seq_dim, causal, out, impl, nee
     if qlen == 1 and klen > 1 and inference and _decode_eligible(q, plan, impl):
         o, lse = decode(q, k, v, plan, sm_scale, seq_dim=seq_dim, out=out)
         return o, lse.unsqueeze(-1)
+    # A single query token against a longer key sequence takes its pattern row from the key
+    # position; the backward kernels index rows by q tile, so that case has no backward.
+    assert inference or qlen > 1 or klen == 1, \
+        "a single query token against a longer key sequence is an inference-only call (inference=True)"
     row_mode = _lib.ROWS_BY_POSITION if qlen == 1 else _lib.ROWS_BY_TILE
     q, k, v = _tma_friendly(q), _tma_friendly(k), _tma_friendly(v)
     o = out if out is not None else torch.empty(q.shape, dtype=q.dtype, device=dev)
     lse = torch.empty((q.size(0), hq, qlen), dtype=torch.float32, device=dev) if need_lse else None
     p = _fwd_params(q, k, v, o, lse, seq_dim, plan, sm_scale, causal, row_mode, impl=impl)
-    with torch.cuda.device(dev):
-        _lib.check(_lib.lib().bsa_fwd(C.byref(p), _lib.stream_of(q)), "bsa_fwd")
+    _launch_fwd(p, q)
     if ctx is not None and not inference:
         ctx.save_for_backward(q, k, v, o, lse)
         ctx.sm_scale, ctx.seq_dim, ctx.causal, ctx.plan = sm_scale, seq_dim, causal, plan
@@ -496,11 +518,12 @@ class _sparse_attention(torch.autograd.Function):
                 output, lse = _padded(q, k, v, sm_scale, plan, left_paddings, seqlens, seq_dim,
                                       max_seqlen, causal, out, impl, return_lse)
             else:
-                ctx.support_backward = True
-                ctx.message = ""
                 inference = kwargs.get("inference", None)
                 if inference is None:
                     inference = not needs_grad
+                # an inference call saves nothing for backward
+                ctx.support_backward = not inference
+                ctx.message = "the forward pass ran with inference=True: nothing was saved for backward"
                 output, lse = _train_forward(ctx, q, k, v, sm_scale, plan, seq_dim, causal, out, impl,
                                              need_lse=return_lse or not inference, inference=inference)
         if not return_lse:

@@ -142,6 +142,12 @@ int bsa_fwd(const bsa_fwd_params* p, void* stream);
  * does, negative on invalid parameters. */
 int bsa_fwd_uses_sm100(const bsa_fwd_params* p);
 
+/* NULL if the tcgen05 kernel serves these parameters, else the reason why
+ * bsa_fwd with BSA_IMPL_AUTO would run them on the (much slower) CUDA-core
+ * kernel, as static text (or the validation error).  Lets a host make the
+ * fall-back visible; the reference has one kernel family and no such case. */
+const char* bsa_fwd_why_not_sm100(const bsa_fwd_params* p);
+
 /* ---------------------------------------------------------------------------
  * Attention backward.  Replaces _bwd_preprocess + _sparse_bwd_kernel
  * (dkernel/ops/sparse_attn_bwd.py:781-788, :811-850).  dQ walks the CSR, dK/dV
@@ -257,6 +263,36 @@ int bsa_merge_partials(const void* o_parts, const float* lse_parts, int32_t P,
                        float* lse, int32_t dtype, void* stream);
 
 /* ---------------------------------------------------------------------------
+ * KV-sharded decode on one node: exchange of the ranks' partial (O, LSE) rows
+ * over peer memory and their merge, in one kernel per rank.  Replaces "gather
+ * the partitions, then combine_attn_partitions" (dkernel/interface.py:303-324,
+ * README "KV partition") and needs no collective library.
+ *
+ * Every rank allocates an exchange buffer of bsa_xchg_buffer_bytes() bytes,
+ * zero-filled once, 256-byte aligned, and maps the buffers of all ranks (CUDA
+ * IPC, or torch symmetric memory): xbuf[w] is rank w's buffer as addressed by
+ * THIS process; xbuf[rank] is the local one.  Per step every rank calls
+ * bsa_xchg_merge once with its partial rows (stage_o (rows, d) 16-bit
+ * contiguous, stage_lse (rows) fp32): the kernel stores them into every rank's
+ * buffer (remote stores only; nothing is loaded from peer memory), publishes a
+ * flag per CTA, waits -- bounded, see bsa_wait_status, code 601 -- for the flags
+ * of all ranks in the local buffer and writes the merged out (rows, d) and
+ * out_lse (rows, or NULL).  All ranks must make the same sequence of calls with
+ * the same (world, rows, d); the step counter lives in the buffer, so a captured
+ * CUDA graph of the call can be replayed.  Limits: world <= 8, d % 8 == 0.
+ * ------------------------------------------------------------------------- */
+typedef struct {
+  const void* stage_o; const float* stage_lse;
+  void* out; float* out_lse;
+  void* xbuf[8];
+  int64_t rows;
+  int32_t world, rank, d, dtype;
+} bsa_xchg_params;
+
+size_t bsa_xchg_buffer_bytes(int32_t world, int64_t rows, int32_t d);
+int bsa_xchg_merge(const bsa_xchg_params* p, void* stream);
+
+/* ---------------------------------------------------------------------------
  * Device-side waits (on TMA / tensor-core completion barriers) are bounded.  A
  * wait that gives up records a non-zero code in a device status word and the
  * kernels of the library become no-ops until it is cleared.  This call
@@ -265,6 +301,22 @@ int bsa_merge_partials(const void* o_parts, const float* lse_parts, int32_t P,
  * reference (Triton kernels have no such waits).
  * ------------------------------------------------------------------------- */
 int bsa_wait_status(int32_t* status, int32_t reset);
+
+/* Optional host-visible copy of that status word for the current device: the
+ * first wait that gives up also stores its code in *host_word, which must be
+ * page-locked host memory the device can address (cudaHostAlloc / a pinned
+ * torch tensor; the caller owns it and keeps it alive).  A host can then notice
+ * a failed wait by reading the word, without synchronising.  NULL removes the
+ * registration; bsa_wait_status(reset) also clears the word.  No counterpart in
+ * the reference. */
+int bsa_set_wait_status_mirror(int32_t* host_word);
+
+/* Test hook: enqueues one tiny kernel that waits (at most limit_us
+ * microseconds, 1..100000) on a barrier nothing ever arrives at, so that the
+ * give-up path above can be observed: afterwards bsa_wait_status reports code
+ * 900 and launches are no-ops until it is reset.  Nothing faults or hangs.  No
+ * counterpart in the reference. */
+int bsa_selftest_wait_timeout(uint32_t limit_us, void* stream);
 
 #ifdef __cplusplus
 }

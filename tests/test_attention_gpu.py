@@ -180,3 +180,40 @@ def test_errors_are_python_exceptions():
     o = mod(qg, q, q, left_paddings=torch.tensor([3], device="cuda"))
     with pytest.raises(AssertionError):
         o.sum().backward()
+
+
+def test_bounded_wait_gives_up_and_service_resumes():
+    """A device-side wait whose barrier nothing ever arrives at (1 ms limit) must give up, record
+    its code, make later launches no-ops, raise on the host without a sync, and be clearable."""
+    import ctypes as C
+    from dkernel_b200 import LocalStrideSparseAttention, _lib
+    lib = _lib.lib()
+    mod = LocalStrideSparseAttention.__wrapped__(2, 256, 64, 2, 2, seq_dim=1)
+    q, k, v = seeded_qkv(40, (1, 256, 2, 128), (1, 256, 2, 128), torch.bfloat16, device="cuda")
+    with torch.no_grad():
+        good = mod(q, k, v)
+    assert _lib.wait_status() == 0
+    stream = torch.cuda.current_stream().cuda_stream
+    assert lib.bsa_selftest_wait_timeout(1000, stream) == 0
+    torch.cuda.synchronize()
+    # the mirror word already tells the host, and the next checked call raises
+    assert C.c_int32.from_address(_lib._mirror_addr).value == 900
+    with pytest.raises(_lib.BsaError, match="900"):
+        with torch.no_grad():
+            mod(q, k, v)
+    assert _lib.wait_status(reset=False) == 900
+    # kernels are no-ops while the status is set: the output buffer keeps its contents
+    from dkernel_b200.ops import _fwd_params
+    o = torch.full_like(q, 7.0)
+    p = _fwd_params(q, k, v, o, None, 1, mod._plan(), 0.1, True, _lib.ROWS_BY_TILE)
+    assert lib.bsa_fwd(C.byref(p), stream) == 0
+    torch.cuda.synchronize()
+    assert (o == 7.0).all()
+    # clearing restores service
+    assert _lib.wait_status() == 900
+    assert _lib.wait_status() == 0
+    assert C.c_int32.from_address(_lib._mirror_addr).value == 0
+    with torch.no_grad():
+        again = mod(q, k, v)
+    assert torch.equal(good, again)
+    assert _lib.wait_status() == 0

@@ -31,14 +31,14 @@ def test_struct_layouts_match_the_header(tmp_path):
     import subprocess
     from dkernel_b200 import _lib
     src = tmp_path / "sz.c"
-    src.write_text('#include <stdio.h>\n#include "bsa.h"\nint main(void){printf("%zu %zu %zu %zu\\n",'
+    src.write_text('#include <stdio.h>\n#include "bsa.h"\nint main(void){printf("%zu %zu %zu %zu %zu\\n",'
                    'sizeof(bsa_local_stride_params),sizeof(bsa_fwd_params),sizeof(bsa_bwd_params),'
-                   'sizeof(bsa_decode_params));return 0;}\n')
+                   'sizeof(bsa_decode_params),sizeof(bsa_xchg_params));return 0;}\n')
     exe = tmp_path / "sz"
     subprocess.check_call(["gcc", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)])
     sizes = [int(x) for x in subprocess.check_output([str(exe)]).split()]
     assert sizes == [C.sizeof(_lib.LocalStrideParams), C.sizeof(_lib.FwdParams), C.sizeof(_lib.BwdParams),
-                     C.sizeof(_lib.DecodeParams)]
+                     C.sizeof(_lib.DecodeParams), C.sizeof(_lib.XchgParams)]
 
 
 def test_argument_validation_needs_no_device():
@@ -86,3 +86,60 @@ def test_decode_split_choice_needs_no_device():
     assert lib.bsa_decode_workspace_bytes(C.byref(p)) // (4 * p.batch * p.hq * (p.d + 1)) == 2
     p.max_row_nnz = 12
     assert lib.bsa_decode_workspace_bytes(C.byref(p)) == 0   # one split: no workspace
+
+
+def test_zeroed_decode_params_are_rejected_not_divided_by():
+    """The split planning divides by the head counts: a zeroed struct must come back as
+    BSA_E_BADARG (0 bytes from the size query), never as a host arithmetic fault."""
+    from dkernel_b200 import _lib
+    lib = _lib.lib()
+    d = _lib.DecodeParams()
+    assert lib.bsa_decode_workspace_bytes(C.byref(d)) == 0
+    assert lib.bsa_decode_workspace_bytes(None) == 0
+    assert lib.bsa_decode(C.byref(d), None) == -1
+    assert lib.bsa_decode_static(C.byref(d), None) == -1
+    assert b"head counts" in lib.bsa_last_error()
+    assert lib.bsa_decode_static(None, None) == -1
+    d.hq, d.hkv, d.d = 8, 2, 128
+    assert lib.bsa_decode_static(C.byref(d), None) == -1       # heads_per_cta = 0
+    assert b"heads_per_cta" in lib.bsa_last_error()
+    d.heads_per_cta = 3                                        # does not divide the group size 4
+    assert lib.bsa_decode_workspace_bytes(C.byref(d)) == 0
+    assert lib.bsa_decode(C.byref(d), None) == -1
+
+
+def test_a_recorded_wait_failure_raises_on_the_next_call():
+    """The kernels mirror the code of a bounded wait that gave up into a host-visible word;
+    every later checked call raises until the status is cleared."""
+    from dkernel_b200 import _lib
+    word = C.c_int32(0)
+    old = _lib._mirror_addr
+    try:
+        _lib._mirror_addr = C.addressof(word)
+        _lib.check(0, "bsa_fwd")                               # healthy
+        word.value = 423
+        with pytest.raises(_lib.BsaError, match="423"):
+            _lib.check(0, "bsa_fwd")
+    finally:
+        _lib._mirror_addr = old
+
+
+def test_exchange_buffer_geometry_and_validation_need_no_device():
+    """bsa_xchg_buffer_bytes: two parities x world slots of (rows, d) 16-bit rows and fp32 LSEs,
+    flag words and a control block, every region 256-byte aligned; bad geometry gives 0 / BADARG."""
+    from dkernel_b200 import _lib
+    lib = _lib.lib()
+    n = lib.bsa_xchg_buffer_bytes(8, 2048, 128)
+    assert n >= 2 * 8 * (2048 * 128 * 2 + 2048 * 4) and n % 256 == 0 and n < 10 << 20
+    assert lib.bsa_xchg_buffer_bytes(2, 2048, 128) < n
+    assert lib.bsa_xchg_buffer_bytes(9, 16, 128) == 0          # more ranks than one node has
+    assert lib.bsa_xchg_buffer_bytes(2, 16, 12) == 0           # rows must be whole 16-byte chunks
+    p = _lib.XchgParams()
+    assert lib.bsa_xchg_merge(C.byref(p), None) == -1
+    p.world, p.rank, p.rows, p.d, p.dtype = 2, 2, 16, 128, _lib.BSA_BF16
+    assert lib.bsa_xchg_merge(C.byref(p), None) == -1 and b"world/rank" in lib.bsa_last_error()
+    p.rank = 1
+    assert lib.bsa_xchg_merge(C.byref(p), None) == -1 and b"null" in lib.bsa_last_error()
+    p.stage_o = p.stage_lse = p.out = 4096
+    p.xbuf[0] = 4096
+    assert lib.bsa_xchg_merge(C.byref(p), None) == -1 and b"exchange buffer 1" in lib.bsa_last_error()

@@ -1,7 +1,8 @@
 """Multi-rank host logic on CPU (gloo, world_size 2): head sharding, KV-sequence
-sharding and the one-message gather of decode partials.  The per-rank compute is
-done by the CPU oracle here (the GPU tests cover the kernels); what is checked is
-that the partitioning + gather + merge reproduce the un-partitioned result."""
+sharding with the one-message gather of packed decode partials, and the ring
+schedule of context-parallel attention (forward and backward).  The per-rank
+compute is done by the CPU oracle here (the GPU tests cover the kernels); what is
+checked is that partitioning + exchange + merge reproduce the un-partitioned result."""
 import os
 import socket
 
@@ -27,7 +28,8 @@ def _worker(rank, world, port, ret):
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        from dkernel_b200.dist import head_shard, kv_shard_ranges, pack_kv_shard, gather_partials
+        from dkernel_b200.dist import (head_shard, kv_shard_ranges, pack_kv_shard, packed_partial_views,
+                                       partial_row_bytes, gather_packed_partials, split_gathered_partials)
         torch.manual_seed(0)                      # identical inputs on every rank
         B, Hq, Hkv, S, D, bs = 3, 4, 2, 512, 32, 64
         q = torch.randn(B, 1, Hq, D)
@@ -54,11 +56,22 @@ def _worker(rank, world, port, ret):
             # and the packed shard really is that slice of the sequence
             s0 = int(left[b] + lo[b])
             assert torch.equal(ks[b, :int(n[b])], k[b, s0:s0 + int(n[b])])
-        o_parts, l_parts = gather_partials(part_o.reshape(B * Hq, D), part_l.reshape(B * Hq))
+        # the byte packing sharded_decode uses: 16-bit outputs and the fp32 LSE of a row side by
+        # side, written through strided views, one message, read back through strided views
+        packed = torch.zeros((B * Hq, partial_row_bytes(D)), dtype=torch.uint8)
+        o_view, lse_view = packed_partial_views(packed, D, torch.bfloat16)
+        assert o_view.shape == (B * Hq, D) and o_view.stride() == (D + 2, 1) and lse_view.stride() == ((2 * D + 4) // 4,)
+        o_view.copy_(part_o.reshape(B * Hq, D))
+        lse_view.copy_(part_l.reshape(B * Hq))
+        gathered = gather_packed_partials(packed)
+        o_parts, l_parts = split_gathered_partials(gathered, world, D, torch.bfloat16)
         assert o_parts.shape == (world, B * Hq, D) and l_parts.shape == (world, B * Hq)
-        parts = [(o_parts[r].view(B, 1, Hq, D).transpose(1, 2), l_parts[r].view(B, Hq, 1)) for r in range(world)]
+        assert torch.equal(o_parts[rank], part_o.reshape(B * Hq, D).to(torch.bfloat16))
+        assert torch.equal(l_parts[rank], part_l.reshape(B * Hq))
+        parts = [(o_parts[r].float().reshape(B, 1, Hq, D).transpose(1, 2), l_parts[r].reshape(B, Hq, 1))
+                 for r in range(world)]
         merged, mlse = O.combine_attn_partitions(*parts)
-        assert (merged.transpose(1, 2) - ref).abs().max() < 1e-5
+        assert (merged.transpose(1, 2) - ref).abs().max() < 2e-2       # partials rounded to bf16
         assert (mlse - ref_lse).abs().max() < 1e-4
 
         # ---- head sharding: rank-local heads, no collective; concatenation == whole
@@ -85,6 +98,77 @@ def test_two_ranks_gloo():
     ret = mgr.dict()
     mp.spawn(_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
     assert dict(ret) == {0: "ok", 1: "ok"}
+
+
+def _ring_worker(rank, world, port, ret):
+    """Ring attention schedule (K/V chunks round the ring, LSE merge, dK/dV accumulators round
+    the ring) with the oracle as the per-chunk compute; compared with full-sequence autograd."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from dkernel_b200.dist import chunk_bounds, ring_backward, ring_forward, ring_steps
+        torch.manual_seed(1)
+        B, H, S, D, bs = 2, 2, 512, 16, 64
+        scale = 1.0 / D ** 0.5
+        q, k, v, do = (torch.randn(B, S, H, D) for _ in range(4))
+        dl = torch.randn(B, H, S)
+        bm = O.block_mask(H, S, bs, 2, 3)
+        dense = O.token_mask(bm, bs, S, S).bool()                   # (H, S, S), causal
+        bounds = chunk_bounds(S, world, bs)
+        assert [s for _, s, a in ring_steps(rank, world) if a] == list(range(rank, -1, -1))
+
+        qf, kf, vf = (t.clone().requires_grad_() for t in (q, k, v))
+        ref, ref_lse = O.masked_dense_attention(qf, kf, vf, dense.to(torch.uint8), scale, seq_dim=1,
+                                                return_lse=True)
+        ((ref * do).sum() + (ref_lse * dl).sum()).backward()
+
+        def pair_mask(r, s):
+            return dense[:, bounds[r][0]:bounds[r][1], bounds[s][0]:bounds[s][1]]
+
+        def fwd_chunk(qc, kc, vc, r, s):
+            return O.masked_dense_attention(qc, kc, vc, pair_mask(r, s).to(torch.uint8), scale, seq_dim=1,
+                                            return_lse=True)
+
+        def merge(parts):
+            if len(parts) == 1:
+                return parts[0]
+            o, l = O.combine_attn_partitions(*[(o.transpose(1, 2), l) for o, l in parts])
+            return o.transpose(1, 2), l
+
+        def bwd_chunk(qc, kc, vc, o, lse, dout, dlse, r, s):
+            # gradients of one chunk pair from the merged output and LSE
+            sc = torch.einsum("bmhd,bnhd->bhmn", qc, kc) * scale
+            sc = sc.masked_fill(~pair_mask(r, s)[None], float("-inf"))
+            p = torch.exp(sc - lse[..., None])
+            dp = torch.einsum("bmhd,bnhd->bhmn", dout, vc)
+            delta = (dout * o).sum(-1).transpose(1, 2) - (dlse if dlse is not None else 0)
+            ds = p * (dp - delta[..., None])
+            return (torch.einsum("bhmn,bnhd->bmhd", ds, kc) * scale,
+                    torch.einsum("bhmn,bmhd->bnhd", ds, qc) * scale,
+                    torch.einsum("bhmn,bmhd->bnhd", p, dout))
+
+        a, b_ = bounds[rank]
+        ql, kl, vl = q[:, a:b_].contiguous(), k[:, a:b_].contiguous(), v[:, a:b_].contiguous()
+        out, lse = ring_forward(ql, kl, vl, fwd_chunk, merge)
+        assert (out - ref[:, a:b_].detach()).abs().max() < 1e-5
+        assert (lse - ref_lse[:, :, a:b_].detach()).abs().max() < 1e-5
+        dq, dk, dv = ring_backward(ql, kl, vl, out, lse, do[:, a:b_].contiguous(), dl[:, :, a:b_].contiguous(),
+                                   bwd_chunk)
+        for got, want, name in ((dq, qf.grad, "dq"), (dk, kf.grad, "dk"), (dv, vf.grad, "dv")):
+            err = (got - want[:, a:b_]).abs().max().item()
+            assert err < 1e-4, f"{name}: {err}"
+        ret[rank] = "ok"
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_ring_attention_schedule_gloo(world):
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_ring_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
+    assert dict(ret) == {r: "ok" for r in range(world)}
 
 
 def test_planning_functions():

@@ -5,7 +5,10 @@ them), through properties that do not depend on the size, plus oracle checks on 
   to one vector per kv head the output is exactly that vector (a convex combination).
 * A handful of (batch, head, row) samples are recomputed on the CPU in fp32 from the oracle's
   block mask.
-* The tensor-core kernels are compared with the CUDA-core kernels on the same device.
+* Config 3 (training) and config 5 (packed varlen): one (batch, head) pair, resp. two short
+  sequences x two heads, are recomputed by the CPU oracle (masked-dense attention with autograd /
+  per-sequence evaluator) at the full sequence length and compared with the tensor-core results;
+  the tensor-core kernels are also compared with the CUDA-core kernels on the whole problem.
 """
 import math
 
@@ -103,6 +106,23 @@ def test_config3_training_full_size_matches_cuda_core_kernels():
         assert rel.item() <= GRAD_REL_NORM, f"{name}: relative norm {rel.item():.3e}"
     from dkernel_b200 import _lib
     assert _lib.wait_status() == 0
+    # One (batch, head) pair against the CPU oracle with autograd at the full length.  Here every
+    # q head has its own kv head, so the pair's dK and dV depend on no other head.
+    bm = O.block_mask(H, S, block_size=bs, local_blocks=32, vert_stride=8)
+    for b, h in ((1, 13),):
+        dense = O.token_mask(bm[h:h + 1], bs, S, S)
+        qf, kf, vf = (t[b:b + 1, :, h:h + 1].float().cpu().requires_grad_() for t in (q, k, v))
+        ref, ref_lse = O.masked_dense_attention(qf, kf, vf, dense, None, seq_dim=1, return_lse=True)
+        ref.backward(do[b:b + 1, :, h:h + 1].float().cpu())
+        out, dq, dk, dv = grads[0]
+        assert_out_close(out[b:b + 1, :, h:h + 1], ref)
+        for got, want, name in ((dq, qf.grad, "dq"), (dk, kf.grad, "dk"), (dv, vf.grad, "dv")):
+            g_ = got[b:b + 1, :, h:h + 1].float().cpu()
+            rel = (g_ - want).norm() / want.norm()
+            assert rel.item() <= GRAD_REL_NORM, f"{name} vs oracle: relative norm {rel.item():.3e}"
+        with torch.no_grad():
+            _, lse = fast(q[b:b + 1], k[b:b + 1], v[b:b + 1], return_lse=True)
+        assert_lse_close(lse[:, h:h + 1], ref_lse.detach())
 
 
 def test_config4_decode_full_size():
@@ -162,8 +182,17 @@ def test_config5_varlen_full_size_matches_cuda_core_kernels():
         fast = SparseAttention(bs, pat.cuda(), impl="sm100")
         slow = SparseAttention(bs, pat.cuda(), impl="generic")
     with torch.no_grad():
-        o1 = fast(q, k, v, cu_seqlen_k=cu)
+        o1, l1 = fast(q, k, v, cu_seqlen_k=cu, return_lse=True)
         o2 = slow(q, k, v, cu_seqlen_k=cu)
     assert_out_close(o1, o2, max_abs=2e-2, mean_abs=1e-3)
     from dkernel_b200 import _lib
     assert _lib.wait_status() == 0
+    # the two shortest sequences x two heads against the CPU oracle's per-sequence evaluator
+    cu_h = cu.cpu().tolist()
+    heads = [3, 30]
+    for sidx in torch.argsort(lens)[:2].tolist():
+        a, b_ = cu_h[sidx], cu_h[sidx + 1]
+        sub = lambda t: t[a:b_][:, heads].float().cpu()
+        ref, ref_lse = O.varlen_attention(sub(q), sub(k), sub(v), [0, b_ - a], pat[heads].numpy(), bs)
+        assert_out_close(o1[a:b_][:, heads], ref)
+        assert_lse_close(l1[heads][:, a:b_], ref_lse)

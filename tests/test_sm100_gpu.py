@@ -42,9 +42,9 @@ CASES = [
 ]
 
 
+@pytest.mark.parametrize("D", [128, 64])
 @pytest.mark.parametrize("B,Hq,Hkv,Sq,Sk,dtype,seq_dim,pk", CASES)
-def test_sm100_forward_vs_oracle(B, Hq, Hkv, Sq, Sk, dtype, seq_dim, pk):
-    D = 128
+def test_sm100_forward_vs_oracle(B, Hq, Hkv, Sq, Sk, dtype, seq_dim, pk, D):
     causal = pk.get("causal", True)
     bs = pk["block_size"]
     shape = (lambda h, s: (B, h, s, D)) if seq_dim == 2 else (lambda h, s: (B, s, h, D))
@@ -100,9 +100,10 @@ def test_sm100_shared_pattern_pairs_heads_over_many_tiles():
     assert_lse_close(l1, l2)
 
 
-def test_sm100_varlen_and_padded_routes():
+@pytest.mark.parametrize("D", [128, 64])
+def test_sm100_varlen_and_padded_routes(D):
     from dkernel_b200 import SparseAttention
-    Hq, Hkv, D, bs, nb = 4, 4, 128, 64, 16
+    Hq, Hkv, bs, nb = 4, 4, 64, 16
     g = torch.Generator().manual_seed(0)
     pat = torch.rand(Hq, nb, nb, generator=g) < 0.3
     pat |= torch.eye(nb, dtype=torch.bool)[None]
@@ -203,17 +204,74 @@ def test_sm100_backward_matches_generic_on_long_sequences(B, Hq, Hkv, S, pk):
         assert torch.equal(a, b_)
 
 
-def test_one_tile_per_cta_forward_kernel_in_a_subprocess():
-    """The persistent forward kernel is the default; BSA_FWD_TILED=1 (read once per process)
-    selects the one-tile-per-CTA kernel.  Its parity cases run in a child process."""
-    import os
-    import subprocess
-    import sys
-    env = dict(os.environ, BSA_FWD_TILED="1")
-    here = os.path.dirname(os.path.abspath(__file__))
-    res = subprocess.run(
-        [sys.executable, "-m", "pytest", "-x", "-q", "-m", "gpu",
-         os.path.join(here, "test_sm100_gpu.py") + "::test_sm100_forward_vs_oracle",
-         os.path.join(here, "test_sm100_gpu.py") + "::test_sm100_varlen_and_padded_routes"],
-        env=env, cwd=os.path.dirname(here), capture_output=True, text=True, timeout=900)
-    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+def test_sm100_head_dim_64_matches_generic_over_many_tiles():
+    """Head dim 64 on the tensor-core forward: several tiles per persistent CTA, GQA head pairs
+    and per-head patterns (row pairs), against the CUDA-core kernel on the same device."""
+    for Hq, Hkv, pk in ((16, 4, dict(block_size=64, local_blocks=4, vert_stride=4, num_kv_heads=4)),
+                        (8, 8, dict(block_size=64, local_blocks=8, vert_stride=8))):
+        B, S, D = 2, 4096, 64
+        q, k, v = seeded_qkv(11, (B, S, Hq, D), (B, S, Hkv, D), torch.bfloat16, device="cuda")
+        fast = _module(Hq, S, pk, seq_dim=1, impl="sm100")
+        slow = _module(Hq, S, pk, seq_dim=1, impl="generic")
+        with torch.no_grad():
+            o1, l1 = fast(q, k, v, return_lse=True)
+            o2, l2 = slow(q, k, v, return_lse=True)
+            o3 = fast(q, k, v)
+        _wait_status_clean()
+        assert_out_close(o1, o2, max_abs=2e-2, mean_abs=1e-3)
+        assert_lse_close(l1, l2)
+        assert torch.equal(o1, o3)
+
+
+@pytest.mark.parametrize("D", [128, 64])
+def test_sm100_padding_may_hold_nan_or_inf(D):
+    """Whatever sits in the padding of K/V (a torch.empty cache, NaN, Inf) must not reach the
+    output: right padding (seqlens), left + right padding, and the tail behind a packed batch
+    whose last block crosses the end of the buffer's last sequence."""
+    from dkernel_b200 import SparseAttention
+    B, S, Hq, Hkv, bs = 3, 512, 4, 2, 64
+    pk = dict(block_size=bs, local_blocks=2, vert_stride=4, num_kv_heads=Hkv)
+    bm = O.block_mask(Hq, S, **pk)
+    mod = _module(Hq, S, pk, seq_dim=1, impl="sm100")
+    q, k, v = seeded_qkv(31, (B, S, Hq, D), (B, S, Hkv, D), torch.bfloat16)
+    for left, lens in ((torch.tensor([0, 0, 0]), torch.tensor([500, 77, 301])),
+                       (torch.tensor([5, 100, 64]), torch.tensor([480, 33, 300]))):
+        kk, vv, qq = k.clone(), v.clone(), q.clone()
+        for b in range(B):
+            lo, hi = int(left[b]), int(left[b] + lens[b])
+            for t, bad in ((kk, float("nan")), (vv, float("inf")), (qq, float("nan"))):
+                t[b, :lo] = bad
+                t[b, hi:] = bad
+        ref, ref_lse = O.padded_attention(q.float(), k.float(), v.float(), bm, bs, left_paddings=left,
+                                          seqlens=lens, seq_dim=1)
+        out, lse = mod(qq.cuda(), kk.cuda(), vv.cuda(), left_paddings=left.cuda(), seqlens=lens.cuda(),
+                       return_lse=True)
+        _wait_status_clean()
+        assert torch.isfinite(out.float()).all()
+        assert_out_close(out, ref)
+        assert_lse_close(lse, ref_lse)
+    # packed batch inside a larger buffer whose tail is NaN: the last sequence's last block crosses
+    # the end of the real tokens
+    lens = [130, 70, 257]
+    T = sum(lens)
+    H = 4
+    nb = 8
+    g = torch.Generator().manual_seed(3)
+    pat = torch.rand(H, nb, nb, generator=g) < 0.4
+    pat |= torch.eye(nb, dtype=torch.bool)[None]
+    pat &= torch.tril(torch.ones(nb, nb, dtype=torch.bool))[None]
+    q, k, v = seeded_qkv(32, (T, H, D), (T, H, D), torch.bfloat16)
+    cu = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32)
+    ref, ref_lse = O.varlen_attention(q.float(), k.float(), v.float(), cu, pat.numpy().astype(np.uint8), bs)
+    big = [torch.full((T + 100, H, D), float("nan"), dtype=torch.bfloat16) for _ in range(3)]
+    for dst, src in zip(big, (q, k, v)):
+        dst[:T] = src
+    import warnings
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        modv = SparseAttention(bs, pat.cuda(), impl="sm100")
+    qg, kg, vg = (t.cuda()[:T] for t in big)
+    out, lse = modv(qg, kg, vg, cu_seqlen_k=cu.cuda(), return_lse=True)
+    _wait_status_clean()
+    assert_out_close(out, ref)
+    assert_lse_close(lse, ref_lse)
