@@ -96,7 +96,12 @@ class ClockSampler:
             import pynvml
             pynvml.nvmlInit()
             self.nv = pynvml
-            self.handle = pynvml.nvmlDeviceGetHandleByIndex(self._physical_index())
+            try:      # the CUDA ordinal and the NVML index need not agree: look the device up by UUID
+                uuid = str(torch.cuda.get_device_properties(self.gpu).uuid)
+                uuid = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            except Exception:
+                self.handle = pynvml.nvmlDeviceGetHandleByIndex(self._physical_index())
             self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
             self.thread = threading.Thread(target=self._poll, daemon=True)
             self.thread.start()

@@ -144,12 +144,16 @@ def _arm_mirror(device_index: int) -> None:
     _armed.add(device_index)
 
 
-def check(rc: int, what: str) -> None:
-    """Raise on a failed call, or when a device-side wait has given up since the last
-    ``wait_status()``: from then on the kernels are no-ops and outputs are undefined."""
+def check_rc(rc: int, what: str) -> None:
     if rc != 0:
         msg = lib().bsa_last_error()
         raise BsaError(f"{what} failed ({rc}): {msg.decode() if msg else ''}")
+
+
+def check(rc: int, what: str) -> None:
+    """Raise on a failed call, or when a device-side wait has given up since the last
+    ``wait_status()``: from then on the kernels are no-ops and outputs are undefined."""
+    check_rc(rc, what)
     if _mirror_addr is not None:
         code = C.c_int32.from_address(_mirror_addr).value
         if code != 0:
@@ -188,5 +192,5 @@ def require_cuda(t: torch.Tensor, name: str) -> None:
 def wait_status(reset: bool = True) -> int:
     """Synchronise and return the device wait-status word (0 = healthy)."""
     s = _i32(0)
-    check(lib().bsa_wait_status(C.byref(s), 1 if reset else 0), "bsa_wait_status")
+    check_rc(lib().bsa_wait_status(C.byref(s), 1 if reset else 0), "bsa_wait_status")
     return s.value
