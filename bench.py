@@ -534,7 +534,8 @@ def run_decode(args, world, rank):
     the merged result of both exchange routes is checked against the one-GPU decode of the same
     cache on every rank before anything is timed."""
     from dkernel_b200 import LocalStrideSparseAttention, _lib
-    from dkernel_b200.dist import ShardedDecoder, kv_shard_ranges, pack_kv_shard, sharded_decode
+    from dkernel_b200.dist import (ShardedDecoder, kv_shard_ranges, pack_kv_shard, pack_kv_shard_cyclic,
+                                   sharded_decode)
     cfg = WORKLOADS["decode"]
     B, S, Hq, Hkv, D, bs = cfg["B"], cfg["S"], cfg["Hq"], cfg["Hkv"], cfg["D"], cfg["block"]
     lens = decode_lens(cfg)
@@ -589,11 +590,16 @@ def run_decode(args, world, rank):
     k_full, v_full = make_kv()
     with torch.no_grad():
         ref_o, ref_lse = attn(q, k_full, v_full, sm_scale=scale, left_paddings=left, return_lse=True)
-    lo, hi = kv_shard_ranges(lens, rank, world, bs)
+    # Two shard layouts of the same cache: block-cyclic (block j of a sequence on rank j % N: the
+    # 16-block local window spreads evenly) and contiguous position ranges (it stays on the last rank).
     cap = int(((S // world + bs - 1) // bs + 1) * bs)
-    ks, vs, n = pack_kv_shard(k_full, v_full, left.cpu(), lo, hi, capacity=cap)
+    lens_d = lens.cuda()
+    ks, vs, n = pack_kv_shard_cyclic(k_full, v_full, left, lens_d, rank, world, bs, capacity=cap)
+    lo, hi = kv_shard_ranges(lens, rank, world, bs)
+    ks2, vs2, n2 = pack_kv_shard(k_full, v_full, left.cpu(), lo, hi, capacity=cap)
     del k_full, v_full
-    n_d, lo_d, len_d = (t.to(torch.int32).cuda() for t in (n, lo, lens))
+    n_d, len_d = n.to(torch.int32).cuda(), lens.to(torch.int32).cuda()
+    n2_d, lo_d = n2.to(torch.int32).cuda(), lo.to(torch.int32).cuda()
     dec, dec_err = None, ""
     try:
         dec = ShardedDecoder(attn, B, Hq, D, torch.bfloat16, torch.device("cuda", torch.cuda.current_device()))
@@ -607,8 +613,9 @@ def run_decode(args, world, rank):
     routes = []
     with torch.no_grad():
         if dec is not None:
-            routes.append(("xchg",) + tuple(dec.step(q, ks, vs, n_d, lo_d, len_d, scale)))
-        routes.append(("nccl",) + tuple(sharded_decode(attn, q, ks, vs, n_d, lo_d, len_d, scale)))
+            routes.append(("xchg",) + tuple(dec.step(q, ks, vs, n_d, None, len_d, scale, cyclic=True)))
+            routes.append(("xchg_contig",) + tuple(dec.step(q, ks2, vs2, n2_d, lo_d, len_d, scale)))
+        routes.append(("nccl",) + tuple(sharded_decode(attn, q, ks, vs, n_d, None, len_d, scale, cyclic=True)))
     torch.cuda.synchronize()
     assert _lib.wait_status() == 0, "a bounded wait gave up"
     errs = {}
@@ -622,6 +629,7 @@ def run_decode(args, world, rank):
     # the second buffer set holds other random shards of the same geometry
     bufs = [(ks, vs), (torch.randn(ks.shape, generator=g, device="cuda").to(torch.bfloat16),
                        torch.randn(vs.shape, generator=g, device="cuda").to(torch.bfloat16))]
+    bufs2 = [(ks2, vs2), bufs[1]]
     nbuf = len(bufs)
     it = [0]
 
@@ -629,16 +637,23 @@ def run_decode(args, world, rank):
         a, b_ = bufs[it[0] % nbuf]
         it[0] += 1
         with torch.no_grad():
-            dec.step(q, a, b_, n_d, lo_d, len_d, scale)
+            dec.step(q, a, b_, n_d, None, len_d, scale, cyclic=True)
+
+    def step_contig():
+        a, b_ = bufs2[it[0] % nbuf]
+        it[0] += 1
+        with torch.no_grad():
+            dec.step(q, a, b_, n2_d, lo_d, len_d, scale)
 
     def step_nccl():
         a, b_ = bufs[it[0] % nbuf]
         it[0] += 1
         with torch.no_grad():
-            sharded_decode(attn, q, a, b_, n_d, lo_d, len_d, scale)
+            sharded_decode(attn, q, a, b_, n_d, None, len_d, scale, cyclic=True)
 
     results = {}
-    for name, fn in ((("xchg", step_xchg),) if dec is not None else ()) + (("nccl", step_nccl),):
+    for name, fn in ((("xchg", step_xchg), ("xchg_contig", step_contig)) if dec is not None else ()) + \
+            (("nccl", step_nccl),):
         it[0] = 0
         mode = "graph"
         try:
@@ -662,10 +677,11 @@ def run_decode(args, world, rank):
     ms, spread, clocks, mode = results["xchg" if dec is not None else "nccl"]
     gbs = bytes_alg / world / (ms * 1e-3) / 1e9
     rec.update({"us_xchg": ms * 1e3 if dec is not None else None, "us_nccl": results["nccl"][0] * 1e3,
+                "us_xchg_contiguous_shards": results["xchg_contig"][0] * 1e3 if dec is not None else None,
                 "mode_xchg": mode if dec is not None else None,
                 "mode_nccl": results["nccl"][3], "gbs_per_gpu": gbs, **spread,
                 "exchange": "xchg = peer-store exchange + merge kernel (bsa_xchg_merge); "
-                            "nccl = one all-gather + merge kernel",
+                            "nccl = one all-gather + merge kernel; KV shards block-cyclic unless named",
                 "sm_mhz": clocks.get("sm_mhz"), "reasons": clocks.get("reasons"), "launches_per_step": 3})
     return rec, ms, clocks, gbs
 

@@ -62,7 +62,7 @@ class DecodeParams(C.Structure):
         + [(n, _i64) for n in ("crow_sh", "col_sh")]
         + [(n, _i32) for n in ("h_pat", "n_rows", "block_size", "heads_per_cta", "blocks_per_split",
                                "max_row_nnz", "dtype")]
-        + [("sm_scale", _f32), ("ws", _vp)]
+        + [("sm_scale", _f32), ("ws", _vp), ("k_blk_mod", _i32), ("k_blk_rem", _i32)]
     )
 
 
@@ -115,7 +115,7 @@ def lib() -> C.CDLL:
             fn = getattr(l, name)  # AttributeError if the symbol is not exported
             fn.restype = res
             fn.argtypes = args
-        if l.bsa_abi_version() != 1:
+        if l.bsa_abi_version() != 2:
             raise RuntimeError("libbsa_b200.so has an unexpected ABI version; rebuild it")
         _lib = l
     return _lib

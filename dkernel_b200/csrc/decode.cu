@@ -124,9 +124,13 @@ decode_kernel(const __grid_constant__ Tmap4 tmK, const __grid_constant__ Tmap4 t
   const int local_len = ke - ks;
   const int pos0 = p.k_pos0 ? p.k_pos0[b] : 0;
   const int total = p.k_total ? p.k_total[b] : pos0 + local_len;
-  const int end_pos = min(total, pos0 + local_len);
+  const int end_pos = p.k_blk_mod > 1 ? total : min(total, pos0 + local_len);
 
   // ---- which attended blocks belong to this CTA
+  // A KV shard is either a contiguous position range [pos0, pos0 + stored) or, with k_blk_mod = W
+  // > 1, the blocks whose index is congruent to k_blk_rem modulo W, stored back to back (block c
+  // of the sequence is local block c / W).
+  const int mod = p.k_blk_mod > 1 ? p.k_blk_mod : 1;
   int n_units = 0;
   if (total > 0 && local_len > 0) {
     const int row = (total - 1) / bs;
@@ -138,19 +142,39 @@ decode_kernel(const __grid_constant__ Tmap4 tmK, const __grid_constant__ Tmap4 t
       c_end = cr[row + 1];
     }
     const int32_t* cols = p.col + (int64_t)hp * p.col_sh;
-    int lo = c_beg;
-    while (lo < c_end && cols[lo] * bs < pos0) ++lo;
-    const int first = lo + sp * p.blocks_per_split;
-    const int last = min(c_end, first + p.blocks_per_split);
     const int subs = bs / kTok;
-    for (int e = first; e < last; ++e) {
-      const int base = cols[e] * bs;
-      for (int s = 0; s < subs; ++s) {
-        const int pos = base + s * kTok;
-        if (pos < end_pos && n_units < kMaxUnits) {
-          if (tid == kConsumers * 32) sm->unit_pos[n_units] = pos;
-          ++n_units;
+    if (mod == 1) {
+      int lo = c_beg;
+      while (lo < c_end && cols[lo] * bs < pos0) ++lo;
+      const int first = lo + sp * p.blocks_per_split;
+      const int last = min(c_end, first + p.blocks_per_split);
+      for (int e = first; e < last; ++e) {
+        const int base = cols[e] * bs;
+        for (int s = 0; s < subs; ++s) {
+          const int pos = base + s * kTok;
+          if (pos < end_pos && n_units < kMaxUnits) {
+            if (tid == kConsumers * 32) sm->unit_pos[n_units] = pos;
+            ++n_units;
+          }
         }
+      }
+    } else {
+      // this CTA takes the sp-th group of blocks_per_split local entries of the row
+      const int want0 = sp * p.blocks_per_split, want1 = want0 + p.blocks_per_split;
+      int seen = 0;
+      for (int e = c_beg; e < c_end && seen < want1; ++e) {
+        const int c = cols[e];
+        if (c < 0 || c % mod != p.k_blk_rem) continue;
+        if (seen >= want0) {
+          for (int s = 0; s < subs; ++s) {
+            const int pos = c * bs + s * kTok;
+            if (pos < total && n_units < kMaxUnits) {
+              if (tid == kConsumers * 32) sm->unit_pos[n_units] = pos;
+              ++n_units;
+            }
+          }
+        }
+        ++seen;
       }
     }
   }
@@ -180,7 +204,8 @@ decode_kernel(const __grid_constant__ Tmap4 tmK, const __grid_constant__ Tmap4 t
   auto issue_unit = [&](int u) {
     const int s = u % kStages;
     mbar_expect_tx(&sm->full[s], kStageBytes);
-    const int tok = ks + (sm->unit_pos[u] - pos0);
+    const int upos = sm->unit_pos[u];
+    const int tok = mod == 1 ? ks + (upos - pos0) : ks + (upos / bs / mod) * bs + upos % bs;
     uint8_t* kdst = ring + s * kStageBytes;
     uint8_t* vdst = kdst + kTileBytes;
 #pragma unroll
@@ -454,6 +479,8 @@ int decode_validate_heads(const bsa_decode_params* p, const char* who) {
                 p->heads_per_cta, G);
   BSA_CHECK_ARG(p->d >= 1 && p->max_row_nnz >= 0, "%s: bad sizes d=%d max_row_nnz=%d", who, p->d,
                 p->max_row_nnz);
+  BSA_CHECK_ARG(p->k_blk_mod >= 0 && (p->k_blk_mod <= 1 || (p->k_blk_rem >= 0 && p->k_blk_rem < p->k_blk_mod)),
+                "%s: bad block-cyclic shard %d mod %d", who, p->k_blk_rem, p->k_blk_mod);
   return BSA_OK;
 }
 

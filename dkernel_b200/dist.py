@@ -82,6 +82,40 @@ def pack_kv_shard(k: Tensor, v: Tensor, left_paddings: Tensor, lo: Tensor, hi: T
     return ks, vs, n
 
 
+def kv_shard_cyclic_blocks(lens: Tensor, rank: int, world: int, block_size: int) -> Tensor:
+    """Stored tokens per sequence of ``rank`` under block-cyclic sharding: block j of a sequence
+    (positions re-based to its first token) lives on rank j % world, as local block j // world.
+    A window of consecutive blocks -- the bulk of a local-stride row -- then spreads evenly over
+    the ranks, where a split into contiguous position ranges leaves it all on the last one."""
+    lens = lens.to(torch.int64)
+    nblk = (lens + block_size - 1) // block_size
+    mine = (nblk - rank + world - 1) // world                 # blocks j < nblk with j % world == rank
+    mine = mine.clamp_min(0)
+    last_is_mine = (nblk > 0) & ((nblk - 1) % world == rank)
+    tail = lens - (nblk - 1) * block_size                     # tokens of the last block
+    return torch.where(last_is_mine, (mine - 1) * block_size + tail, mine * block_size)
+
+
+def pack_kv_shard_cyclic(k: Tensor, v: Tensor, left_paddings: Tensor, lens: Tensor, rank: int, world: int,
+                         block_size: int, capacity: Optional[int] = None) -> Tuple[Tensor, Tensor, Tensor]:
+    """Cut the block-cyclic shard of ``rank`` out of left-padded (B,S,Hkv,D) K/V buffers into
+    left-aligned (B,capacity,Hkv,D) buffers.  Returns (k_shard, v_shard, n) with n the stored
+    tokens per sequence.  Host-side data preparation for tests and benchmarks (a serving system
+    appends block j of a sequence to rank j % world directly)."""
+    B, S = k.size(0), k.size(1)
+    n = kv_shard_cyclic_blocks(lens, rank, world, block_size)
+    cap = capacity if capacity is not None else max(int(n.max().item()), 1)
+    ks = k.new_zeros((B, cap) + tuple(k.shape[2:]))
+    vs = v.new_zeros((B, cap) + tuple(v.shape[2:]))
+    for b in range(B):
+        L, left = int(lens[b]), int(left_paddings[b])
+        pos = torch.arange(L, device=k.device)
+        sel = pos[(pos // block_size) % world == rank] + left
+        ks[b, :sel.numel()] = k[b, sel]
+        vs[b, :sel.numel()] = v[b, sel]
+    return ks, vs, n
+
+
 def partial_row_bytes(d: int, elem_size: int = 2) -> int:
     """Bytes of one packed partial row: d 16-bit outputs followed by the fp32 LSE."""
     return d * elem_size + 4
@@ -115,8 +149,8 @@ def split_gathered_partials(gathered: Tensor, world: int, d: int, dtype: torch.d
 
 
 def sharded_decode(attn, q: Tensor, k_shard: Tensor, v_shard: Tensor, n_local: Tensor,
-                   pos0: Tensor, total_len: Tensor, sm_scale: Optional[float] = None,
-                   group=None) -> Tuple[Tensor, Tensor]:
+                   pos0: Optional[Tensor], total_len: Tensor, sm_scale: Optional[float] = None,
+                   group=None, cyclic: bool = False) -> Tuple[Tensor, Tensor]:
     """One decode step with the KV sequence sharded over the ranks of ``group``, exchanged by
     ONE NCCL all-gather (the portable route; ``ShardedDecoder`` is the faster one).
 
@@ -124,7 +158,8 @@ def sharded_decode(attn, q: Tensor, k_shard: Tensor, v_shard: Tensor, n_local: T
     q: (B,1,Hq,D) replicated on every rank.  k_shard/v_shard: (B,cap,Hkv,D) this
     rank's left-aligned slice; n_local (B,) stored tokens; pos0 (B,) position of the
     first stored token (multiple of the block size); total_len (B,) full lengths
-    (int32 device tensors are used as they are).
+    (int32 device tensors are used as they are).  With ``cyclic=True`` the shard is block-cyclic
+    (``pack_kv_shard_cyclic``) and pos0 is ignored.
     Returns the merged (out (B,1,Hq,D), lse (B,Hq)) on every rank.
 
     Per step: the decode kernel (+ its split merge) writes this rank's partial O (input
@@ -140,8 +175,9 @@ def sharded_decode(attn, q: Tensor, k_shard: Tensor, v_shard: Tensor, n_local: T
     packed = torch.empty((rows, row_bytes), dtype=torch.uint8, device=q.device)
     o_view, lse_view = packed_partial_views(packed, D, q.dtype)
     decode(q, k_shard, v_shard, attn._plan(), scale, seq_dim=1, k_start=None,
-           k_end=_as_i32(n_local, q.device), k_pos0=_as_i32(pos0, q.device),
-           k_total=_as_i32(total_len, q.device), out=o_view, lse_out=lse_view)
+           k_end=_as_i32(n_local, q.device), k_pos0=None if cyclic else _as_i32(pos0, q.device),
+           k_total=_as_i32(total_len, q.device), out=o_view, lse_out=lse_view,
+           k_blk=(world, dist.get_rank(group)) if cyclic else None)
     gathered = gather_packed_partials(packed, group)
     merged = torch.empty((B, 1, Hq, D), dtype=q.dtype, device=q.device)
     mlse = torch.empty((B, Hq), dtype=torch.float32, device=q.device)
@@ -193,9 +229,10 @@ class ShardedDecoder:
         self.stage_o = torch.empty((self.rows, head_dim), dtype=dtype, device=device)
         self.stage_lse = torch.empty((self.rows,), dtype=torch.float32, device=device)
 
-    def step(self, q: Tensor, k_shard: Tensor, v_shard: Tensor, n_local: Tensor, pos0: Tensor,
+    def step(self, q: Tensor, k_shard: Tensor, v_shard: Tensor, n_local: Tensor, pos0: Optional[Tensor],
              total_len: Tensor, sm_scale: Optional[float] = None,
-             out: Optional[Tensor] = None, lse: Optional[Tensor] = None) -> Tuple[Tensor, Tensor]:
+             out: Optional[Tensor] = None, lse: Optional[Tensor] = None, cyclic: bool = False
+             ) -> Tuple[Tensor, Tensor]:
         """Arguments as for ``sharded_decode``; returns the merged (out (B,1,Hq,D), lse (B,Hq))."""
         from . import _lib
         from .ops import decode
@@ -203,8 +240,9 @@ class ShardedDecoder:
         assert (B, Hq, D) == (self.B, self.Hq, self.D) and q.dtype == self.dtype
         scale = sm_scale or 1.0 / math.sqrt(D)
         decode(q, k_shard, v_shard, self.attn._plan(), scale, seq_dim=1, k_start=None,
-               k_end=_as_i32(n_local, q.device), k_pos0=_as_i32(pos0, q.device),
-               k_total=_as_i32(total_len, q.device), out=self.stage_o, lse_out=self.stage_lse)
+               k_end=_as_i32(n_local, q.device), k_pos0=None if cyclic else _as_i32(pos0, q.device),
+               k_total=_as_i32(total_len, q.device), out=self.stage_o, lse_out=self.stage_lse,
+               k_blk=(self.world, self.rank) if cyclic else None)
         merged = out if out is not None else torch.empty((B, 1, Hq, D), dtype=q.dtype, device=q.device)
         mlse = lse if lse is not None else torch.empty((B, Hq), dtype=torch.float32, device=q.device)
         assert merged.is_contiguous() and mlse.is_contiguous()
@@ -400,6 +438,7 @@ class ContextParallelSparseAttention(torch.nn.Module):
         return (out, lse) if return_lse else out
 
 
-__all__ = ["head_shard", "kv_shard_ranges", "pack_kv_shard", "sharded_decode", "ShardedDecoder",
+__all__ = ["head_shard", "kv_shard_ranges", "pack_kv_shard", "kv_shard_cyclic_blocks", "pack_kv_shard_cyclic",
+           "sharded_decode", "ShardedDecoder",
            "chunk_bounds", "ring_steps", "ring_forward", "ring_backward",
            "ContextParallelSparseAttention"]

@@ -54,6 +54,17 @@ class _Plan:
         self._group_shared: Dict[int, bool] = {}
         self._kv_pairs: Dict[Tuple[int, int, int], Optional[Tensor]] = {}
         self._fine: Optional["_Plan"] = None
+        self._cyclic_nnz: Dict[Tuple[int, int], int] = {}
+
+    def max_row_nnz_cyclic(self, mod: int, rem: int) -> int:
+        """Longest pattern row when only the blocks congruent to ``rem`` modulo ``mod`` count
+        (what one rank of a block-cyclic KV shard sees): bounds the decode split count."""
+        key = (mod, rem)
+        if key not in self._cyclic_nnz:
+            from .utils import crow_col_to_dense
+            dense = crow_col_to_dense(self.crow, self.col, torch.int32)
+            self._cyclic_nnz[key] = int(dense[:, :, rem::mod].sum(-1).max().item()) if dense.numel() else 0
+        return self._cyclic_nnz[key]
 
     def for_kernels(self, q: Tensor) -> "_Plan":
         """The layouts the prefill / backward kernels should read.  The tensor-core kernels work
@@ -232,13 +243,14 @@ def decode(q: Tensor, k: Tensor, v: Tensor, plan: _Plan, sm_scale: float, *, seq
            k_start: Optional[Tensor] = None, k_end: Optional[Tensor] = None,
            k_pos0: Optional[Tensor] = None, k_total: Optional[Tensor] = None,
            out: Optional[Tensor] = None, blocks_per_split: int = 0,
-           workspace: Optional[Tensor] = None, lse_out: Optional[Tensor] = None
-           ) -> Tuple[Tensor, Tensor]:
+           workspace: Optional[Tensor] = None, lse_out: Optional[Tensor] = None,
+           k_blk: Optional[Tuple[int, int]] = None) -> Tuple[Tensor, Tensor]:
     """One query token per sequence (split-KV decode kernel).
 
     q: (B,1,Hq,D)/(B,Hq,1,D) or packed (B,Hq,D); k, v: 4-D with the module's
     seq_dim, or packed (T,Hkv,D) with ``k_start``/``k_end`` = cu_seqlens slices.
-    ``k_pos0``/``k_total`` describe a KV shard (see include/bsa.h).
+    ``k_pos0``/``k_total`` describe a contiguous KV shard, ``k_blk = (W, r)`` with ``k_total`` a
+    block-cyclic one (see include/bsa.h).
     Returns (out shaped like q, lse fp32 (B,Hq))."""
     lib = _lib.lib()
     q = _last_dim_contig(q)     # before the strides are read: a copy has its own
@@ -284,6 +296,9 @@ def decode(q: Tensor, k: Tensor, v: Tensor, plan: _Plan, sm_scale: float, *, seq
     p.heads_per_cta = _pick_heads_per_cta(g) if plan.heads_shared_in_group(hq, hkv) else 1
     p.blocks_per_split = blocks_per_split if blocks_per_split > 0 else 0   # 0: the library picks
     p.max_row_nnz = plan.max_row_nnz
+    if k_blk is not None and k_blk[0] > 1:
+        p.k_blk_mod, p.k_blk_rem = k_blk
+        p.max_row_nnz = plan.max_row_nnz_cyclic(*k_blk)
     p.dtype = _lib.dtype_code(q.dtype)
     p.sm_scale = float(sm_scale)
     need = lib.bsa_decode_workspace_bytes(C.byref(p))

@@ -28,7 +28,7 @@
 extern "C" {
 #endif
 
-#define BSA_ABI_VERSION 1
+#define BSA_ABI_VERSION 2
 
 enum {
   BSA_OK = 0,
@@ -214,6 +214,11 @@ typedef struct {
   int32_t dtype;
   float sm_scale;
   float* ws;                  /* workspace, bsa_decode_workspace_bytes()        */
+  /* Block-cyclic KV shard (k_blk_mod = W > 1): the stored tokens of sequence b are
+   * the blocks c with c % W == k_blk_rem of a sequence of k_total[b] tokens, back
+   * to back (block c is local block c / W; k_pos0 is ignored).  A local window of
+   * consecutive blocks then spreads evenly over the W shards.  0 or 1 = off.   */
+  int32_t k_blk_mod, k_blk_rem;
 } bsa_decode_params;
 
 size_t bsa_decode_workspace_bytes(const bsa_decode_params* p);

@@ -188,6 +188,38 @@ def test_kv_sharded_decode_merges_to_whole():
     assert_lse_close(mlse, ref_lse)
 
 
+@pytest.mark.parametrize("W", [2, 4, 8])
+def test_block_cyclic_kv_shards_merge_to_whole(W):
+    """Block-cyclic KV shards (block j of a sequence on rank j % W) decoded one rank after the
+    other on this GPU + combine_attn_partitions == un-sharded decode; ranks without any attended
+    block give O = 0, LSE = -inf."""
+    from dkernel_b200.ops import decode
+    from dkernel_b200.dist import kv_shard_cyclic_blocks, pack_kv_shard_cyclic
+    from dkernel_b200 import combine_attn_partitions
+    B, Hq, Hkv, S, D, bs = 5, 8, 2, 2048, 128, 64
+    pk = dict(block_size=bs, local_blocks=6, vert_stride=4, num_kv_heads=Hkv)
+    q, k, v = seeded_qkv(29, (B, 1, Hq, D), (B, S, Hkv, D), torch.bfloat16)
+    lens = torch.tensor([2048, 700, 65, 1, 1300])
+    left = S - lens
+    bm = O.block_mask(Hq, S, **pk)
+    ref, ref_lse = O.decode_attention(q.float(), k.float(), v.float(), bm, bs, left_paddings=left)
+    mod = _module(Hq, S, pk, seq_dim=1)
+    parts, stored = [], torch.zeros_like(lens)
+    for r in range(W):
+        ks, vs, n = pack_kv_shard_cyclic(k, v, left, lens, r, W, bs)
+        assert torch.equal(n, kv_shard_cyclic_blocks(lens, r, W, bs))
+        stored += n
+        o, l = decode(q.cuda(), ks.cuda(), vs.cuda(), mod._plan(), 1 / math.sqrt(D), seq_dim=1,
+                      k_end=n.to(torch.int32).cuda(), k_total=lens.to(torch.int32).cuda(), k_blk=(W, r))
+        parts.append((o, l.unsqueeze(-1)))
+    assert torch.equal(stored, lens)                       # every token lives on exactly one rank
+    merged, mlse = combine_attn_partitions(*parts, hdim=2, return_lse=True)
+    assert_out_close(merged, ref)
+    assert_lse_close(mlse, ref_lse)
+    from dkernel_b200 import _lib
+    assert _lib.wait_status() == 0
+
+
 def test_sharded_decode_single_rank_group(tmp_path):
     """sharded_decode end to end (packed (O, LSE) rows -> all-gather -> fused merge) with a
     one-rank NCCL group: the whole sequence is the only shard."""

@@ -37,7 +37,7 @@ def _worker(rank, world, port, ret):
         from oracle import dkernel_oracle as O
         from dkernel_b200 import LocalStrideSparseAttention, _lib
         from dkernel_b200.dist import (ContextParallelSparseAttention, ShardedDecoder, kv_shard_ranges,
-                                       pack_kv_shard, sharded_decode)
+                                       pack_kv_shard, pack_kv_shard_cyclic, sharded_decode)
         # ---------------------------------------------------------------- KV-sharded decode
         B, S, Hq, Hkv, D, bs = 5, 2048, 8, 2, 128, 64
         attn = LocalStrideSparseAttention.__wrapped__(Hq, S, bs, 4, 4, num_kv_heads=Hkv, seq_dim=1)
@@ -67,6 +67,16 @@ def _worker(rank, world, port, ret):
                 assert (lse.cpu().unsqueeze(-1) - ref_lse).abs().max().item() <= 1e-3, f"{name} step {step}: lse"
                 assert (out.float() - one.float()).abs().max().item() <= 2e-2
             assert torch.equal(out_x, out_n) or (out_x.float() - out_n.float()).abs().max().item() <= 4e-3
+            # block-cyclic shards (block j of a sequence on rank j % world)
+            kc, vc, nc = pack_kv_shard_cyclic(k, v, left, lens, rank, world, bs)
+            cargs = (q.to(dev), kc.to(dev), vc.to(dev), nc.int().to(dev), None, lens.int().to(dev), scale)
+            out_c, lse_c = dec.step(*cargs, cyclic=True)
+            out_cn, lse_cn = sharded_decode(attn, *cargs, cyclic=True)
+            torch.cuda.synchronize()
+            assert _lib.wait_status() == 0
+            for out, lse, name in ((out_c, lse_c, "cyclic peer-store"), (out_cn, lse_cn, "cyclic all-gather")):
+                assert (out.float().cpu() - ref).abs().max().item() <= 2e-2, f"{name} step {step}: output"
+                assert (lse.cpu().unsqueeze(-1) - ref_lse).abs().max().item() <= 1e-3, f"{name} step {step}: lse"
         # graph replay of the peer-store route: the step counter lives in the exchange buffer
         out_g = torch.empty_like(out_x)
         lse_g = torch.empty_like(lse_x)
