@@ -665,7 +665,7 @@ def run_decode(args, world, rank):
                 it[0] += 1
             run = gstep
         except Exception as e:     # capture unsupported in this setup: time the eager calls
-            mode, run = f"eager ({type(e).__name__})", fn
+            mode, run = f"eager ({type(e).__name__}: {str(e)[:80]})", fn
         flag = torch.tensor([1.0 if mode == "graph" else 0.0], device="cuda")
         torch.distributed.all_reduce(flag, op=torch.distributed.ReduceOp.MIN)
         if flag.item() == 0.0 and mode == "graph":
@@ -828,7 +828,8 @@ def run_all(args, world, rank):
     def decode():
         rec, ms, clocks, gbs = run_decode(args, world, rank)
         name = "decode_c4" if world == 1 else "decode_c4_kv_sharded"
-        sub[name] = {k: v for k, v in rec.items() if not isinstance(v, str)}
+        sub[name] = {k: v for k, v in rec.items() if not isinstance(v, str) or k.startswith("mode_")
+                     or k == "xchg_unavailable"}
         if world == 1:
             rsub["decode"] = {"achieved": gbs, "frac": rec["hbm_frac"], "unit": "GB/s", "bound": "hbm"}
 

@@ -69,7 +69,8 @@ class DecodeParams(C.Structure):
 class XchgParams(C.Structure):
     _fields_ = ([(n, _vp) for n in ("stage_o", "stage_lse", "out", "out_lse")]
                 + [("xbuf", _vp * 8), ("rows", _i64)]
-                + [(n, _i32) for n in ("world", "rank", "d", "dtype")])
+                + [(n, _i32) for n in ("world", "rank", "d", "dtype")]
+                + [("part_o", _vp), ("part_lse", _vp), ("nsplit", _i32)])
 
 
 EXPORTS = {

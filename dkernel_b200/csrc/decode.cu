@@ -82,6 +82,7 @@ struct DecodeSmem {
   // after the 1024-aligned stage ring
   uint64_t full[kStages];
   uint64_t empty[kStages];
+  int n_units;              // stage-units of this CTA
   int unit_pos[kMaxUnits];  // first position of each stage-unit
   float wm[kConsumers][16];
   float wl[kConsumers][16];
@@ -126,81 +127,10 @@ decode_kernel(const __grid_constant__ Tmap4 tmK, const __grid_constant__ Tmap4 t
   const int total = p.k_total ? p.k_total[b] : pos0 + local_len;
   const int end_pos = p.k_blk_mod > 1 ? total : min(total, pos0 + local_len);
 
-  // ---- which attended blocks belong to this CTA
   // A KV shard is either a contiguous position range [pos0, pos0 + stored) or, with k_blk_mod = W
   // > 1, the blocks whose index is congruent to k_blk_rem modulo W, stored back to back (block c
   // of the sequence is local block c / W).
   const int mod = p.k_blk_mod > 1 ? p.k_blk_mod : 1;
-  int n_units = 0;
-  if (total > 0 && local_len > 0) {
-    const int row = (total - 1) / bs;
-    const int hp = pattern_head(h0, p.h_pat, p.hq, p.hkv);
-    int c_beg = 0, c_end = 0;
-    if (row < p.n_rows) {
-      const int32_t* cr = p.crow + (int64_t)hp * p.crow_sh;
-      c_beg = cr[row];
-      c_end = cr[row + 1];
-    }
-    const int32_t* cols = p.col + (int64_t)hp * p.col_sh;
-    const int subs = bs / kTok;
-    if (mod == 1) {
-      int lo = c_beg;
-      while (lo < c_end && cols[lo] * bs < pos0) ++lo;
-      const int first = lo + sp * p.blocks_per_split;
-      const int last = min(c_end, first + p.blocks_per_split);
-      for (int e = first; e < last; ++e) {
-        const int base = cols[e] * bs;
-        for (int s = 0; s < subs; ++s) {
-          const int pos = base + s * kTok;
-          if (pos < end_pos && n_units < kMaxUnits) {
-            if (tid == kConsumers * 32) sm->unit_pos[n_units] = pos;
-            ++n_units;
-          }
-        }
-      }
-    } else {
-      // this CTA takes the sp-th group of blocks_per_split local entries of the row
-      const int want0 = sp * p.blocks_per_split, want1 = want0 + p.blocks_per_split;
-      int seen = 0;
-      for (int e = c_beg; e < c_end && seen < want1; ++e) {
-        const int c = cols[e];
-        if (c < 0 || c % mod != p.k_blk_rem) continue;
-        if (seen >= want0) {
-          for (int s = 0; s < subs; ++s) {
-            const int pos = c * bs + s * kTok;
-            if (pos < total && n_units < kMaxUnits) {
-              if (tid == kConsumers * 32) sm->unit_pos[n_units] = pos;
-              ++n_units;
-            }
-          }
-        }
-        ++seen;
-      }
-    }
-  }
-
-  if (n_units == 0) {  // nothing attended here: an empty partial (uniform exit)
-    for (int i = tid; i < GH * D; i += kDecThreads) {
-      const int h = h0 + i / D, d = i % D;
-      if (nsplit == 1) {
-        reinterpret_cast<T*>(p.o)[(int64_t)b * p.o_sb + (int64_t)h * p.o_sh + d] = Elem<T>::from_f(0.f);
-      } else {
-        p.ws[(((int64_t)b * p.hq + h) * nsplit + sp) * D + d] = 0.f;
-      }
-    }
-    for (int i = tid; i < GH; i += kDecThreads) {
-      const int h = h0 + i;
-      if (nsplit == 1) {
-        if (p.lse) p.lse[(int64_t)b * p.lse_sb + (int64_t)h * p.lse_sh] = -INFINITY;
-      } else {
-        p.ws[(int64_t)p.batch * p.hq * nsplit * D + ((int64_t)b * p.hq + h) * nsplit + sp] = -INFINITY;
-      }
-    }
-    return;
-  }
-
-  // The producer thread owns the barriers and the unit list, so its first loads go out
-  // before the rest of the CTA has staged Q.
   auto issue_unit = [&](int u) {
     const int s = u % kStages;
     mbar_expect_tx(&sm->full[s], kStageBytes);
@@ -214,32 +144,101 @@ decode_kernel(const __grid_constant__ Tmap4 tmK, const __grid_constant__ Tmap4 t
       tma_load_tile(vdst + c * (kTok * 128), &tmV, &sm->full[s], c * 64, tok, kvh, b);
     }
   };
-  if (tid == kConsumers * 32) {
-    for (int s = 0; s < kStages; ++s) {
-      mbar_init(&sm->full[s], 1);
-      mbar_init(&sm->empty[s], kConsumers);
-    }
-    mbar_fence_init();
-    for (int u = 0; u < n_units && u < kStages; ++u) issue_unit(u);
-  }
-  // q heads of the group -> rows of the 16-row A tile (rows >= GH are zero), 16 bytes a thread
-  for (int i = tid; i < 16 * D / 8; i += kDecThreads) {
-    const int r = i / (D / 8), c = i % (D / 8);
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (r < GH) {
-      const T* src = reinterpret_cast<const T*>(p.q) + (int64_t)b * p.q_sb + (int64_t)(h0 + r) * p.q_sh + c * 8;
-      if (q_vec) {
-        v = *reinterpret_cast<const uint4*>(src);
-      } else {
-        T tmp[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) tmp[e] = src[e];
-        v = *reinterpret_cast<const uint4*>(tmp);
+
+  if (warp == kConsumers) {
+    // ---- the producer warp finds the attended blocks of this CTA: the sp-th group of
+    // blocks_per_split row entries that lie in the shard.  The row is read 32 entries at a time
+    // (one coalesced load and one vote per chunk instead of a chain of dependent loads), and the
+    // first tiles are requested before the rest of the CTA has staged Q.
+    int nu = 0;
+    if (total > 0 && local_len > 0) {
+      const int row = (total - 1) / bs;
+      const int hp = pattern_head(h0, p.h_pat, p.hq, p.hkv);
+      int c_beg = 0, c_end = 0;
+      if (row < p.n_rows) {
+        const int32_t* cr = p.crow + (int64_t)hp * p.crow_sh;
+        c_beg = __ldg(cr + row);
+        c_end = __ldg(cr + row + 1);
+      }
+      const int32_t* cols = p.col + (int64_t)hp * p.col_sh;
+      const int subs = bs / kTok;
+      const int want0 = sp * p.blocks_per_split, want1 = want0 + p.blocks_per_split;
+      int seen = 0;   // row entries of the shard met so far
+      for (int e0 = c_beg; e0 < c_end && seen < want1; e0 += 32) {
+        const int e = e0 + lane;
+        const int c = e < c_end ? __ldg(cols + e) : -1;
+        const bool mine = c >= 0 && (mod == 1 ? c * bs >= pos0 : c % mod == p.k_blk_rem);
+        const uint32_t vote = __ballot_sync(0xffffffffu, mine);
+        const int idx = seen + __popc(vote & ((1u << lane) - 1u));
+        int valid_units = 0;
+        if (mine && idx >= want0 && idx < want1) {
+          for (int s = 0; s < subs; ++s) {
+            // positions grow with the entry index, so the units past the end form a tail
+            const int pos = c * bs + s * kTok;
+            const int u = (idx - want0) * subs + s;
+            if (pos < end_pos && u < kMaxUnits) {
+              sm->unit_pos[u] = pos;
+              ++valid_units;
+            }
+          }
+        }
+        nu += __reduce_add_sync(0xffffffffu, valid_units);
+        seen += __popc(vote);
       }
     }
-    reinterpret_cast<uint4*>(Qs)[i] = v;
+    __syncwarp();
+    if (lane == 0) {
+      sm->n_units = nu;
+      for (int s = 0; s < kStages; ++s) {
+        mbar_init(&sm->full[s], 1);
+        mbar_init(&sm->empty[s], kConsumers);
+      }
+      mbar_fence_init();
+      for (int u = 0; u < nu && u < kStages; ++u) issue_unit(u);
+    }
+  } else {
+    // q heads of the group -> rows of the 16-row A tile (rows >= GH are zero), 16 bytes a thread
+    for (int i = tid; i < 16 * D / 8; i += kConsumers * 32) {
+      const int r = i / (D / 8), c = i % (D / 8);
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (r < GH) {
+        const T* src = reinterpret_cast<const T*>(p.q) + (int64_t)b * p.q_sb + (int64_t)(h0 + r) * p.q_sh + c * 8;
+        if (q_vec) {
+          v = *reinterpret_cast<const uint4*>(src);
+        } else {
+          T tmp[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) tmp[e] = src[e];
+          v = *reinterpret_cast<const uint4*>(tmp);
+        }
+      }
+      reinterpret_cast<uint4*>(Qs)[i] = v;
+    }
   }
   __syncthreads();
+  const int n_units = sm->n_units;
+  // one split and an output tensor: write the final rows; otherwise an fp32 partial per split
+  const bool final_out = nsplit == 1 && p.o != nullptr;
+
+  if (n_units == 0) {  // nothing attended here: an empty partial (uniform exit)
+    for (int i = tid; i < GH * D; i += kDecThreads) {
+      const int h = h0 + i / D, d = i % D;
+      if (final_out) {
+        reinterpret_cast<T*>(p.o)[(int64_t)b * p.o_sb + (int64_t)h * p.o_sh + d] = Elem<T>::from_f(0.f);
+      } else {
+        p.ws[(((int64_t)b * p.hq + h) * nsplit + sp) * D + d] = 0.f;
+      }
+    }
+    for (int i = tid; i < GH; i += kDecThreads) {
+      const int h = h0 + i;
+      if (final_out) {
+        if (p.lse) p.lse[(int64_t)b * p.lse_sb + (int64_t)h * p.lse_sh] = -INFINITY;
+      } else {
+        p.ws[(int64_t)p.batch * p.hq * nsplit * D + ((int64_t)b * p.hq + h) * nsplit + sp] = -INFINITY;
+      }
+    }
+    return;
+  }
 
   const int g = lane >> 2, tq = lane & 3;
   float oacc[D / 8][4];
@@ -404,7 +403,7 @@ decode_kernel(const __grid_constant__ Tmap4 tmK, const __grid_constant__ Tmap4 t
     const float inv = l > 0.f ? 1.f / l : 0.f;
     const float lse = l > 0.f ? (mf + log2f(l)) * kLn2 : -INFINITY;
     const int h = h0 + r;
-    if (nsplit == 1) {
+    if (final_out) {
       reinterpret_cast<T*>(p.o)[(int64_t)b * p.o_sb + (int64_t)h * p.o_sh + d] =
           Elem<T>::from_f(acc * inv);
       if (d == 0 && p.lse) p.lse[(int64_t)b * p.lse_sb + (int64_t)h * p.lse_sh] = lse;
@@ -531,7 +530,7 @@ int launch_decode(const bsa_decode_params* p, cudaStream_t s) {
   kern<<<grid, kDecThreads, smem, s>>>(tmK, tmV, q, nsplit, status);
   rc = check_launch("decode_kernel");
   if (rc) return rc;
-  if (nsplit > 1) {
+  if (nsplit > 1 && p->o) {
     const int64_t rows = (int64_t)p->batch * p->hq;
     float* ws_lse = p->ws + rows * nsplit * D;
     // partial o: (rows, nsplit, D) -> partition stride D, row stride nsplit*D
@@ -558,14 +557,14 @@ int launch_decode(const bsa_decode_params* p, cudaStream_t s) {
 size_t decode_workspace_bytes(const bsa_decode_params* p) {
   if (decode_validate_heads(p, "bsa_decode_workspace_bytes") != BSA_OK) return 0;
   const int nsplit = decode_nsplit(p);
-  if (nsplit <= 1) return 0;
+  if (nsplit <= 1 && p->o) return 0;   // without an output tensor even a single split stays a partial
   return sizeof(float) * (size_t)p->batch * p->hq * nsplit * (p->d + 1);
 }
 
 int decode_run(const bsa_decode_params* p, cudaStream_t s) {
   int vrc = decode_validate_heads(p, "bsa_decode");
   if (vrc) return vrc;
-  BSA_CHECK_ARG(p->q && p->k && p->v && p->o && p->crow && p->col, "bsa_decode: null pointer");
+  BSA_CHECK_ARG(p->q && p->k && p->v && (p->o || p->ws) && p->crow && p->col, "bsa_decode: null pointer");
   BSA_CHECK_ARG(p->h_pat == 1 || p->h_pat == p->hkv || p->h_pat == p->hq,
                 "bsa_decode: pattern has %d heads, expected 1, %d or %d", p->h_pat, p->hkv, p->hq);
   if (p->batch == 0) return BSA_OK;
@@ -587,7 +586,7 @@ int decode_run(const bsa_decode_params* p, cudaStream_t s) {
     return BSA_E_TOOBIG;
   }
   const int nsplit = decode_nsplit(p);
-  BSA_CHECK_ARG(nsplit == 1 || p->ws, "bsa_decode: workspace required for %d splits", nsplit);
+  BSA_CHECK_ARG((nsplit == 1 && p->o) || p->ws, "bsa_decode: workspace required for %d splits", nsplit);
   if (p->dtype == BSA_BF16)
     return p->d == 128 ? launch_decode<__nv_bfloat16, 128>(p, s) : launch_decode<__nv_bfloat16, 64>(p, s);
   return p->d == 128 ? launch_decode<__half, 128>(p, s) : launch_decode<__half, 64>(p, s);

@@ -201,10 +201,10 @@ class ShardedDecoder:
 
     Construction (collective over ``group``, once): every rank allocates an exchange buffer in
     torch's symmetric memory and maps the buffers of all ranks of the node.  A step is then
-    three launches on the caller's stream and no host synchronisation: the decode kernel and its
-    split merge write this rank's partial (O, LSE) rows into a local staging buffer, and
-    ``bsa_xchg_merge`` stores them into every rank's exchange buffer over NVLink, waits (bounded)
-    for the peers' rows to land in the local buffer and merges them.  All ranks must call
+    two launches on the caller's stream and no host synchronisation: the decode kernel leaves this
+    rank's split-KV partials in its workspace, and ``bsa_xchg_merge`` (launched as its programmatic
+    dependent) merges the splits, stores the rank's (O, LSE) rows into every rank's exchange buffer
+    over NVLink, waits (bounded) for the peers' rows to land in the local buffer and merges them.  All ranks must call
     ``step`` the same number of times.  The call can be captured in a CUDA graph and replayed."""
 
     def __init__(self, attn, batch: int, num_heads: int, head_dim: int, dtype: torch.dtype,
@@ -226,8 +226,6 @@ class ShardedDecoder:
         self.peer_ptrs = [int(p) for p in self.handle.buffer_ptrs]
         assert len(self.peer_ptrs) == self.world and self.peer_ptrs[self.rank] == self.xbuf.data_ptr()
         dist.barrier(group)      # every buffer is zeroed before anyone's first push can arrive
-        self.stage_o = torch.empty((self.rows, head_dim), dtype=dtype, device=device)
-        self.stage_lse = torch.empty((self.rows,), dtype=torch.float32, device=device)
 
     def step(self, q: Tensor, k_shard: Tensor, v_shard: Tensor, n_local: Tensor, pos0: Optional[Tensor],
              total_len: Tensor, sm_scale: Optional[float] = None,
@@ -239,15 +237,16 @@ class ShardedDecoder:
         B, _, Hq, D = q.shape
         assert (B, Hq, D) == (self.B, self.Hq, self.D) and q.dtype == self.dtype
         scale = sm_scale or 1.0 / math.sqrt(D)
-        decode(q, k_shard, v_shard, self.attn._plan(), scale, seq_dim=1, k_start=None,
-               k_end=_as_i32(n_local, q.device), k_pos0=None if cyclic else _as_i32(pos0, q.device),
-               k_total=_as_i32(total_len, q.device), out=self.stage_o, lse_out=self.stage_lse,
-               k_blk=(self.world, self.rank) if cyclic else None)
+        part_o, part_lse = decode(q, k_shard, v_shard, self.attn._plan(), scale, seq_dim=1, k_start=None,
+                                  k_end=_as_i32(n_local, q.device),
+                                  k_pos0=None if cyclic else _as_i32(pos0, q.device),
+                                  k_total=_as_i32(total_len, q.device),
+                                  k_blk=(self.world, self.rank) if cyclic else None, partials_only=True)
         merged = out if out is not None else torch.empty((B, 1, Hq, D), dtype=q.dtype, device=q.device)
         mlse = lse if lse is not None else torch.empty((B, Hq), dtype=torch.float32, device=q.device)
         assert merged.is_contiguous() and mlse.is_contiguous()
         p = _lib.XchgParams()
-        p.stage_o, p.stage_lse = _lib.ptr(self.stage_o), _lib.ptr(self.stage_lse)
+        p.part_o, p.part_lse, p.nsplit = _lib.ptr(part_o), _lib.ptr(part_lse), part_o.size(1)
         p.out, p.out_lse = _lib.ptr(merged), _lib.ptr(mlse)
         for w in range(self.world):
             p.xbuf[w] = self.peer_ptrs[w]

@@ -244,14 +244,17 @@ def decode(q: Tensor, k: Tensor, v: Tensor, plan: _Plan, sm_scale: float, *, seq
            k_pos0: Optional[Tensor] = None, k_total: Optional[Tensor] = None,
            out: Optional[Tensor] = None, blocks_per_split: int = 0,
            workspace: Optional[Tensor] = None, lse_out: Optional[Tensor] = None,
-           k_blk: Optional[Tuple[int, int]] = None) -> Tuple[Tensor, Tensor]:
+           k_blk: Optional[Tuple[int, int]] = None, partials_only: bool = False
+           ) -> Tuple[Tensor, Tensor]:
     """One query token per sequence (split-KV decode kernel).
 
     q: (B,1,Hq,D)/(B,Hq,1,D) or packed (B,Hq,D); k, v: 4-D with the module's
     seq_dim, or packed (T,Hkv,D) with ``k_start``/``k_end`` = cu_seqlens slices.
     ``k_pos0``/``k_total`` describe a contiguous KV shard, ``k_blk = (W, r)`` with ``k_total`` a
     block-cyclic one (see include/bsa.h).
-    Returns (out shaped like q, lse fp32 (B,Hq))."""
+    Returns (out shaped like q, lse fp32 (B,Hq)); with ``partials_only`` the split-KV partials
+    stay unmerged and (o_parts fp32 (B*Hq, splits, D), lse_parts fp32 (B*Hq, splits)) are returned
+    (views of one workspace tensor) for a consumer that merges them itself."""
     lib = _lib.lib()
     q = _last_dim_contig(q)     # before the strides are read: a copy has its own
     if q.dim() == 4:
@@ -262,7 +265,9 @@ def decode(q: Tensor, k: Tensor, v: Tensor, plan: _Plan, sm_scale: float, *, seq
     else:
         B, hq, d = q.shape
         q_sb, q_sh = q.stride(0), q.stride(1)
-    if out is not None and out.dim() == 2:
+    if partials_only:
+        o, o_sh, lse, lse_sh = None, d, None, 1
+    elif out is not None and out.dim() == 2:
         # rows = (batch, head) with a row stride, e.g. packed next to the LSE for one all-gather
         assert out.shape == (B * hq, d) and out.stride(1) == 1 and out.dtype == q.dtype
         o, o_sh = out, out.stride(0)
@@ -270,7 +275,9 @@ def decode(q: Tensor, k: Tensor, v: Tensor, plan: _Plan, sm_scale: float, *, seq
         o = out if out is not None else torch.empty(q.shape, dtype=q.dtype, device=q.device)
         assert o.is_contiguous(), "decode output must be contiguous"
         o_sh = d
-    if lse_out is not None:
+    if partials_only:
+        pass
+    elif lse_out is not None:
         assert lse_out.dtype == torch.float32 and lse_out.numel() == B * hq and lse_out.dim() == 1
         lse, lse_sh = lse_out, lse_out.stride(0)
     else:
@@ -311,6 +318,12 @@ def decode(q: Tensor, k: Tensor, v: Tensor, plan: _Plan, sm_scale: float, *, seq
     p.ws = _lib.ptr(ws)
     with torch.cuda.device(q.device):
         _lib.check(lib.bsa_decode(C.byref(p), _lib.stream_of(q)), "bsa_decode")
+    if partials_only:
+        rows = B * hq
+        nsplit = need // (4 * rows * (d + 1))
+        flat = ws.view(-1)
+        return (flat[:rows * nsplit * d].view(rows, nsplit, d),
+                flat[rows * nsplit * d:rows * nsplit * (d + 1)].view(rows, nsplit))
     return o, lse
 
 

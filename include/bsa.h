@@ -191,7 +191,11 @@ int bsa_bwd(const bsa_bwd_params* p, void* stream);
 typedef struct {
   const void* q;              /* (batch, hq, d), strides q_sb, q_sh             */
   const void* k; const void* v;
-  void* o; float* lse;        /* o like q; lse (batch, hq) or NULL              */
+  void* o; float* lse;        /* o like q; lse (batch, hq) or NULL.  o = NULL: leave the
+                                 per-split partials unmerged in ws (fp32 o (batch, hq,
+                                 splits, d) normalised per split, then lse (batch, hq,
+                                 splits)); splits = bsa_decode_workspace_bytes(p) /
+                                 (4 * batch * hq * (d + 1)), at least 1               */
   int64_t q_sb, q_sh;
   int64_t k_sb, k_ss, k_sh;
   int64_t v_sb, v_ss, v_sh;
@@ -278,11 +282,13 @@ int bsa_merge_partials(const void* o_parts, const float* lse_parts, int32_t P,
  * IPC, or torch symmetric memory): xbuf[w] is rank w's buffer as addressed by
  * THIS process; xbuf[rank] is the local one.  Per step every rank calls
  * bsa_xchg_merge once with its partial rows (stage_o (rows, d) 16-bit
- * contiguous, stage_lse (rows) fp32): the kernel stores them into every rank's
- * buffer (remote stores only; nothing is loaded from peer memory), publishes a
- * flag per CTA, waits -- bounded, see bsa_wait_status, code 601 -- for the flags
- * of all ranks in the local buffer and writes the merged out (rows, d) and
- * out_lse (rows, or NULL).  All ranks must make the same sequence of calls with
+ * contiguous, stage_lse (rows) fp32; or the unmerged split partials, see the
+ * struct): the kernel stores them into every rank's
+ * buffer (remote stores only; nothing is loaded from peer memory) as 8-byte
+ * words that carry the step number beside their payload, waits -- bounded, see
+ * bsa_wait_status, code 601 -- until the words of all ranks in the local buffer
+ * show the current step and writes the merged out (rows, d) and out_lse (rows,
+ * or NULL).  All ranks must make the same sequence of calls with
  * the same (world, rows, d); the step counter lives in the buffer, so a captured
  * CUDA graph of the call can be replayed.  Limits: world <= 8, d % 8 == 0.
  * ------------------------------------------------------------------------- */
@@ -292,6 +298,12 @@ typedef struct {
   void* xbuf[8];
   int64_t rows;
   int32_t world, rank, d, dtype;
+  /* Alternative input (stage_o = NULL): the unmerged split-KV partials a bsa_decode call with
+   * o = NULL left in its workspace, fp32 (rows, nsplit, d) and (rows, nsplit).  The kernel merges
+   * the splits itself, which saves the split-merge launch; it may then be enqueued right behind
+   * that bsa_decode call on the same stream (it is launched as its programmatic dependent). */
+  const float* part_o; const float* part_lse;
+  int32_t nsplit;
 } bsa_xchg_params;
 
 size_t bsa_xchg_buffer_bytes(int32_t world, int64_t rows, int32_t d);

@@ -125,12 +125,13 @@ def test_a_recorded_wait_failure_raises_on_the_next_call():
 
 
 def test_exchange_buffer_geometry_and_validation_need_no_device():
-    """bsa_xchg_buffer_bytes: two parities x world slots of (rows, d) 16-bit rows and fp32 LSEs,
-    flag words and a control block, every region 256-byte aligned; bad geometry gives 0 / BADARG."""
+    """bsa_xchg_buffer_bytes: two parities x world slots of (rows, d) 16-bit rows and fp32 LSEs, every
+    4 payload bytes paired with a 4-byte step word, plus a control block; 256-byte aligned regions;
+    bad geometry gives 0 / BADARG."""
     from dkernel_b200 import _lib
     lib = _lib.lib()
     n = lib.bsa_xchg_buffer_bytes(8, 2048, 128)
-    assert n >= 2 * 8 * (2048 * 128 * 2 + 2048 * 4) and n % 256 == 0 and n < 10 << 20
+    assert n >= 2 * 8 * 2 * (2048 * 128 * 2 + 2048 * 4) and n % 256 == 0 and n < 20 << 20
     assert lib.bsa_xchg_buffer_bytes(2, 2048, 128) < n
     assert lib.bsa_xchg_buffer_bytes(9, 16, 128) == 0          # more ranks than one node has
     assert lib.bsa_xchg_buffer_bytes(2, 16, 12) == 0           # rows must be whole 16-byte chunks
