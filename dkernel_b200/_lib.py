@@ -13,7 +13,7 @@ import torch
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("BSA_B200_LIB") or os.path.join(_HERE, "libbsa_b200.so")
 
-BSA_F16, BSA_BF16, BSA_F32 = 0, 1, 2
+BSA_F16, BSA_BF16, BSA_F32, BSA_F8E4M3 = 0, 1, 2, 3
 IMPL_AUTO, IMPL_GENERIC, IMPL_SM100 = 0, 1, 2
 ROWS_BY_TILE, ROWS_BY_POSITION = 0, 1
 
@@ -62,7 +62,8 @@ class DecodeParams(C.Structure):
         + [(n, _i64) for n in ("crow_sh", "col_sh")]
         + [(n, _i32) for n in ("h_pat", "n_rows", "block_size", "heads_per_cta", "blocks_per_split",
                                "max_row_nnz", "dtype")]
-        + [("sm_scale", _f32), ("ws", _vp), ("k_blk_mod", _i32), ("k_blk_rem", _i32)]
+        + [("sm_scale", _f32), ("ws", _vp), ("k_blk_mod", _i32), ("k_blk_rem", _i32),
+           ("kv_dtype", _i32), ("k_scale", _f32), ("v_scale", _f32)]
     )
 
 

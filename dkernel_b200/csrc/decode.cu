@@ -17,6 +17,7 @@
 // first real token, the pattern row is (len - 1) / block_size, every real token
 // of an attended block is visible.
 #include <mutex>
+#include <type_traits>
 
 #include "ptx.cuh"
 
@@ -80,8 +81,8 @@ __device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t&
 
 struct DecodeSmem {
   // after the 1024-aligned stage ring
-  uint64_t full[kStages];
-  uint64_t empty[kStages];
+  uint64_t full[2 * kStages];   // the 8-bit K/V ring is twice as deep
+  uint64_t empty[2 * kStages];
   int n_units;              // stage-units of this CTA
   int unit_pos[kMaxUnits];  // first position of each stage-unit
   float wm[kConsumers][16];
@@ -94,18 +95,56 @@ __device__ __forceinline__ uint32_t tile_off(int tok, int chunk) {
   return (uint32_t)((chunk >> 3) * (kTok * 128) + tok * 128 + (((chunk & 7) ^ (tok & 7)) << 4));
 }
 
-template <typename T, int D>
-__global__ void __launch_bounds__(kDecThreads, kMinCtas)
+// Shared-memory geometry.  16-bit K/V: a stage holds a K and a V tile as the tensor cores read
+// them (D/64 sub-tiles of [64 tokens][128 bytes], 128-byte swizzled).  8-bit (e4m3) K/V: a stage
+// holds the two tiles as stored ([64 tokens][D bytes], half the bytes, so twice the stages keep
+// the same number of bytes in flight) and one extra pair of 16-bit tiles receives the converted
+// values; every consumer warp converts and then reads its own 16 token rows only.
+template <int D, bool FP8> struct DecGeo {
+  static constexpr int kStages = FP8 ? 2 * bsa::kStages : bsa::kStages;
+  static constexpr int kTileBytes = kTok * D * (FP8 ? 1 : 2);
+  static constexpr int kStageBytes = 2 * kTileBytes;
+  static constexpr int kTile16 = kTok * D * 2;
+  static constexpr int kConvBytes = FP8 ? 2 * kTile16 : 0;
+  static constexpr int kRing = kStages * kStageBytes;
+  static constexpr size_t kSmem = 1024 + kRing + kConvBytes + 16 * D * 2 + sizeof(DecodeSmem);
+};
+
+// eight e4m3 values (two 32-bit words) -> eight T values (one 16-byte chunk); exact
+template <typename T>
+__device__ __forceinline__ uint4 cvt_e4m3x8(uint32_t lo, uint32_t hi) {
+  uint32_t h[4];
+  asm("{\n\t.reg .b16 a, b;\n\tmov.b32 {a, b}, %2;\n\t"
+      "cvt.rn.f16x2.e4m3x2 %0, a;\n\tcvt.rn.f16x2.e4m3x2 %1, b;\n\t}"
+      : "=r"(h[0]), "=r"(h[1]) : "r"(lo));
+  asm("{\n\t.reg .b16 a, b;\n\tmov.b32 {a, b}, %2;\n\t"
+      "cvt.rn.f16x2.e4m3x2 %0, a;\n\tcvt.rn.f16x2.e4m3x2 %1, b;\n\t}"
+      : "=r"(h[2]), "=r"(h[3]) : "r"(hi));
+  if (sizeof(T) == 2 && std::is_same<T, __half>::value) return make_uint4(h[0], h[1], h[2], h[3]);
+  uint32_t o[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h[i]));
+    o[i] = MmaType<T>::pack(f.x, f.y);
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+template <typename T, int D, bool FP8>
+__global__ void __launch_bounds__(kDecThreads, FP8 ? 2 : kMinCtas)
 decode_kernel(const __grid_constant__ Tmap4 tmK, const __grid_constant__ Tmap4 tmV,
               bsa_decode_params p, int nsplit, int* wait_status) {
-  constexpr int kTileBytes = kTok * D * 2;
-  constexpr int kStageBytes = 2 * kTileBytes;
+  using Geo = DecGeo<D, FP8>;
+  constexpr int kStages = Geo::kStages;
+  constexpr int kTileBytes = Geo::kTileBytes;
+  constexpr int kStageBytes = Geo::kStageBytes;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
   uint8_t* ring = smem;
-  T* Qs = reinterpret_cast<T*>(smem + kStages * kStageBytes);  // [16][D]
-  DecodeSmem* sm = reinterpret_cast<DecodeSmem*>(smem + kStages * kStageBytes + 16 * D * 2);
+  uint8_t* conv = smem + Geo::kRing;                            // FP8: converted K tile, then V tile
+  T* Qs = reinterpret_cast<T*>(smem + Geo::kRing + Geo::kConvBytes);  // [16][D]
+  DecodeSmem* sm = reinterpret_cast<DecodeSmem*>(smem + Geo::kRing + Geo::kConvBytes + 16 * D * 2);
 
   // the merge kernel behind this one may be made resident as soon as every CTA got here
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -138,10 +177,15 @@ decode_kernel(const __grid_constant__ Tmap4 tmK, const __grid_constant__ Tmap4 t
     const int tok = mod == 1 ? ks + (upos - pos0) : ks + (upos / bs / mod) * bs + upos % bs;
     uint8_t* kdst = ring + s * kStageBytes;
     uint8_t* vdst = kdst + kTileBytes;
+    if (FP8) {   // one box of [64 tokens][D bytes] per tensor, as stored
+      tma_load_tile(kdst, &tmK, &sm->full[s], 0, tok, kvh, b);
+      tma_load_tile(vdst, &tmV, &sm->full[s], 0, tok, kvh, b);
+    } else {
 #pragma unroll
-    for (int c = 0; c < D / 64; ++c) {
-      tma_load_tile(kdst + c * (kTok * 128), &tmK, &sm->full[s], c * 64, tok, kvh, b);
-      tma_load_tile(vdst + c * (kTok * 128), &tmV, &sm->full[s], c * 64, tok, kvh, b);
+      for (int c = 0; c < D / 64; ++c) {
+        tma_load_tile(kdst + c * (kTok * 128), &tmK, &sm->full[s], c * 64, tok, kvh, b);
+        tma_load_tile(vdst + c * (kTok * 128), &tmV, &sm->full[s], c * 64, tok, kvh, b);
+      }
     }
   };
 
@@ -267,7 +311,8 @@ decode_kernel(const __grid_constant__ Tmap4 tmK, const __grid_constant__ Tmap4 t
       qa[kk][3] = q32[((g + 8) * D + kk * 16 + 8 + tq * 2) >> 1];
     }
     float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
-    const float scale2 = p.sm_scale * kLog2e;
+    // e4m3 K carries a per-tensor scale: it folds into the logit scale (V's goes on the output)
+    const float scale2 = p.sm_scale * kLog2e * (FP8 ? p.k_scale : 1.f);
     const uint32_t ring_u32 = smem_u32(ring);
     bool alive = true;
 
@@ -277,10 +322,33 @@ decode_kernel(const __grid_constant__ Tmap4 tmK, const __grid_constant__ Tmap4 t
       alive = mbar_wait(&sm->full[s], ph, wait_status, 102);
       if (!alive) break;
       const int pos_u = sm->unit_pos[u];
-      const uint32_t kbase = ring_u32 + s * kStageBytes;
-      const uint32_t vbase = kbase + kTileBytes;
+      const uint32_t kbase = FP8 ? smem_u32(conv) : ring_u32 + s * kStageBytes;
+      const uint32_t vbase = FP8 ? kbase + Geo::kTile16 : kbase + kTileBytes;
       const int valid = end_pos - pos_u;  // tokens of this unit that exist (may exceed 64)
-      if (valid < kTok) {
+      if (FP8) {
+        // this warp's 16 token rows of K and V: e4m3 as stored -> T in the swizzled tile layout
+        // the ldmatrix addressing below expects; V rows past the end of the sequence become zero.
+        // Two lanes share a row (D/2 bytes each).  The stage is free as soon as the rows are read.
+        const uint8_t* k8 = ring + s * kStageBytes;
+        const uint8_t* v8 = k8 + kTileBytes;
+        const int tok = warp * 16 + (lane >> 1);
+        const bool v_ok = tok < valid;
+#pragma unroll
+        for (int i = 0; i < D / 32; ++i) {
+          const int piece = (lane & 1) * (D / 32) + i;           // 16 stored bytes = two 16-byte chunks of T
+          const uint4 kk8 = *reinterpret_cast<const uint4*>(k8 + tok * D + piece * 16);
+          const uint4 vv8 = *reinterpret_cast<const uint4*>(v8 + tok * D + piece * 16);
+          *reinterpret_cast<uint4*>(conv + tile_off(tok, 2 * piece)) = cvt_e4m3x8<T>(kk8.x, kk8.y);
+          *reinterpret_cast<uint4*>(conv + tile_off(tok, 2 * piece + 1)) = cvt_e4m3x8<T>(kk8.z, kk8.w);
+          const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+          *reinterpret_cast<uint4*>(conv + Geo::kTile16 + tile_off(tok, 2 * piece)) =
+              v_ok ? cvt_e4m3x8<T>(vv8.x, vv8.y) : z;
+          *reinterpret_cast<uint4*>(conv + Geo::kTile16 + tile_off(tok, 2 * piece + 1)) =
+              v_ok ? cvt_e4m3x8<T>(vv8.z, vv8.w) : z;
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm->empty[s]);
+      } else if (valid < kTok) {
         // rows past the end of the sequence may hold anything: clear them in V so
         // that 0 * garbage cannot produce NaN
         uint8_t* vgen = ring + s * kStageBytes + kTileBytes;
@@ -359,8 +427,8 @@ decode_kernel(const __grid_constant__ Tmap4 tmK, const __grid_constant__ Tmap4 t
         MmaType<T>::mma(oacc[2 * dn], pa, r0, r1);
         MmaType<T>::mma(oacc[2 * dn + 1], pa, r2, r3);
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&sm->empty[s]);
+      __syncwarp();   // (8-bit K/V: also orders this unit's reads before the next conversion)
+      if (!FP8 && lane == 0) mbar_arrive(&sm->empty[s]);
     }
     // quad-reduce the row sums
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
@@ -400,7 +468,7 @@ decode_kernel(const __grid_constant__ Tmap4 tmK, const __grid_constant__ Tmap4 t
       acc += Om[(w * 16 + r) * D + d] * sc;
       l += sm->wl[w][r] * sc;
     }
-    const float inv = l > 0.f ? 1.f / l : 0.f;
+    const float inv = (l > 0.f ? 1.f / l : 0.f) * (FP8 ? p.v_scale : 1.f);   // e4m3 V: per-tensor scale
     const float lse = l > 0.f ? (mf + log2f(l)) * kLn2 : -INFINITY;
     const int h = h0 + r;
     if (final_out) {
@@ -507,19 +575,21 @@ int decode_nsplit(const bsa_decode_params* p) {
   return n < 1 ? 1 : n;
 }
 
-template <typename T, int D>
+template <typename T, int D, bool FP8>
 int launch_decode(const bsa_decode_params* p, cudaStream_t s) {
   Tmap4 tmK, tmV;
   const bool bf16 = p->dtype == BSA_BF16;
-  int rc = make_tmap_4d(&tmK, p->k, 2, D, p->sk, p->hkv, p->batch, p->k_ss * 2, p->k_sh * 2,
-                        p->k_sb * 2, 64, kTok, true, bf16);
+  const int eb = FP8 ? 1 : 2;
+  const uint32_t box_d = FP8 ? D : 64;    // 8-bit tiles are copied as stored, 16-bit ones 128-byte swizzled
+  int rc = make_tmap_4d(&tmK, p->k, eb, D, p->sk, p->hkv, p->batch, p->k_ss * eb, p->k_sh * eb,
+                        p->k_sb * eb, box_d, kTok, !FP8, bf16);
   if (rc) return rc;
-  rc = make_tmap_4d(&tmV, p->v, 2, D, p->sk, p->hkv, p->batch, p->v_ss * 2, p->v_sh * 2,
-                    p->v_sb * 2, 64, kTok, true, bf16);
+  rc = make_tmap_4d(&tmV, p->v, eb, D, p->sk, p->hkv, p->batch, p->v_ss * eb, p->v_sh * eb,
+                    p->v_sb * eb, box_d, kTok, !FP8, bf16);
   if (rc) return rc;
   const int nsplit = decode_nsplit(p);
-  const size_t smem = 1024 + kStages * 2 * kTok * D * 2 + 16 * D * 2 + sizeof(DecodeSmem);
-  auto kern = decode_kernel<T, D>;
+  const size_t smem = DecGeo<D, FP8>::kSmem;
+  auto kern = decode_kernel<T, D, FP8>;
   BSA_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const int G = p->hq / p->hkv;
   dim3 grid(nsplit, p->hkv * (G / p->heads_per_cta), p->batch);
@@ -574,8 +644,11 @@ int decode_run(const bsa_decode_params* p, cudaStream_t s) {
               "(got dtype %d, d %d, block %d)", p->dtype, p->d, p->block_size);
     return BSA_E_UNSUPPORTED;
   }
-  if (!tma_compatible(p->k, 2, p->k_ss, p->k_sh, p->k_sb) ||
-      !tma_compatible(p->v, 2, p->v_ss, p->v_sh, p->v_sb)) {
+  const bool fp8 = p->kv_dtype == BSA_F8E4M3;
+  BSA_CHECK_ARG(p->kv_dtype == 0 || fp8, "bsa_decode: kv_dtype must be 0 (as q) or BSA_F8E4M3, got %d", p->kv_dtype);
+  BSA_CHECK_ARG(!fp8 || (p->k_scale > 0.f && p->v_scale > 0.f), "bsa_decode: e4m3 K/V need positive k_scale and v_scale");
+  if (!tma_compatible(p->k, fp8 ? 1 : 2, p->k_ss, p->k_sh, p->k_sb) ||
+      !tma_compatible(p->v, fp8 ? 1 : 2, p->v_ss, p->v_sh, p->v_sb)) {
     set_error("bsa_decode: K/V need a 16-byte aligned base and strides that are multiples of 16 bytes");
     return BSA_E_UNSUPPORTED;
   }
@@ -587,9 +660,14 @@ int decode_run(const bsa_decode_params* p, cudaStream_t s) {
   }
   const int nsplit = decode_nsplit(p);
   BSA_CHECK_ARG((nsplit == 1 && p->o) || p->ws, "bsa_decode: workspace required for %d splits", nsplit);
+  if (fp8) {
+    if (p->dtype == BSA_BF16)
+      return p->d == 128 ? launch_decode<__nv_bfloat16, 128, true>(p, s) : launch_decode<__nv_bfloat16, 64, true>(p, s);
+    return p->d == 128 ? launch_decode<__half, 128, true>(p, s) : launch_decode<__half, 64, true>(p, s);
+  }
   if (p->dtype == BSA_BF16)
-    return p->d == 128 ? launch_decode<__nv_bfloat16, 128>(p, s) : launch_decode<__nv_bfloat16, 64>(p, s);
-  return p->d == 128 ? launch_decode<__half, 128>(p, s) : launch_decode<__half, 64>(p, s);
+    return p->d == 128 ? launch_decode<__nv_bfloat16, 128, false>(p, s) : launch_decode<__nv_bfloat16, 64, false>(p, s);
+  return p->d == 128 ? launch_decode<__half, 128, false>(p, s) : launch_decode<__half, 64, false>(p, s);
 }
 
 int merge_partials(const void* o_parts, const float* lse_parts, int P, int64_t rows, int d,

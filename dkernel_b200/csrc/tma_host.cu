@@ -91,9 +91,10 @@ int make_tmap_4d(Tmap4* out, const void* base, int elem_bytes, uint64_t d, uint6
     if (dims3[i].logical == 1) out->head_pos = i + 1;
     if (dims3[i].logical == 2) out->batch_pos = i + 1;
   }
-  CUtensorMapDataType dt = elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
-                           : is_bf16       ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                           : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUtensorMapDataType dt = elem_bytes == 4   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                           : elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                           : is_bf16         ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                             : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   CUresult r = enc(&out->map, dt, 4, const_cast<void*>(base), gdim, gstr, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE,
                    swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,

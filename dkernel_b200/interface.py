@@ -148,11 +148,17 @@ class SparseAttention(torch.nn.Module):
                 seqlens: Optional[Tensor] = None,
                 return_lse: bool = False,
                 split_qkv: Optional[callable] = None,
+                kv_scales: Optional[Tuple[float, float]] = None,
                 ) -> Tensor:
+        """As the reference's forward.  One extension (its README lists it as future work): a decode
+        call (one query token per sequence) may pass ``k`` and ``v`` as ``torch.float8_e4m3fn``
+        tensors together with ``kv_scales = (k_scale, v_scale)``; they stand for ``k * k_scale``
+        and ``v * v_scale``, and the kernel reads half the bytes."""
         inf_kwargs = {"cu_seqlen_k": cu_seqlen_k,
                       "cu_seqlen_q": cu_seqlen_q,
                       "left_paddings": left_paddings,
-                      "seqlens": seqlens}
+                      "seqlens": seqlens,
+                      "kv_scales": kv_scales}
         kwargs = copy.copy(self.kwargs)
         kwargs["return_lse"] = return_lse
         kwargs["split_qkv"] = split_qkv

@@ -28,9 +28,10 @@ def _tma_friendly(t: Tensor) -> Tensor:
     """Tensor-map requirements of the tcgen05 / decode kernels: 16-byte aligned
     base and strides that are multiples of 16 bytes.  Anything else is copied."""
     t = _last_dim_contig(t)
-    if t.element_size() != 2:
+    if t.element_size() > 2:
         return t
-    ok = t.data_ptr() % 16 == 0 and all(s % 8 == 0 for s in t.stride()[:-1])
+    per16 = 16 // t.element_size()
+    ok = t.data_ptr() % 16 == 0 and all(s % per16 == 0 for s in t.stride()[:-1])
     return t if ok else t.contiguous()
 
 
@@ -215,16 +216,33 @@ def _launch_fwd(p, q: Tensor) -> None:
         _lib.check(lib.bsa_fwd(C.byref(p), _lib.stream_of(q)), "bsa_fwd")
 
 
+_FP8 = getattr(torch, "float8_e4m3fn", None)
+
+
 def _check_inputs(q: Tensor, k: Tensor, v: Tensor) -> None:
     for n, t in (("q", q), ("k", k), ("v", v)):
         _lib.require_cuda(t, n)
-    assert q.dtype == k.dtype == v.dtype, f"q/k/v dtypes differ: {q.dtype}, {k.dtype}, {v.dtype}"
+    if _FP8 is not None and k.dtype == _FP8 and v.dtype == _FP8:
+        assert q.dtype in (torch.float16, torch.bfloat16), "an e4m3 K/V cache needs f16/bf16 queries"
+    else:
+        assert q.dtype == k.dtype == v.dtype, f"q/k/v dtypes differ: {q.dtype}, {k.dtype}, {v.dtype}"
     assert q.device == k.device == v.device
     _lib.dtype_code(q.dtype)
 
 
 _IMPL_NAMES = {None: _lib.IMPL_AUTO, "auto": _lib.IMPL_AUTO, "generic": _lib.IMPL_GENERIC,
                "sm100": _lib.IMPL_SM100}
+
+
+def _fp8_kv_scales(q: Tensor, k: Tensor, kv_scales) -> Optional[Tuple[float, float]]:
+    """The (k_scale, v_scale) of an e4m3 K/V cache, or None for K/V of q's type.  Only the decode
+    kernel reads 8-bit K/V: a single query token per sequence on 64/128-wide heads."""
+    if _FP8 is None or k.dtype != _FP8:
+        assert kv_scales is None, "kv_scales only applies to float8_e4m3fn K/V"
+        return None
+    assert kv_scales is not None and len(kv_scales) == 2, \
+        "float8_e4m3fn K/V need kv_scales=(k_scale, v_scale)"
+    return float(kv_scales[0]), float(kv_scales[1])
 
 
 def _decode_eligible(q: Tensor, plan: _Plan, impl: int) -> bool:
@@ -244,8 +262,8 @@ def decode(q: Tensor, k: Tensor, v: Tensor, plan: _Plan, sm_scale: float, *, seq
            k_pos0: Optional[Tensor] = None, k_total: Optional[Tensor] = None,
            out: Optional[Tensor] = None, blocks_per_split: int = 0,
            workspace: Optional[Tensor] = None, lse_out: Optional[Tensor] = None,
-           k_blk: Optional[Tuple[int, int]] = None, partials_only: bool = False
-           ) -> Tuple[Tensor, Tensor]:
+           k_blk: Optional[Tuple[int, int]] = None, partials_only: bool = False,
+           kv_scales: Optional[Tuple[float, float]] = None) -> Tuple[Tensor, Tensor]:
     """One query token per sequence (split-KV decode kernel).
 
     q: (B,1,Hq,D)/(B,Hq,1,D) or packed (B,Hq,D); k, v: 4-D with the module's
@@ -308,6 +326,9 @@ def decode(q: Tensor, k: Tensor, v: Tensor, plan: _Plan, sm_scale: float, *, seq
         p.max_row_nnz = plan.max_row_nnz_cyclic(*k_blk)
     p.dtype = _lib.dtype_code(q.dtype)
     p.sm_scale = float(sm_scale)
+    if kv_scales is not None:       # e4m3 K/V cache
+        assert k.dtype == _FP8 and v.dtype == _FP8
+        p.kv_dtype, p.k_scale, p.v_scale = _lib.BSA_F8E4M3, float(kv_scales[0]), float(kv_scales[1])
     need = lib.bsa_decode_workspace_bytes(C.byref(p))
     ws = None
     if need:
@@ -328,7 +349,8 @@ def decode(q: Tensor, k: Tensor, v: Tensor, plan: _Plan, sm_scale: float, *, seq
 
 
 # --------------------------------------------------------------------------- routes
-def _varlen(q, k, v, cu_seqlens_k, cu_seqlens_q, sm_scale, plan, causal, out, impl, return_lse):
+def _varlen(q, k, v, cu_seqlens_k, cu_seqlens_q, sm_scale, plan, causal, out, impl, return_lse,
+            kv_scales=None):
     """Packed variable-length batch (dkernel/ops/sparse_attn_inference.py:150-287).
     Unlike the reference nothing is copied to the host: the kernels read the
     cu_seqlens on the device and enumerate q tiles themselves."""
@@ -350,10 +372,12 @@ def _varlen(q, k, v, cu_seqlens_k, cu_seqlens_q, sm_scale, plan, causal, out, im
     else:
         assert cu_seqlens_k.size(0) == cu_seqlens_q.size(0)
         cu_q = cu_seqlens_q.to(device=q.device, dtype=torch.int32).contiguous()
+    fp8 = _fp8_kv_scales(q, k, kv_scales)
     if decoding and _decode_eligible(q, plan, impl):
         o, lse = decode(q, k, v, plan, sm_scale, seq_dim=None, k_start=cu_k[:-1], k_end=cu_k[1:],
-                        out=out)
+                        out=out, kv_scales=fp8)
         return o, (lse.transpose(0, 1) if return_lse else None)
+    assert fp8 is None, "an e4m3 K/V cache is only read by the decode kernel (one query token per sequence)"
     if decoding:
         cu_q = torch.arange(0, batch + 1, dtype=torch.int32, device=q.device)
     q, k, v = _tma_friendly(q), _tma_friendly(k), _tma_friendly(v)
@@ -367,7 +391,7 @@ def _varlen(q, k, v, cu_seqlens_k, cu_seqlens_q, sm_scale, plan, causal, out, im
 
 
 def _padded(q, k, v, sm_scale, plan, left_paddings, seqlens, seq_dim, max_seqlen, causal, out,
-            impl, return_lse):
+            impl, return_lse, kv_scales=None):
     """Left/right padded batch (dkernel/ops/sparse_attn_inference.py:10-147): pad
     rows of the output are zero, positions are re-based to the first real token."""
     assert seq_dim in (1, 2)
@@ -393,9 +417,12 @@ def _padded(q, k, v, sm_scale, plan, left_paddings, seqlens, seq_dim, max_seqlen
         k_ends = k_starts + seqlens.to(dev, dtype=torch.int32)
     else:
         k_ends = None   # every sequence ends at k_len
+    fp8 = _fp8_kv_scales(q, k, kv_scales)
     if q_len == 1 and _decode_eligible(q, plan, impl):
-        o, lse = decode(q, k, v, plan, sm_scale, seq_dim=seq_dim, k_start=k_starts, k_end=k_ends, out=out)
+        o, lse = decode(q, k, v, plan, sm_scale, seq_dim=seq_dim, k_start=k_starts, k_end=k_ends, out=out,
+                        kv_scales=fp8)
         return o, (lse.unsqueeze(-1) if return_lse else None)
+    assert fp8 is None, "an e4m3 K/V cache is only read by the decode kernel (one query token per sequence)"
     if k_ends is None:
         k_ends = torch.full_like(k_starts, k_len)
     if q_len == 1:
@@ -413,7 +440,8 @@ def _padded(q, k, v, sm_scale, plan, left_paddings, seqlens, seq_dim, max_seqlen
     return o, lse
 
 
-def _train_forward(ctx, q, k, v, sm_scale, plan, seq_dim, causal, out, impl, need_lse, inference):
+def _train_forward(ctx, q, k, v, sm_scale, plan, seq_dim, causal, out, impl, need_lse, inference,
+                   kv_scales=None):
     """Un-padded forward (dkernel/ops/sparse_attn_fwd.py:383-567).  Pattern rows are
     q tile indices; a single query token uses the row of the last key block
     (:435-440)."""
@@ -425,9 +453,11 @@ def _train_forward(ctx, q, k, v, sm_scale, plan, seq_dim, causal, out, impl, nee
     hq, hkv = q.size(hdim), k.size(hdim)
     assert hq % hkv == 0
     dev = q.device
+    fp8 = _fp8_kv_scales(q, k, kv_scales)
     if qlen == 1 and klen > 1 and inference and _decode_eligible(q, plan, impl):
-        o, lse = decode(q, k, v, plan, sm_scale, seq_dim=seq_dim, out=out)
+        o, lse = decode(q, k, v, plan, sm_scale, seq_dim=seq_dim, out=out, kv_scales=fp8)
         return o, lse.unsqueeze(-1)
+    assert fp8 is None, "an e4m3 K/V cache is only read by the decode kernel (one query token per sequence)"
     # A single query token against a longer key sequence takes its pattern row from the key
     # position; the backward kernels index rows by q tile, so that case has no backward.
     assert inference or qlen > 1 or klen == 1, \
@@ -533,7 +563,8 @@ class _sparse_attention(torch.autograd.Function):
             ctx.support_backward = False
             ctx.message = "Currently does not suppoort variable length inputs. WIP."
             output, lse = _varlen(q, k, v, inf_kwargs["cu_seqlen_k"], inf_kwargs.get("cu_seqlen_q", None),
-                                  sm_scale, plan, causal, out, impl, return_lse)
+                                  sm_scale, plan, causal, out, impl, return_lse,
+                                  kv_scales=inf_kwargs.get("kv_scales"))
         else:
             assert k.size(seq_dim) <= max_seqlen, \
                 (f"Input length {k.size(seq_dim)} is larger "
@@ -544,7 +575,8 @@ class _sparse_attention(torch.autograd.Function):
                 ctx.support_backward = False
                 ctx.message = "Currently does not support paddings in inputs. WIP."
                 output, lse = _padded(q, k, v, sm_scale, plan, left_paddings, seqlens, seq_dim,
-                                      max_seqlen, causal, out, impl, return_lse)
+                                      max_seqlen, causal, out, impl, return_lse,
+                                      kv_scales=inf_kwargs.get("kv_scales"))
             else:
                 inference = kwargs.get("inference", None)
                 if inference is None:
@@ -553,7 +585,8 @@ class _sparse_attention(torch.autograd.Function):
                 ctx.support_backward = not inference
                 ctx.message = "the forward pass ran with inference=True: nothing was saved for backward"
                 output, lse = _train_forward(ctx, q, k, v, sm_scale, plan, seq_dim, causal, out, impl,
-                                             need_lse=return_lse or not inference, inference=inference)
+                                             need_lse=return_lse or not inference, inference=inference,
+                                             kv_scales=inf_kwargs.get("kv_scales"))
         if not return_lse:
             lse = None
         if lse is not None and not ctx.support_backward:

@@ -38,7 +38,7 @@ enum {
   BSA_E_TOOBIG = -4       /* problem exceeds a documented fixed limit           */
 };
 
-enum { BSA_F16 = 0, BSA_BF16 = 1, BSA_F32 = 2 };
+enum { BSA_F16 = 0, BSA_BF16 = 1, BSA_F32 = 2, BSA_F8E4M3 = 3 /* K/V storage of bsa_decode only */ };
 
 /* which kernel family serves a call */
 enum { BSA_IMPL_AUTO = 0, BSA_IMPL_GENERIC = 1, BSA_IMPL_SM100 = 2 };
@@ -223,6 +223,13 @@ typedef struct {
    * to back (block c is local block c / W; k_pos0 is ignored).  A local window of
    * consecutive blocks then spreads evenly over the W shards.  0 or 1 = off.   */
   int32_t k_blk_mod, k_blk_rem;
+  /* 8-bit K/V cache (the reference lists "FP8 K/V" as future work, README.md:245-247):
+   * kv_dtype = BSA_F8E4M3 makes k and v e4m3 tensors (strides in 1-byte elements) that
+   * stand for k * k_scale and v * v_scale (per-tensor scales); q, o and the arithmetic
+   * stay in `dtype`.  The kernel converts the stored bytes exactly, so the result equals
+   * attention over the de-quantised cache.  0 = K/V have q's type.                     */
+  int32_t kv_dtype;
+  float k_scale, v_scale;
 } bsa_decode_params;
 
 size_t bsa_decode_workspace_bytes(const bsa_decode_params* p);

@@ -72,6 +72,7 @@ def test_decode_split_choice_needs_no_device():
     p = _lib.DecodeParams()
     p.batch, p.hq, p.hkv, p.d, p.sk = 64, 32, 8, 128, 8192
     p.block_size, p.heads_per_cta, p.max_row_nnz = 64, 4, 30
+    p.o = 16                                   # an output tensor is given (NULL = leave the partials unmerged)
 
     def splits():
         return lib.bsa_decode_workspace_bytes(C.byref(p)) // (4 * p.batch * p.hq * (p.d + 1))
@@ -86,6 +87,8 @@ def test_decode_split_choice_needs_no_device():
     assert lib.bsa_decode_workspace_bytes(C.byref(p)) // (4 * p.batch * p.hq * (p.d + 1)) == 2
     p.max_row_nnz = 12
     assert lib.bsa_decode_workspace_bytes(C.byref(p)) == 0   # one split: no workspace
+    p.o = 0                                    # partials only: even one split goes to the workspace
+    assert lib.bsa_decode_workspace_bytes(C.byref(p)) == 4 * p.batch * p.hq * (p.d + 1)
 
 
 def test_zeroed_decode_params_are_rejected_not_divided_by():

@@ -220,6 +220,59 @@ def test_block_cyclic_kv_shards_merge_to_whole(W):
     assert _lib.wait_status() == 0
 
 
+@pytest.mark.parametrize("D,dtype", [(128, torch.bfloat16), (64, torch.bfloat16), (128, torch.float16)])
+def test_decode_reads_an_e4m3_kv_cache(D, dtype):
+    """K/V stored as float8_e4m3fn with per-tensor scales: the decode kernel converts the stored
+    bytes exactly, so the result must equal the oracle on the de-quantised cache -- left padding,
+    right padding, the split-KV path (long rows) and a packed batch."""
+    from dkernel_b200 import SparseAttention
+    B, Hq, Hkv, S, bs = 5, 8, 2, 2048, 64
+    pk = dict(block_size=bs, local_blocks=6, vert_stride=4, num_kv_heads=Hkv)
+    q, k, v = seeded_qkv(61, (B, 1, Hq, D), (B, S, Hkv, D), dtype)
+    ks, vs = float(k.float().abs().max()) / 448.0, float(v.float().abs().max()) / 448.0
+    k8 = (k.float() / ks).to(torch.float8_e4m3fn)
+    v8 = (v.float() / vs).to(torch.float8_e4m3fn)
+    kd, vd = k8.float() * ks, v8.float() * vs                  # what the cache stands for
+    bm = O.block_mask(Hq, S, **pk)
+    mod = _module(Hq, S, pk, seq_dim=1)
+    lens = torch.tensor([2048, 700, 65, 1, 1300])
+    left = S - lens
+    ref, ref_lse = O.decode_attention(q.float(), kd, vd, bm, bs, left_paddings=left)
+    with torch.no_grad():
+        out, lse = mod(q.cuda(), k8.cuda(), v8.cuda(), left_paddings=left.cuda(), return_lse=True,
+                       kv_scales=(ks, vs))
+    assert_out_close(out, ref)
+    assert_lse_close(lse, ref_lse)
+    # right padding: whatever follows the sequence in the cache is ignored (0xff bytes are NaN in e4m3)
+    k8r, v8r = k8.clone(), v8.clone()
+    for b in range(B):
+        k8r[b, int(lens[b]):].view(torch.uint8).fill_(0xff)
+        v8r[b, int(lens[b]):].view(torch.uint8).fill_(0xff)
+    ref, ref_lse = O.decode_attention(q.float(), kd, vd, bm, bs, seqlens=lens)
+    with torch.no_grad():
+        out, lse = mod(q.cuda(), k8r.cuda(), v8r.cuda(), seqlens=lens.cuda(), return_lse=True, kv_scales=(ks, vs))
+    assert_out_close(out, ref)
+    assert_lse_close(lse, ref_lse)
+    # packed batch, one query token per sequence
+    lens2 = [300, 64, 1, 999]
+    cu = torch.tensor([0] + list(np.cumsum(lens2)), dtype=torch.int32)
+    T = int(cu[-1])
+    kp, vp = seeded_qkv(62, (T, Hkv, D), (T, Hkv, D), dtype)[:2]
+    kp8, vp8 = (kp.float() / ks).to(torch.float8_e4m3fn), (vp.float() / vs).to(torch.float8_e4m3fn)
+    qp = q[:4, 0]
+    refp, _ = O.varlen_attention(qp.float(), kp8.float() * ks, vp8.float() * vs, cu, bm, bs)
+    with torch.no_grad():
+        outp = mod(qp.cuda(), kp8.cuda(), vp8.cuda(), cu_seqlen_k=cu.cuda(), kv_scales=(ks, vs))
+    assert_out_close(outp, refp)
+    # an 8-bit cache without scales, or on a prefill call, is refused before any launch
+    with pytest.raises(AssertionError):
+        mod(q.cuda(), k8.cuda(), v8.cuda(), left_paddings=left.cuda())
+    with pytest.raises(AssertionError):
+        mod(q.expand(B, 1, Hq, D).repeat(1, S, 1, 1).cuda(), k8.cuda(), v8.cuda(), kv_scales=(ks, vs))
+    from dkernel_b200 import _lib
+    assert _lib.wait_status() == 0
+
+
 def test_sharded_decode_single_rank_group(tmp_path):
     """sharded_decode end to end (packed (O, LSE) rows -> all-gather -> fused merge) with a
     one-rank NCCL group: the whole sequence is the only shard."""
