@@ -30,7 +30,6 @@
 namespace bsa {
 namespace {
 
-constexpr int kD = 128;
 constexpr int kBS = 64;
 constexpr int kDqEwWarps = 16;        // dQ kernel: 16 element-wise warps, producer, two issuers
 constexpr int kBwdThreads = 32 * (kDqEwWarps + 3);
@@ -65,8 +64,8 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 // dK/dV kernel copy a block's 64 values with one bulk copy.
 __host__ __device__ inline int padded_sq(int sq) { return (sq + kBS - 1) / kBS * kBS; }
 
-// Eight lanes per (b, h, i) row of 128 elements (four rows per warp): a lane reads two
-// 16-byte pieces of O and of dO, so that every thread has four independent loads in flight.
+// Eight lanes per (b, h, i) row of D elements (four rows per warp): a lane reads D/64
+// 16-byte pieces of O and of dO, so that every thread has several independent loads in flight.
 template <bool BF16>
 __device__ __forceinline__ float dot8(const uint4& a, const uint4& g) {
   float s = 0.f;
@@ -91,7 +90,7 @@ __device__ __forceinline__ uint4 load16(const uint8_t* p, bool wide) {
   return make_uint4(a.x, a.y, b.x, b.y);
 }
 
-template <bool BF16>
+template <bool BF16, int D>
 __global__ void bwd_delta_vec_kernel(bsa_bwd_params bp) {
   const bsa_fwd_params& p = bp.f;
   const int lane = threadIdx.x & 31, sub = lane & 7;
@@ -112,9 +111,14 @@ __global__ void bwd_delta_vec_kernel(bsa_bwd_params bp) {
                         ((int64_t)b * p.o_sb + (int64_t)h * p.o_sh + (int64_t)i * p.o_ss) * 2 + sub * 16;
     const uint8_t* gp = reinterpret_cast<const uint8_t*>(bp.d_o) +
                         ((int64_t)b * bp.do_sb + (int64_t)h * bp.do_sh + (int64_t)i * bp.do_ss) * 2 + sub * 16;
-    const uint4 o0 = load16(op, wide), o1 = load16(op + 128, wide);
-    const uint4 g0 = load16(gp, wide), g1 = load16(gp + 128, wide);
-    s = dot8<BF16>(o0, g0) + dot8<BF16>(o1, g1);
+    uint4 ov[D / 64], gv[D / 64];
+#pragma unroll
+    for (int j = 0; j < D / 64; ++j) {
+      ov[j] = load16(op + j * 128, wide);
+      gv[j] = load16(gp + j * 128, wide);
+    }
+#pragma unroll
+    for (int j = 0; j < D / 64; ++j) s += dot8<BF16>(ov[j], gv[j]);
   }
 #pragma unroll
   for (int off = 4; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
@@ -167,8 +171,12 @@ __device__ __forceinline__ void append_union(const uint32_t* bits0, const uint32
 
 // ------------------------------------------------------------------ dK / dV
 constexpr int kQdoStages = 4;
-constexpr int kKVResident = 2 * 128 * kD * 2;      // K and V tiles, 32 KB each
-constexpr int kQdoStageBytes = 2 * kBS * kD * 2;   // Q_r and dO_r, 16 KB each
+template <int D> struct DkdvGeo {
+  static constexpr int kSub = D / 64;                    // 64-dim sub-tiles of [rows][128 bytes]
+  static constexpr int kKVResident = 2 * 128 * D * 2;    // K and V tiles (128 kv rows each)
+  static constexpr int kQdoTile = kBS * D * 2;           // one Q_r or dO_r tile
+  static constexpr int kQdoStageBytes = 2 * kQdoTile;
+};
 
 struct DkdvTail {
   uint64_t kv_full;
@@ -182,9 +190,11 @@ struct DkdvTail {
   uint32_t bits[2][kMaxBlocks / 32];
   uint32_t list[kMaxEntries];
 };
-constexpr size_t kDkdvSmem = 1024 + kKVResident + kQdoStages * kQdoStageBytes + sizeof(DkdvTail);
+template <int D> constexpr size_t dkdv_smem() {
+  return 1024 + DkdvGeo<D>::kKVResident + kQdoStages * DkdvGeo<D>::kQdoStageBytes + sizeof(DkdvTail);
+}
 
-template <bool BF16>
+template <bool BF16, int D>
 __global__ void __launch_bounds__(kDkdvThreads, 1)
 bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap4 tmK,
                       const __grid_constant__ Tmap4 tmV, const __grid_constant__ Tmap4 tmDO,
@@ -193,9 +203,11 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
-  uint8_t* sK = smem;                    // [2 subtiles][128 rows][128 B]
-  uint8_t* sV = smem + 128 * kD * 2;
-  uint8_t* sQdo = smem + kKVResident;    // stage s: Q_r at s*32K, dO_r at s*32K + 16K
+  constexpr int kSub = DkdvGeo<D>::kSub, kKVResident = DkdvGeo<D>::kKVResident;
+  constexpr int kQdoTile = DkdvGeo<D>::kQdoTile, kQdoStageBytes = DkdvGeo<D>::kQdoStageBytes;
+  uint8_t* sK = smem;                    // [kSub subtiles][128 rows][128 B]
+  uint8_t* sV = smem + 128 * D * 2;
+  uint8_t* sQdo = smem + kKVResident;    // stage s: Q_r, then dO_r
   DkdvTail* tl = reinterpret_cast<DkdvTail*>(smem + kKVResident + kQdoStages * kQdoStageBytes);
 
   // The dQ kernel is launched behind this one as a programmatic dependent and reads nothing
@@ -242,10 +254,10 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
   __syncthreads();
   // resident K / V tiles and the TMEM allocation overlap the list construction
   if (warp == kDkdvProducer && lane == 0) {
-    mbar_expect_tx(&tl->kv_full, (uint32_t)(kvalid[0] + kvalid[1]) * 2 * (kBS * kD * 2));
+    mbar_expect_tx(&tl->kv_full, (uint32_t)(kvalid[0] + kvalid[1]) * 2 * (kBS * D * 2));
     for (int t = 0; t < 2; ++t) {
       if (!kvalid[t]) continue;
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < kSub; ++c) {
         tma_load_tile(sK + c * 16384 + t * 8192, &tmK, &tl->kv_full, c * 64, kblk[t] * kBS, hk, b);
         tma_load_tile(sV + c * 16384 + t * 8192, &tmV, &tl->kv_full, c * 64, kblk[t] * kBS, hk, b);
       }
@@ -287,7 +299,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
   const uint32_t tmem = tl->tmem_base;
   const uint32_t tST[2] = {tmem, tmem + 64};
   const uint32_t tDP[2] = {tmem + 128, tmem + 192};
-  const uint32_t tDV = tmem + 256, tDK = tmem + 384;
+  const uint32_t tDV = tmem + 256, tDK = tmem + 256 + D;
 
   if (n > 0 && warp == kDkdvProducer) {
     // ------------------------------------------------------------ TMA producer
@@ -299,8 +311,8 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
         if (!mbar_wait(&tl->qdo_empty[s], ((e / kQdoStages) & 1) ^ 1, wait_status, 301)) break;
         mbar_expect_tx(&tl->qdo_full[s], kQdoStageBytes + 2 * kBS * 4);
         uint8_t* qd = sQdo + s * kQdoStageBytes;
-        uint8_t* gd = qd + kBS * kD * 2;
-        for (int c = 0; c < 2; ++c) {
+        uint8_t* gd = qd + kQdoTile;
+        for (int c = 0; c < kSub; ++c) {
           tma_load_tile(qd + c * 8192, &tmQ, &tl->qdo_full[s], c * 64, r * kBS, h, b);
           tma_load_tile(gd + c * 8192, &tmDO, &tl->qdo_full[s], c * 64, r * kBS, h, b);
         }
@@ -325,13 +337,13 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
     {
       const int path = warp - kDkdvIssuer;
       const uint32_t idesc_nt = umma_idesc(BF16, 128, kBS, false, false);
-      const uint32_t idesc_acc = umma_idesc(BF16, 128, kD, false, true);
+      const uint32_t idesc_acc = umma_idesc(BF16, 128, D, false, true);
       // first stage: A = resident K (path 0) or V (path 1); B = Q_e or dO_e, K-major
       const uint64_t adesc = umma_desc_sw128(smem_u32(path ? sV : sK), 16, 1024);
-      const uint64_t bdesc0 = umma_desc_sw128(smem_u32(sQdo) + (path ? kBS * kD * 2 : 0), 16, 1024);
+      const uint64_t bdesc0 = umma_desc_sw128(smem_u32(sQdo) + (path ? kQdoTile : 0), 16, 1024);
       // second stage: B = dO_e (path 0) or Q_e (path 1) read MN-major: 16 q rows (2 KB) per
       // k-step, the two 64-dim halves 8 KB apart
-      const uint64_t mdesc0 = umma_desc_sw128(smem_u32(sQdo) + (path ? 0 : kBS * kD * 2), 8192, 1024);
+      const uint64_t mdesc0 = umma_desc_sw128(smem_u32(sQdo) + (path ? 0 : kQdoTile), 8192, 1024);
       const uint32_t tFirst[2] = {path ? tDP[0] : tST[0], path ? tDP[1] : tST[1]};
       const uint32_t tAcc = path ? tDK : tDV;
       auto first_stage = [&](int e) -> bool {
@@ -341,7 +353,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
         const uint64_t bd = bdesc0 + (uint64_t)((s * kQdoStageBytes) >> 4);
         if (elect_one()) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i)   // i = c * 4 + kk
+          for (int i = 0; i < D / 16; ++i)   // i = c * 4 + kk
             tc_mma_ss(tFirst[bf], adesc + (uint64_t)(((i >> 2) * 16384 + (i & 3) * 32) >> 4),
                       bd + (uint64_t)(((i >> 2) * 8192 + (i & 3) * 32) >> 4), idesc_nt, i ? 1u : 0u);
           tc_commit(&tl->sdp_full[bf]);
@@ -447,7 +459,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
     if (alive) alive = mbar_wait(&tl->all_done, 0, wait_status, 306);
     tc_fence_after();
     if (alive) {
-      const int is_dk = (warp >> 2) & 1, ch0 = (warp >> 3) * 2;
+      const int is_dk = (warp >> 2) & 1, ch0 = (warp >> 3) * (D / 64);
       const int kv = kblk[t] * kBS + (r_kv & 63);
       const bool row_ok = kvalid[t] && kv < p.sk;
       void* gbase = is_dk ? bp.dk : bp.dv;
@@ -458,7 +470,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
       const float scale = is_dk ? p.sm_scale : 1.f;
       const uint32_t tacc = is_dk ? tDK : tDV;
 #pragma unroll
-      for (int ch = ch0; ch < ch0 + 2; ++ch) {
+      for (int ch = ch0; ch < ch0 + D / 64; ++ch) {
         uint32_t o[32];
         tmem_ld32(tacc + lane_off + ch * 32, o);
         tmem_ld_wait();
@@ -491,7 +503,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
           ((int64_t)b * bp.dk_sb + (int64_t)hk * bp.dk_sh + (int64_t)kv * bp.dk_ss) * 2);
       uint2* d2 = reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(bp.dv) +
           ((int64_t)b * bp.dv_sb + (int64_t)hk * bp.dv_sh + (int64_t)kv * bp.dv_ss) * 2);
-      for (int i = 0; i < 32; ++i) { d1[i] = make_uint2(0u, 0u); d2[i] = make_uint2(0u, 0u); }
+      for (int i = 0; i < D / 4; ++i) { d1[i] = make_uint2(0u, 0u); d2[i] = make_uint2(0u, 0u); }
     }
   }
   tc_fence_before();
@@ -501,7 +513,6 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
 
 // ------------------------------------------------------------------ dQ
 constexpr int kDqKStages = 3, kDqVStages = 2;
-constexpr int kTileKV = kBS * kD * 2;  // 16 KB
 enum { kPairHeads = 0, kPairRows = 1 };
 
 struct DqTail {
@@ -515,9 +526,11 @@ struct DqTail {
   uint32_t bits[2][kMaxBlocks / 32];
   uint32_t list[kMaxBlocks];
 };
-constexpr size_t kDqSmem = 1024 + 2 * 128 * kD * 2 + (kDqKStages + kDqVStages) * kTileKV + sizeof(DqTail);
+template <int D> constexpr size_t dq_smem() {
+  return 1024 + 2 * 128 * D * 2 + (kDqKStages + kDqVStages) * (kBS * D * 2) + sizeof(DqTail);
+}
 
-template <bool BF16>
+template <bool BF16, int D>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap4 tmK,
                     const __grid_constant__ Tmap4 tmV, const __grid_constant__ Tmap4 tmDO,
@@ -526,9 +539,10 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
-  uint8_t* sQ = smem;                       // [2 subtiles][128 rows][128 B]
-  uint8_t* sDO = smem + 128 * kD * 2;
-  uint8_t* sKs = smem + 2 * 128 * kD * 2;   // K stages
+  constexpr int kSub = D / 64, kTileKV = kBS * D * 2;
+  uint8_t* sQ = smem;                       // [kSub subtiles][128 rows][128 B]
+  uint8_t* sDO = smem + 128 * D * 2;
+  uint8_t* sKs = smem + 2 * 128 * D * 2;    // K stages
   uint8_t* sVs = sKs + kDqKStages * kTileKV;
   DqTail* tl = reinterpret_cast<DqTail*>(sVs + kDqVStages * kTileKV);
 
@@ -582,10 +596,10 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
   if (tid < 2 * (kMaxBlocks / 32)) (&tl->bits[0][0])[tid] = 0u;
   __syncthreads();
   if (warp == kWarpProducer && lane == 0) {
-    mbar_expect_tx(&tl->q_full, (uint32_t)(valid[0] + valid[1]) * 2 * (kBS * kD * 2));
+    mbar_expect_tx(&tl->q_full, (uint32_t)(valid[0] + valid[1]) * 2 * (kBS * D * 2));
     for (int t = 0; t < 2; ++t) {
       if (!valid[t]) continue;
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < kSub; ++c) {
         tma_load_tile(sQ + c * 16384 + t * 8192, &tmQ, &tl->q_full, c * 64, qblk[t] * kBS, head[t], b);
         tma_load_tile(sDO + c * 16384 + t * 8192, &tmDO, &tl->q_full, c * 64, qblk[t] * kBS, head[t], b);
       }
@@ -619,9 +633,9 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
   const uint32_t tDP[2] = {tmem + 128, tmem + 192};
   const uint32_t tDQ = tmem + 256;
   // Q and dO are the A operands of every first-stage product: they are copied once
-  // from their TMA tiles into TMEM (64 columns each), which takes their 64 KB per
-  // step off the shared-memory read path that the tensor pipe saturates.
-  const uint32_t tQ = tmem + 384, tDO = tmem + 448;
+  // from their TMA tiles into TMEM (D/2 columns each), which takes them off the
+  // shared-memory read path that the tensor pipe saturates.
+  const uint32_t tQ = tmem + 256 + D, tDO = tQ + D / 2;
 
   if (n > 0 && warp == kWarpProducer) {
     if (lane == 0) {
@@ -630,12 +644,12 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
         const int sk_ = e % kDqKStages, sv_ = e % kDqVStages;
         if (!mbar_wait(&tl->k_empty[sk_], ((e / kDqKStages) & 1) ^ 1, wait_status, 311)) break;
         mbar_expect_tx(&tl->k_full[sk_], kTileKV);
-        tma_load_tile(sKs + sk_ * kTileKV, &tmK, &tl->k_full[sk_], 0, tok, kvh, b);
-        tma_load_tile(sKs + sk_ * kTileKV + 8192, &tmK, &tl->k_full[sk_], 64, tok, kvh, b);
+        for (int c = 0; c < kSub; ++c)
+          tma_load_tile(sKs + sk_ * kTileKV + c * 8192, &tmK, &tl->k_full[sk_], c * 64, tok, kvh, b);
         if (!mbar_wait(&tl->v_empty[sv_], ((e / kDqVStages) & 1) ^ 1, wait_status, 312)) break;
         mbar_expect_tx(&tl->v_full[sv_], kTileKV);
-        tma_load_tile(sVs + sv_ * kTileKV, &tmV, &tl->v_full[sv_], 0, tok, kvh, b);
-        tma_load_tile(sVs + sv_ * kTileKV + 8192, &tmV, &tl->v_full[sv_], 64, tok, kvh, b);
+        for (int c = 0; c < kSub; ++c)
+          tma_load_tile(sVs + sv_ * kTileKV + c * 8192, &tmV, &tl->v_full[sv_], c * 64, tok, kvh, b);
       }
     }
   } else if (n > 0 && warp == kWarpIssueA) {
@@ -655,7 +669,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
         tc_fence_after();
         if (elect_one()) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {   // one k-step (16 head dims = 8 packed columns) per copy
+          for (int i = 0; i < D / 16; ++i) {   // one k-step (16 head dims = 8 packed columns) per copy
             const uint64_t off = (uint64_t)(((i >> 2) * 16384 + (i & 3) * 32) >> 4);
             tc_cp_128x256b(tQ + i * 8, qdesc + off);
             tc_cp_128x256b(tDO + i * 8, gdesc + off);
@@ -673,7 +687,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
         const uint64_t kd = kdesc0 + (uint64_t)((sk_ * kTileKV) >> 4);
         if (elect_one()) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i)   // i = c * 4 + kk
+          for (int i = 0; i < D / 16; ++i)   // i = c * 4 + kk
             tc_mma_ts(tS[bf], tQ + i * 8, kd + (uint64_t)(((i >> 2) * 8192 + (i & 3) * 32) >> 4), idesc_nt,
                       i ? 1u : 0u);
           tc_commit(&tl->k_empty[sk_]);
@@ -687,7 +701,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
     // ------------------------------------------------------------ dP = dO V^T, dQ += dS K
     {
       const uint32_t idesc_nt = umma_idesc(BF16, 128, kBS, false, false);
-      const uint32_t idesc_acc = umma_idesc(BF16, 128, kD, false, true);
+      const uint32_t idesc_acc = umma_idesc(BF16, 128, D, false, true);
       const uint64_t vdesc0 = umma_desc_sw128(smem_u32(sVs), 16, 1024);
       // B = K_j read MN-major: 16 kv rows (2 KB) per k-step, 64-dim halves 8 KB apart
       const uint64_t kdesc0 = umma_desc_sw128(smem_u32(sKs), 8192, 1024);
@@ -698,7 +712,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
         const uint64_t vd = vdesc0 + (uint64_t)((sv_ * kTileKV) >> 4);
         if (elect_one()) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i)
+          for (int i = 0; i < D / 16; ++i)
             tc_mma_ts(tDP[bf], tDO + i * 8, vd + (uint64_t)(((i >> 2) * 8192 + (i & 3) * 32) >> 4), idesc_nt,
                       i ? 1u : 0u);
           tc_commit(&tl->v_empty[sv_]);
@@ -794,7 +808,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
     // stores 64 contiguous bytes straight from registers
     if (alive) alive = mbar_wait(&tl->all_done, 0, wait_status, 318);
     tc_fence_after();
-    if (alive) {
+    if (alive && qtr < D / 32) {
       const bool row_ok = valid[t] && q_row < p.sq;
       uint8_t* grow = reinterpret_cast<uint8_t*>(bp.dq) +
                       ((int64_t)b * bp.dq_sb + (int64_t)head[t] * bp.dq_sh + (int64_t)q_row * bp.dq_ss) * 2 +
@@ -828,7 +842,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
     if (valid[t] && q_row < p.sq) {
       uint2* d = reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(bp.dq) +
           ((int64_t)b * bp.dq_sb + (int64_t)head[t] * bp.dq_sh + (int64_t)q_row * bp.dq_ss) * 2);
-      for (int i = 0; i < 32; ++i) d[i] = make_uint2(0u, 0u);
+      for (int i = 0; i < D / 4; ++i) d[i] = make_uint2(0u, 0u);
     }
   }
   tc_fence_before();
@@ -841,8 +855,10 @@ bool rows8(const void* ptr, int64_t ss, int64_t sh, int64_t sb) {
   return reinterpret_cast<uintptr_t>(ptr) % 8 == 0 && ss % 4 == 0 && sh % 4 == 0 && sb % 4 == 0;
 }
 
-template <bool BF16>
+template <bool BF16, int D>
 int launch_bwd(const bsa_bwd_params* bp, cudaStream_t s) {
+  constexpr int kD = D;
+  constexpr size_t kDkdvSmem = dkdv_smem<D>(), kDqSmem = dq_smem<D>();
   const bsa_fwd_params* p = &bp->f;
   Tmap4 tmQ, tmK, tmV, tmDO;
   int rc = make_tmap_4d(&tmQ, p->q, 2, kD, p->sq, p->hq, p->batch, p->q_ss * 2, p->q_sh * 2, p->q_sb * 2,
@@ -861,12 +877,12 @@ int launch_bwd(const bsa_bwd_params* bp, cudaStream_t s) {
   if (!status) return BSA_E_CUDA;
   {
     const long long rows = (long long)p->batch * p->hq * padded_sq(p->sq);
-    bwd_delta_vec_kernel<BF16><<<(unsigned)((rows + 31) / 32), 256, 0, s>>>(*bp);
+    bwd_delta_vec_kernel<BF16, D><<<(unsigned)((rows + 31) / 32), 256, 0, s>>>(*bp);
     rc = check_launch("bwd_delta_vec_kernel");
     if (rc) return rc;
   }
   {
-    auto kern = bwd_dkdv_sm100_kernel<BF16>;
+    auto kern = bwd_dkdv_sm100_kernel<BF16, D>;
     BSA_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDkdvSmem));
     dim3 grid(bp->kv_pairs ? bp->n_pairs : cdiv_i(cdiv_i(p->sk, kBS), 2), p->hkv, p->batch);
     kern<<<grid, kDkdvThreads, kDkdvSmem, s>>>(tmQ, tmK, tmV, tmDO, *bp, status);
@@ -877,7 +893,7 @@ int launch_bwd(const bsa_bwd_params* bp, cudaStream_t s) {
     const int G = p->hq / p->hkv;
     // as in the forward: two q heads share a tile only when they share a block list
     const int mode = (G % 2 == 0 && p->h_pat != p->hq) ? kPairHeads : kPairRows;
-    auto kern = bwd_dq_sm100_kernel<BF16>;
+    auto kern = bwd_dq_sm100_kernel<BF16, D>;
     BSA_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDqSmem));
     dim3 grid(cdiv_i(p->sq, mode == kPairHeads ? 64 : 128), mode == kPairHeads ? p->hq / 2 : p->hq,
               p->batch);
@@ -904,7 +920,7 @@ bool sm100_bwd_supported(const bsa_bwd_params* bp, const char** why) {
   const bsa_fwd_params* p = &bp->f;
   auto no = [&](const char* w) { *why = w; return false; };
   if (!(p->dtype == BSA_F16 || p->dtype == BSA_BF16)) return no("dtype is not f16/bf16");
-  if (p->d != kD) return no("head dim is not 128");
+  if (p->d != 128 && p->d != 64) return no("head dim is not 64 or 128");
   if (p->block_size != kBS) return no("block size is not 64");
   if (p->sk > kMaxBlocks * kBS || p->sq > kMaxBlocks * kBS) return no("more than 65536 positions");
   if ((p->hq / p->hkv) * cdiv_i(p->sq, kBS) > kMaxEntries)
@@ -926,7 +942,9 @@ bool sm100_bwd_supported(const bsa_bwd_params* bp, const char** why) {
 }
 
 int sm100_bwd(const bsa_bwd_params* bp, cudaStream_t s) {
-  return bp->f.dtype == BSA_BF16 ? launch_bwd<true>(bp, s) : launch_bwd<false>(bp, s);
+  const bool bf16 = bp->f.dtype == BSA_BF16;
+  if (bp->f.d == 128) return bf16 ? launch_bwd<true, 128>(bp, s) : launch_bwd<false, 128>(bp, s);
+  return bf16 ? launch_bwd<true, 64>(bp, s) : launch_bwd<false, 64>(bp, s);
 }
 
 }  // namespace bsa

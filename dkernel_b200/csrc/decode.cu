@@ -98,40 +98,42 @@ __device__ __forceinline__ uint32_t tile_off(int tok, int chunk) {
 // Shared-memory geometry.  16-bit K/V: a stage holds a K and a V tile as the tensor cores read
 // them (D/64 sub-tiles of [64 tokens][128 bytes], 128-byte swizzled).  8-bit (e4m3) K/V: a stage
 // holds the two tiles as stored ([64 tokens][D bytes], half the bytes, so twice the stages keep
-// the same number of bytes in flight) and one extra pair of 16-bit tiles receives the converted
-// values; every consumer warp converts and then reads its own 16 token rows only.
+// the same number of bytes in flight); the consumer warps read the stored bytes with plain
+// 16-byte loads and convert them straight into tensor-core fragments in registers.  e4m3 converts
+// to f16 exactly and in one instruction per pair, so with an 8-bit cache the products run in f16
+// whatever the type of q (q is converted once while it is staged; P lies in [0, 1]).
+//
+// Fragment trick of the 8-bit path: a product's contraction index may be enumerated in any order,
+// and so may the output columns, as long as both operands (resp. the epilogue) agree.
+//   Q K^T: thread (g, tq) of an m16n8k16 step holds k slots {2tq, 2tq+1, 8+2tq, 9+2tq}.  Over the
+//          four steps of a 64-dim chunk these are made to stand for dims 16 tq .. 16 tq + 15 of the
+//          chunk (step kk: dims 16 tq + 4 kk + {0,1} and + {2,3}), so a thread's share of a K row
+//          is ONE 16-byte load and each of its four words converts into one step's B fragment.
+//   P V:   output column j of n-tile nt stands for dim (D/8) j + nt, so thread g owns D/8
+//          consecutive dims: its share of a V row is one 16-byte (D = 128) load, and a byte
+//          permute pairs the bytes of two token rows into the B fragment of an n-tile.
 template <int D, bool FP8> struct DecGeo {
   static constexpr int kStages = FP8 ? 2 * bsa::kStages : bsa::kStages;
   static constexpr int kTileBytes = kTok * D * (FP8 ? 1 : 2);
   static constexpr int kStageBytes = 2 * kTileBytes;
-  static constexpr int kTile16 = kTok * D * 2;
-  static constexpr int kConvBytes = FP8 ? 2 * kTile16 : 0;
   static constexpr int kRing = kStages * kStageBytes;
-  static constexpr size_t kSmem = 1024 + kRing + kConvBytes + 16 * D * 2 + sizeof(DecodeSmem);
+  static constexpr size_t kSmem = 1024 + kRing + 16 * D * 2 + sizeof(DecodeSmem);
 };
 
-// eight e4m3 values (two 32-bit words) -> eight T values (one 16-byte chunk); exact
-template <typename T>
-__device__ __forceinline__ uint4 cvt_e4m3x8(uint32_t lo, uint32_t hi) {
-  uint32_t h[4];
+// four e4m3 bytes of a word -> two f16x2: (byte 0, byte 1) and (byte 2, byte 3); exact
+__device__ __forceinline__ void cvt_e4m3x4(uint32_t w, uint32_t& lo, uint32_t& hi) {
   asm("{\n\t.reg .b16 a, b;\n\tmov.b32 {a, b}, %2;\n\t"
       "cvt.rn.f16x2.e4m3x2 %0, a;\n\tcvt.rn.f16x2.e4m3x2 %1, b;\n\t}"
-      : "=r"(h[0]), "=r"(h[1]) : "r"(lo));
-  asm("{\n\t.reg .b16 a, b;\n\tmov.b32 {a, b}, %2;\n\t"
-      "cvt.rn.f16x2.e4m3x2 %0, a;\n\tcvt.rn.f16x2.e4m3x2 %1, b;\n\t}"
-      : "=r"(h[2]), "=r"(h[3]) : "r"(hi));
-  if (sizeof(T) == 2 && std::is_same<T, __half>::value) return make_uint4(h[0], h[1], h[2], h[3]);
-  uint32_t o[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h[i]));
-    o[i] = MmaType<T>::pack(f.x, f.y);
-  }
-  return make_uint4(o[0], o[1], o[2], o[3]);
+      : "=r"(lo), "=r"(hi) : "r"(w));
+}
+__device__ __forceinline__ uint32_t byte_perm(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t d;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+  return d;
 }
 
 template <typename T, int D, bool FP8>
-__global__ void __launch_bounds__(kDecThreads, FP8 ? 2 : kMinCtas)
+__global__ void __launch_bounds__(kDecThreads, kMinCtas)
 decode_kernel(const __grid_constant__ Tmap4 tmK, const __grid_constant__ Tmap4 tmV,
               bsa_decode_params p, int nsplit, int* wait_status) {
   using Geo = DecGeo<D, FP8>;
@@ -142,9 +144,9 @@ decode_kernel(const __grid_constant__ Tmap4 tmK, const __grid_constant__ Tmap4 t
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
   uint8_t* ring = smem;
-  uint8_t* conv = smem + Geo::kRing;                            // FP8: converted K tile, then V tile
-  T* Qs = reinterpret_cast<T*>(smem + Geo::kRing + Geo::kConvBytes);  // [16][D]
-  DecodeSmem* sm = reinterpret_cast<DecodeSmem*>(smem + Geo::kRing + Geo::kConvBytes + 16 * D * 2);
+  using MT = typename std::conditional<FP8, __half, T>::type;   // type of the tensor-core products
+  MT* Qs = reinterpret_cast<MT*>(smem + Geo::kRing);  // [16][D]
+  DecodeSmem* sm = reinterpret_cast<DecodeSmem*>(smem + Geo::kRing + 16 * D * 2);
 
   // the merge kernel behind this one may be made resident as soon as every CTA got here
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -255,6 +257,13 @@ decode_kernel(const __grid_constant__ Tmap4 tmK, const __grid_constant__ Tmap4 t
           for (int e = 0; e < 8; ++e) tmp[e] = src[e];
           v = *reinterpret_cast<const uint4*>(tmp);
         }
+        if (!std::is_same<MT, T>::value) {   // bf16 queries against an 8-bit cache: products run in f16
+          const T* e = reinterpret_cast<const T*>(&v);
+          __half hq[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) hq[j] = __float2half_rn(fminf(fmaxf(Elem<T>::to_f(e[j]), -65504.f), 65504.f));
+          v = *reinterpret_cast<const uint4*>(hq);
+        }
       }
       reinterpret_cast<uint4*>(Qs)[i] = v;
     }
@@ -305,10 +314,14 @@ decode_kernel(const __grid_constant__ Tmap4 tmK, const __grid_constant__ Tmap4 t
 #pragma unroll
     for (int kk = 0; kk < D / 16; ++kk) {
       const uint32_t* q32 = reinterpret_cast<const uint32_t*>(Qs);
-      qa[kk][0] = q32[(g * D + kk * 16 + tq * 2) >> 1];
-      qa[kk][1] = q32[((g + 8) * D + kk * 16 + tq * 2) >> 1];
-      qa[kk][2] = q32[(g * D + kk * 16 + 8 + tq * 2) >> 1];
-      qa[kk][3] = q32[((g + 8) * D + kk * 16 + 8 + tq * 2) >> 1];
+      // k slots (2tq, 2tq+1) and (8+2tq, 9+2tq) of step kk: the dims of the same numbers, or
+      // (8-bit K/V) dims 16 tq + 4 (kk % 4) + {0,1} / {2,3} of 64-dim chunk kk / 4
+      const int d0 = FP8 ? (kk >> 2) * 64 + tq * 16 + (kk & 3) * 4 : kk * 16 + tq * 2;
+      const int d1 = FP8 ? d0 + 2 : d0 + 8;
+      qa[kk][0] = q32[(g * D + d0) >> 1];
+      qa[kk][1] = q32[((g + 8) * D + d0) >> 1];
+      qa[kk][2] = q32[(g * D + d1) >> 1];
+      qa[kk][3] = q32[((g + 8) * D + d1) >> 1];
     }
     float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
     // e4m3 K carries a per-tensor scale: it folds into the logit scale (V's goes on the output)
@@ -322,32 +335,13 @@ decode_kernel(const __grid_constant__ Tmap4 tmK, const __grid_constant__ Tmap4 t
       alive = mbar_wait(&sm->full[s], ph, wait_status, 102);
       if (!alive) break;
       const int pos_u = sm->unit_pos[u];
-      const uint32_t kbase = FP8 ? smem_u32(conv) : ring_u32 + s * kStageBytes;
-      const uint32_t vbase = FP8 ? kbase + Geo::kTile16 : kbase + kTileBytes;
+      const uint32_t kbase = ring_u32 + s * kStageBytes;
+      const uint32_t vbase = kbase + kTileBytes;
       const int valid = end_pos - pos_u;  // tokens of this unit that exist (may exceed 64)
+      const uint8_t* k8 = ring + s * kStageBytes;    // the tiles as generic pointers (8-bit path)
+      const uint8_t* v8 = k8 + kTileBytes;
       if (FP8) {
-        // this warp's 16 token rows of K and V: e4m3 as stored -> T in the swizzled tile layout
-        // the ldmatrix addressing below expects; V rows past the end of the sequence become zero.
-        // Two lanes share a row (D/2 bytes each).  The stage is free as soon as the rows are read.
-        const uint8_t* k8 = ring + s * kStageBytes;
-        const uint8_t* v8 = k8 + kTileBytes;
-        const int tok = warp * 16 + (lane >> 1);
-        const bool v_ok = tok < valid;
-#pragma unroll
-        for (int i = 0; i < D / 32; ++i) {
-          const int piece = (lane & 1) * (D / 32) + i;           // 16 stored bytes = two 16-byte chunks of T
-          const uint4 kk8 = *reinterpret_cast<const uint4*>(k8 + tok * D + piece * 16);
-          const uint4 vv8 = *reinterpret_cast<const uint4*>(v8 + tok * D + piece * 16);
-          *reinterpret_cast<uint4*>(conv + tile_off(tok, 2 * piece)) = cvt_e4m3x8<T>(kk8.x, kk8.y);
-          *reinterpret_cast<uint4*>(conv + tile_off(tok, 2 * piece + 1)) = cvt_e4m3x8<T>(kk8.z, kk8.w);
-          const uint4 z = make_uint4(0u, 0u, 0u, 0u);
-          *reinterpret_cast<uint4*>(conv + Geo::kTile16 + tile_off(tok, 2 * piece)) =
-              v_ok ? cvt_e4m3x8<T>(vv8.x, vv8.y) : z;
-          *reinterpret_cast<uint4*>(conv + Geo::kTile16 + tile_off(tok, 2 * piece + 1)) =
-              v_ok ? cvt_e4m3x8<T>(vv8.z, vv8.w) : z;
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sm->empty[s]);
+        // nothing to prepare: rows past the end of the sequence are zeroed when V is read
       } else if (valid < kTok) {
         // rows past the end of the sequence may hold anything: clear them in V so
         // that 0 * garbage cannot produce NaN
@@ -367,13 +361,28 @@ decode_kernel(const __grid_constant__ Tmap4 tmK, const __grid_constant__ Tmap4 t
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt) {
         sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.f;
-        const int tok = warp * 16 + nt * 8 + (lane & 7);
+        if (FP8) {
+          const int tok = warp * 16 + nt * 8 + g;      // B fragment column n = g
 #pragma unroll
-        for (int kk = 0; kk < D / 32; ++kk) {
-          uint32_t r0, r1, r2, r3;
-          ldsm_x4(kbase + tile_off(tok, kk * 4 + (lane >> 3)), r0, r1, r2, r3);
-          MmaType<T>::mma(sacc[nt], qa[2 * kk], r0, r1);
-          MmaType<T>::mma(sacc[nt], qa[2 * kk + 1], r2, r3);
+          for (int c = 0; c < D / 64; ++c) {
+            const uint4 kb = *reinterpret_cast<const uint4*>(k8 + tok * D + c * 64 + tq * 16);
+            const uint32_t w[4] = {kb.x, kb.y, kb.z, kb.w};
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+              uint32_t b0, b1;
+              cvt_e4m3x4(w[kk], b0, b1);
+              MmaType<MT>::mma(sacc[nt], qa[c * 4 + kk], b0, b1);
+            }
+          }
+        } else {
+          const int tok = warp * 16 + nt * 8 + (lane & 7);
+#pragma unroll
+          for (int kk = 0; kk < D / 32; ++kk) {
+            uint32_t r0, r1, r2, r3;
+            ldsm_x4(kbase + tile_off(tok, kk * 4 + (lane >> 3)), r0, r1, r2, r3);
+            MmaType<MT>::mma(sacc[nt], qa[2 * kk], r0, r1);
+            MmaType<MT>::mma(sacc[nt], qa[2 * kk + 1], r2, r3);
+          }
         }
       }
       // mask + online softmax (rows g and g+8)
@@ -407,10 +416,10 @@ decode_kernel(const __grid_constant__ Tmap4 tmK, const __grid_constant__ Tmap4 t
         const float p12 = exp2f(sacc[1][2] - ms_hi), p13 = exp2f(sacc[1][3] - ms_hi);
         l_lo = l_lo * a_lo + (p00 + p01 + p10 + p11);
         l_hi = l_hi * a_hi + (p02 + p03 + p12 + p13);
-        pa[0] = MmaType<T>::pack(p00, p01);
-        pa[1] = MmaType<T>::pack(p02, p03);
-        pa[2] = MmaType<T>::pack(p10, p11);
-        pa[3] = MmaType<T>::pack(p12, p13);
+        pa[0] = MmaType<MT>::pack(p00, p01);
+        pa[1] = MmaType<MT>::pack(p02, p03);
+        pa[2] = MmaType<MT>::pack(p10, p11);
+        pa[3] = MmaType<MT>::pack(p12, p13);
       }
 #pragma unroll
       for (int i = 0; i < D / 8; ++i) {
@@ -418,17 +427,46 @@ decode_kernel(const __grid_constant__ Tmap4 tmK, const __grid_constant__ Tmap4 t
         oacc[i][2] *= a_hi; oacc[i][3] *= a_hi;
       }
       // O += P V over this warp's 16 tokens
+      if (FP8) {
+        // k slots (2tq, 2tq+1, 8+2tq, 9+2tq) are this warp's token rows of the same numbers; the
+        // thread's D/8 consecutive dims of each row arrive in one load (zero past the sequence end)
+        constexpr int kNT = D / 8;                       // n-tiles = dims per thread
+        uint32_t rows[4][kNT / 4];
 #pragma unroll
-      for (int dn = 0; dn < D / 16; ++dn) {
-        const int mi = lane >> 3;
-        const int tok = warp * 16 + (mi & 1) * 8 + (lane & 7);
-        uint32_t r0, r1, r2, r3;
-        ldsm_x4_t(vbase + tile_off(tok, dn * 2 + (mi >> 1)), r0, r1, r2, r3);
-        MmaType<T>::mma(oacc[2 * dn], pa, r0, r1);
-        MmaType<T>::mma(oacc[2 * dn + 1], pa, r2, r3);
+        for (int i = 0; i < 4; ++i) {
+          const int tok = warp * 16 + (i >> 1) * 8 + tq * 2 + (i & 1);
+          const uint8_t* src = v8 + tok * D + g * kNT;
+          if (kNT == 16) {
+            const uint4 r = tok < valid ? *reinterpret_cast<const uint4*>(src) : make_uint4(0u, 0u, 0u, 0u);
+            rows[i][0] = r.x; rows[i][1] = r.y; rows[i][kNT / 4 - 2] = r.z; rows[i][kNT / 4 - 1] = r.w;
+          } else {
+            const uint2 r = tok < valid ? *reinterpret_cast<const uint2*>(src) : make_uint2(0u, 0u);
+            rows[i][0] = r.x; rows[i][kNT / 4 - 1] = r.y;
+          }
+        }
+#pragma unroll
+        for (int nt2 = 0; nt2 < kNT / 2; ++nt2) {         // two n-tiles (dims 2 nt2, 2 nt2 + 1 of the thread) per permute
+          const int wi = nt2 >> 1;
+          const uint32_t sel = (nt2 & 1) ? 0x7362u : 0x5140u;   // {a.b, b.b, a.b+1, b.b+1}, b = 0 or 2
+          uint32_t b0a, b0b, b1a, b1b;
+          cvt_e4m3x4(byte_perm(rows[0][wi], rows[1][wi], sel), b0a, b0b);   // tokens 2tq, 2tq+1
+          cvt_e4m3x4(byte_perm(rows[2][wi], rows[3][wi], sel), b1a, b1b);   // tokens 8+2tq, 9+2tq
+          MmaType<MT>::mma(oacc[2 * nt2], pa, b0a, b1a);
+          MmaType<MT>::mma(oacc[2 * nt2 + 1], pa, b0b, b1b);
+        }
+      } else {
+#pragma unroll
+        for (int dn = 0; dn < D / 16; ++dn) {
+          const int mi = lane >> 3;
+          const int tok = warp * 16 + (mi & 1) * 8 + (lane & 7);
+          uint32_t r0, r1, r2, r3;
+          ldsm_x4_t(vbase + tile_off(tok, dn * 2 + (mi >> 1)), r0, r1, r2, r3);
+          MmaType<MT>::mma(oacc[2 * dn], pa, r0, r1);
+          MmaType<MT>::mma(oacc[2 * dn + 1], pa, r2, r3);
+        }
       }
-      __syncwarp();   // (8-bit K/V: also orders this unit's reads before the next conversion)
-      if (!FP8 && lane == 0) mbar_arrive(&sm->empty[s]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sm->empty[s]);
     }
     // quad-reduce the row sums
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
@@ -445,11 +483,13 @@ decode_kernel(const __grid_constant__ Tmap4 tmK, const __grid_constant__ Tmap4 t
     float* Omw = reinterpret_cast<float*>(ring);  // [kConsumers][16][D]
 #pragma unroll
     for (int i = 0; i < D / 8; ++i) {
-      const int d = i * 8 + tq * 2;
-      float* lo = Omw + ((warp * 16 + g) * D + d);
-      float* hi = Omw + ((warp * 16 + g + 8) * D + d);
-      lo[0] = oacc[i][0]; lo[1] = oacc[i][1];
-      hi[0] = oacc[i][2]; hi[1] = oacc[i][3];
+      // column j = 2tq (+1) of n-tile i is dim 8 i + j, or (8-bit K/V) dim (D/8) j + i
+      const int d0 = FP8 ? (D / 8) * (tq * 2) + i : i * 8 + tq * 2;
+      const int d1 = FP8 ? d0 + D / 8 : d0 + 1;
+      float* lo = Omw + ((warp * 16 + g) * D);
+      float* hi = Omw + ((warp * 16 + g + 8) * D);
+      lo[d0] = oacc[i][0]; lo[d1] = oacc[i][1];
+      hi[d0] = oacc[i][2]; hi[d1] = oacc[i][3];
     }
   }
   __syncthreads();  // partial outputs are in shared memory

@@ -148,10 +148,10 @@ BWD_CASES = [
 ]
 
 
+@pytest.mark.parametrize("D", [128, 64])
 @pytest.mark.parametrize("B,Hq,Hkv,Sq,Sk,dtype,seq_dim,pk", BWD_CASES)
-def test_sm100_backward_vs_oracle(B, Hq, Hkv, Sq, Sk, dtype, seq_dim, pk):
+def test_sm100_backward_vs_oracle(B, Hq, Hkv, Sq, Sk, dtype, seq_dim, pk, D):
     from helpers import assert_grad_close
-    D = 128
     causal = pk.get("causal", True)
     bs = pk["block_size"]
     shape = (lambda h, s: (B, h, s, D)) if seq_dim == 2 else (lambda h, s: (B, s, h, D))
@@ -178,14 +178,15 @@ def test_sm100_backward_vs_oracle(B, Hq, Hkv, Sq, Sk, dtype, seq_dim, pk):
     assert_grad_close(vg.grad, vf.grad, "dv")
 
 
+@pytest.mark.parametrize("D", [128, 64])
 @pytest.mark.parametrize("B,Hq,Hkv,S,pk", [
     (1, 4, 4, 2048, dict(block_size=64, local_blocks=8, vert_stride=8)),
     (1, 8, 2, 2048, dict(block_size=64, local_blocks=4, vert_stride=4, num_kv_heads=2)),
     (2, 2, 2, 4096, dict(block_size=64, local_blocks=32, vert_stride=8)),
 ])
-def test_sm100_backward_matches_generic_on_long_sequences(B, Hq, Hkv, S, pk):
+def test_sm100_backward_matches_generic_on_long_sequences(B, Hq, Hkv, S, pk, D):
     from helpers import assert_grad_close
-    q, k, v, do = seeded_qkv(3, (B, S, Hq, 128), (B, S, Hkv, 128), torch.bfloat16, device="cuda", with_do=True)
+    q, k, v, do = seeded_qkv(3, (B, S, Hq, D), (B, S, Hkv, D), torch.bfloat16, device="cuda", with_do=True)
     grads = {}
     for name in ("sm100", "generic"):
         mod = _module(Hq, S, pk, seq_dim=1, impl=name, bwd_impl=name)
