@@ -874,8 +874,28 @@ def run_all(args, world, rank):
         r = run_prefill(args, world, rank, strong=True, with_e2e=False)
         sub["prefill_c2_strong"] = {k: v for k, v in r.items() if not isinstance(v, (str, list))}
 
+    def reference_triton():
+        # optional comparator in a child process (Triton JIT; bounded): the reference's own kernels, same GPU
+        if not os.path.isdir(os.path.join(ROOT, "baseline", "_ref", "dkernel")):
+            sub["reference_triton_c2"] = {"unavailable": "baseline/_ref not installed"}
+            return
+        try:
+            r = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "reference-gpu", "--steps",
+                                str(args.steps), "--warmup", str(args.warmup)], capture_output=True, text=True,
+                               timeout=300, cwd=ROOT)
+            ref = json.loads(r.stdout.strip().splitlines()[-1])
+        except Exception as e:
+            ref = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
+        if "value" in ref:
+            sub["reference_triton_c2"] = {"tflops": ref["value"], "ms": ref["ms_per_step"],
+                                          "max_abs_diff_vs_this_repo": ref.get("max_abs_diff_vs_this_repo"),
+                                          "speedup_of_this_repo": line["value"] / ref["value"]}
+        else:
+            sub["reference_triton_c2"] = {"unavailable": str(ref.get("unavailable"))[:200]}
+
     if world == 1:
-        for name, fn in (("train_c3", train), ("decode_c4", decode), ("varlen_c5", varlen), ("prefill_d64", d64)):
+        for name, fn in (("train_c3", train), ("decode_c4", decode), ("varlen_c5", varlen), ("prefill_d64", d64),
+                         ("reference_triton_c2", reference_triton)):
             guarded(name, fn)
     else:
         for name, fn in (("decode_c4_kv_sharded", decode), ("varlen_c5_strong", varlen),
@@ -936,13 +956,63 @@ def run_reference(args):
     return line
 
 
+def run_reference_gpu(args):
+    """Optional comparator, bench side only: the UNMODIFIED reference (installed under baseline/_ref)
+    running its own Triton kernels on this GPU, BASELINE config 2 forward.  Its training-path kernel
+    indexes K/V with the q-head id (dkernel/ops/sparse_attn_fwd.py:217-218), so K/V are repeated to
+    32 heads as its callers must.  Prints one JSON line; any failure is reported in the line."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    line = {"impl": "reference-gpu", "metric": METRIC, "unit": "TFLOP/s", "n_gpus": 1, "dtype": "bf16",
+            "data": "synthetic", "higher_is_better": True, "steps": args.steps, "warmup": args.warmup}
+    try:
+        if not os.path.isdir(os.path.join(ref_dir, "dkernel")):
+            raise RuntimeError("baseline/_ref is missing (pip install --no-deps --target baseline/_ref of the reference)")
+        sys.path.insert(0, ref_dir)
+        import dkernel as ref
+        cfg = WORKLOADS["prefill"]
+        B, S, Hq, Hkv, D = cfg["B"], cfg["S"], cfg["Hq"], cfg["Hkv"], cfg["D"]
+        torch.cuda.set_device(0)
+        attn = ref.LocalStrideSparseAttention(Hq, S, cfg["block"], cfg["local"], cfg["stride"], num_kv_heads=Hkv,
+                                              seq_dim=1)
+        attn = attn.cuda() if hasattr(attn, "cuda") else attn
+        g = torch.Generator(device="cuda").manual_seed(1234)
+        q = torch.randn((B, S, Hq, D), generator=g, device="cuda").to(torch.bfloat16)
+        k, v = (torch.randn((B, S, Hkv, D), generator=g, device="cuda").to(torch.bfloat16) for _ in range(2))
+        kr, vr = k.repeat_interleave(Hq // Hkv, dim=2), v.repeat_interleave(Hq // Hkv, dim=2)
+        scale = 1.0 / math.sqrt(D)
+
+        def step():
+            with torch.no_grad():
+                return attn(q, kr, vr, sm_scale=scale)
+
+        out = step()
+        torch.cuda.synchronize()
+        # same inputs through this repository's kernels: the comparator must compute the same thing
+        from dkernel_b200 import LocalStrideSparseAttention
+        mine = LocalStrideSparseAttention(Hq, S, cfg["block"], cfg["local"], cfg["stride"], num_kv_heads=Hkv, seq_dim=1)
+        with torch.no_grad():
+            want = mine(q, k, v, sm_scale=scale)
+        line["max_abs_diff_vs_this_repo"] = (out.float() - want.float()).abs().max().item()
+        ms, regions = time_steps(step, args.steps, max(args.warmup, 3), 1)
+        tiles = int(local_stride_mask_np(Hq, S, cfg["block"], cfg["local"], cfg["stride"], Hkv).sum()) * B
+        line.update({"value": tiles * tile_flops(cfg["block"], D) / (ms * 1e-3) / 1e12, "ms_per_step": ms,
+                     "ms_min": min(regions), "ms_max": max(regions),
+                     "config": {"workload": "prefill_fwd: BASELINE config 2, the reference's Triton kernels on this GPU "
+                                            "(K/V repeated to 32 heads, as that kernel requires)"}})
+        import triton
+        line["triton"] = triton.__version__
+    except Exception as e:
+        line["unavailable"] = f"{type(e).__name__}: {e}"[:300]
+    return line
+
+
 def main():
     global REPEATS
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-gpu"])
     ap.add_argument("--workload", default="all", choices=["all"] + list(WORKLOADS))
     ap.add_argument("--repeats", type=int, default=REPEATS, help="timed regions of K steps each (median reported)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -956,6 +1026,13 @@ def main():
         line = run_reference(args)
         if line is not None:
             print(json.dumps(line), flush=True)
+        return
+    if args.impl == "reference-gpu":
+        if not torch.cuda.is_available():
+            print(json.dumps({"impl": "reference-gpu", "unavailable": "no CUDA device"}), flush=True)
+            return
+        REPEATS = max(1, args.repeats)
+        print(json.dumps(run_reference_gpu(args)), flush=True)
         return
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (the product has no CPU path); "

@@ -1,4 +1,6 @@
-// Prefill / training forward on the tcgen05 tensor cores (head dim 64 or 128, 64-token blocks).
+// Prefill / training forward on the tcgen05 tensor cores (64-token blocks; head dim any multiple
+// of 8 up to 256: the kernel is built for widths 64, 128 and 256, a narrower head is padded with
+// the zeros TMA supplies for out-of-range columns, and only the real columns are stored).
 //
 // A 128-row query tile = two 64-row halves that share a kv head; S double buffered in TMEM,
 // P overwrites S, O accumulates in TMEM; one converged issuer warp queues Q K_{j+2} right
@@ -188,7 +190,7 @@ __device__ __forceinline__ void build_plan(const bsa_fwd_params& p, int mode, in
 }
 
 template <bool BF16, int D>
-__global__ void __launch_bounds__(kThreadsP, 2)
+__global__ void __launch_bounds__(kThreadsP, D <= 128 ? 2 : 1)
 fwd_persist_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap4 tmK,
                    const __grid_constant__ Tmap4 tmV, bsa_fwd_params p, int mode, int n_items,
                    int tiles_x, int head_items, int* wait_status) {
@@ -220,7 +222,7 @@ fwd_persist_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tm
     }
   }
   if (warp == kWarpIssue) {
-    tmem_alloc(&tl->tmem_base, 256);
+    tmem_alloc(&tl->tmem_base, D <= 128 ? 256 : 512);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -404,7 +406,7 @@ fwd_persist_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tm
                              : nullptr;
       if (n == 0) {
         if (pl->valid && row_ok) {   // a tile that attends nothing: zero rows, LSE = -inf
-          for (int i = 0; i < D / 4; ++i) reinterpret_cast<uint2*>(orow)[i] = make_uint2(0u, 0u);
+          for (int i = 0; i < p.d / 4; ++i) reinterpret_cast<uint2*>(orow)[i] = make_uint2(0u, 0u);
           if (lse_ptr) *lse_ptr = -INFINITY;
         }
         __syncwarp();
@@ -547,16 +549,18 @@ fwd_persist_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tm
           __syncwarp();
           if (lane == 0) mbar_arrive(&tl->o_free);
         }
-        if (row_ok) {
+        if (row_ok) {   // columns at or past the real head dim are padding
           if (wide) {
 #pragma unroll
             for (int i = 0; i < 4; ++i)
-              *reinterpret_cast<uint4*>(orow + ch * 64 + i * 16) =
-                  make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+              if (ch * 32 + i * 8 < p.d)
+                *reinterpret_cast<uint4*>(orow + ch * 64 + i * 16) =
+                    make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
           } else {
 #pragma unroll
             for (int i = 0; i < 8; ++i)
-              *reinterpret_cast<uint2*>(orow + ch * 64 + i * 8) = make_uint2(w[2 * i], w[2 * i + 1]);
+              if (ch * 32 + i * 4 < p.d)
+                *reinterpret_cast<uint2*>(orow + ch * 64 + i * 8) = make_uint2(w[2 * i], w[2 * i + 1]);
           }
         }
       }
@@ -568,7 +572,7 @@ fwd_persist_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tm
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == kWarpIssue) tmem_dealloc(tmem, 256);
+  if (warp == kWarpIssue) tmem_dealloc(tmem, D <= 128 ? 256 : 512);
 }
 
 }  // namespace
@@ -576,7 +580,7 @@ fwd_persist_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tm
 bool sm100_fwd_supported(const bsa_fwd_params* p, const char** why) {
   auto no = [&](const char* w) { *why = w; return false; };
   if (!(p->dtype == BSA_F16 || p->dtype == BSA_BF16)) return no("dtype is not f16/bf16");
-  if (p->d != 128 && p->d != 64) return no("head dim is not 64 or 128");
+  if (p->d < 16 || p->d > 256 || p->d % 8) return no("head dim is not a multiple of 8 in [16, 256]");
   if (p->block_size != kBS) return no("block size is not 64");
   if (p->sk > kMaxList * kBS) return no("more than 65536 key positions");
   if (!tma_compatible(p->q, 2, p->q_ss, p->q_sh, p->q_sb) ||
@@ -595,13 +599,13 @@ template <bool BF16, int D>
 int launch_fwd(const bsa_fwd_params* p, cudaStream_t s) {
   Tmap4 tmQ, tmK, tmV;
   const uint64_t nb = p->total_q > 0 ? 1 : p->batch;
-  int rc = make_tmap_4d(&tmQ, p->q, 2, D, p->sq, p->hq, nb, p->q_ss * 2, p->q_sh * 2, p->q_sb * 2, 64, 64,
+  int rc = make_tmap_4d(&tmQ, p->q, 2, p->d, p->sq, p->hq, nb, p->q_ss * 2, p->q_sh * 2, p->q_sb * 2, 64, 64,
                         true, BF16);
   if (rc) return rc;
-  rc = make_tmap_4d(&tmK, p->k, 2, D, p->sk, p->hkv, nb, p->k_ss * 2, p->k_sh * 2, p->k_sb * 2, 64, 64,
+  rc = make_tmap_4d(&tmK, p->k, 2, p->d, p->sk, p->hkv, nb, p->k_ss * 2, p->k_sh * 2, p->k_sb * 2, 64, 64,
                     true, BF16);
   if (rc) return rc;
-  rc = make_tmap_4d(&tmV, p->v, 2, D, p->sk, p->hkv, nb, p->v_ss * 2, p->v_sh * 2, p->v_sb * 2, 64, 64,
+  rc = make_tmap_4d(&tmV, p->v, 2, p->d, p->sk, p->hkv, nb, p->v_ss * 2, p->v_sh * 2, p->v_sb * 2, 64, 64,
                     true, BF16);
   if (rc) return rc;
   const int G = p->hq / p->hkv;
@@ -622,7 +626,8 @@ int launch_fwd(const bsa_fwd_params* p, cudaStream_t s) {
   int dev = 0, sms = 148;
   BSA_CHECK_CUDA(cudaGetDevice(&dev));
   BSA_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  const int grid = n_items < 2 * sms ? n_items : 2 * sms;   // two resident CTAs per SM
+  const int per_sm = D <= 128 ? 2 : 1;                       // resident CTAs per SM (TMEM, shared memory)
+  const int grid = n_items < per_sm * sms ? n_items : per_sm * sms;
   int* status = wait_status_ptr();
   if (!status) return BSA_E_CUDA;
   constexpr size_t smem = Geo<D>::kSmem + sizeof(TailP);
@@ -635,8 +640,9 @@ int launch_fwd(const bsa_fwd_params* p, cudaStream_t s) {
 
 int sm100_fwd(const bsa_fwd_params* p, cudaStream_t s) {
   const bool bf16 = p->dtype == BSA_BF16;
-  if (p->d == 128) return bf16 ? launch_fwd<true, 128>(p, s) : launch_fwd<false, 128>(p, s);
-  return bf16 ? launch_fwd<true, 64>(p, s) : launch_fwd<false, 64>(p, s);
+  if (p->d <= 64) return bf16 ? launch_fwd<true, 64>(p, s) : launch_fwd<false, 64>(p, s);
+  if (p->d <= 128) return bf16 ? launch_fwd<true, 128>(p, s) : launch_fwd<false, 128>(p, s);
+  return bf16 ? launch_fwd<true, 256>(p, s) : launch_fwd<false, 256>(p, s);
 }
 
 }  // namespace bsa

@@ -75,7 +75,7 @@ class _Plan:
         instead of falling back to the CUDA-core kernels."""
         bs = self.block_size
         if not (bs > 64 and bs % 64 == 0 and q.dtype in (torch.float16, torch.bfloat16)
-                and q.size(-1) in (64, 128)):
+                and q.size(-1) % 8 == 0 and q.size(-1) <= 256):
             return self
         if self._fine is None:
             from .utils import crow_col_to_dense, dense_to_crow_col, dense_to_ccol_row, zero_stride
@@ -204,7 +204,7 @@ def _launch_fwd(p, q: Tensor) -> None:
     which would still run on the CUDA-core kernel (an unaligned output view, for instance) is
     reported once per reason: that path is tens of times slower."""
     lib = _lib.lib()
-    if (p.impl == _lib.IMPL_AUTO and p.dtype != _lib.BSA_F32 and p.d in (64, 128)
+    if (p.impl == _lib.IMPL_AUTO and p.dtype != _lib.BSA_F32 and p.d % 8 == 0 and p.d <= 256
             and p.block_size == 64):
         why = lib.bsa_fwd_why_not_sm100(C.byref(p))
         if why and why not in _warned_fallback:

@@ -276,3 +276,22 @@ def test_sm100_padding_may_hold_nan_or_inf(D):
     _wait_status_clean()
     assert_out_close(out, ref)
     assert_lse_close(lse, ref_lse)
+
+
+@pytest.mark.parametrize("D", [48, 96, 160, 192, 256])
+@pytest.mark.parametrize("B,Hq,Hkv,Sq,Sk,dtype,seq_dim,pk", [CASES[1], CASES[2], CASES[4], CASES[7]])
+def test_sm100_forward_other_head_dims(B, Hq, Hkv, Sq, Sk, dtype, seq_dim, pk, D):
+    """The reference's head-dim matrix (tests/test_sparse_attn.py: 48 .. 256) on the tensor-core
+    forward: a head narrower than the kernel's 64 / 128 / 256 columns is padded with zeros by the
+    TMA loads and only its real columns are stored."""
+    bs = pk["block_size"]
+    shape = (lambda h, s: (B, h, s, D)) if seq_dim == 2 else (lambda h, s: (B, s, h, D))
+    q, k, v = seeded_qkv(23, shape(Hq, Sq), shape(Hkv, Sk), dtype)
+    bm = O.block_mask(Hq, Sk, **pk)
+    ref, ref_lse = O.block_sparse_attention(q, k, v, bm, bs, None, seq_dim=seq_dim, causal=pk.get("causal", True))
+    mod = _module(Hq, Sk, pk, seq_dim=seq_dim, impl="sm100")
+    with torch.no_grad():
+        out, lse = mod(q.cuda(), k.cuda(), v.cuda(), return_lse=True)
+    _wait_status_clean()
+    assert_out_close(out, ref)
+    assert_lse_close(lse, ref_lse)
