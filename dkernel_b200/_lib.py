@@ -36,7 +36,7 @@ class FwdParams(C.Structure):
         + [(n, _vp) for n in ("q_start", "q_end", "k_start", "k_end", "crow", "col")]
         + [(n, _i64) for n in ("crow_sh", "col_sh")]
         + [(n, _i32) for n in ("h_pat", "n_rows", "block_size", "causal", "row_mode", "dtype", "impl")]
-        + [("sm_scale", _f32)]
+        + [("sm_scale", _f32), ("col_bits", _vp), ("col_bits_sh", _i64), ("fine_block", _i32)]
     )
 
 

@@ -73,6 +73,11 @@ int bsa_fwd(const bsa_fwd_params* p, void* stream) {
       return BSA_E_UNSUPPORTED;
     }
   }
+  if (p->fine_block != 0) {
+    set_error("bsa_fwd: a coarsened fine-block layout (fine_block = %d) is only read by the tcgen05 kernel; "
+              "pass the pattern's own layout to the generic kernel", p->fine_block);
+    return BSA_E_UNSUPPORTED;
+  }
   return generic_fwd(p, s);
 }
 
@@ -82,6 +87,7 @@ int bsa_bwd(const bsa_bwd_params* p, void* stream) {
   if (rc) return rc;
   BSA_CHECK_ARG(p->f.lse && p->d_o && p->dq && p->dk && p->dv && p->delta && p->ccol && p->row,
                 "bsa_bwd: null pointer (lse, dO, dQ, dK, dV, delta and the CSC layout are required)");
+  BSA_CHECK_ARG(p->f.fine_block == 0, "bsa_bwd: pass the pattern's own layout, not a coarsened fine-block one");
   BSA_CHECK_ARG(!p->f.q_start && !p->f.k_start && p->f.row_mode == BSA_ROWS_BY_TILE,
                 "bsa_bwd: padded / packed batches have no backward "
                 "(as in dkernel/ops/__init__.py:57-58,79-80)");

@@ -43,6 +43,7 @@ struct Plan {
   int n;                     // number of kv blocks in list
   int b, kvh;
   int head[2], qblk[2], hvalid[2];
+  int cbeg[2];               // first CSR entry of each half's pattern row (fine-block patterns)
   int q_start, q_len, k_start, k_len, past;
   uint16_t list[kMaxList];   // block | attended-by-half-0 << 14 | attended-by-half-1 << 15
 };
@@ -132,6 +133,7 @@ __device__ __forceinline__ void build_plan(const bsa_fwd_params& p, int mode, in
   const int nkb = min((k_len + kBS - 1) / kBS, kMaxList);
   bits[0][lane] = 0u;
   bits[1][lane] = 0u;
+  int cbeg[2] = {0, 0};
   __syncwarp();
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
@@ -143,6 +145,7 @@ __device__ __forceinline__ void build_plan(const bsa_fwd_params& p, int mode, in
     const int32_t* cr = p.crow + (int64_t)hp * p.crow_sh;
     const int32_t* cols = p.col + (int64_t)hp * p.col_sh;
     const int c_beg = __ldg(cr + row), c_end = __ldg(cr + row + 1);
+    cbeg[t] = c_beg;
     const int q_pos_last = past + min(q_first + kBS, q_len) - 1;
     for (int i = c_beg + lane; i < c_end; i += 32) {
       const int blk = __ldg(cols + i);
@@ -183,13 +186,17 @@ __device__ __forceinline__ void build_plan(const bsa_fwd_params& p, int mode, in
     pl->head[0] = head[0]; pl->head[1] = head[1];
     pl->qblk[0] = qblk[0]; pl->qblk[1] = qblk[1];
     pl->hvalid[0] = hvalid[0]; pl->hvalid[1] = hvalid[1];
+    pl->cbeg[0] = cbeg[0]; pl->cbeg[1] = cbeg[1];
     pl->q_start = q_start; pl->q_len = q_len; pl->k_start = k_start; pl->k_len = k_len;
     pl->past = past;
   }
   __syncwarp();
 }
 
-template <bool BF16, int D>
+// FB: 0, or the pattern's own block size (16 or 32) when it is finer than the 64-token tiles: the
+// CSR then describes the pattern coarsened to 64 x 64 blocks and col_bits holds, per CSR entry,
+// one bit per (sub-row, sub-column) pair of the block (bit a * (64/FB) + b).
+template <bool BF16, int D, int FB>
 __global__ void __launch_bounds__(kThreadsP, D <= 128 ? 2 : 1)
 fwd_persist_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tmap4 tmK,
                    const __grid_constant__ Tmap4 tmV, bsa_fwd_params p, int mode, int n_items,
@@ -415,6 +422,14 @@ fwd_persist_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tm
         continue;
       }
       float m_used = -INFINITY, l = 0.f;
+      // fine-block patterns: this half's entries of the tile are a prefix of its CSR row, in order
+      constexpr int kF = FB ? kBS / FB : 1;                  // sub-blocks per side
+      constexpr uint32_t kFull = (1u << kF) - 1u;
+      const int32_t* fbits = nullptr;
+      if (FB) {
+        const int hp = pattern_head(head, p.h_pat, p.hq, p.hkv);
+        fbits = p.col_bits + (int64_t)hp * p.col_bits_sh + pl->cbeg[t];
+      }
       for (int j = 0; j < n; ++j, ++g) {
         const int s = g & 1;
         // everything that only depends on the block list is done before the barrier probe
@@ -423,6 +438,8 @@ fwd_persist_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tm
         const bool att = ((ent >> (14 + t)) & 1u) != 0 && hvalid;
         int lim = k_len - kbase;
         if (p.causal) lim = min(lim, qpos - kbase + 1);
+        uint32_t cm = kFull;     // which sub-columns this row attends inside the block
+        if (FB && att) cm = ((uint32_t)__ldg(fbits++) >> ((rr / (FB ? FB : 1)) * kF)) & kFull;
         if (!mbar_wait(&tl->qk_done[s], (g >> 1) & 1, wait_status, 423)) { alive = false; break; }
         tc_fence_after();
         uint32_t sv[64];
@@ -438,6 +455,11 @@ fwd_persist_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tm
 #pragma unroll
             for (int c = 0; c < 64; ++c)
               if (c >= lim) sv[c] = 0xff800000u;  // -inf
+          }
+          if (FB && cm != kFull) {
+#pragma unroll
+            for (int c = 0; c < 64; ++c)
+              if (!((cm >> (c / (FB ? FB : 1))) & 1u)) sv[c] = 0xff800000u;
           }
           float m4[4];
 #pragma unroll
@@ -582,6 +604,11 @@ bool sm100_fwd_supported(const bsa_fwd_params* p, const char** why) {
   if (!(p->dtype == BSA_F16 || p->dtype == BSA_BF16)) return no("dtype is not f16/bf16");
   if (p->d < 16 || p->d > 256 || p->d % 8) return no("head dim is not a multiple of 8 in [16, 256]");
   if (p->block_size != kBS) return no("block size is not 64");
+  if (p->fine_block != 0) {
+    if (p->fine_block != 16 && p->fine_block != 32) return no("fine_block is not 16 or 32");
+    if (!p->col_bits) return no("fine_block without col_bits");
+    if (p->d > 128) return no("fine-block patterns are served for head dims up to 128");
+  }
   if (p->sk > kMaxList * kBS) return no("more than 65536 key positions");
   if (!tma_compatible(p->q, 2, p->q_ss, p->q_sh, p->q_sb) ||
       !tma_compatible(p->k, 2, p->k_ss, p->k_sh, p->k_sb) ||
@@ -595,7 +622,7 @@ bool sm100_fwd_supported(const bsa_fwd_params* p, const char** why) {
 }
 
 namespace {
-template <bool BF16, int D>
+template <bool BF16, int D, int FB>
 int launch_fwd(const bsa_fwd_params* p, cudaStream_t s) {
   Tmap4 tmQ, tmK, tmV;
   const uint64_t nb = p->total_q > 0 ? 1 : p->batch;
@@ -631,7 +658,7 @@ int launch_fwd(const bsa_fwd_params* p, cudaStream_t s) {
   int* status = wait_status_ptr();
   if (!status) return BSA_E_CUDA;
   constexpr size_t smem = Geo<D>::kSmem + sizeof(TailP);
-  auto kern = fwd_persist_kernel<BF16, D>;
+  auto kern = fwd_persist_kernel<BF16, D, FB>;
   BSA_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   kern<<<grid, kThreadsP, smem, s>>>(tmQ, tmK, tmV, *p, mode, n_items, tiles_x, head_items, status);
   return check_launch("fwd_persist_kernel");
@@ -640,9 +667,17 @@ int launch_fwd(const bsa_fwd_params* p, cudaStream_t s) {
 
 int sm100_fwd(const bsa_fwd_params* p, cudaStream_t s) {
   const bool bf16 = p->dtype == BSA_BF16;
-  if (p->d <= 64) return bf16 ? launch_fwd<true, 64>(p, s) : launch_fwd<false, 64>(p, s);
-  if (p->d <= 128) return bf16 ? launch_fwd<true, 128>(p, s) : launch_fwd<false, 128>(p, s);
-  return bf16 ? launch_fwd<true, 256>(p, s) : launch_fwd<false, 256>(p, s);
+  if (p->fine_block == 16) {
+    if (p->d <= 64) return bf16 ? launch_fwd<true, 64, 16>(p, s) : launch_fwd<false, 64, 16>(p, s);
+    return bf16 ? launch_fwd<true, 128, 16>(p, s) : launch_fwd<false, 128, 16>(p, s);
+  }
+  if (p->fine_block == 32) {
+    if (p->d <= 64) return bf16 ? launch_fwd<true, 64, 32>(p, s) : launch_fwd<false, 64, 32>(p, s);
+    return bf16 ? launch_fwd<true, 128, 32>(p, s) : launch_fwd<false, 128, 32>(p, s);
+  }
+  if (p->d <= 64) return bf16 ? launch_fwd<true, 64, 0>(p, s) : launch_fwd<false, 64, 0>(p, s);
+  if (p->d <= 128) return bf16 ? launch_fwd<true, 128, 0>(p, s) : launch_fwd<false, 128, 0>(p, s);
+  return bf16 ? launch_fwd<true, 256, 0>(p, s) : launch_fwd<false, 256, 0>(p, s);
 }
 
 }  // namespace bsa

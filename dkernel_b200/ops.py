@@ -48,10 +48,14 @@ class _Plan:
     launchers need to know without touching the device."""
 
     def __init__(self, crow: Tensor, col: Tensor, ccol: Tensor, row: Tensor, block_size: int,
-                 max_row_nnz: int):
+                 max_row_nnz: int, col_bits: Optional[Tensor] = None, fine_block: int = 0):
         self.crow, self.col, self.ccol, self.row = crow, col, ccol, row
         self.block_size = block_size
         self.max_row_nnz = max_row_nnz
+        # a pattern with 16/32-token blocks coarsened to 64-token blocks: per entry of col one bit
+        # per (sub-row, sub-column) pair of the block; only the tensor-core forward reads this form
+        self.col_bits, self.fine_block = col_bits, fine_block
+        self._coarse: Optional["_Plan"] = None
         self._group_shared: Dict[int, bool] = {}
         self._kv_pairs: Dict[Tuple[int, int, int], Optional[Tensor]] = {}
         self._fine: Optional["_Plan"] = None
@@ -67,13 +71,17 @@ class _Plan:
             self._cyclic_nnz[key] = int(dense[:, :, rem::mod].sum(-1).max().item()) if dense.numel() else 0
         return self._cyclic_nnz[key]
 
-    def for_kernels(self, q: Tensor) -> "_Plan":
+    def for_kernels(self, q: Tensor, backward: bool = False) -> "_Plan":
         """The layouts the prefill / backward kernels should read.  The tensor-core kernels work
         on 64 x 64 blocks; a pattern with blocks of 128, 256, ... tokens is the same attention
         as its refinement to 64-token blocks (every block becomes a square of sub-blocks; the
         kernels mask the diagonal per element anyway), so such patterns get refined layouts
-        instead of falling back to the CUDA-core kernels."""
+        instead of falling back to the CUDA-core kernels.  A pattern with 16- or 32-token blocks
+        is coarsened to 64-token blocks with a bit mask per block (forward only)."""
         bs = self.block_size
+        if bs in (16, 32) and not backward and q.dtype in (torch.float16, torch.bfloat16) \
+                and q.size(-1) % 8 == 0 and q.size(-1) <= 128:
+            return self._coarsened()
         if not (bs > 64 and bs % 64 == 0 and q.dtype in (torch.float16, torch.bfloat16)
                 and q.size(-1) % 8 == 0 and q.size(-1) <= 256):
             return self
@@ -91,6 +99,35 @@ class _Plan:
                 lay = [zero_stride(x) for x in lay]
             self._fine = _Plan(lay[0], lay[1], lay[2], lay[3], 64, self.max_row_nnz * f)
         return self._fine
+
+    def _coarsened(self) -> "_Plan":
+        if self._coarse is None:
+            from .utils import crow_col_to_dense, dense_to_crow_col, dense_to_ccol_row, zero_stride
+            bs = self.block_size
+            f = 64 // bs
+            dense = crow_col_to_dense(self.crow, self.col, torch.uint8)          # (H, M, N')
+            n_cols = max(self.ccol.size(1) - 1, dense.size(2))
+            H, M = dense.size(0), dense.size(1)
+            Mp, Np = (M + f - 1) // f * f, (n_cols + f - 1) // f * f
+            dense = torch.nn.functional.pad(dense, (0, Np - dense.size(2), 0, Mp - M))
+            sub = dense.view(H, Mp // f, f, Np // f, f).permute(0, 1, 3, 2, 4).reshape(H, Mp // f, Np // f, f * f)
+            weights = (1 << torch.arange(f * f, device=dense.device, dtype=torch.int32))
+            bits_dense = (sub.to(torch.int32) * weights).sum(-1).to(torch.int32)      # (H, Mc, Nc)
+            coarse = (bits_dense != 0).to(torch.uint8).contiguous()
+            lay = [x.to(torch.int32) for x in
+                   list(dense_to_crow_col(coarse)) + list(dense_to_ccol_row(coarse, include_values=False))]
+            crow_c, col_c = lay[0], lay[1]
+            width = col_c.size(1)
+            pos = torch.arange(width, device=dense.device, dtype=crow_c.dtype)[None].expand(H, -1).contiguous()
+            rows = torch.searchsorted(crow_c[:, 1:].contiguous(), pos, right=True).clamp_(max=coarse.size(1) - 1)
+            hidx = torch.arange(H, device=dense.device)[:, None].expand(-1, width)
+            col_bits = (bits_dense[hidx, rows, col_c.clamp_min(0).long()] * (col_c >= 0)).to(torch.int32).contiguous()
+            max_nnz = int((crow_c[:, 1:] - crow_c[:, :-1]).max().item()) if crow_c.size(1) > 1 else 0
+            if H == 1:
+                lay = [zero_stride(x) for x in lay]
+                col_bits = zero_stride(col_bits)
+            self._coarse = _Plan(lay[0], lay[1], lay[2], lay[3], 64, max_nnz, col_bits=col_bits, fine_block=bs)
+        return self._coarse
 
     def heads_shared_in_group(self, hq: int, hkv: int) -> bool:
         """True when all q heads of a kv group use the same pattern rows (then the
@@ -160,12 +197,18 @@ def _fill_layout(p, plan: _Plan) -> None:
     p.h_pat = plan.crow.size(0)
     p.n_rows = plan.crow.size(1) - 1
     p.block_size = plan.block_size
+    if hasattr(p, "fine_block"):
+        cb = getattr(plan, "col_bits", None)
+        p.col_bits = _lib.ptr(cb)
+        p.col_bits_sh = cb.stride(0) if cb is not None and cb.size(0) > 1 else 0
+        p.fine_block = plan.fine_block if cb is not None else 0
 
 
 def _fwd_params(q, k, v, o, lse, seq_dim, plan: _Plan, sm_scale, causal, row_mode,
-                q_start=None, q_end=None, k_start=None, k_end=None, total_q=0, impl=0):
+                q_start=None, q_end=None, k_start=None, k_end=None, total_q=0, impl=0, kernel_plan=True):
     p = _lib.FwdParams()
-    if impl != _lib.IMPL_GENERIC:
+    own_plan = plan
+    if impl != _lib.IMPL_GENERIC and kernel_plan:
         plan = plan.for_kernels(q)
     p.q, p.k, p.v, p.o, p.lse = _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(lse)
     p.q_sb, p.q_ss, p.q_sh = _strides_bsh(q, seq_dim)
@@ -193,6 +236,9 @@ def _fwd_params(q, k, v, o, lse, seq_dim, plan: _Plan, sm_scale, causal, row_mod
     p.dtype = _lib.dtype_code(q.dtype)
     p.impl = impl
     p.sm_scale = float(sm_scale)
+    if plan.fine_block and impl == _lib.IMPL_AUTO and _lib.lib().bsa_fwd_why_not_sm100(C.byref(p)):
+        # the coarsened form is only read by the tensor-core kernel: hand the pattern's own layout on
+        _fill_layout(p, own_plan)
     return p
 
 
@@ -479,7 +525,7 @@ def _backward(ctx, do: Tensor, dlse: Optional[Tensor], dq=None, dk=None, dv=None
     q, k, v, o, lse = ctx.saved_tensors
     seq_dim, plan = ctx.seq_dim, ctx.plan
     if ctx.bwd_impl != _lib.IMPL_GENERIC:
-        plan = plan.for_kernels(q)
+        plan = plan.for_kernels(q, backward=True)
     do = _tma_friendly(do)
     if dq is None:
         dq = torch.empty_like(q, memory_format=torch.contiguous_format)
@@ -491,7 +537,7 @@ def _backward(ctx, do: Tensor, dlse: Optional[Tensor], dq=None, dk=None, dv=None
         assert t.stride(-1) == 1, f"{n} must be contiguous in the head dimension"
     bp = _lib.BwdParams()
     bp.f = _fwd_params(q, k, v, o, lse, seq_dim, plan, ctx.sm_scale, ctx.causal, _lib.ROWS_BY_TILE,
-                       impl=ctx.bwd_impl)
+                       impl=ctx.bwd_impl, kernel_plan=False)
     bp.d_o = _lib.ptr(do)
     bp.do_sb, bp.do_ss, bp.do_sh = _strides_bsh(do, seq_dim)
     if dlse is not None:

@@ -134,6 +134,15 @@ typedef struct {
   int32_t dtype;              /* BSA_F16 / BSA_BF16 / BSA_F32                   */
   int32_t impl;               /* BSA_IMPL_*                                     */
   float sm_scale;
+  /* Patterns with 16- or 32-token blocks on the tensor-core forward (BSA_IMPL_SM100 /
+   * AUTO only): crow/col describe the pattern coarsened to block_size = 64, fine_block is
+   * the pattern's own block size and col_bits holds, for every entry of col, one bit per
+   * (sub-row a, sub-column b) pair of the 64 x 64 block, bit a * (64 / fine_block) + b.
+   * 0 / NULL = the pattern's blocks are the kernel's.  The reference runs such patterns
+   * through merged "micro_M" layouts (dkernel/utils.py:262-310).                       */
+  const int32_t* col_bits;
+  int64_t col_bits_sh;
+  int32_t fine_block;
 } bsa_fwd_params;
 
 int bsa_fwd(const bsa_fwd_params* p, void* stream);

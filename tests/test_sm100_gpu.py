@@ -295,3 +295,82 @@ def test_sm100_forward_other_head_dims(B, Hq, Hkv, Sq, Sk, dtype, seq_dim, pk, D
     _wait_status_clean()
     assert_out_close(out, ref)
     assert_lse_close(lse, ref_lse)
+
+
+FINE_CASES = [
+    # B, Hq, Hkv, Sq, Sk, D, dtype, seq_dim, pattern kwargs
+    (1, 2, 2, 512, 512, 128, torch.bfloat16, 1, dict(block_size=16, local_blocks=4, vert_stride=4)),
+    (2, 4, 2, 320, 320, 64, torch.float16, 2, dict(block_size=32, local_blocks=2, vert_stride=3, num_kv_heads=2)),
+    (1, 3, 3, 1000, 1000, 128, torch.bfloat16, 1, dict(block_size=32, local_blocks=5, vert_stride=7)),
+    (1, 2, 2, 256, 640, 96, torch.bfloat16, 1, dict(block_size=16, local_blocks=3, vert_stride=5)),
+    (1, 2, 2, 256, 256, 128, torch.bfloat16, 2, dict(block_size=16, local_blocks=2, vert_stride=3, causal=False)),
+    (1, 4, 4, 77, 77, 64, torch.float16, 1, dict(block_size=16, local_blocks=2, vert_stride=2)),
+]
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,Sq,Sk,D,dtype,seq_dim,pk", FINE_CASES)
+def test_sm100_forward_with_16_and_32_token_blocks(B, Hq, Hkv, Sq, Sk, D, dtype, seq_dim, pk):
+    """Patterns with blocks finer than the kernel's 64-token tiles: the layout is coarsened to
+    64 x 64 blocks on the host side and the kernel masks with one bit per sub-block; forward on the
+    tensor cores (impl="sm100" would raise otherwise), backward on the CUDA-core kernels."""
+    from helpers import assert_grad_close
+    from dkernel_b200 import _lib
+    bs = pk["block_size"]
+    causal = pk.get("causal", True)
+    shape = (lambda h, s: (B, h, s, D)) if seq_dim == 2 else (lambda h, s: (B, s, h, D))
+    q, k, v, do = seeded_qkv(27, shape(Hq, Sq), shape(Hkv, Sk), dtype, with_do=True)
+    bm = O.block_mask(Hq, Sk, **pk)
+    qf, kf, vf = (t.detach().clone().float().requires_grad_() for t in (q, k, v))
+    nq = (Sq + bs - 1) // bs
+    dense = torch.from_numpy(bm[:, :nq]).repeat_interleave(bs, 1).repeat_interleave(bs, 2)[:, :Sq, :Sk].bool()
+    if causal:
+        dense = dense & (torch.arange(Sq)[:, None] + (Sk - Sq) >= torch.arange(Sk)[None, :])
+    ref, ref_lse = O.masked_dense_attention(qf, kf, vf, dense[None].to(torch.uint8), None, seq_dim=seq_dim,
+                                            return_lse=True)
+    ref.backward(do.float())
+    mod = _module(Hq, Sk, pk, seq_dim=seq_dim, impl="sm100", bwd_impl="generic")
+    assert mod._plan().for_kernels(q.cuda()).fine_block == bs
+    qg, kg, vg = (t.cuda().requires_grad_() for t in (q, k, v))
+    out, lse = mod(qg, kg, vg, return_lse=True)
+    out.backward(do.cuda())
+    _wait_status_clean()
+    assert_out_close(out, ref)
+    assert_lse_close(lse, ref_lse)
+    assert_grad_close(qg.grad, qf.grad, "dq")
+    assert_grad_close(kg.grad, kf.grad, "dk")
+    assert_grad_close(vg.grad, vf.grad, "dv")
+
+
+def test_sm100_fine_block_user_pattern_varlen_and_padded():
+    """A Bernoulli pattern of 16-token blocks on the packed and padded routes of the tensor-core forward."""
+    from dkernel_b200 import SparseAttention
+    H, D, bs, nb = 4, 128, 16, 64
+    g = torch.Generator().manual_seed(4)
+    pat = torch.rand(H, nb, nb, generator=g) < 0.25
+    pat |= torch.eye(nb, dtype=torch.bool)[None]
+    pat &= torch.tril(torch.ones(nb, nb, dtype=torch.bool))[None]
+    import warnings
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        mod = SparseAttention(bs, pat.cuda(), impl="sm100")
+    lens = [512, 100, 333, 64, 1, 700]
+    T = sum(lens)
+    q, k, v = seeded_qkv(5, (T, H, D), (T, H, D), torch.bfloat16)
+    cu = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32)
+    ref, ref_lse = O.varlen_attention(q.float(), k.float(), v.float(), cu, pat.numpy().astype(np.uint8), bs)
+    out, lse = mod(q.cuda(), k.cuda(), v.cuda(), cu_seqlen_k=cu.cuda(), return_lse=True)
+    _wait_status_clean()
+    assert_out_close(out, ref)
+    assert_lse_close(lse, ref_lse)
+    B, S = 3, 1024
+    q, k, v = seeded_qkv(6, (B, S, H, D), (B, S, H, D), torch.bfloat16)
+    lens_t, left = torch.tensor([1000, 77, 300]), torch.tensor([24, 900, 0])
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        mod2 = SparseAttention(bs, pat.cuda(), seq_dim=1, impl="sm100")
+    ref, ref_lse = O.padded_attention(q.float(), k.float(), v.float(), pat.numpy().astype(np.uint8), bs,
+                                      left_paddings=left, seqlens=lens_t, seq_dim=1)
+    out, lse = mod2(q.cuda(), k.cuda(), v.cuda(), left_paddings=left.cuda(), seqlens=lens_t.cuda(), return_lse=True)
+    _wait_status_clean()
+    assert_out_close(out, ref)
+    assert_lse_close(lse, ref_lse)
