@@ -536,7 +536,9 @@ def run_decode(args, world, rank):
     from dkernel_b200 import LocalStrideSparseAttention, _lib
     from dkernel_b200.dist import (ShardedDecoder, kv_shard_ranges, pack_kv_shard, pack_kv_shard_cyclic,
                                    sharded_decode)
-    cfg = WORKLOADS["decode"]
+    cfg = dict(WORKLOADS["decode"])
+    if getattr(args, "decode_batch", 0):
+        cfg["B"] = args.decode_batch        # a smaller batch of the same shapes (profiler captures)
     B, S, Hq, Hkv, D, bs = cfg["B"], cfg["S"], cfg["Hq"], cfg["Hkv"], cfg["D"], cfg["block"]
     lens = decode_lens(cfg)
     attn = LocalStrideSparseAttention(Hq, S, bs, cfg["local"], cfg["stride"], num_kv_heads=Hkv, seq_dim=1)
@@ -578,7 +580,7 @@ def run_decode(args, world, rank):
         ms, spread, clocks, _ = timed(graph_step, steps, args.warmup, world)
         # the same step against an e4m3 K/V cache (per-tensor scales): half the K/V bytes
         us_fp8 = gbs_fp8 = None
-        if hasattr(torch, "float8_e4m3fn"):
+        if hasattr(torch, "float8_e4m3fn") and not getattr(args, "no_fp8", False):
             ksc = vsc = 6.0 / 448.0              # N(0,1) data: |x| < 6
             bufs8 = [((k.float() / ksc).to(torch.float8_e4m3fn), (v.float() / vsc).to(torch.float8_e4m3fn))
                      for k, v in bufs]
@@ -817,6 +819,38 @@ def run_fwd_d64(args, world, rank):
             "shape": "B4 S8192 Hq32 Hkv8 D64 bf16, config 2's pattern", "sm_mhz": clocks.get("sm_mhz")}
 
 
+def run_ring(args, world, rank):
+    """Context-parallel training step (N > 1): BASELINE config 3's problem (B=2, S=8192, H=32, D=128) with
+    the SEQUENCE split over the ranks (ring attention: K/V chunks round the ring over NCCL send/recv, LSE
+    merge, dK/dV accumulators round the ring); fixed total size ("strong")."""
+    from dkernel_b200 import _lib
+    from dkernel_b200.dist import ContextParallelSparseAttention
+    cfg = WORKLOADS["train"]
+    B, S, H, D = cfg["B"], cfg["S"], cfg["Hq"], cfg["D"]
+    cp = ContextParallelSparseAttention(H, S, cfg["block"], cfg["local"], cfg["stride"], seq_dim=1)
+    a, b_ = cp.bounds[rank]
+    g = torch.Generator(device="cuda").manual_seed(99 + rank)
+    q, k, v, do = (torch.randn((B, b_ - a, H, D), generator=g, device="cuda").to(torch.bfloat16) for _ in range(4))
+    q.requires_grad_(), k.requires_grad_(), v.requires_grad_()
+
+    def step():
+        q.grad = k.grad = v.grad = None
+        cp(q, k, v).backward(do)
+
+    def step_fwd():
+        with torch.no_grad():
+            cp(q, k, v)
+
+    steps = max(2, args.steps // 4)
+    ms_fwd, _, _, _ = timed(step_fwd, steps, 3, world, repeats=3)
+    ms, spread, clocks, _ = timed(step, steps, 3, world, repeats=3)
+    assert _lib.wait_status() == 0
+    tiles = int(local_stride_mask_np(H, S, cfg["block"], cfg["local"], cfg["stride"], H).sum()) * B
+    flops = tiles * tile_flops(cfg["block"], D) * 3.5
+    return {"ms": ms, "fwd_ms": ms_fwd, "tflops": flops / (ms * 1e-3) / 1e12, "steps": steps, **spread,
+            "sm_mhz": clocks.get("sm_mhz")}
+
+
 def compact(line, keys=()):
     """A sub-record of the combined line: numbers only, no prose."""
     c = line["config"]
@@ -897,9 +931,13 @@ def run_all(args, world, rank):
         for name, fn in (("train_c3", train), ("decode_c4", decode), ("varlen_c5", varlen), ("prefill_d64", d64),
                          ("reference_triton_c2", reference_triton)):
             guarded(name, fn)
-    else:
+
+    def ring():
+        sub["train_c3_ring"] = run_ring(args, world, rank)
+
+    if world > 1:
         for name, fn in (("decode_c4_kv_sharded", decode), ("varlen_c5_strong", varlen),
-                         ("prefill_c2_strong", prefill_strong)):
+                         ("prefill_c2_strong", prefill_strong), ("train_c3_ring", ring)):
             guarded(name, fn)
     _free()
     line["config"]["sub"] = sub
@@ -1016,6 +1054,9 @@ def main():
     ap.add_argument("--workload", default="all", choices=["all"] + list(WORKLOADS))
     ap.add_argument("--repeats", type=int, default=REPEATS, help="timed regions of K steps each (median reported)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--decode-batch", type=int, default=0,
+                    help="decode: sequences per step instead of config 4's 64 (small case for profiler captures)")
+    ap.add_argument("--no-fp8", action="store_true", help="decode: skip the e4m3 K/V measurement")
     ap.add_argument("--e2e-chunk", type=int, default=E2E_CHUNK,
                     help="prefill: query rows per pipelined chunk of the end-to-end step")
     args = ap.parse_args()
