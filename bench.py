@@ -188,10 +188,32 @@ def tile_flops(block, D):
 
 
 # --------------------------------------------------------------------------- GPU arm
+def bind_to_gpu_cpus(local_rank: int):
+    """Pin this process to the host cores NVML reports as local to its GPU, before any pinned host
+    memory is allocated (first touch then places the staging buffers on that NUMA node).  Returns
+    the number of cores bound to, or None when NVML or the affinity call is unavailable."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        uuid = str(torch.cuda.get_device_properties(local_rank).uuid)
+        uuid = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
+        h = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (os.cpu_count() + 63) // 64)
+        cpus = {64 * i + b for i, w in enumerate(words) for b in range(64) if (int(w) >> b) & 1}
+        cpus &= set(os.sched_getaffinity(0))
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+            return len(cpus)
+    except Exception:
+        pass
+    return None
+
+
 def setup_dist(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    args.bound_cpus = bind_to_gpu_cpus(local_rank) if world > 1 else None
     if world > 1:
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
@@ -446,6 +468,7 @@ def run_prefill(args, world, rank, strong=False, with_e2e=True):
     line["e2e"] = {"value": flops_all / (ms_e2e_max * 1e-3) / 1e12, "unit": "TFLOP/s",
                    "ms_per_step": ms_e2e_max, "steps_per_region": e2e_steps,
                    "pipeline": f"chunked prefill, {chunk} query rows per module call, copies overlapped",
+                   "host_cores_bound": getattr(args, "bound_cpus", None),
                    "h2d_bytes_per_step": (hq_host.numel() + hk_host.numel() + hv_host.numel()) * 2,
                    "d2h_bytes_per_step": out_host.numel() * 2 + lse_host.numel() * 4}
     return line
