@@ -6,15 +6,15 @@
 // payload, 4 bytes = step number}: a word is written by one store and read by one load, so a
 // reader that sees the current step number in a word also sees its payload, whatever the order in
 // which the words of a row arrive.  Per step, on every rank r:
-//   phase 1  each thread turns 16 bytes of this rank's partial row into four such words and
-//            stores them into slot r of EVERY rank's buffer (two 16-byte stores per destination,
-//            remote for the peers);
-//   phase 2  the same thread reads the words of its 16 bytes from the W slots of the LOCAL
-//            buffer, spinning -- bounded -- on words whose step number is not the current one,
-//            merges the W partials with the semantics of combine_attn_partitions
-//            (dkernel/interface.py:319-324) and writes the result.
-// Only stores cross NVLink; every load is from local memory.  A thread pushes before it waits,
-// and waits only for words written by phase 1 of the peers, which waits for nothing: the kernel
+//   push   each thread turns 16 bytes of this rank's partial row into four such words and stores
+//          them into slot r of every PEER's buffer (two 16-byte stores per destination); its own
+//          copy stays in registers;
+//   wait   the same thread reads the words of its 16 bytes from the peers' slots of the LOCAL
+//          buffer, spinning -- bounded -- on words whose step number is not the current one,
+//          merges the W partials with the semantics of combine_attn_partitions
+//          (dkernel/interface.py:319-324) and writes the result.
+// Only stores cross NVLink; every load is from local memory.  A thread's first action is a push and
+// every wait is for words that some thread pushes before it waits for anything: the kernel
 // cannot deadlock.  The step number lives in the buffer and is advanced by the last CTA to
 // finish, so a captured CUDA graph can be replayed.  Slots are double buffered by step parity:
 // a rank can be at most one step ahead of a peer (finishing a step needs that peer's words of the
@@ -89,15 +89,20 @@ xchg_merge_kernel(XPtrs ptrs, int world, int rank, int64_t rows, int d, const T*
   const size_t slot_o_w = (size_t)(par * world + rank) * L.slot_o;     // where this rank writes
   const size_t slot_l_w = (size_t)(par * world + rank) * L.slot_lse;
 
-  // ---- phase 1: this rank's rows -> slot `rank` of every rank's buffer
-  for (int64_t i = tid; i < n_items; i += kXThreads) {
+  // ---- per 16 bytes of a row: this rank's words go to slot `rank` of every PEER's buffer (the
+  // thread keeps its own copy in registers), then the same 16 bytes of every peer are awaited in
+  // the local buffer.  A thread's first action is a push, so no wait can be circular.
+  const uint8_t* po = mine + L.o_off + (size_t)par * world * L.slot_o;
+  const uint8_t* pl = mine + L.lse_off + (size_t)par * world * L.slot_lse;
+  bool failed = false;
+  for (int64_t i = tid; i < n_items && !failed; i += kXThreads) {
     const int64_t r = r0 + i / cpr;
     const int c = (int)(i % cpr);
     uint4 v;
     uint32_t l;
     if (stage_o) {
       v = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(stage_o) + (r * d + c * 8) * 2);
-      l = c == 0 ? __float_as_uint(stage_lse[r]) : 0u;
+      l = __float_as_uint(stage_lse[r]);
     } else {
       // merge the split-KV partials of this rank first (each normalised by its own LSE)
       float mx = -INFINITY;
@@ -121,26 +126,24 @@ xchg_merge_kernel(XPtrs ptrs, int world, int rank, int64_t rows, int d, const T*
       for (int j = 0; j < 8; ++j) e[j] = Elem<T>::from_f(acc[j] * inv);
       l = __float_as_uint(den > 0.f ? ms + __logf(den) : -INFINITY);
     }
-    const size_t off = L.o_off + slot_o_w + ((size_t)(r * d + c * 8) * 2) * 2;
+    const size_t off = ((size_t)(r * d + c * 8) * 2) * 2;
     for (int w = 0; w < world; ++w) {
+      if (w == rank) continue;
       uint8_t* dst = ptrs.buf[w];
-      st_words(dst + off, v.x, step, v.y, step);
-      st_words(dst + off + 16, v.z, step, v.w, step);
+      st_words(dst + L.o_off + slot_o_w + off, v.x, step, v.y, step);
+      st_words(dst + L.o_off + slot_o_w + off + 16, v.z, step, v.w, step);
       if (c == 0) st_word(dst + L.lse_off + slot_l_w + (size_t)r * 8, l, step);
     }
-  }
-
-  // ---- phase 2: the same 16 bytes of every rank's partial, as soon as they have landed here
-  const uint8_t* po = mine + L.o_off + (size_t)par * world * L.slot_o;
-  const uint8_t* pl = mine + L.lse_off + (size_t)par * world * L.slot_lse;
-  bool failed = false;
-  for (int64_t i = tid; i < n_items && !failed; i += kXThreads) {
-    const int64_t r = r0 + i / cpr;
-    const int c = (int)(i % cpr);
-    const size_t off = ((size_t)(r * d + c * 8) * 2) * 2;
     uint32_t pay[kXMaxWorld][4];
     float lse_w[kXMaxWorld];
-    uint32_t pending = (1u << world) - 1u;
+    uint32_t pending = ((1u << world) - 1u) & ~(1u << rank);
+#pragma unroll
+    for (int w = 0; w < kXMaxWorld; ++w) {
+      if (w == rank) {
+        pay[w][0] = v.x; pay[w][1] = v.y; pay[w][2] = v.z; pay[w][3] = v.w;
+        lse_w[w] = __uint_as_float(l);
+      }
+    }
     const uint64_t t0 = global_timer_ns();
     while (pending) {
 #pragma unroll
@@ -148,10 +151,10 @@ xchg_merge_kernel(XPtrs ptrs, int world, int rank, int64_t rows, int d, const T*
         if (w < world && (pending >> w) & 1u) {
           const uint4 a = ld_words(po + (size_t)w * L.slot_o + off);
           const uint4 b = ld_words(po + (size_t)w * L.slot_o + off + 16);
-          const uint2 l = ld_word(pl + (size_t)w * L.slot_lse + (size_t)r * 8);
-          if (a.y == step && a.w == step && b.y == step && b.w == step && l.y == step) {
+          const uint2 l2 = ld_word(pl + (size_t)w * L.slot_lse + (size_t)r * 8);
+          if (a.y == step && a.w == step && b.y == step && b.w == step && l2.y == step) {
             pay[w][0] = a.x; pay[w][1] = a.z; pay[w][2] = b.x; pay[w][3] = b.z;
-            lse_w[w] = __uint_as_float(l.x);
+            lse_w[w] = __uint_as_float(l2.x);
             pending &= ~(1u << w);
           }
         }
