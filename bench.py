@@ -845,7 +845,7 @@ def run_fwd_d64(args, world, rank):
 def run_ring(args, world, rank):
     """Context-parallel training step (N > 1): BASELINE config 3's problem (B=2, S=8192, H=32, D=128) with
     the SEQUENCE split over the ranks (ring attention: K/V chunks round the ring over NCCL send/recv, LSE
-    merge, dK/dV accumulators round the ring); fixed total size ("strong")."""
+    merge, dK/dV contributions sent to the chunk owner); fixed total size ("strong")."""
     from dkernel_b200 import _lib
     from dkernel_b200.dist import ContextParallelSparseAttention
     cfg = WORKLOADS["train"]

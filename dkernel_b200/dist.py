@@ -15,8 +15,9 @@ Three schemes, matching what the attention path allows:
   ``sharded_decode`` (one NCCL all-gather + the fused merge kernel).
 * **Context-parallel (ring) prefill / training** -- the sequence is cut into one
   chunk per rank; K/V chunks travel round the ring while every rank attends its
-  q chunk to the chunk it currently holds, partial results are merged by LSE and
-  gradients travel back the same way.  This is the multi-GPU form of what the
+  q chunk to the chunk it currently holds, partial results are merged by LSE, and in
+  the backward pass each rank sends its dK/dV contribution for a chunk straight to the
+  chunk's owner.  This is the multi-GPU form of what the
   reference simulates on one GPU in tests/test_seq_partition.py:83-139.
 
 The planning functions and the ring schedule are pure Python / torch so that they
@@ -311,9 +312,13 @@ def ring_backward(q: Tensor, k: Tensor, v: Tensor, o: Tensor, lse: Tensor, do: T
     """Backward pass of ring attention.  backward_chunk(q, k_s, v_s, o, lse, do, dlse, r, s) ->
     (dq, dk_s, dv_s) evaluates the gradients of the (r, s) chunk pair from the MERGED output and
     LSE of the forward pass (the probabilities exp(S - lse) are then already globally normalised,
-    so the pair's contributions simply add up).  dQ accumulates locally in fp32; the dK/dV
-    accumulator travels round the ring with its K/V chunk and is home after ``world`` hops."""
+    so the pair's contributions simply add up).  dQ accumulates locally in fp32.  The K/V chunks
+    travel round the ring as in the forward pass; the dK/dV contribution a rank computes for
+    another rank's chunk is sent straight to that rank (one message per chunk pair, in the
+    gradients' own dtype), which adds the messages to its fp32 accumulator in step order, so the
+    result does not depend on timing."""
     world, rank = dist.get_world_size(group), dist.get_rank(group)
+    peer = (lambda r_: dist.get_global_rank(group, r_)) if group is not None else (lambda r_: r_)
     kv = torch.stack([k, v]).contiguous()
     dkv = torch.zeros(kv.shape, dtype=torch.float32, device=kv.device)
     dq = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
@@ -322,18 +327,30 @@ def ring_backward(q: Tensor, k: Tensor, v: Tensor, o: Tensor, lse: Tensor, do: T
         if t < world - 1:
             nxt = torch.empty_like(kv)
             reqs = _ring_exchange(kv, nxt, group)
+        part = None
         if active:
             dq_p, dk_p, dv_p = backward_chunk(q, kv[0], kv[1], o, lse, do, dlse, rank, s)
             dq += dq_p
-            dkv[0] += dk_p
-            dkv[1] += dv_p
+            if t == 0:
+                dkv[0] += dk_p
+                dkv[1] += dv_p
+            else:
+                part = torch.stack([dk_p, dv_p])
+        # this step's chunk belongs to rank s; the rank that holds MY chunk now is (rank + t) % world
+        src = (rank + t) % world
+        src_active = t > 0 and ((not causal) or rank <= src)     # does it compute a pair with my chunk?
+        ops, got = [], None
+        if part is not None:
+            ops.append(dist.P2POp(dist.isend, part, peer(s), group))
+        if src_active:
+            got = torch.empty((2,) + tuple(k.shape), dtype=k.dtype, device=k.device)
+            ops.append(dist.P2POp(dist.irecv, got, peer(src), group))
+        for r_ in (dist.batch_isend_irecv(ops) if ops else []):
+            r_.wait()
+        if got is not None:
+            dkv += got
         for r_ in reqs:
             r_.wait()
-        # the gradient accumulator follows its chunk (one hop more than the chunk itself)
-        dnxt = torch.empty_like(dkv)
-        for r_ in _ring_exchange(dkv, dnxt, group):
-            r_.wait()
-        dkv = dnxt
         if nxt is not None:
             kv = nxt
     return dq.to(q.dtype), dkv[0].to(k.dtype), dkv[1].to(v.dtype)
@@ -366,7 +383,7 @@ class ContextParallelSparseAttention(torch.nn.Module):
     of that chunk pair (``get_sparse_attn_mask`` with ``q_start_position`` / ``kv_start_position``,
     dkernel/utils.py:161-169,185-191), causal only on the diagonal pair; the K/V chunks travel
     round the ring over NCCL send/recv while the previous pair is computed, partial results are
-    merged by LSE, and the backward pass sends the dK/dV accumulators round the same ring.
+    merged by LSE, and the backward pass sends every dK/dV contribution to the owner of its chunk.
 
     forward(q, k, v, sm_scale=None, return_lse=False): tensors are this rank's chunk,
     (B, S/world, H, D) for ``seq_dim=1`` or (B, H, S/world, D) for ``seq_dim=2``."""

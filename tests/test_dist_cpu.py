@@ -101,8 +101,8 @@ def test_two_ranks_gloo():
 
 
 def _ring_worker(rank, world, port, ret):
-    """Ring attention schedule (K/V chunks round the ring, LSE merge, dK/dV accumulators round
-    the ring) with the oracle as the per-chunk compute; compared with full-sequence autograd."""
+    """Ring attention schedule (K/V chunks round the ring, LSE merge, dK/dV contributions sent to
+    the chunk's owner) with the oracle as the per-chunk compute; compared with full-sequence autograd."""
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
