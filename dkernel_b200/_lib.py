@@ -36,7 +36,8 @@ class FwdParams(C.Structure):
         + [(n, _vp) for n in ("q_start", "q_end", "k_start", "k_end", "crow", "col")]
         + [(n, _i64) for n in ("crow_sh", "col_sh")]
         + [(n, _i32) for n in ("h_pat", "n_rows", "block_size", "causal", "row_mode", "dtype", "impl")]
-        + [("sm_scale", _f32), ("col_bits", _vp), ("col_bits_sh", _i64), ("fine_block", _i32)]
+        + [("sm_scale", _f32), ("col_bits", _vp), ("col_bits_sh", _i64), ("fine_block", _i32),
+           ("tile_counter", _vp)]
     )
 
 
@@ -117,7 +118,7 @@ def lib() -> C.CDLL:
             fn = getattr(l, name)  # AttributeError if the symbol is not exported
             fn.restype = res
             fn.argtypes = args
-        if l.bsa_abi_version() != 2:
+        if l.bsa_abi_version() != 3:
             raise RuntimeError("libbsa_b200.so has an unexpected ABI version; rebuild it")
         _lib = l
     return _lib

@@ -238,27 +238,36 @@ fwd_persist_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tm
   const uint32_t tmem = tl->tmem_base;
   const uint32_t tS[2] = {tmem, tmem + 64};
   const uint32_t tO = tmem + 128;
-  // Round r hands items [r * grid, (r + 1) * grid) to the CTAs.
-  // -2: no more rounds; -1: nothing for this CTA in this round.
-  auto item_of = [&](int r) -> int {
-    const long long base = (long long)r * gridDim.x;
-    if (base >= n_items) return -2;
-    const long long it = base + blockIdx.x;
-    return it < n_items ? (int)it : -1;
-  };
 
   if (warp == kWarpPlan) {
     // ============================================================ planner
-    int k = 0;
-    for (int r = 0;; ++r) {
-      const int item = item_of(r);
-      if (item == -2) break;
-      if (item < 0) continue;
+    // The planner alone decides which items this CTA works on; the other warps follow the
+    // plans until one is marked as the end (valid < 0).  With a tile counter the CTAs draw
+    // items from it as they go (long tiles first, so the CTAs finish within one short tile of
+    // each other); without one, round r hands items [r * grid, (r + 1) * grid) to the CTAs,
+    // odd rounds in reverse CTA order so that no CTA collects the longest tile of every round.
+    for (int k = 0;; ++k) {
+      int item;
+      if (p.tile_counter) {
+        item = 0;
+        if (lane == 0) item = atomicAdd(p.tile_counter, 1);
+        item = __shfl_sync(0xffffffffu, item, 0);
+      } else {
+        const long long it = (long long)k * gridDim.x + ((k & 1) ? gridDim.x - 1 - blockIdx.x : blockIdx.x);
+        item = it < n_items ? (int)it : n_items;
+      }
       const int pb = k & 1;
       if (!mbar_wait(&tl->plan_free[pb], ((k >> 1) & 1) ^ 1, wait_status, 401)) break;
+      if (item >= n_items || item < 0) {
+        if (lane == 0) {
+          tl->plan[pb].valid = -1;
+          tl->plan[pb].n = 0;
+          mbar_arrive(&tl->plan_full[pb]);
+        }
+        break;
+      }
       build_plan(p, mode, item, tiles_x, head_items, &tl->plan[pb], tl->bits, lane);
       if (lane == 0) mbar_arrive(&tl->plan_full[pb]);
-      ++k;
     }
   } else if (warp == kWarpProd) {
     // ============================================================ TMA producer
@@ -266,13 +275,11 @@ fwd_persist_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tm
       uint32_t g = 0;      // kv blocks issued so far, over all tiles
       int k = 0, ko = 0;   // tiles seen / tiles with work
       bool ok = true;
-      for (int r = 0; ok; ++r) {
-        const int item = item_of(r);
-        if (item == -2) break;
-        if (item < 0) continue;
+      while (ok) {
         const int pb = k & 1;
         if (!mbar_wait(&tl->plan_full[pb], (k >> 1) & 1, wait_status, 402)) break;
         const Plan* pl = &tl->plan[pb];
+        if (pl->valid < 0) break;
         const int n = pl->n;
         if (n > 0) {
           // the Q tile may be replaced once the previous tile's last Q K^T has completed
@@ -339,12 +346,10 @@ fwd_persist_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tm
       __syncwarp();
       return true;
     };
-    for (int r = 0; ok; ++r) {
-      const int item = item_of(r);
-      if (item == -2) break;
-      if (item < 0) continue;
+    while (ok) {
       const int pb = k & 1;
       if (!mbar_wait(&tl->plan_full[pb], (k >> 1) & 1, wait_status, 412)) break;
+      if (tl->plan[pb].valid < 0) break;
       const int n = tl->plan[pb].n;
       if (n > 0) {
         if (!mbar_wait(&tl->q_full, ko & 1, wait_status, 413)) break;
@@ -394,13 +399,11 @@ fwd_persist_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tm
     };
     int k = 0;
     bool alive = true;
-    for (int r = 0; alive; ++r) {
-      const int item = item_of(r);
-      if (item == -2) break;
-      if (item < 0) continue;
+    while (alive) {
       const int pb = k & 1;
       if (!mbar_wait(&tl->plan_full[pb], (k >> 1) & 1, wait_status, 422)) break;
       const Plan* pl = &tl->plan[pb];
+      if (pl->valid < 0) break;
       const int n = pl->n;
       const int hvalid = pl->hvalid[t], head = pl->head[t];
       const int q_row = pl->qblk[t] * kBS + rr;   // row inside the sequence

@@ -243,6 +243,7 @@ def _fwd_params(q, k, v, o, lse, seq_dim, plan: _Plan, sm_scale, causal, row_mod
 
 
 _warned_fallback = set()
+_DYNAMIC_TILES_FROM = 1024     # 128-row tiles from which a forward launch gets a tile counter
 
 
 def _launch_fwd(p, q: Tensor) -> None:
@@ -250,14 +251,21 @@ def _launch_fwd(p, q: Tensor) -> None:
     which would still run on the CUDA-core kernel (an unaligned output view, for instance) is
     reported once per reason: that path is tens of times slower."""
     lib = _lib.lib()
-    if (p.impl == _lib.IMPL_AUTO and p.dtype != _lib.BSA_F32 and p.d % 8 == 0 and p.d <= 256
+    counter = None
+    if (p.impl != _lib.IMPL_GENERIC and p.dtype != _lib.BSA_F32 and p.d % 8 == 0 and p.d <= 256
             and p.block_size == 64):
         why = lib.bsa_fwd_why_not_sm100(C.byref(p))
-        if why and why not in _warned_fallback:
+        if why and p.impl == _lib.IMPL_AUTO and why not in _warned_fallback:
             _warned_fallback.add(why)
             import warnings
             warnings.warn("dkernel_b200: this attention call runs on the CUDA-core fallback kernel, "
                           f"not on the tensor cores: {why.decode()}", RuntimeWarning, stacklevel=3)
+        rows = p.total_q if p.total_q > 0 else p.batch * p.sq
+        if not why and rows * p.hq >= _DYNAMIC_TILES_FROM * 128:
+            # more tiles than a few rounds of the persistent grid: let the CTAs draw them from a
+            # counter (zeroed on this stream; a memset node under graph capture)
+            counter = torch.zeros(1, dtype=torch.int32, device=q.device)
+            p.tile_counter = _lib.ptr(counter)
     with torch.cuda.device(q.device):
         _lib.check(lib.bsa_fwd(C.byref(p), _lib.stream_of(q)), "bsa_fwd")
 

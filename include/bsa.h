@@ -28,7 +28,7 @@
 extern "C" {
 #endif
 
-#define BSA_ABI_VERSION 2
+#define BSA_ABI_VERSION 3
 
 enum {
   BSA_OK = 0,
@@ -143,6 +143,13 @@ typedef struct {
   const int32_t* col_bits;
   int64_t col_bits_sh;
   int32_t fine_block;
+  /* Optional: 4 bytes of device memory holding 0 when the launch starts, used by this launch
+   * alone (the caller zeroes them on the launch's stream, e.g. a memset node in a graph).
+   * The persistent CTAs of the tensor-core forward then draw their tiles from this counter
+   * as they go instead of following a fixed assignment; the outputs are the same bit for
+   * bit.  NULL = fixed assignment.  No reference counterpart (Triton's grid is scheduled by
+   * the hardware).                                                                       */
+  int32_t* tile_counter;
 } bsa_fwd_params;
 
 int bsa_fwd(const bsa_fwd_params* p, void* stream);

@@ -23,7 +23,7 @@ def test_header_symbols_are_exported_and_bound():
     for n in names:
         assert hasattr(lib, n), f"{n} is declared in include/bsa.h but not exported"
     assert set(names) == set(_lib.EXPORTS), "ctypes binding table and header differ"
-    assert _lib.lib().bsa_abi_version() == 2
+    assert _lib.lib().bsa_abi_version() == 3
 
 
 def test_struct_layouts_match_the_header(tmp_path):

@@ -134,6 +134,52 @@ def test_sm100_varlen_and_padded_routes(D):
     assert_lse_close(lse, ref_lse)
 
 
+def test_sm100_tile_counter_gives_the_same_bits(monkeypatch):
+    """Tiles drawn from a counter (dynamic order, any CTA may take any tile) against the fixed
+    assignment: outputs and LSE must agree bit for bit on the dense-grid, padded and packed routes,
+    including tiles that attend nothing, and repeated launches must each start from a zeroed counter."""
+    import dkernel_b200.ops as ops
+    from dkernel_b200 import SparseAttention
+    D = 128
+    runs = {}
+    for mode, threshold in (("fixed", 10 ** 12), ("counter", 0)):
+        monkeypatch.setattr(ops, "_DYNAMIC_TILES_FROM", threshold)
+        res = []
+        # dense grid, more tiles than CTAs (2 * 8 * 32 = 512 tiles of 128 rows on 296 CTAs)
+        B, S, Hq, Hkv = 2, 4096, 8, 2
+        pk = dict(block_size=64, local_blocks=3, vert_stride=5, num_kv_heads=Hkv)
+        q, k, v = seeded_qkv(31, (B, S, Hq, D), (B, S, Hkv, D), torch.bfloat16)
+        mod = _module(Hq, S, pk, seq_dim=1, impl="sm100")
+        with torch.no_grad():
+            for _ in range(3):
+                res.append(mod(q.cuda(), k.cuda(), v.cuda(), return_lse=True))
+            lens = torch.tensor([4096, 130])
+            res.append(mod(q.cuda(), k.cuda(), v.cuda(), left_paddings=(S - lens).cuda(), return_lse=True))
+        # packed batch with a user pattern whose first rows of some heads attend nothing
+        Hq2, nb = 4, 16
+        g = torch.Generator().manual_seed(3)
+        pat = torch.rand(Hq2, nb, nb, generator=g) < 0.3
+        pat &= torch.tril(torch.ones(nb, nb, dtype=torch.bool))[None]
+        pat[:, -1, -1] = True
+        lens = [512, 100, 333, 64, 1, 700, 1024]
+        cu = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32)
+        q2, k2, v2 = seeded_qkv(32, (sum(lens), Hq2, D), (sum(lens), Hq2, D), torch.bfloat16)
+        with pytest.warns(UserWarning):
+            mod2 = SparseAttention(64, pat.cuda(), impl="sm100")
+        with torch.no_grad():
+            res.append(mod2(q2.cuda(), k2.cuda(), v2.cuda(), cu_seqlen_k=cu.cuda(), return_lse=True))
+        torch.cuda.synchronize()
+        _wait_status_clean()
+        runs[mode] = res
+    for (o1, l1), (o2, l2) in zip(runs["fixed"], runs["counter"]):
+        assert torch.equal(o1, o2)
+        assert torch.equal(torch.nan_to_num(l1, neginf=-1e30), torch.nan_to_num(l2, neginf=-1e30))
+    # and the counter route against the oracle on the packed case
+    ref, ref_lse = O.varlen_attention(q2.float(), k2.float(), v2.float(), cu, pat.numpy().astype(np.uint8), 64)
+    assert_out_close(runs["counter"][-1][0], ref)
+    assert_lse_close(runs["counter"][-1][1], ref_lse)
+
+
 BWD_CASES = [
     # B, Hq, Hkv, Sq, Sk, dtype, seq_dim, pattern kwargs
     (1, 2, 2, 128, 128, torch.bfloat16, 1, dict(block_size=64, local_blocks=2, vert_stride=2)),
