@@ -59,6 +59,9 @@ struct TailP {
   uint32_t tmem_base;
   uint32_t bits[2][kMaxList / 32];
   Plan plan[2];
+  // epilogue: 32 rows x 64 bytes per softmax warp, so that a store instruction covers whole
+  // 64-byte row pieces of eight rows instead of 16 bytes of thirty-two rows
+  alignas(16) uint8_t ostage[4][2048];
 };
 
 
@@ -293,22 +296,36 @@ fwd_persist_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tm
                             pl->q_start + pl->qblk[t] * kBS, pl->head[t], pl->b);
           }
           ++ko;
-          for (int j = 0; j < n; ++j, ++g) {
-            const int s = g & 1;
-            const uint32_t ph = ((g >> 1) & 1) ^ 1;   // completion of the slot's previous user
+          // K runs one block ahead of V: the slot of K_{g+1} is free once Q K_{g-1}^T has completed,
+          // which is earlier than P V_{g-2} (the products run in the order P V_{g-3}, Q K_{g-1}^T,
+          // P V_{g-2}); one thread waiting for the two in block order would hold K_{g+1} back by
+          // most of a block period.
+          auto load_k = [&](int j) -> bool {
+            const uint32_t gk = g + (uint32_t)j;
+            const int s = gk & 1;
             const int tok = pl->k_start + (int)(pl->list[j] & 0x3fffu) * kBS;
             uint8_t* kdst = sRing + s * 2 * kTile;
-            if (!mbar_wait(&tl->qk_done[s], ph, wait_status, 404)) { ok = false; break; }
+            if (!mbar_wait(&tl->qk_done[s], ((gk >> 1) & 1) ^ 1, wait_status, 404)) return false;
             mbar_expect_tx(&tl->k_full[s], kTile);
 #pragma unroll
             for (int c = 0; c < kSub; ++c)
               tma_load_tile(kdst + c * 8192, &tmK, &tl->k_full[s], c * 64, tok, pl->kvh, pl->b);
-            if (!mbar_wait(&tl->pv_done[s], ph, wait_status, 405)) { ok = false; break; }
+            return true;
+          };
+          ok = load_k(0);
+          for (int j = 0; j < n && ok; ++j) {
+            if (j + 1 < n && !load_k(j + 1)) { ok = false; break; }
+            const uint32_t gv = g + (uint32_t)j;
+            const int s = gv & 1;
+            const int tok = pl->k_start + (int)(pl->list[j] & 0x3fffu) * kBS;
+            if (!mbar_wait(&tl->pv_done[s], ((gv >> 1) & 1) ^ 1, wait_status, 405)) { ok = false; break; }
             mbar_expect_tx(&tl->v_full[s], kTile);
 #pragma unroll
             for (int c = 0; c < kSub; ++c)
-              tma_load_tile(kdst + kTile + c * 8192, &tmV, &tl->v_full[s], c * 64, tok, pl->kvh, pl->b);
+              tma_load_tile(sRing + s * 2 * kTile + kTile + c * 8192, &tmV, &tl->v_full[s], c * 64, tok, pl->kvh,
+                            pl->b);
           }
+          g += (uint32_t)n;
         }
         if (ok) mbar_arrive(&tl->plan_free[pb]);
         ++k;
@@ -574,19 +591,30 @@ fwd_persist_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tm
           __syncwarp();
           if (lane == 0) mbar_arrive(&tl->o_free);
         }
-        if (row_ok) {   // columns at or past the real head dim are padding
-          if (wide) {
+        if (wide) {
+          // own row -> staging (16-byte pieces, swizzled by the row pair: conflict-free both ways),
+          // then lane L stores piece L % 4 of rows L / 4, L / 4 + 8, ...
+          uint8_t* stg = tl->ostage[warp];
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-              if (ch * 32 + i * 8 < p.d)
-                *reinterpret_cast<uint4*>(orow + ch * 64 + i * 16) =
-                    make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
-          } else {
+          for (int i = 0; i < 4; ++i)
+            *reinterpret_cast<uint4*>(stg + lane * 64 + ((i ^ ((lane >> 1) & 3)) * 16)) =
+                make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+          __syncwarp();
+          const int pc = lane & 3;
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
-              if (ch * 32 + i * 4 < p.d)
-                *reinterpret_cast<uint2*>(orow + ch * 64 + i * 8) = make_uint2(w[2 * i], w[2 * i + 1]);
+          for (int i = 0; i < 4; ++i) {
+            const int sr = i * 8 + (lane >> 2);            // row of this warp's 32
+            const uint4 val = *reinterpret_cast<const uint4*>(stg + sr * 64 + ((pc ^ ((sr >> 1) & 3)) * 16));
+            const int srow = q_row - lane + sr;            // row inside the sequence
+            if (hvalid && srow < q_len && ch * 32 + pc * 8 < p.d)   // columns past the real head dim are padding
+              *reinterpret_cast<uint4*>(orow + (int64_t)(sr - lane) * p.o_ss * 2 + ch * 64 + pc * 16) = val;
           }
+          __syncwarp();   // the next chunk overwrites the staging rows
+        } else if (row_ok) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            if (ch * 32 + i * 4 < p.d)
+              *reinterpret_cast<uint2*>(orow + ch * 64 + i * 8) = make_uint2(w[2 * i], w[2 * i + 1]);
         }
       }
       if (row_ok && lse_ptr) *lse_ptr = l > 0.f ? (m_used + log2f(l)) * kLn2 : -INFINITY;
