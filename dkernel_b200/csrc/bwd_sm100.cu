@@ -181,7 +181,9 @@ template <int D> struct DkdvGeo {
 struct DkdvTail {
   uint64_t kv_full;
   uint64_t qdo_full[kQdoStages], qdo_empty[kQdoStages];
-  uint64_t sdp_full[2], p_full[2];
+  // s_full / dp_full: S^T_e / dP^T_e have completed; pt_full / ds_full: every element-wise warp has
+  // stored its part of P^T_e / dS^T_e (and has read S^T_e / dP^T_e before)
+  uint64_t s_full[2], dp_full[2], pt_full[2], ds_full[2];
   uint64_t all_done;
   uint32_t tmem_base;
   int n_list;
@@ -240,8 +242,10 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
       mbar_init(&tl->qdo_empty[s], 2);   // both issuers have finished with the stage
     }
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&tl->sdp_full[s], 2);    // S^T and dP^T, one commit each
-      mbar_init(&tl->p_full[s], kDkdvEwWarps);   // one arrival per element-wise warp
+      mbar_init(&tl->s_full[s], 1);
+      mbar_init(&tl->dp_full[s], 1);
+      mbar_init(&tl->pt_full[s], kDkdvEwWarps);   // one arrival per element-wise warp
+      mbar_init(&tl->ds_full[s], kDkdvEwWarps);
     }
     mbar_init(&tl->all_done, 2);
     mbar_fence_init();
@@ -356,7 +360,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
           for (int i = 0; i < D / 16; ++i)   // i = c * 4 + kk
             tc_mma_ss(tFirst[bf], adesc + (uint64_t)(((i >> 2) * 16384 + (i & 3) * 32) >> 4),
                       bd + (uint64_t)(((i >> 2) * 8192 + (i & 3) * 32) >> 4), idesc_nt, i ? 1u : 0u);
-          tc_commit(&tl->sdp_full[bf]);
+          tc_commit(path ? &tl->dp_full[bf] : &tl->s_full[bf]);
         }
         __syncwarp();
         return true;
@@ -365,7 +369,10 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
       for (int e = 0; e < 2 && e < n && ok; ++e) ok = first_stage(e);
       for (int e = 0; e < n && ok; ++e) {
         const int s = e % kQdoStages, bf = e & 1;
-        if (!mbar_wait(&tl->p_full[bf], (e >> 1) & 1, wait_status, 304)) { ok = false; break; }
+        if (!mbar_wait(path ? &tl->ds_full[bf] : &tl->pt_full[bf], (e >> 1) & 1, wait_status, 304)) {
+          ok = false;
+          break;
+        }
         tc_fence_after();
         const uint64_t md = mdesc0 + (uint64_t)((s * kQdoStageBytes) >> 4);
         const uint32_t acc0 = e ? 1u : 0u;
@@ -399,7 +406,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
       const int st = e % kQdoStages;
       // the stage's lse / delta rows arrive with its tiles
       if (!mbar_wait(&tl->qdo_full[st], (e / kQdoStages) & 1, wait_status, 309)) { alive = false; break; }
-      if (!mbar_wait(&tl->sdp_full[e & 1], (e >> 1) & 1, wait_status, 305)) { alive = false; break; }
+      if (!mbar_wait(&tl->s_full[e & 1], (e >> 1) & 1, wait_status, 305)) { alive = false; break; }
       tc_fence_after();
       const uint32_t ent = tl->list[e];
       const int r = ent & 0xffff;
@@ -408,11 +415,13 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
       const int c0 = (p.causal ? kpos - past - r * kBS : 0) - qtr * 16;
       const float* lse_s = tl->ld[st][0] + qtr * 16;
       const float* del_s = tl->ld[st][1] + qtr * 16;
-      uint32_t sv[16], dv[16];
+      // P^T is published as soon as S^T allows it, while dP^T_e may still be on the tensor pipe:
+      // dV += P^T dO and the S^T of entry e+2 behind it then start without waiting for dS^T.
+      uint32_t sv[16];
       tmem_ld16(tST[e & 1] + lane_off + qtr * 16, sv);
-      tmem_ld16(tDP[e & 1] + lane_off + qtr * 16, dv);
       tmem_ld_wait();
-      uint32_t pp[8], ds[8];
+      uint64_t pv2[8];   // P as packed fp32 pairs, kept for dS
+      uint32_t pp[8];
       if (att) {
         // only a diagonal entry has masked columns: they get S = -inf, hence P = dS = 0
         if (c0 > 0) {
@@ -423,36 +432,54 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
 #pragma unroll
         for (int c4 = 0; c4 < 4; ++c4) {
           const float4 l4 = *reinterpret_cast<const float4*>(lse_s + c4 * 4);
-          const float4 d4 = *reinterpret_cast<const float4*>(del_s + c4 * 4);
-          // two columns per instruction: P = exp2(S c - lse), dS = P (dP - delta)
+          // two columns per instruction: P = exp2(S c - lse)
           const uint64_t nl[2] = {f32x2(l4.x, l4.y), f32x2(l4.z, l4.w)};
-          const uint64_t nd[2] = {f32x2(d4.x, d4.y), f32x2(d4.z, d4.w)};
-          float pv[4], dsv[4];
 #pragma unroll
           for (int i = 0; i < 2; ++i) {
             float x0, x1;
             f32x2_split(fma_f32x2(f32x2(sv[c4 * 4 + 2 * i], sv[c4 * 4 + 2 * i + 1]), scale_2, nl[i]), x0, x1);
-            pv[2 * i] = ex2(x0);
-            pv[2 * i + 1] = ex2(x1);
-            f32x2_split(mul_f32x2(f32x2(pv[2 * i], pv[2 * i + 1]),
-                                  add_f32x2(f32x2(dv[c4 * 4 + 2 * i], dv[c4 * 4 + 2 * i + 1]), nd[i])),
-                        dsv[2 * i], dsv[2 * i + 1]);
+            const float p0 = ex2(x0), p1 = ex2(x1);
+            pv2[c4 * 2 + i] = f32x2(p0, p1);
+            pp[c4 * 2 + i] = pack2<BF16>(p0, p1);
           }
-          pp[c4 * 2] = pack2<BF16>(pv[0], pv[1]);
-          pp[c4 * 2 + 1] = pack2<BF16>(pv[2], pv[3]);
-          ds[c4 * 2] = pack2<BF16>(dsv[0], dsv[1]);
-          ds[c4 * 2 + 1] = pack2<BF16>(dsv[2], dsv[3]);
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) { pp[i] = 0u; ds[i] = 0u; }
+        for (int i = 0; i < 8; ++i) { pp[i] = 0u; pv2[i] = 0ull; }
       }
       tmem_st8(tST[e & 1] + lane_off + qtr * 16, pp);
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tl->pt_full[e & 1]);
+      if (!mbar_wait(&tl->dp_full[e & 1], (e >> 1) & 1, wait_status, 307)) { alive = false; break; }
+      tc_fence_after();
+      uint32_t dv[16], ds[8];
+      tmem_ld16(tDP[e & 1] + lane_off + qtr * 16, dv);
+      tmem_ld_wait();
+      if (att) {
+#pragma unroll
+        for (int c4 = 0; c4 < 4; ++c4) {
+          const float4 d4 = *reinterpret_cast<const float4*>(del_s + c4 * 4);
+          const uint64_t nd[2] = {f32x2(d4.x, d4.y), f32x2(d4.z, d4.w)};
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            // dS = P (dP - delta)
+            float d0, d1;
+            f32x2_split(mul_f32x2(pv2[c4 * 2 + i],
+                                  add_f32x2(f32x2(dv[c4 * 4 + 2 * i], dv[c4 * 4 + 2 * i + 1]), nd[i])), d0, d1);
+            ds[c4 * 2 + i] = pack2<BF16>(d0, d1);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ds[i] = 0u;
+      }
       tmem_st8(tDP[e & 1] + lane_off + qtr * 16, ds);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&tl->p_full[e & 1]);
+      if (lane == 0) mbar_arrive(&tl->ds_full[e & 1]);
     }
     // ---- epilogue: warp = (lane quadrant, dV or dK, 64-column half); every thread scales
     // its row and stores 128 contiguous bytes straight from registers
@@ -519,7 +546,9 @@ struct DqTail {
   uint64_t q_full;
   uint64_t k_full[kDqKStages], k_empty[kDqKStages];
   uint64_t v_full[kDqVStages], v_empty[kDqVStages];
-  uint64_t sdp_full[2], p_full[2];
+  // s_full / dp_full: S_e / dP_e have completed; s_free: every element-wise warp has read S_e;
+  // p_full: every element-wise warp has stored its part of dS_e
+  uint64_t s_full[2], dp_full[2], s_free[2], p_full[2];
   uint64_t cp_done, all_done;
   uint32_t tmem_base;
   int n_list;
@@ -581,8 +610,10 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
     for (int s = 0; s < kDqKStages; ++s) { mbar_init(&tl->k_full[s], 1); mbar_init(&tl->k_empty[s], 2); }
     for (int s = 0; s < kDqVStages; ++s) { mbar_init(&tl->v_full[s], 1); mbar_init(&tl->v_empty[s], 1); }
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&tl->sdp_full[s], 2);   // S and dP, one commit each
-      mbar_init(&tl->p_full[s], kDqEwWarps);   // one arrival per element-wise warp
+      mbar_init(&tl->s_full[s], 1);
+      mbar_init(&tl->dp_full[s], 1);
+      mbar_init(&tl->s_free[s], kDqEwWarps);   // one arrival per element-wise warp
+      mbar_init(&tl->p_full[s], kDqEwWarps);
     }
     mbar_init(&tl->cp_done, 1);
     mbar_init(&tl->all_done, 1);
@@ -680,8 +711,8 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
       }
       for (int e = 0; e < n && ok; ++e) {
         const int sk_ = e % kDqKStages, bf = e & 1;
-        // S[bf] is free once the element-wise warps have consumed entry e-2
-        if (e >= 2 && !mbar_wait(&tl->p_full[bf], ((e - 2) >> 1) & 1, wait_status, 319)) break;
+        // S[bf] is free once the element-wise warps have read entry e-2
+        if (e >= 2 && !mbar_wait(&tl->s_free[bf], ((e - 2) >> 1) & 1, wait_status, 319)) break;
         if (!mbar_wait(&tl->k_full[sk_], (e / kDqKStages) & 1, wait_status, 314)) break;
         tc_fence_after();
         const uint64_t kd = kdesc0 + (uint64_t)((sk_ * kTileKV) >> 4);
@@ -691,7 +722,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
             tc_mma_ts(tS[bf], tQ + i * 8, kd + (uint64_t)(((i >> 2) * 8192 + (i & 3) * 32) >> 4), idesc_nt,
                       i ? 1u : 0u);
           tc_commit(&tl->k_empty[sk_]);
-          tc_commit(&tl->sdp_full[bf]);
+          tc_commit(&tl->s_full[bf]);
         }
         __syncwarp();
       }
@@ -716,7 +747,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
             tc_mma_ts(tDP[bf], tDO + i * 8, vd + (uint64_t)(((i >> 2) * 8192 + (i & 3) * 32) >> 4), idesc_nt,
                       i ? 1u : 0u);
           tc_commit(&tl->v_empty[sv_]);
-          tc_commit(&tl->sdp_full[bf]);
+          tc_commit(&tl->dp_full[bf]);
         }
         __syncwarp();
         return true;
@@ -764,7 +795,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
                    neg_delta2 = f32x2(neg_delta, neg_delta);
     bool alive = true;
     for (int e = 0; e < n; ++e) {
-      if (!mbar_wait(&tl->sdp_full[e & 1], (e >> 1) & 1, wait_status, 317)) { alive = false; break; }
+      if (!mbar_wait(&tl->s_full[e & 1], (e >> 1) & 1, wait_status, 317)) { alive = false; break; }
       tc_fence_after();
       const uint32_t ent = tl->list[e];
       const int kbase = (int)(ent & 0xffffu) * kBS;
@@ -772,11 +803,15 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
       int lim = p.sk - kbase;
       if (p.causal) lim = min(lim, qpos - kbase + 1);
       lim -= qtr * 16;   // relative to this warp's 16 columns
-      uint32_t sv[16], dv[16];
+      // The exponentials run as soon as S_e is there, while dP_e may still be on the tensor pipe,
+      // and S's columns are handed back for entry e+2 right after they have been read.
+      uint32_t sv[16];
       tmem_ld16(tS[e & 1] + lane_off + qtr * 16, sv);
-      tmem_ld16(tDP[e & 1] + lane_off + qtr * 16, dv);
       tmem_ld_wait();
-      uint32_t ds[8];
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tl->s_free[e & 1]);
+      uint64_t pv2[8];   // P as packed fp32 pairs
       if (att) {
         // only blocks on the diagonal or at the end of the keys have masked columns:
         // they get S = -inf, hence P = dS = 0
@@ -787,11 +822,23 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
         }
 #pragma unroll
         for (int c2 = 0; c2 < 8; ++c2) {
-          // two columns per instruction: P = exp2(S c - lse), dS = P (dP - delta)
-          float x0, x1, d0, d1;
+          // two columns per instruction: P = exp2(S c - lse)
+          float x0, x1;
           f32x2_split(fma_f32x2(f32x2(sv[2 * c2], sv[2 * c2 + 1]), scale_2, neg_lse2), x0, x1);
-          f32x2_split(mul_f32x2(f32x2(ex2(x0), ex2(x1)),
-                                add_f32x2(f32x2(dv[2 * c2], dv[2 * c2 + 1]), neg_delta2)), d0, d1);
+          pv2[c2] = f32x2(ex2(x0), ex2(x1));
+        }
+      }
+      if (!mbar_wait(&tl->dp_full[e & 1], (e >> 1) & 1, wait_status, 322)) { alive = false; break; }
+      tc_fence_after();
+      uint32_t dv[16], ds[8];
+      tmem_ld16(tDP[e & 1] + lane_off + qtr * 16, dv);
+      tmem_ld_wait();
+      if (att) {
+#pragma unroll
+        for (int c2 = 0; c2 < 8; ++c2) {
+          // dS = P (dP - delta)
+          float d0, d1;
+          f32x2_split(mul_f32x2(pv2[c2], add_f32x2(f32x2(dv[2 * c2], dv[2 * c2 + 1]), neg_delta2)), d0, d1);
           ds[c2] = pack2<BF16>(d0, d1);
         }
       } else {
