@@ -49,7 +49,8 @@ class BwdParams(C.Structure):
         + [(n, _i64) for n in ("dq_sb", "dq_ss", "dq_sh", "dk_sb", "dk_ss", "dk_sh",
                                "dv_sb", "dv_ss", "dv_sh")]
         + [("ccol", _vp), ("row", _vp), ("ccol_sh", _i64), ("row_sh", _i64), ("n_cols", _i32),
-           ("delta", _vp), ("kv_pairs", _vp), ("kv_pairs_sh", _i64), ("n_pairs", _i32)]
+           ("delta", _vp), ("kv_pairs", _vp), ("kv_pairs_sh", _i64), ("n_pairs", _i32),
+           ("ds_ws", _vp), ("ds_tiles_per_head", _i64), ("csc_csr", _vp)]
     )
 
 

@@ -91,6 +91,10 @@ int bsa_bwd(const bsa_bwd_params* p, void* stream) {
   BSA_CHECK_ARG(!p->f.q_start && !p->f.k_start && p->f.row_mode == BSA_ROWS_BY_TILE,
                 "bsa_bwd: padded / packed batches have no backward "
                 "(as in dkernel/ops/__init__.py:57-58,79-80)");
+  if (p->ds_ws)
+    BSA_CHECK_ARG(p->csc_csr && p->ds_tiles_per_head > 0 && reinterpret_cast<uintptr_t>(p->ds_ws) % 128 == 0 &&
+                      p->ds_tiles_per_head * 64 < (1ll << 31),
+                  "bsa_bwd: a dS workspace needs csc_csr, ds_tiles_per_head in (0, 2^25) and 128-byte alignment");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (p->f.impl != BSA_IMPL_GENERIC) {
     const char* why = nullptr;

@@ -35,8 +35,9 @@ constexpr int kDqEwWarps = 16;        // dQ kernel: 16 element-wise warps, produ
 constexpr int kBwdThreads = 32 * (kDqEwWarps + 3);
 constexpr int kWarpProducer = kDqEwWarps, kWarpIssueA = kDqEwWarps + 1, kWarpIssueB = kDqEwWarps + 2;
 constexpr int kDkdvEwWarps = 16;      // dK/dV kernel: 16 element-wise warps, producer, two issuers
-constexpr int kDkdvThreads = 32 * (kDkdvEwWarps + 3);
+constexpr int kDkdvThreads = 32 * (kDkdvEwWarps + 3 + 4);
 constexpr int kDkdvProducer = kDkdvEwWarps, kDkdvIssuer = kDkdvEwWarps + 1;   // issuers: +1 and +2
+constexpr int kDkdvCopier = kDkdvEwWarps + 3;   // four warps that hand dS^T tiles to the dQ kernel
 constexpr int kMaxBlocks = 1024;   // q or kv blocks per sequence (64K tokens)
 constexpr int kMaxEntries = 2048;  // list entries per CTA
 
@@ -138,9 +139,11 @@ __global__ void bwd_delta_vec_kernel(bsa_bwd_params bp) {
 // ------------------------------------------------------------------ shared list builder
 // Ordered union of two sets of block indices given as bitmaps; appended to `list`
 // starting at *count.  entry = block | extra | (in set 0) << 24 | (in set 1) << 25.
+// wordpos (optional): list position of the first entry of every 32-block word, so that the
+// position of a block known to be in the union is wordpos[blk / 32] + popc(lower bits of its word).
 __device__ __forceinline__ void append_union(const uint32_t* bits0, const uint32_t* bits1,
                                              uint32_t* list, int* count, uint32_t extra, int lane,
-                                             int cap) {
+                                             int cap, int* wordpos = nullptr) {
   const uint32_t u0 = bits0[lane], u1 = bits1[lane];
   const uint32_t u = u0 | u1;
   const int cnt = __popc(u);
@@ -152,6 +155,7 @@ __device__ __forceinline__ void append_union(const uint32_t* bits0, const uint32
   }
   const int base = *count;
   const int first = base + incl - cnt;   // list position of this lane's word
+  if (wordpos) wordpos[lane] = first;
   // one word at a time; within a word every lane owns one bit
   uint32_t nonzero = __ballot_sync(0xffffffffu, u != 0u);
   while (nonzero) {
@@ -184,6 +188,7 @@ struct DkdvTail {
   // s_full / dp_full: S^T_e / dP^T_e have completed; pt_full / ds_full: every element-wise warp has
   // stored its part of P^T_e / dS^T_e (and has read S^T_e / dP^T_e before)
   uint64_t s_full[2], dp_full[2], pt_full[2], ds_full[2];
+  uint64_t ds_read[2];   // dS hand-over: the copier warps have read dS^T_e out of tensor memory
   uint64_t all_done;
   uint32_t tmem_base;
   int n_list;
@@ -191,6 +196,9 @@ struct DkdvTail {
   alignas(128) float ld[kQdoStages][2][kBS];
   uint32_t bits[2][kMaxBlocks / 32];
   uint32_t list[kMaxEntries];
+  // dS hand-over: index in the CSR (= tile of the dS workspace) of the entry's block in either half
+  int wordpos[32];
+  int32_t cidx[kMaxEntries][2];
 };
 template <int D> constexpr size_t dkdv_smem() {
   return 1024 + DkdvGeo<D>::kKVResident + kQdoStages * DkdvGeo<D>::kQdoStageBytes + sizeof(DkdvTail);
@@ -246,6 +254,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
       mbar_init(&tl->dp_full[s], 1);
       mbar_init(&tl->pt_full[s], kDkdvEwWarps);   // one arrival per element-wise warp
       mbar_init(&tl->ds_full[s], kDkdvEwWarps);
+      mbar_init(&tl->ds_read[s], 4);
     }
     mbar_init(&tl->all_done, 2);
     mbar_fence_init();
@@ -279,22 +288,50 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
     const int hp = pattern_head(h, p.h_pat, p.hq, p.hkv);
     const int32_t* cc = bp.ccol + (int64_t)hp * bp.ccol_sh;
     const int32_t* rows = bp.row + (int64_t)hp * bp.row_sh;
+    // With the dS hand-over every (entry, half) also needs the block's index in the CSR: it is
+    // fetched together with the row (a column has at most kMaxBlocks rows, i.e. at most kKeep per
+    // thread) and stored once the row's list position is known.
+    constexpr int kKeep = (kMaxBlocks + kDkdvThreads - 1) / kDkdvThreads;
+    int keep_r[2][kKeep], keep_c[2][kKeep];
+    const int32_t* c2r = bp.ds_ws ? bp.csc_csr + (int64_t)hp * bp.row_sh : nullptr;
+#pragma unroll
     for (int t = 0; t < 2; ++t) {
+#pragma unroll
+      for (int k = 0; k < kKeep; ++k) keep_r[t][k] = -1;
       if (!kvalid[t] || kblk[t] >= bp.n_cols) continue;
       const int r_beg = cc[kblk[t]], r_end = cc[kblk[t] + 1];
-      for (int i = r_beg + tid; i < r_end; i += kDkdvThreads) {
+#pragma unroll
+      for (int k = 0; k < kKeep; ++k) {
+        const int i = r_beg + tid + k * kDkdvThreads;
+        if (i >= r_end) continue;
         const int r = rows[i];
+        const int ci = c2r ? c2r[i] : 0;
         if (r < 0 || r >= nqb) continue;
         const int q_pos_last = past + min(r * kBS + kBS, p.sq) - 1;
         if (p.causal && kblk[t] * kBS > q_pos_last) continue;
         atomicOr(&tl->bits[t][r >> 5], 1u << (r & 31));
+        keep_r[t][k] = r;
+        keep_c[t][k] = ci;
       }
     }
     __syncthreads();
     if (warp == 0)
       append_union(tl->bits[0], tl->bits[1], tl->list, &tl->n_list, (uint32_t)g << 16, lane,
-                   kMaxEntries);
+                   kMaxEntries, tl->wordpos);
     __syncthreads();
+    if (bp.ds_ws) {
+#pragma unroll
+      for (int t = 0; t < 2; ++t)
+#pragma unroll
+        for (int k = 0; k < kKeep; ++k) {
+          const int r = keep_r[t][k];
+          if (r < 0) continue;
+          const uint32_t u = tl->bits[0][r >> 5] | tl->bits[1][r >> 5];
+          const int pos = tl->wordpos[r >> 5] + __popc(u & ((1u << (r & 31)) - 1u));
+          if (pos < kMaxEntries) tl->cidx[pos][t] = keep_c[t][k];
+        }
+      __syncthreads();
+    }
   }
   tc_fence_before();
   __syncthreads();
@@ -384,11 +421,57 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
           tc_commit(&tl->qdo_empty[s]);
         }
         __syncwarp();
+        // dP^T of entry e+2 overwrites dS^T_e: with the dS hand-over the copier warps must have read it
+        if (path == 1 && bp.ds_ws && e + 2 < n &&
+            !mbar_wait(&tl->ds_read[bf], (e >> 1) & 1, wait_status, 310)) {
+          ok = false;
+          break;
+        }
         if (e + 2 < n) ok = first_stage(e + 2);
       }
       if (ok && elect_one()) tc_commit(&tl->all_done);
     }
     __syncwarp();
+  } else if (n > 0 && warp >= kDkdvCopier) {
+    // ------------------------------------------------------------ dS hand-over (four warps)
+    // One warp per TMEM lane quadrant reads the packed dS^T rows of an entry (64 q columns =
+    // 128 bytes per kv row, in the first 8 of every 16 columns) once the element-wise warps have
+    // stored them, releases the columns, and writes the attended half's tile for the dQ kernel as
+    // eight slabs of [64 kv rows][8 q columns] (16 bytes per row): the warp's 32 kv rows are
+    // contiguous within a slab, so every store instruction is one 512-byte run, and a slab is a
+    // column of the 8 x 16-byte core matrices the tensor core reads without swizzle.  The
+    // element-wise warps, whose time per entry sets the pace of this kernel, do none of this.
+    if (bp.ds_ws) {
+      const int quad = warp & 3, t = quad >> 1;
+      const int rk = (quad & 1) * 32 + lane;   // kv row inside the half's block
+      const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
+      for (int e = 0; e < n; ++e) {
+        if (!mbar_wait(&tl->ds_full[e & 1], (e >> 1) & 1, wait_status, 323)) break;
+        tc_fence_after();
+        const uint32_t ent = tl->list[e];
+        const bool att_blk = ((ent >> (24 + t)) & 1u) != 0 && kvalid[t];
+        uint32_t w[32];
+        if (att_blk) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            tmem_ld8(tDP[e & 1] + lane_off + j * 16, *reinterpret_cast<uint32_t(*)[8]>(&w[8 * j]));
+          tmem_ld_wait();
+        }
+        tc_fence_before();
+        __syncwarp();
+        // relaxed: the loads have completed (wait::ld) and nothing is published; a release would
+        // wait for the previous entry's stores
+        if (lane == 0) mbar_arrive_relaxed(&tl->ds_read[e & 1]);
+        if (att_blk) {
+          const int h = hk * G + (int)((ent >> 16) & 0xffu);
+          const int64_t tile = ((int64_t)b * p.hq + h) * bp.ds_tiles_per_head + tl->cidx[e][t];
+          uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(bp.ds_ws) + tile * 8192) + rk;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            __stcs(dst + j * kBS, make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]));
+        }
+      }
+    }
   } else if (n > 0 && warp < kDkdvEwWarps) {
     // ------------------------------------------------------------ P^T / dS^T (warps 0-15)
     // A warp owns a TMEM lane quadrant (32 kv rows) and 16 of the 64 q columns; its packed
@@ -410,7 +493,8 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
       tc_fence_after();
       const uint32_t ent = tl->list[e];
       const int r = ent & 0xffff;
-      const bool att = ((ent >> (24 + t)) & 1u) != 0 && kvalid[t];
+      const bool att_blk = ((ent >> (24 + t)) & 1u) != 0 && kvalid[t];   // the same for the whole warp
+      const bool att = att_blk && kpos < p.sk;   // rows past the end of the keys hold P = dS = 0
       // causal: q position past + r*64 + c must be >= kpos  ->  c >= c0
       const int c0 = (p.causal ? kpos - past - r * kBS : 0) - qtr * 16;
       const float* lse_s = tl->ld[st][0] + qtr * 16;
@@ -898,6 +982,218 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
   wait_for_dkdv();
 }
 
+// ------------------------------------------------------------------ dQ from handed-over dS
+// With a dS workspace the dK/dV kernel has stored the dS^T tile (64 kv rows x 64 q columns, 8 KB, as
+// eight slabs of [64 kv rows][8 q columns]) of every attended block at the block's CSR index, and
+// dQ needs one product per block,
+// dQ += dS K, instead of the three of the kernel above (S and dP again, then dQ): no
+// element-wise work, no Q / dO / V / lse / delta.  One CTA per 128-row query tile as above
+// (two 64-row halves, union of the halves' CSR rows); per entry the producer warp loads the K
+// block and the attended halves' dS^T tiles (a half that does not attend the block gets zeros)
+// (plain 8 KB bulk copies) and the issuer runs four SS products with both operands MN-major
+// (dS^T: q contiguous, K: head dim contiguous).  Two CTAs per SM (D columns of TMEM each).  The kernel is bound by the
+// L2 -> SM traffic of its operands (32 KB per entry against 256 tensor-pipe cycles).
+constexpr int kDqsStages = 3;
+constexpr int kDqsThreads = 192;   // warps 0-3 epilogue, 4 producer, 5 issuer
+constexpr int kDqsProducer = 4, kDqsIssuer = 5;
+
+struct DqsTail {
+  uint64_t full[kDqsStages], empty[kDqsStages];
+  uint64_t all_done;
+  uint32_t tmem_base;
+  int n_list;
+  int wordpos[32];
+  uint32_t bits[2][kMaxBlocks / 32];
+  uint32_t list[kMaxBlocks];
+  int32_t cidx[kMaxBlocks][2];
+};
+template <int D> constexpr size_t dqs_smem() {
+  return 1024 + kDqsStages * (2 * 8192 + kBS * D * 2) + sizeof(DqsTail);
+}
+
+template <bool BF16, int D>
+__global__ void __launch_bounds__(kDqsThreads, 2)
+bwd_dq_from_ds_kernel(const __grid_constant__ Tmap4 tmK, bsa_bwd_params bp, int mode, int* wait_status) {
+  const bsa_fwd_params& p = bp.f;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  constexpr int kSub = D / 64, kTileKV = kBS * D * 2, kStageBytes = 2 * 8192 + kTileKV;
+  DqsTail* tl = reinterpret_cast<DqsTail*>(smem + kDqsStages * kStageBytes);
+
+  // Programmatic dependent of the dK/dV kernel, whose dS tiles it reads: everything up to the
+  // block list is built while that grid drains, the loads start after it has completed.
+  auto wait_for_dkdv = [] { asm volatile("griddepcontrol.wait;" ::: "memory"); };
+  if (*reinterpret_cast<volatile int*>(wait_status) != 0) { wait_for_dkdv(); return; }
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int G = p.hq / p.hkv;
+  const int b = blockIdx.z;
+  const int tile = gridDim.x - 1 - blockIdx.x;
+  const int past = p.causal ? p.sk - p.sq : 0;
+  int head[2], qblk[2], valid[2], kvh;
+  if (mode == kPairHeads) {
+    const int pairs = G / 2;
+    kvh = blockIdx.y / pairs;
+    head[0] = kvh * G + 2 * (blockIdx.y % pairs);
+    head[1] = head[0] + 1;
+    qblk[0] = qblk[1] = tile;
+    valid[0] = valid[1] = 1;
+  } else {
+    head[0] = head[1] = blockIdx.y;
+    kvh = blockIdx.y / G;
+    qblk[0] = 2 * tile;
+    qblk[1] = 2 * tile + 1;
+    valid[0] = 1;
+    valid[1] = qblk[1] * kBS < p.sq ? 1 : 0;
+  }
+  if (qblk[0] * kBS >= p.sq) { wait_for_dkdv(); return; }
+  const int nkb = min((p.sk + kBS - 1) / kBS, kMaxBlocks);
+
+  if (tid == 0) {
+    for (int s = 0; s < kDqsStages; ++s) { mbar_init(&tl->full[s], 1); mbar_init(&tl->empty[s], 1); }
+    mbar_init(&tl->all_done, 1);
+    mbar_fence_init();
+    tma_prefetch_desc(&tmK.map);
+    tl->n_list = 0;
+  }
+  if (tid < 2 * (kMaxBlocks / 32)) (&tl->bits[0][0])[tid] = 0u;
+  __syncthreads();
+  if (warp == kDqsIssuer) {
+    tmem_alloc(&tl->tmem_base, D);
+    tmem_relinquish();
+  }
+  // block list (as in the kernel above) and, per entry and half, the block's CSR index
+  auto for_entries = [&](auto&& fn) {
+    for (int t = 0; t < 2; ++t) {
+      if (!valid[t] || qblk[t] >= p.n_rows) continue;
+      const int hp = pattern_head(head[t], p.h_pat, p.hq, p.hkv);
+      const int32_t* cr = p.crow + (int64_t)hp * p.crow_sh;
+      const int32_t* cols = p.col + (int64_t)hp * p.col_sh;
+      const int c_beg = cr[qblk[t]], c_end = cr[qblk[t] + 1];
+      const int q_pos_last = past + min(qblk[t] * kBS + kBS, p.sq) - 1;
+      for (int i = c_beg + tid; i < c_end; i += kDqsThreads) {
+        const int blk = cols[i];
+        if (blk >= 0 && blk < nkb && !(p.causal && blk * kBS > q_pos_last)) fn(t, blk, i);
+      }
+    }
+  };
+  for_entries([&](int t, int blk, int) { atomicOr(&tl->bits[t][blk >> 5], 1u << (blk & 31)); });
+  __syncthreads();
+  if (warp == 0)
+    append_union(tl->bits[0], tl->bits[1], tl->list, &tl->n_list, 0u, lane, kMaxBlocks, tl->wordpos);
+  __syncthreads();
+  for_entries([&](int t, int blk, int i) {
+    const uint32_t u = tl->bits[0][blk >> 5] | tl->bits[1][blk >> 5];
+    const int pos = tl->wordpos[blk >> 5] + __popc(u & ((1u << (blk & 31)) - 1u));
+    if (pos < kMaxBlocks) tl->cidx[pos][t] = i;
+  });
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const int n = tl->n_list;
+  const uint32_t tmem = tl->tmem_base;
+  wait_for_dkdv();
+
+  if (n > 0 && warp == kDqsProducer) {
+    // ------------------------------------------------------------ producer (whole warp)
+    for (int e = 0; e < n; ++e) {
+      const int s = e % kDqsStages;
+      if (!mbar_wait(&tl->empty[s], ((e / kDqsStages) & 1) ^ 1, wait_status, 331)) break;
+      const uint32_t ent = tl->list[e];
+      uint8_t* st = smem + s * kStageBytes;
+      const bool a0 = ((ent >> 24) & 1u) != 0 && valid[0], a1 = ((ent >> 25) & 1u) != 0 && valid[1];
+      if (!a0 || !a1) {
+        // the half that does not attend this block contributes nothing: zeros for its dS^T tile
+        uint4* z = reinterpret_cast<uint4*>(st + (a0 ? 8192 : 0));
+        for (int i = lane; i < 8192 / 16; i += 32) z[i] = make_uint4(0u, 0u, 0u, 0u);
+        fence_proxy_async();   // generic-proxy writes -> visible to the tensor core's reads
+      }
+      __syncwarp();
+      if (lane == 0) {
+        mbar_expect_tx(&tl->full[s], kTileKV + (uint32_t)((a0 ? 1 : 0) + (a1 ? 1 : 0)) * 8192u);
+        const int tok = (int)(ent & 0xffffu) * kBS;
+        for (int c = 0; c < kSub; ++c)
+          tma_load_tile(st + 16384 + c * 8192, &tmK, &tl->full[s], c * 64, tok, kvh, b);
+        const uint8_t* ws = reinterpret_cast<const uint8_t*>(bp.ds_ws);
+        if (a0)
+          bulk_load(st, ws + (((int64_t)b * p.hq + head[0]) * bp.ds_tiles_per_head + tl->cidx[e][0]) * 8192, 8192,
+                    &tl->full[s]);
+        if (a1)
+          bulk_load(st + 8192, ws + (((int64_t)b * p.hq + head[1]) * bp.ds_tiles_per_head + tl->cidx[e][1]) * 8192,
+                    8192, &tl->full[s]);
+      }
+      __syncwarp();
+    }
+  } else if (n > 0 && warp == kDqsIssuer) {
+    // ------------------------------------------------------------ dQ += dS K
+    // A = the two dS^T tiles, MN-major and un-swizzled: sixteen slabs of 8 q columns, 1 KB apart,
+    // each a column of core matrices (8 kv rows x 16 bytes, 128 bytes apart); a k-step is 16 kv rows
+    // = 256 bytes down every slab.  B = K read MN-major from its swizzled TMA tile (16 kv rows = 2 KB
+    // per k-step, 64-dim halves 8 KB apart).
+    const uint32_t idesc = umma_idesc(BF16, 128, D, true, true);
+    const uint64_t adesc0 = umma_desc_plain(smem_u32(smem), 128, 1024);
+    const uint64_t bdesc0 = umma_desc_sw128(smem_u32(smem) + 16384, 8192, 1024);
+    bool ok = true;
+    for (int e = 0; e < n && ok; ++e) {
+      const int s = e % kDqsStages;
+      if (!mbar_wait(&tl->full[s], (e / kDqsStages) & 1, wait_status, 332)) { ok = false; break; }
+      tc_fence_after();
+      const uint64_t so = (uint64_t)((s * kStageBytes) >> 4);
+      if (elect_one()) {
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          tc_mma_ss(tmem, adesc0 + so + (uint64_t)((kk * 256) >> 4), bdesc0 + so + (uint64_t)((kk * 2048) >> 4),
+                    idesc, (e | kk) ? 1u : 0u);
+        tc_commit(&tl->empty[s]);
+      }
+      __syncwarp();
+    }
+    if (ok && elect_one()) tc_commit(&tl->all_done);
+    __syncwarp();
+  } else if (warp < 4) {
+    // ------------------------------------------------------------ epilogue (or zero rows)
+    const int r = tid, t = r >> 6;
+    const int q_row = qblk[t] * kBS + (r & 63);
+    const bool row_ok = valid[t] && q_row < p.sq;
+    uint8_t* grow = reinterpret_cast<uint8_t*>(bp.dq) +
+                    ((int64_t)b * bp.dq_sb + (int64_t)head[t] * bp.dq_sh + (int64_t)q_row * bp.dq_ss) * 2;
+    if (n == 0) {
+      if (row_ok)
+        for (int i = 0; i < D / 4; ++i) reinterpret_cast<uint2*>(grow)[i] = make_uint2(0u, 0u);
+    } else if (mbar_wait(&tl->all_done, 0, wait_status, 333)) {
+      tc_fence_after();
+      const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+      const bool wide = reinterpret_cast<uintptr_t>(bp.dq) % 16 == 0 && bp.dq_sb % 8 == 0 &&
+                        bp.dq_sh % 8 == 0 && bp.dq_ss % 8 == 0;
+#pragma unroll
+      for (int ch = 0; ch < D / 32; ++ch) {
+        uint32_t o[32];
+        tmem_ld32(tmem + lane_off + ch * 32, o);
+        tmem_ld_wait();
+        uint32_t w[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          w[i] = pack2<BF16>(__uint_as_float(o[2 * i]) * p.sm_scale, __uint_as_float(o[2 * i + 1]) * p.sm_scale);
+        if (row_ok) {
+          if (wide) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              *reinterpret_cast<uint4*>(grow + ch * 64 + i * 16) =
+                  make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              *reinterpret_cast<uint2*>(grow + ch * 64 + i * 8) = make_uint2(w[2 * i], w[2 * i + 1]);
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kDqsIssuer) tmem_dealloc(tmem, D);
+}
+
 bool rows8(const void* ptr, int64_t ss, int64_t sh, int64_t sb) {
   return reinterpret_cast<uintptr_t>(ptr) % 8 == 0 && ss % 4 == 0 && sh % 4 == 0 && sb % 4 == 0;
 }
@@ -936,10 +1232,28 @@ int launch_bwd(const bsa_bwd_params* bp, cudaStream_t s) {
     rc = check_launch("bwd_dkdv_sm100_kernel");
     if (rc) return rc;
   }
-  {
-    const int G = p->hq / p->hkv;
-    // as in the forward: two q heads share a tile only when they share a block list
-    const int mode = (G % 2 == 0 && p->h_pat != p->hq) ? kPairHeads : kPairRows;
+  const int G = p->hq / p->hkv;
+  // as in the forward: two q heads share a tile only when they share a block list
+  const int mode = (G % 2 == 0 && p->h_pat != p->hq) ? kPairHeads : kPairRows;
+  if (bp->ds_ws) {
+    // dQ from the dS tiles the dK/dV kernel has stored (one product per block)
+    constexpr size_t kDqsSmem = dqs_smem<D>();
+    auto kern = bwd_dq_from_ds_kernel<BF16, D>;
+    BSA_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDqsSmem));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(cdiv_i(p->sq, mode == kPairHeads ? 64 : 128), mode == kPairHeads ? p->hq / 2 : p->hq,
+                       p->batch);
+    cfg.blockDim = dim3(kDqsThreads);
+    cfg.dynamicSmemBytes = kDqsSmem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    BSA_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, tmK, *bp, mode, status));
+    rc = check_launch("bwd_dq_from_ds_kernel");
+  } else {
     auto kern = bwd_dq_sm100_kernel<BF16, D>;
     BSA_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDqSmem));
     dim3 grid(cdiv_i(p->sq, mode == kPairHeads ? 64 : 128), mode == kPairHeads ? p->hq / 2 : p->hq,

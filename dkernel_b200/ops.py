@@ -60,6 +60,8 @@ class _Plan:
         self._kv_pairs: Dict[Tuple[int, int, int], Optional[Tensor]] = {}
         self._fine: Optional["_Plan"] = None
         self._cyclic_nnz: Dict[Tuple[int, int], int] = {}
+        self._max_head_nnz: Optional[int] = None
+        self._csc_csr: Optional[Tensor] = None
 
     def max_row_nnz_cyclic(self, mod: int, rem: int) -> int:
         """Longest pattern row when only the blocks congruent to ``rem`` modulo ``mod`` count
@@ -128,6 +130,39 @@ class _Plan:
                 col_bits = zero_stride(col_bits)
             self._coarse = _Plan(lay[0], lay[1], lay[2], lay[3], 64, max_nnz, col_bits=col_bits, fine_block=bs)
         return self._coarse
+
+    def max_head_nnz(self) -> int:
+        """Attended blocks of the pattern head that has the most."""
+        if self._max_head_nnz is None:
+            self._max_head_nnz = int(self.crow[:, -1].max().item()) if self.crow.numel() else 0
+        return self._max_head_nnz
+
+    def csc_to_csr(self) -> Tensor:
+        """int32, shape and head stride of ``row``: for every CSC entry the position of the same
+        block in ``col`` (the CSR); -1 in the padding."""
+        if self._csc_csr is None:
+            crow, col, ccol, row = self.crow, self.col, self.ccol, self.row
+            dev = crow.device
+            H, R, Cn = crow.size(0), crow.size(1) - 1, ccol.size(1) - 1
+            hh = torch.arange(H, device=dev)[:, None]
+            # CSR position of every (head, row, column)
+            i = torch.arange(col.size(1), device=dev, dtype=torch.int64)[None].expand(H, -1)
+            rows_of = torch.searchsorted(crow[:, 1:].contiguous().long(), i.contiguous(), right=True).clamp_(max=max(R - 1, 0))
+            ok = (i < crow[:, -1:].long()) & (col >= 0) & (col < Cn)
+            where = torch.full((H, max(R, 1), max(Cn, 1)), -1, dtype=torch.int32, device=dev)
+            hsel = hh.expand(-1, col.size(1))[ok]
+            where[hsel, rows_of[ok], col.long()[ok]] = i[ok].to(torch.int32)
+            # ... looked up in CSC order
+            j = torch.arange(row.size(1), device=dev, dtype=torch.int64)[None].expand(H, -1)
+            cols_of = torch.searchsorted(ccol[:, 1:].contiguous().long(), j.contiguous(), right=True).clamp_(max=max(Cn - 1, 0))
+            okc = (j < ccol[:, -1:].long()) & (row >= 0) & (row < R)
+            out = torch.full(tuple(row.shape), -1, dtype=torch.int32, device=dev)
+            hselc = hh.expand(-1, row.size(1))[okc]
+            out[okc] = where[hselc, row.long()[okc], cols_of[okc]]
+            assert H == 1 or row.size(1) <= 1 or out.stride(0) == row.stride(0), \
+                "the CSC row array is expected to be dense"
+            self._csc_csr = out
+        return self._csc_csr
 
     def heads_shared_in_group(self, hq: int, hkv: int) -> bool:
         """True when all q heads of a kv group use the same pattern rows (then the
@@ -244,6 +279,7 @@ def _fwd_params(q, k, v, o, lse, seq_dim, plan: _Plan, sm_scale, causal, row_mod
 
 _warned_fallback = set()
 _DYNAMIC_TILES_FROM = 1024     # 128-row tiles from which a forward launch gets a tile counter
+_DS_WS_MAX_BYTES = 8 << 30     # largest dS scratch the backward allocates by itself
 
 
 def _launch_fwd(p, q: Tensor) -> None:
@@ -569,6 +605,18 @@ def _backward(ctx, do: Tensor, dlse: Optional[Tensor], dq=None, dk=None, dv=None
     sq_pad = (q.size(seq_dim) + 63) // 64 * 64
     delta = torch.empty((2, q.size(0), q.size(3 - seq_dim), sq_pad), dtype=torch.float32, device=q.device)
     bp.delta = _lib.ptr(delta)
+    ds_ws = None
+    if (ctx.bwd_impl != _lib.IMPL_GENERIC and plan.block_size == 64 and q.size(3) in (64, 128)
+            and q.dtype in (torch.float16, torch.bfloat16)):
+        # dS hand-over between the two tensor-core backward kernels (five products per block instead
+        # of seven) when its scratch, one 8 KB tile per attended block and (batch, head), is affordable
+        tiles = plan.max_head_nnz()
+        need = q.size(0) * q.size(hdim) * tiles * 8192
+        if 0 < need <= _DS_WS_MAX_BYTES:
+            ds_ws = torch.empty(need, dtype=torch.uint8, device=q.device)
+            bp.ds_ws = _lib.ptr(ds_ws)
+            bp.ds_tiles_per_head = tiles
+            bp.csc_csr = _lib.ptr(plan.csc_to_csr())
     with torch.cuda.device(q.device):
         _lib.check(_lib.lib().bsa_bwd(C.byref(bp), _lib.stream_of(q)), "bsa_bwd")
     return dq, dk, dv

@@ -192,6 +192,20 @@ typedef struct {
   const int32_t* kv_pairs;
   int64_t kv_pairs_sh;
   int32_t n_pairs;
+  /* Optional dS hand-over (tensor-core kernels only; the CUDA-core kernels ignore it).  With
+   * ds_ws != NULL the dK/dV kernel also stores the dS^T tile (64 x 64 elements of the input
+   * dtype) of every attended block, and dQ is computed as dQ += dS K from those tiles instead
+   * of recomputing S and dP: five products per attended block instead of seven (the reference's
+   * one backward kernel also computes S and dP once, sparse_attn_bwd.py:86-170).
+   *   ds_ws: batch * hq * ds_tiles_per_head tiles of 8192 bytes, 128-byte aligned; its contents
+   *          need not be initialised and are scratch afterwards;
+   *   ds_tiles_per_head: at least the number of attended blocks of any pattern head
+   *          (crow[h][n_rows]);
+   *   csc_csr: int32, shape and head stride of `row`: for the CSC entry at a position, the
+   *          position of the same block in `col` (the CSR).                                  */
+  void* ds_ws;
+  int64_t ds_tiles_per_head;
+  const int32_t* csc_csr;
 } bsa_bwd_params;
 
 int bsa_bwd(const bsa_bwd_params* p, void* stream);

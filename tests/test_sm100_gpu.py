@@ -194,10 +194,16 @@ BWD_CASES = [
 ]
 
 
+@pytest.mark.parametrize("route", ["ds_handover", "recompute"])
 @pytest.mark.parametrize("D", [128, 64])
 @pytest.mark.parametrize("B,Hq,Hkv,Sq,Sk,dtype,seq_dim,pk", BWD_CASES)
-def test_sm100_backward_vs_oracle(B, Hq, Hkv, Sq, Sk, dtype, seq_dim, pk, D):
+def test_sm100_backward_vs_oracle(B, Hq, Hkv, Sq, Sk, dtype, seq_dim, pk, D, route, monkeypatch):
+    """Both routes of the tensor-core backward: dQ from the dS tiles the dK/dV kernel hands over
+    (the default when the scratch is affordable) and dQ with S and dP recomputed."""
     from helpers import assert_grad_close
+    import dkernel_b200.ops as ops
+    if route == "recompute":
+        monkeypatch.setattr(ops, "_DS_WS_MAX_BYTES", 0)
     causal = pk.get("causal", True)
     bs = pk["block_size"]
     shape = (lambda h, s: (B, h, s, D)) if seq_dim == 2 else (lambda h, s: (B, s, h, D))
@@ -249,6 +255,18 @@ def test_sm100_backward_matches_generic_on_long_sequences(B, Hq, Hkv, S, pk, D):
     mod(qg, kg, vg).backward(do)
     for a, b_ in zip(grads["sm100"], (qg.grad, kg.grad, vg.grad)):
         assert torch.equal(a, b_)
+    # the route that recomputes S and dP for dQ: dK and dV are the same bits, dQ agrees
+    import dkernel_b200.ops as ops
+    saved = ops._DS_WS_MAX_BYTES
+    try:
+        ops._DS_WS_MAX_BYTES = 0
+        qg, kg, vg = (t.clone().requires_grad_() for t in (q, k, v))
+        mod(qg, kg, vg).backward(do)
+    finally:
+        ops._DS_WS_MAX_BYTES = saved
+    _wait_status_clean()
+    assert torch.equal(kg.grad, grads["sm100"][1]) and torch.equal(vg.grad, grads["sm100"][2])
+    assert_grad_close(qg.grad, grads["sm100"][0], "dq (recompute route)", 2e-2)
 
 
 def test_sm100_head_dim_64_matches_generic_over_many_tiles():
