@@ -504,6 +504,11 @@ def run_train(args, world, rank):
     assert _lib.wait_status() == 0
     total = sum_over_ranks(fwd_flops * 3.5, world)
     bwd_ms = ms - ms_fwd
+    # which backward route ran: with an affordable scratch the dK/dV kernel hands dS to the dQ kernel
+    # (5 products per attended block), otherwise dQ recomputes S and dP (7)
+    import dkernel_b200.ops as _ops
+    ds_bytes = B * hl * attn._plan().max_head_nnz() * 8192
+    handover = 0 < ds_bytes <= _ops._DS_WS_MAX_BYTES
     bwd_tflops = sum_over_ranks(fwd_flops * 2.5, world) / world / (bwd_ms * 1e-3) / 1e12
     return {
         "metric": METRIC, "value": total / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world,
@@ -514,9 +519,11 @@ def run_train(args, world, rank):
                                "recomputation not counted)" % B,
                    "fwd_ms": ms_fwd, "bwd_ms": bwd_ms, **spread,
                    "fwd_tflops": sum_over_ranks(fwd_flops, world) / world / (ms_fwd * 1e-3) / 1e12,
-                   "executed_products_per_block": 7, "algorithmic_products_per_block": 5},
+                   "executed_products_per_block": 5 if handover else 7, "algorithmic_products_per_block": 5,
+                   "ds_handover_scratch_bytes": ds_bytes if handover else 0},
         "gpu_launches": args.steps * 4, "clocks": clocks,
-        "roofline": tensor_roofline(bwd_tflops, "bwd_dkdv_sm100_kernel + bwd_dq_sm100_kernel (+ delta pre-pass)",
+        "roofline": tensor_roofline(bwd_tflops, "bwd_dkdv_sm100_kernel + %s (+ delta pre-pass)" %
+                                    ("bwd_dq_from_ds_kernel" if handover else "bwd_dq_sm100_kernel"),
                                     TRAFFIC.get("train")),
     }
 
@@ -882,7 +889,8 @@ def compact(line, keys=()):
            "sm_mhz": line["clocks"].get("sm_mhz"), "reasons": line["clocks"].get("reasons"),
            "clock_samples": line["clocks"].get("samples")}
     for k in ("fwd_ms", "bwd_ms", "fwd_tflops", "ms_min", "ms_max", "repeats", "executed_over_attended",
-              "attended_tiles", "executed_products_per_block", "algorithmic_products_per_block") + tuple(keys):
+              "attended_tiles", "executed_products_per_block", "algorithmic_products_per_block",
+              "ds_handover_scratch_bytes") + tuple(keys):
         if k in c:
             rec[k] = c[k]
     return rec
@@ -1082,7 +1090,12 @@ def main():
     ap.add_argument("--no-fp8", action="store_true", help="decode: skip the e4m3 K/V measurement")
     ap.add_argument("--e2e-chunk", type=int, default=E2E_CHUNK,
                     help="prefill: query rows per pipelined chunk of the end-to-end step")
+    ap.add_argument("--bwd-route", choices=["auto", "recompute"], default="auto",
+                    help="train: 'recompute' gives the backward no dS scratch, so that dQ recomputes S and dP")
     args = ap.parse_args()
+    if args.bwd_route == "recompute":
+        import dkernel_b200.ops as _ops
+        _ops._DS_WS_MAX_BYTES = 0
     if args.impl == "reference":
         # a step takes ~0.2 s of host time: bound the run to a few minutes, and say so in the line
         args.steps_requested = args.steps
