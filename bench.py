@@ -872,8 +872,9 @@ def run_ring(args, world, rank):
             cp(q, k, v)
 
     steps = max(2, args.steps // 4)
-    ms_fwd, _, _, _ = timed(step_fwd, steps, 3, world, repeats=3)
-    ms, spread, clocks, _ = timed(step, steps, 3, world, repeats=3)
+    # the full step first: its warm-up also sets up the point-to-point connections and the allocator's pools
+    ms, spread, clocks, _ = timed(step, steps, 5, world, repeats=3)
+    ms_fwd, _, _, _ = timed(step_fwd, steps, 5, world, repeats=3)
     assert _lib.wait_status() == 0
     tiles = int(local_stride_mask_np(H, S, cfg["block"], cfg["local"], cfg["stride"], H).sum()) * B
     flops = tiles * tile_flops(cfg["block"], D) * 3.5

@@ -226,7 +226,10 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (*reinterpret_cast<volatile int*>(wait_status) != 0) return;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int c2 = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  // Long tiles first: adjacent pairs are longest at the low (causal) end already, the caller's
+  // pairing table lists the pairs by ascending column length.
+  const int c2 = bp.kv_pairs ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
+  const int hk = blockIdx.y, b = blockIdx.z;
   const int G = p.hq / p.hkv;
   const int past = p.causal ? p.sk - p.sq : 0;
   // the two kv blocks of this tile: adjacent ones, or the caller's pairing

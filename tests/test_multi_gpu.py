@@ -1,4 +1,4 @@
-"""Multi-GPU paths on real devices (2 ranks, one process per GPU, NCCL for the plumbing):
+"""Multi-GPU paths on real devices (2 and 4 ranks, one process per GPU, NCCL for the plumbing):
 
 * KV-sharded decode: both exchange routes (the peer-store kernel ``ShardedDecoder`` and the NCCL
   all-gather ``sharded_decode``) against the single-GPU decode of the un-sharded cache and
@@ -6,7 +6,7 @@
 * Context-parallel (ring) attention: forward and backward against the single-GPU module on the
   whole sequence.
 
-Skipped on a machine with fewer than two GPUs (the gloo tests cover the host logic there).
+Skipped on a machine with fewer GPUs than ranks (the gloo tests cover the host logic there).
 """
 import math
 import os
@@ -124,11 +124,12 @@ def _worker(rank, world, port, ret):
         dist.destroy_process_group()
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_sharded_decode_and_ring_attention_on_two_gpus():
+@pytest.mark.parametrize("world", [2, 4])
+def test_sharded_decode_and_ring_attention_on_several_gpus(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
-    world = 2
     mgr = mp.Manager()
     ret = mgr.dict()
     mp.spawn(_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
-    assert dict(ret) == {0: "ok", 1: "ok"}
+    assert dict(ret) == {r: "ok" for r in range(world)}
