@@ -331,7 +331,11 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
           if (r < 0) continue;
           const uint32_t u = tl->bits[0][r >> 5] | tl->bits[1][r >> 5];
           const int pos = tl->wordpos[r >> 5] + __popc(u & ((1u << (r & 31)) - 1u));
-          if (pos < kMaxEntries) tl->cidx[pos][t] = keep_c[t][k];
+          // every attended block has a tile of the scratch, and the list holds all entries
+          if (BSA_IN_BOUNDS(pos >= 0 && pos < kMaxEntries && keep_c[t][k] >= 0 &&
+                                keep_c[t][k] < bp.ds_tiles_per_head, wait_status, 811) &&
+              pos < kMaxEntries)
+            tl->cidx[pos][t] = keep_c[t][k];
         }
       __syncthreads();
     }
@@ -361,6 +365,9 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
           tma_load_tile(gd + c * 8192, &tmDO, &tl->qdo_full[s], c * 64, r * kBS, h, b);
         }
         const int64_t row0 = ((int64_t)b * p.hq + h) * sq_pad + (int64_t)r * kBS;
+        // the entry's q block lies in the sequence, its 64 lse / delta values in their half of the workspace
+        (void)BSA_IN_BOUNDS(r >= 0 && r * kBS < p.sq && h >= 0 && h < p.hq && row0 >= 0 && row0 + kBS <= ws_half,
+                            wait_status, 812);
         bulk_load(tl->ld[s][0], bp.delta + ws_half + row0, kBS * 4, &tl->qdo_full[s]);
         bulk_load(tl->ld[s][1], bp.delta + row0, kBS * 4, &tl->qdo_full[s]);
       }
@@ -469,9 +476,11 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
           const int h = hk * G + (int)((ent >> 16) & 0xffu);
           const int64_t tile = ((int64_t)b * p.hq + h) * bp.ds_tiles_per_head + tl->cidx[e][t];
           uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(bp.ds_ws) + tile * 8192) + rk;
+          if (BSA_IN_BOUNDS(tl->cidx[e][t] >= 0 && tl->cidx[e][t] < bp.ds_tiles_per_head && h < p.hq, wait_status, 813)) {
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
-            __stcs(dst + j * kBS, make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]));
+            for (int j = 0; j < 8; ++j)
+              __stcs(dst + j * kBS, make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]));
+          }
         }
       }
     }
@@ -575,7 +584,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
     if (alive) {
       const int is_dk = (warp >> 2) & 1, ch0 = (warp >> 3) * (D / 64);
       const int kv = kblk[t] * kBS + (r_kv & 63);
-      const bool row_ok = kvalid[t] && kv < p.sk;
+      const bool row_ok = kvalid[t] && kv < p.sk && BSA_IN_BOUNDS(kv >= 0 && hk < p.hkv && b < p.batch, wait_status, 814);
       void* gbase = is_dk ? bp.dk : bp.dv;
       const int64_t sb = is_dk ? bp.dk_sb : bp.dv_sb, sh = is_dk ? bp.dk_sh : bp.dv_sh,
                     ss = is_dk ? bp.dk_ss : bp.dv_ss;
@@ -1088,7 +1097,9 @@ bwd_dq_from_ds_kernel(const __grid_constant__ Tmap4 tmK, bsa_bwd_params bp, int 
   for_entries([&](int t, int blk, int i) {
     const uint32_t u = tl->bits[0][blk >> 5] | tl->bits[1][blk >> 5];
     const int pos = tl->wordpos[blk >> 5] + __popc(u & ((1u << (blk & 31)) - 1u));
-    if (pos < kMaxBlocks) tl->cidx[pos][t] = i;
+    if (BSA_IN_BOUNDS(pos >= 0 && pos < kMaxBlocks && i >= 0 && i < bp.ds_tiles_per_head, wait_status, 815) &&
+        pos < kMaxBlocks)
+      tl->cidx[pos][t] = i;
   });
   tc_fence_before();
   __syncthreads();
@@ -1115,6 +1126,9 @@ bwd_dq_from_ds_kernel(const __grid_constant__ Tmap4 tmK, bsa_bwd_params bp, int 
       if (lane == 0) {
         mbar_expect_tx(&tl->full[s], kTileKV + (uint32_t)((a0 ? 1 : 0) + (a1 ? 1 : 0)) * 8192u);
         const int tok = (int)(ent & 0xffffu) * kBS;
+        (void)BSA_IN_BOUNDS(tok < p.sk && kvh < p.hkv && (!a0 || (tl->cidx[e][0] >= 0 && tl->cidx[e][0] < bp.ds_tiles_per_head)) &&
+                                (!a1 || (tl->cidx[e][1] >= 0 && tl->cidx[e][1] < bp.ds_tiles_per_head)),
+                            wait_status, 816);
         for (int c = 0; c < kSub; ++c)
           tma_load_tile(st + 16384 + c * 8192, &tmK, &tl->full[s], c * 64, tok, kvh, b);
         const uint8_t* ws = reinterpret_cast<const uint8_t*>(bp.ds_ws);
@@ -1157,7 +1171,7 @@ bwd_dq_from_ds_kernel(const __grid_constant__ Tmap4 tmK, bsa_bwd_params bp, int 
     // ------------------------------------------------------------ epilogue (or zero rows)
     const int r = tid, t = r >> 6;
     const int q_row = qblk[t] * kBS + (r & 63);
-    const bool row_ok = valid[t] && q_row < p.sq;
+    const bool row_ok = valid[t] && q_row < p.sq && BSA_IN_BOUNDS(q_row >= 0 && head[t] < p.hq && b < p.batch, wait_status, 817);
     uint8_t* grow = reinterpret_cast<uint8_t*>(bp.dq) +
                     ((int64_t)b * bp.dq_sb + (int64_t)head[t] * bp.dq_sh + (int64_t)q_row * bp.dq_ss) * 2;
     if (n == 0) {

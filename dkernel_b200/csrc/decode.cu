@@ -177,6 +177,8 @@ decode_kernel(const __grid_constant__ Tmap4 tmK, const __grid_constant__ Tmap4 t
     mbar_expect_tx(&sm->full[s], kStageBytes);
     const int upos = sm->unit_pos[u];
     const int tok = mod == 1 ? ks + (upos - pos0) : ks + (upos / bs / mod) * bs + upos % bs;
+    // a unit starts inside the stored tokens of its kv head (its tail may be past them)
+    (void)BSA_IN_BOUNDS(tok >= 0 && tok < p.sk && kvh >= 0 && kvh < p.hkv && b < p.batch, wait_status, 821);
     uint8_t* kdst = ring + s * kStageBytes;
     uint8_t* vdst = kdst + kTileBytes;
     if (FP8) {   // one box of [64 tokens][D bytes] per tensor, as stored
@@ -516,7 +518,8 @@ decode_kernel(const __grid_constant__ Tmap4 tmK, const __grid_constant__ Tmap4 t
           Elem<T>::from_f(acc * inv);
       if (d == 0 && p.lse) p.lse[(int64_t)b * p.lse_sb + (int64_t)h * p.lse_sh] = lse;
     } else {
-      p.ws[(((int64_t)b * p.hq + h) * nsplit + sp) * D + d] = acc * inv;
+      if (BSA_IN_BOUNDS(h < p.hq && sp < nsplit && d < D, wait_status, 822))
+        p.ws[(((int64_t)b * p.hq + h) * nsplit + sp) * D + d] = acc * inv;
       if (d == 0)
         p.ws[(int64_t)p.batch * p.hq * nsplit * D + ((int64_t)b * p.hq + h) * nsplit + sp] = lse;
     }

@@ -89,7 +89,7 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 // item -> plan (executed by the whole planner warp)
 __device__ __forceinline__ void build_plan(const bsa_fwd_params& p, int mode, int item, int tiles_x,
                                            int head_items, Plan* pl, uint32_t (*bits)[kMaxList / 32],
-                                           int lane) {
+                                           int lane, int* wait_status) {
   const int tile_rows = mode == kPairHeads ? 64 : 128;
   // Items are ordered long rows first (the tile index decreases with the item index), all
   // heads and batches of a tile index together: a round of the grid then holds tiles of
@@ -149,6 +149,9 @@ __device__ __forceinline__ void build_plan(const bsa_fwd_params& p, int mode, in
     const int32_t* cols = p.col + (int64_t)hp * p.col_sh;
     const int c_beg = __ldg(cr + row), c_end = __ldg(cr + row + 1);
     cbeg[t] = c_beg;
+    // a CSR row is a range of its head's column array
+    if (!BSA_IN_BOUNDS(c_beg >= 0 && c_beg <= c_end && (p.col_sh == 0 || c_end <= p.col_sh), wait_status, 801))
+      continue;
     const int q_pos_last = past + min(q_first + kBS, q_len) - 1;
     for (int i = c_beg + lane; i < c_end; i += 32) {
       const int blk = __ldg(cols + i);
@@ -176,7 +179,7 @@ __device__ __forceinline__ void build_plan(const bsa_fwd_params& p, int mode, in
     const uint32_t u0w = __shfl_sync(0xffffffffu, u0, w);
     const uint32_t u1w = __shfl_sync(0xffffffffu, u1, w);
     const int bw = __shfl_sync(0xffffffffu, base, w);
-    if ((uw >> lane) & 1u)
+    if (((uw >> lane) & 1u) && BSA_IN_BOUNDS(bw + __popc(uw & ((1u << lane) - 1u)) < kMaxList, wait_status, 802))
       pl->list[bw + __popc(uw & ((1u << lane) - 1u))] =
           (uint16_t)((w * 32 + lane) | (((u0w >> lane) & 1u) << 14) | (((u1w >> lane) & 1u) << 15));
   }
@@ -269,7 +272,7 @@ fwd_persist_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tm
         }
         break;
       }
-      build_plan(p, mode, item, tiles_x, head_items, &tl->plan[pb], tl->bits, lane);
+      build_plan(p, mode, item, tiles_x, head_items, &tl->plan[pb], tl->bits, lane, wait_status);
       if (lane == 0) mbar_arrive(&tl->plan_full[pb]);
     }
   } else if (warp == kWarpProd) {
@@ -291,6 +294,10 @@ fwd_persist_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tm
 #pragma unroll
           for (int t = 0; t < 2; ++t) {
             if (!pl->hvalid[t]) continue;
+            // a tile of a valid half starts inside the stored rows of its head and batch entry
+            (void)BSA_IN_BOUNDS(pl->q_start + pl->qblk[t] * kBS >= 0 && pl->q_start + pl->qblk[t] * kBS < p.sq &&
+                                    pl->head[t] >= 0 && pl->head[t] < p.hq && pl->b >= 0 && pl->b < p.batch,
+                                wait_status, 803);
             for (int c = 0; c < kSub; ++c)
               tma_load_tile(sQ + c * 16384 + t * 8192, &tmQ, &tl->q_full, c * 64,
                             pl->q_start + pl->qblk[t] * kBS, pl->head[t], pl->b);
@@ -305,6 +312,8 @@ fwd_persist_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tm
             const int s = gk & 1;
             const int tok = pl->k_start + (int)(pl->list[j] & 0x3fffu) * kBS;
             uint8_t* kdst = sRing + s * 2 * kTile;
+            // a listed block starts inside the stored keys of its kv head (its tail may be past them)
+            (void)BSA_IN_BOUNDS(tok >= 0 && tok < p.sk && pl->kvh >= 0 && pl->kvh < p.hkv, wait_status, 804);
             if (!mbar_wait(&tl->qk_done[s], ((gk >> 1) & 1) ^ 1, wait_status, 404)) return false;
             mbar_expect_tx(&tl->k_full[s], kTile);
 #pragma unroll
@@ -460,6 +469,11 @@ fwd_persist_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tm
         if (p.causal) lim = min(lim, qpos - kbase + 1);
         uint32_t cm = kFull;     // which sub-columns this row attends inside the block
         if (FB && att) cm = ((uint32_t)__ldg(fbits++) >> ((rr / (FB ? FB : 1)) * kF)) & kFull;
+        // the entries of this half that the tile walks are a prefix of its CSR row
+        if (FB && att)
+          (void)BSA_IN_BOUNDS(p.col_bits_sh == 0 || fbits - p.col_bits - (int64_t)pattern_head(head, p.h_pat, p.hq, p.hkv) *
+                                                                         p.col_bits_sh <= p.col_bits_sh,
+                              wait_status, 806);
         if (!mbar_wait(&tl->qk_done[s], (g >> 1) & 1, wait_status, 423)) { alive = false; break; }
         tc_fence_after();
         uint32_t sv[64];
@@ -606,11 +620,12 @@ fwd_persist_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ Tm
             const int sr = i * 8 + (lane >> 2);            // row of this warp's 32
             const uint4 val = *reinterpret_cast<const uint4*>(stg + sr * 64 + ((pc ^ ((sr >> 1) & 3)) * 16));
             const int srow = q_row - lane + sr;            // row inside the sequence
-            if (hvalid && srow < q_len && ch * 32 + pc * 8 < p.d)   // columns past the real head dim are padding
+            if (hvalid && srow < q_len && ch * 32 + pc * 8 < p.d &&   // columns past the real head dim are padding
+                BSA_IN_BOUNDS(pl->q_start + srow >= 0 && pl->q_start + srow < p.sq, wait_status, 805))
               *reinterpret_cast<uint4*>(orow + (int64_t)(sr - lane) * p.o_ss * 2 + ch * 64 + pc * 16) = val;
           }
           __syncwarp();   // the next chunk overwrites the staging rows
-        } else if (row_ok) {
+        } else if (row_ok && BSA_IN_BOUNDS(pl->q_start + q_row >= 0 && pl->q_start + q_row < p.sq, wait_status, 805)) {
 #pragma unroll
           for (int i = 0; i < 8; ++i)
             if (ch * 32 + i * 4 < p.d)

@@ -93,6 +93,15 @@ static __device__ __noinline__ void record_wait_failure(int* status, int code) {
     }
   }
 }
+// Bounds-checking build (-DBSA_DEBUG_BOUNDS, `python -m dkernel_b200._build --debug`): the index
+// invariants of the kernels are checked where the indices are formed.  A violated one records its
+// code (800 + n) in the status block like a wait that gave up, and the access it guards is skipped:
+// nothing traps, the context stays usable.  The release build compiles the checks away.
+#ifdef BSA_DEBUG_BOUNDS
+#define BSA_IN_BOUNDS(cond, status, code) ((cond) ? true : (::bsa::record_wait_failure((status), (code)), false))
+#else
+#define BSA_IN_BOUNDS(cond, status, code) (true)
+#endif
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code,
                                           uint64_t limit_ns = kWaitLimitNs) {
   if (mbar_try_wait(bar, parity)) return true;

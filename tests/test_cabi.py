@@ -147,3 +147,16 @@ def test_exchange_buffer_geometry_and_validation_need_no_device():
     p.stage_o = p.stage_lse = p.out = 4096
     p.xbuf[0] = 4096
     assert lib.bsa_xchg_merge(C.byref(p), None) == -1 and b"exchange buffer 1" in lib.bsa_last_error()
+
+
+def test_graft_entry_build_compiles_and_checks_the_abi():
+    """The driver's build hook: both libraries compile (cached objects make this quick) and the
+    ABI version it asserts is the header's."""
+    import re
+    import __graft_entry__
+    from dkernel_b200 import _lib
+    __graft_entry__.build()
+    hdr = open(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "include", "bsa.h")).read()
+    assert int(re.search(r"#define BSA_ABI_VERSION (\d+)", hdr).group(1)) == _lib.lib().bsa_abi_version()
+    from dkernel_b200 import _build
+    assert os.path.exists(_build.LIB_DEBUG)
