@@ -851,16 +851,18 @@ def run_fwd_d64(args, world, rank):
 
 def run_ring(args, world, rank):
     """Context-parallel training step (N > 1): BASELINE config 3's problem (B=2, S=8192, H=32, D=128) with
-    the SEQUENCE split over the ranks (ring attention: K/V chunks round the ring over NCCL send/recv, LSE
-    merge, dK/dV contributions sent to the chunk owner); fixed total size ("strong")."""
+    the SEQUENCE split over the ranks (ring attention, zig-zag split: K/V chunks round the ring over NCCL
+    send/recv, LSE merge, dK/dV contributions sent to the chunk owner); fixed total size ("strong")."""
     from dkernel_b200 import _lib
     from dkernel_b200.dist import ContextParallelSparseAttention
     cfg = WORKLOADS["train"]
     B, S, H, D = cfg["B"], cfg["S"], cfg["Hq"], cfg["D"]
-    cp = ContextParallelSparseAttention(H, S, cfg["block"], cfg["local"], cfg["stride"], seq_dim=1)
-    a, b_ = cp.bounds[rank]
+    # zig-zag split: rank r holds pieces r and 2 * world - 1 - r of the sequence, so that every rank
+    # has the same share of the causal mask
+    cp = ContextParallelSparseAttention(H, S, cfg["block"], cfg["local"], cfg["stride"], seq_dim=1, zigzag=True)
     g = torch.Generator(device="cuda").manual_seed(99 + rank)
-    q, k, v, do = (torch.randn((B, b_ - a, H, D), generator=g, device="cuda").to(torch.bfloat16) for _ in range(4))
+    q, k, v, do = (torch.randn((B, S // world, H, D), generator=g, device="cuda").to(torch.bfloat16)
+                   for _ in range(4))
     q.requires_grad_(), k.requires_grad_(), v.requires_grad_()
 
     def step():

@@ -267,10 +267,28 @@ def chunk_bounds(seq_len: int, world: int, block_size: int) -> List[Tuple[int, i
     return [(r * c, (r + 1) * c) for r in range(world)]
 
 
+def zigzag_bounds(seq_len: int, world: int, block_size: int) -> List[List[Tuple[int, int]]]:
+    """Two position ranges per rank: the sequence is cut into 2 * world equal pieces and rank r owns
+    pieces r and 2 * world - 1 - r (its local tensors are the two pieces back to back).  Under a
+    causal mask every rank then has the same share of the work, which contiguous chunks do not
+    give (there the last rank attends everything and the first only itself)."""
+    assert seq_len % (2 * world) == 0 and (seq_len // (2 * world)) % block_size == 0, \
+        f"sequence length {seq_len} must split into {2 * world} pieces that are multiples of {block_size}"
+    c = seq_len // (2 * world)
+    return [[(r * c, (r + 1) * c), ((2 * world - 1 - r) * c, (2 * world - r) * c)] for r in range(world)]
+
+
+def zigzag_shard(x: Tensor, rank: int, world: int, block_size: int, seq_dim: int = 1) -> Tensor:
+    """This rank's part of a whole-sequence tensor under the zig-zag split (for tests and loaders)."""
+    (a0, a1), (b0, b1) = zigzag_bounds(x.size(seq_dim), world, block_size)[rank]
+    return torch.cat([x.narrow(seq_dim, a0, a1 - a0), x.narrow(seq_dim, b0, b1 - b0)], seq_dim).contiguous()
+
+
 def ring_steps(rank: int, world: int, causal: bool = True) -> List[Tuple[int, int, bool]]:
     """The ring schedule of one rank: [(step, kv_chunk, active)].  At step t the rank holds kv
     chunk (rank - t) mod world (its own at t = 0; chunks arrive from the previous rank); with a
-    causal mask only chunks at or before the rank's own q chunk are computed."""
+    causal mask over contiguous chunks only chunks at or before the rank's own q chunk are computed
+    (pass causal=False for the zig-zag split, where every pair of ranks has visible pieces)."""
     return [(t, (rank - t) % world, (not causal) or ((rank - t) % world) <= rank) for t in range(world)]
 
 
@@ -359,7 +377,7 @@ def ring_backward(q: Tensor, k: Tensor, v: Tensor, o: Tensor, lse: Tensor, do: T
 class _RingAttention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, owner):
-        out, lse = ring_forward(q, k, v, owner._forward_chunk, owner._merge, owner.group, owner.causal)
+        out, lse = ring_forward(q, k, v, owner._forward_chunk, owner._merge, owner.group, owner.skip_later_chunks)
         ctx.save_for_backward(q, k, v, out, lse)
         ctx.owner = owner
         return out, lse
@@ -371,13 +389,14 @@ class _RingAttention(torch.autograd.Function):
         if dlse is not None and not bool((dlse != 0).any()):
             dlse = None
         dq, dk, dv = ring_backward(q, k, v, out, lse, do.contiguous(), dlse, owner._backward_chunk,
-                                   owner.group, owner.causal)
+                                   owner.group, owner.skip_later_chunks)
         return dq, dk, dv, None
 
 
 class ContextParallelSparseAttention(torch.nn.Module):
     """Local-stride block-sparse attention over a sequence that is split across the ranks of a
-    process group (one contiguous chunk of q, k and v per rank), forward and backward.
+    process group (one contiguous chunk of q, k and v per rank, or with ``zigzag=True`` the two
+    pieces of ``zigzag_bounds`` back to back, which balances a causal mask), forward and backward.
 
     Rank r attends its q chunk to kv chunk s through a ``SparseAttention`` built on the block mask
     of that chunk pair (``get_sparse_attn_mask`` with ``q_start_position`` / ``kv_start_position``,
@@ -391,17 +410,23 @@ class ContextParallelSparseAttention(torch.nn.Module):
     def __init__(self, num_heads: int, seq_len: int, block_size: int, local_blocks: int,
                  vert_stride: int, *, num_kv_heads: Optional[int] = None, homo_head: bool = False,
                  head_sliding_offset: int = 0, seq_dim: int = 1, causal: bool = True, group=None,
-                 **kwargs):
+                 zigzag: bool = False, **kwargs):
         super().__init__()
         self.group = group
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
-        self.bounds = chunk_bounds(seq_len, self.world, block_size)
+        self.zigzag = bool(zigzag) and causal
+        # per rank: one position range, or two with the zig-zag split
+        self.pieces = (zigzag_bounds(seq_len, self.world, block_size) if self.zigzag
+                       else [[b] for b in chunk_bounds(seq_len, self.world, block_size)])
+        self.bounds = [p[0] for p in self.pieces] if not self.zigzag else None
         self.mask_args = dict(num_heads=num_heads, block_size=block_size, local_blocks=local_blocks,
                               vert_stride=vert_stride, homo_head=homo_head, num_kv_heads=num_kv_heads,
                               head_sliding_offset=head_sliding_offset, causal=causal)
         self.block_size, self.seq_dim, self.causal, self.kwargs = block_size, seq_dim, causal, kwargs
         self._chunks: Dict[int, object] = {}
         self._scale = None
+        # contiguous chunks under a causal mask: kv chunks after the own q chunk are skipped
+        self.skip_later_chunks = causal and not self.zigzag
 
     def _module(self, s: int):
         """SparseAttention of the (own q chunk, kv chunk s) pair, built on first use."""
@@ -409,12 +434,30 @@ class ContextParallelSparseAttention(torch.nn.Module):
             from .interface import SparseAttention
             from .utils import get_sparse_attn_mask
             a = self.mask_args
-            (q0, q1), (k0, k1) = self.bounds[self.rank], self.bounds[s]
-            bmask = get_sparse_attn_mask(a["num_heads"], q1 - q0, a["block_size"], a["local_blocks"],
-                                         a["vert_stride"], homo_head=a["homo_head"], dtype=torch.uint8,
-                                         num_kv_heads=a["num_kv_heads"],
-                                         head_sliding_offset=a["head_sliding_offset"], causal=a["causal"],
-                                         q_start_position=q0, kv_start_position=k0, kv_seqlen=k1 - k0)[1]
+
+            def piece_mask(qr, kr):
+                (q0, q1), (k0, k1) = qr, kr
+                return get_sparse_attn_mask(a["num_heads"], q1 - q0, a["block_size"], a["local_blocks"],
+                                            a["vert_stride"], homo_head=a["homo_head"], dtype=torch.uint8,
+                                            num_kv_heads=a["num_kv_heads"],
+                                            head_sliding_offset=a["head_sliding_offset"], causal=a["causal"],
+                                            q_start_position=q0, kv_start_position=k0, kv_seqlen=k1 - k0)[1]
+            # Block mask of (own pieces) x (pieces of rank s), stitched from the pieces' masks.  A kv
+            # piece that lies after a q piece is invisible under a causal mask.  Own pair: the
+            # pieces are in position order locally, so the kernel's own causal test on local
+            # indices is the right one (the diagonal pieces get it, the later-q / earlier-kv piece
+            # passes it whole, the earlier-q / later-kv piece fails it whole); other pairs have no
+            # diagonal piece and run without it.
+            rows = []
+            for qr in self.pieces[self.rank]:
+                row = []
+                for kr in self.pieces[s]:
+                    m = piece_mask(qr, kr)
+                    if self.causal and kr[0] > qr[0]:
+                        m = torch.zeros_like(m)
+                    row.append(m)
+                rows.append(torch.cat(row, -1))
+            bmask = torch.cat(rows, -2).contiguous()
             self._chunks[s] = SparseAttention(self.block_size, bmask, seq_dim=self.seq_dim,
                                               causal=self.causal and s == self.rank, **self.kwargs)
         return self._chunks[s]
@@ -450,11 +493,11 @@ class ContextParallelSparseAttention(torch.nn.Module):
         if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad):
             out, lse = _RingAttention.apply(q, k, v, self)
         else:
-            out, lse = ring_forward(q, k, v, self._forward_chunk, self._merge, self.group, self.causal)
+            out, lse = ring_forward(q, k, v, self._forward_chunk, self._merge, self.group, self.skip_later_chunks)
         return (out, lse) if return_lse else out
 
 
 __all__ = ["head_shard", "kv_shard_ranges", "pack_kv_shard", "kv_shard_cyclic_blocks", "pack_kv_shard_cyclic",
            "sharded_decode", "ShardedDecoder",
-           "chunk_bounds", "ring_steps", "ring_forward", "ring_backward",
+           "chunk_bounds", "zigzag_bounds", "zigzag_shard", "ring_steps", "ring_forward", "ring_backward",
            "ContextParallelSparseAttention"]

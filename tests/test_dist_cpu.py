@@ -100,14 +100,16 @@ def test_two_ranks_gloo():
     assert dict(ret) == {0: "ok", 1: "ok"}
 
 
-def _ring_worker(rank, world, port, ret):
+def _ring_worker(rank, world, port, ret, zigzag=False):
     """Ring attention schedule (K/V chunks round the ring, LSE merge, dK/dV contributions sent to
-    the chunk's owner) with the oracle as the per-chunk compute; compared with full-sequence autograd."""
+    the chunk's owner) with the oracle as the per-chunk compute; compared with full-sequence autograd.
+    zigzag: every rank owns two pieces of the sequence (r and 2 * world - 1 - r) and no step is skipped."""
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        from dkernel_b200.dist import chunk_bounds, ring_backward, ring_forward, ring_steps
+        from dkernel_b200.dist import (chunk_bounds, ring_backward, ring_forward, ring_steps, zigzag_bounds,
+                                       zigzag_shard)
         torch.manual_seed(1)
         B, H, S, D, bs = 2, 2, 512, 16, 64
         scale = 1.0 / D ** 0.5
@@ -115,8 +117,14 @@ def _ring_worker(rank, world, port, ret):
         dl = torch.randn(B, H, S)
         bm = O.block_mask(H, S, bs, 2, 3)
         dense = O.token_mask(bm, bs, S, S).bool()                   # (H, S, S), causal
-        bounds = chunk_bounds(S, world, bs)
-        assert [s for _, s, a in ring_steps(rank, world) if a] == list(range(rank, -1, -1))
+        if zigzag:
+            pieces = zigzag_bounds(S, world, bs)
+            assert sorted(x for p in pieces for x in p) == [(i * S // (2 * world), (i + 1) * S // (2 * world))
+                                                            for i in range(2 * world)]
+        else:
+            pieces = [[b] for b in chunk_bounds(S, world, bs)]
+            assert [s for _, s, a in ring_steps(rank, world) if a] == list(range(rank, -1, -1))
+        idx = [torch.cat([torch.arange(a, b) for a, b in p]) for p in pieces]     # positions of every rank
 
         qf, kf, vf = (t.clone().requires_grad_() for t in (q, k, v))
         ref, ref_lse = O.masked_dense_attention(qf, kf, vf, dense.to(torch.uint8), scale, seq_dim=1,
@@ -124,7 +132,7 @@ def _ring_worker(rank, world, port, ret):
         ((ref * do).sum() + (ref_lse * dl).sum()).backward()
 
         def pair_mask(r, s):
-            return dense[:, bounds[r][0]:bounds[r][1], bounds[s][0]:bounds[s][1]]
+            return dense[:, idx[r]][:, :, idx[s]]
 
         def fwd_chunk(qc, kc, vc, r, s):
             return O.masked_dense_attention(qc, kc, vc, pair_mask(r, s).to(torch.uint8), scale, seq_dim=1,
@@ -148,26 +156,30 @@ def _ring_worker(rank, world, port, ret):
                     torch.einsum("bhmn,bmhd->bnhd", ds, qc) * scale,
                     torch.einsum("bhmn,bmhd->bnhd", p, dout))
 
-        a, b_ = bounds[rank]
-        ql, kl, vl = q[:, a:b_].contiguous(), k[:, a:b_].contiguous(), v[:, a:b_].contiguous()
-        out, lse = ring_forward(ql, kl, vl, fwd_chunk, merge)
-        assert (out - ref[:, a:b_].detach()).abs().max() < 1e-5
-        assert (lse - ref_lse[:, :, a:b_].detach()).abs().max() < 1e-5
-        dq, dk, dv = ring_backward(ql, kl, vl, out, lse, do[:, a:b_].contiguous(), dl[:, :, a:b_].contiguous(),
-                                   bwd_chunk)
+        mine = idx[rank]
+        ql, kl, vl = q[:, mine].contiguous(), k[:, mine].contiguous(), v[:, mine].contiguous()
+        if zigzag:
+            assert torch.equal(ql, zigzag_shard(q, rank, world, bs, seq_dim=1))
+        skip = not zigzag      # contiguous chunks: kv chunks after the own one are skipped
+        out, lse = ring_forward(ql, kl, vl, fwd_chunk, merge, causal=skip)
+        assert (out - ref[:, mine].detach()).abs().max() < 1e-5
+        assert (lse - ref_lse[:, :, mine].detach()).abs().max() < 1e-5
+        dq, dk, dv = ring_backward(ql, kl, vl, out, lse, do[:, mine].contiguous(), dl[:, :, mine].contiguous(),
+                                   bwd_chunk, causal=skip)
         for got, want, name in ((dq, qf.grad, "dq"), (dk, kf.grad, "dk"), (dv, vf.grad, "dv")):
-            err = (got - want[:, a:b_]).abs().max().item()
+            err = (got - want[:, mine]).abs().max().item()
             assert err < 1e-4, f"{name}: {err}"
         ret[rank] = "ok"
     finally:
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("zigzag", [False, True])
 @pytest.mark.parametrize("world", [2, 4])
-def test_ring_attention_schedule_gloo(world):
+def test_ring_attention_schedule_gloo(world, zigzag):
     mgr = mp.Manager()
     ret = mgr.dict()
-    mp.spawn(_ring_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
+    mp.spawn(_ring_worker, args=(world, _free_port(), ret, zigzag), nprocs=world, join=True)
     assert dict(ret) == {r: "ok" for r in range(world)}
 
 

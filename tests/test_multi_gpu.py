@@ -37,7 +37,7 @@ def _worker(rank, world, port, ret):
         from oracle import dkernel_oracle as O
         from dkernel_b200 import LocalStrideSparseAttention, _lib
         from dkernel_b200.dist import (ContextParallelSparseAttention, ShardedDecoder, kv_shard_ranges,
-                                       pack_kv_shard, pack_kv_shard_cyclic, sharded_decode)
+                                       pack_kv_shard, pack_kv_shard_cyclic, sharded_decode, zigzag_bounds)
         # ---------------------------------------------------------------- KV-sharded decode
         B, S, Hq, Hkv, D, bs = 5, 2048, 8, 2, 128, 64
         attn = LocalStrideSparseAttention.__wrapped__(Hq, S, bs, 4, 4, num_kv_heads=Hkv, seq_dim=1)
@@ -103,22 +103,25 @@ def _worker(rank, world, port, ret):
         qf, kf, vf = (t.clone().requires_grad_() for t in (q, k, v))
         ref, ref_lse = full(qf, kf, vf, return_lse=True)
         ref.backward(do)
-        cp = ContextParallelSparseAttention(H, S, bs, 4, 4, num_kv_heads=Hkv, seq_dim=1)
-        a, b_ = cp.bounds[rank]
-        ql, kl, vl = (t[:, a:b_].clone().requires_grad_() for t in (q, k, v))
-        out, lse = cp(ql, kl, vl, return_lse=True)
-        out.backward(do[:, a:b_])
-        torch.cuda.synchronize()
-        assert _lib.wait_status() == 0
-        assert (out.float() - ref[:, a:b_].float()).abs().max().item() <= 2e-2
-        assert (lse - ref_lse[:, :, a:b_]).abs().max().item() <= 1e-3
-        for got, want, name in ((ql.grad, qf.grad, "dq"), (kl.grad, kf.grad, "dk"), (vl.grad, vf.grad, "dv")):
-            w = want[:, a:b_].float()
-            rel = ((got.float() - w).norm() / w.norm()).item()
-            assert rel <= 5e-2, f"ring {name}: relative norm error {rel:.3e}"
-        with torch.no_grad():
-            out2 = cp(ql, kl, vl)
-        assert (out2.float() - out.float()).abs().max().item() <= 1e-6
+        # contiguous chunks, and the zig-zag split (two pieces per rank, balanced under the causal mask)
+        for zigzag in (False, True):
+            cp = ContextParallelSparseAttention(H, S, bs, 4, 4, num_kv_heads=Hkv, seq_dim=1, zigzag=zigzag)
+            pieces = zigzag_bounds(S, world, bs)[rank] if zigzag else [cp.bounds[rank]]
+            mine = torch.cat([torch.arange(a, b_) for a, b_ in pieces]).to(dev)
+            ql, kl, vl = (t[:, mine].clone().requires_grad_() for t in (q, k, v))
+            out, lse = cp(ql, kl, vl, return_lse=True)
+            out.backward(do[:, mine])
+            torch.cuda.synchronize()
+            assert _lib.wait_status() == 0
+            assert (out.float() - ref[:, mine].float()).abs().max().item() <= 2e-2, f"zigzag={zigzag}"
+            assert (lse - ref_lse[:, :, mine]).abs().max().item() <= 1e-3, f"zigzag={zigzag}"
+            for got, want, name in ((ql.grad, qf.grad, "dq"), (kl.grad, kf.grad, "dk"), (vl.grad, vf.grad, "dv")):
+                w = want[:, mine].float()
+                rel = ((got.float() - w).norm() / w.norm()).item()
+                assert rel <= 5e-2, f"ring {name} (zigzag={zigzag}): relative norm error {rel:.3e}"
+            with torch.no_grad():
+                out2 = cp(ql, kl, vl)
+            assert (out2.float() - out.float()).abs().max().item() <= 1e-6
         ret[rank] = "ok"
     finally:
         dist.destroy_process_group()
