@@ -333,14 +333,16 @@ def tensor_roofline(tflops, kernel, traffic=None, source=None):
          "frac_of_sustained": tflops / peaks["tflops_sustained"] if peaks["tflops_sustained"] else None,
          "frac_of_nominal_2250": tflops / NOMINAL_BF16_TFLOPS, "kernel": kernel}
     if traffic is not None:
-        r["traffic_source"] = source or "ncu capture of the same workload (profiles/), not measured in this run"
+        r["traffic_source"] = source or "ncu capture of the same workload, not measured in this run"
     return r
 
 
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel, taken
 # from ncu captures of the same full-size workloads on one GPU; None = not captured.
-# train: dK/dV 796.7 MB + dQ 664.6 MB (the roofline line covers both backward kernels).
-TRAFFIC = {"prefill": 684.5e6, "train": 796.7e6 + 664.6e6, "decode": 406.3e6, "varlen": None}
+# train: dK/dV 3035.4 MB + dQ 2477.2 MB with the dS hand-over, 2 x 2.19 GB of which is the dS scratch
+# written and read back (the roofline line covers both backward kernels); the recompute route moves
+# 796.7 + 664.6 MB.
+TRAFFIC = {"prefill": 670.8e6, "train": 3035.4e6 + 2477.2e6, "decode": 406.3e6, "varlen": 1249.4e6}
 
 
 def run_prefill(args, world, rank, strong=False, with_e2e=True):
@@ -524,7 +526,7 @@ def run_train(args, world, rank):
         "gpu_launches": args.steps * 4, "clocks": clocks,
         "roofline": tensor_roofline(bwd_tflops, "bwd_dkdv_sm100_kernel + %s (+ delta pre-pass)" %
                                     ("bwd_dq_from_ds_kernel" if handover else "bwd_dq_sm100_kernel"),
-                                    TRAFFIC.get("train")),
+                                    TRAFFIC.get("train") if handover else 796.7e6 + 664.6e6),
     }
 
 
@@ -757,7 +759,7 @@ def decode_line(args, world, rank):
         "gpu_launches": rec["steps"] * rec["launches_per_step"], "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm"], "unit": "GB/s",
                      "frac": gbs / peaks["hbm"], "traffic": TRAFFIC.get("decode"),
-                     "traffic_source": "ncu capture of the same workload (profiles/), not measured in this run",
+                     "traffic_source": "ncu capture of the same workload, not measured in this run",
                      "peak_source": peaks["source"], "frac_of_nominal_8000": gbs / NOMINAL_HBM_GBS,
                      "kernel": "decode_kernel<bf16,128> (+ merge_kernel)", "per_gpu": True},
     }
