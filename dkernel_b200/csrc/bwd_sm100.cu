@@ -115,8 +115,10 @@ __global__ void bwd_delta_vec_kernel(bsa_bwd_params bp) {
     uint4 ov[D / 64], gv[D / 64];
 #pragma unroll
     for (int j = 0; j < D / 64; ++j) {
-      ov[j] = load16(op + j * 128, wide);
-      gv[j] = load16(gp + j * 128, wide);
+      // D is the kernels' padded width; the rows hold p.d columns
+      const bool in = j * 64 + sub * 8 < p.d;
+      ov[j] = in ? load16(op + j * 128, wide) : make_uint4(0u, 0u, 0u, 0u);
+      gv[j] = in ? load16(gp + j * 128, wide) : make_uint4(0u, 0u, 0u, 0u);
     }
 #pragma unroll
     for (int j = 0; j < D / 64; ++j) s += dot8<BF16>(ov[j], gv[j]);
@@ -605,12 +607,14 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
           if (wide) {
 #pragma unroll
             for (int i = 0; i < 4; ++i)
-              *reinterpret_cast<uint4*>(grow + ch * 64 + i * 16) =
-                  make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+              if (ch * 32 + i * 8 < p.d)   // columns at or past the real head dim are padding
+                *reinterpret_cast<uint4*>(grow + ch * 64 + i * 16) =
+                    make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
           } else {
 #pragma unroll
             for (int i = 0; i < 8; ++i)
-              *reinterpret_cast<uint2*>(grow + ch * 64 + i * 8) = make_uint2(w[2 * i], w[2 * i + 1]);
+              if (ch * 32 + i * 4 < p.d)
+                *reinterpret_cast<uint2*>(grow + ch * 64 + i * 8) = make_uint2(w[2 * i], w[2 * i + 1]);
           }
         }
       }
@@ -626,7 +630,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
           ((int64_t)b * bp.dk_sb + (int64_t)hk * bp.dk_sh + (int64_t)kv * bp.dk_ss) * 2);
       uint2* d2 = reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(bp.dv) +
           ((int64_t)b * bp.dv_sb + (int64_t)hk * bp.dv_sh + (int64_t)kv * bp.dv_ss) * 2);
-      for (int i = 0; i < D / 4; ++i) { d1[i] = make_uint2(0u, 0u); d2[i] = make_uint2(0u, 0u); }
+      for (int i = 0; i < p.d / 4; ++i) { d1[i] = make_uint2(0u, 0u); d2[i] = make_uint2(0u, 0u); }
     }
   }
   tc_fence_before();
@@ -969,11 +973,13 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
         if (wide) {
 #pragma unroll
           for (int i = 0; i < 4; ++i)
-            *reinterpret_cast<uint4*>(grow + i * 16) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+            if (qtr * 32 + i * 8 < p.d)   // columns at or past the real head dim are padding
+              *reinterpret_cast<uint4*>(grow + i * 16) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
         } else {
 #pragma unroll
           for (int i = 0; i < 8; ++i)
-            *reinterpret_cast<uint2*>(grow + i * 8) = make_uint2(w[2 * i], w[2 * i + 1]);
+            if (qtr * 32 + i * 4 < p.d)
+              *reinterpret_cast<uint2*>(grow + i * 8) = make_uint2(w[2 * i], w[2 * i + 1]);
         }
       }
     }
@@ -985,7 +991,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__ T
     if (valid[t] && q_row < p.sq) {
       uint2* d = reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(bp.dq) +
           ((int64_t)b * bp.dq_sb + (int64_t)head[t] * bp.dq_sh + (int64_t)q_row * bp.dq_ss) * 2);
-      for (int i = 0; i < D / 4; ++i) d[i] = make_uint2(0u, 0u);
+      for (int i = 0; i < p.d / 4; ++i) d[i] = make_uint2(0u, 0u);
     }
   }
   tc_fence_before();
@@ -1176,7 +1182,7 @@ bwd_dq_from_ds_kernel(const __grid_constant__ Tmap4 tmK, bsa_bwd_params bp, int 
                     ((int64_t)b * bp.dq_sb + (int64_t)head[t] * bp.dq_sh + (int64_t)q_row * bp.dq_ss) * 2;
     if (n == 0) {
       if (row_ok)
-        for (int i = 0; i < D / 4; ++i) reinterpret_cast<uint2*>(grow)[i] = make_uint2(0u, 0u);
+        for (int i = 0; i < p.d / 4; ++i) reinterpret_cast<uint2*>(grow)[i] = make_uint2(0u, 0u);
     } else if (mbar_wait(&tl->all_done, 0, wait_status, 333)) {
       tc_fence_after();
       const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
@@ -1195,12 +1201,14 @@ bwd_dq_from_ds_kernel(const __grid_constant__ Tmap4 tmK, bsa_bwd_params bp, int 
           if (wide) {
 #pragma unroll
             for (int i = 0; i < 4; ++i)
-              *reinterpret_cast<uint4*>(grow + ch * 64 + i * 16) =
-                  make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+              if (ch * 32 + i * 8 < p.d)   // columns at or past the real head dim are padding
+                *reinterpret_cast<uint4*>(grow + ch * 64 + i * 16) =
+                    make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
           } else {
 #pragma unroll
             for (int i = 0; i < 8; ++i)
-              *reinterpret_cast<uint2*>(grow + ch * 64 + i * 8) = make_uint2(w[2 * i], w[2 * i + 1]);
+              if (ch * 32 + i * 4 < p.d)
+                *reinterpret_cast<uint2*>(grow + ch * 64 + i * 8) = make_uint2(w[2 * i], w[2 * i + 1]);
           }
         }
       }
@@ -1221,16 +1229,18 @@ int launch_bwd(const bsa_bwd_params* bp, cudaStream_t s) {
   constexpr size_t kDkdvSmem = dkdv_smem<D>(), kDqSmem = dq_smem<D>();
   const bsa_fwd_params* p = &bp->f;
   Tmap4 tmQ, tmK, tmV, tmDO;
-  int rc = make_tmap_4d(&tmQ, p->q, 2, kD, p->sq, p->hq, p->batch, p->q_ss * 2, p->q_sh * 2, p->q_sb * 2,
+  // the maps carry the real head dim: columns between it and the kernels' width D come back as zeros
+  (void)kD;
+  int rc = make_tmap_4d(&tmQ, p->q, 2, p->d, p->sq, p->hq, p->batch, p->q_ss * 2, p->q_sh * 2, p->q_sb * 2,
                         64, 64, true, BF16);
   if (rc) return rc;
-  rc = make_tmap_4d(&tmDO, bp->d_o, 2, kD, p->sq, p->hq, p->batch, bp->do_ss * 2, bp->do_sh * 2,
+  rc = make_tmap_4d(&tmDO, bp->d_o, 2, p->d, p->sq, p->hq, p->batch, bp->do_ss * 2, bp->do_sh * 2,
                     bp->do_sb * 2, 64, 64, true, BF16);
   if (rc) return rc;
-  rc = make_tmap_4d(&tmK, p->k, 2, kD, p->sk, p->hkv, p->batch, p->k_ss * 2, p->k_sh * 2, p->k_sb * 2,
+  rc = make_tmap_4d(&tmK, p->k, 2, p->d, p->sk, p->hkv, p->batch, p->k_ss * 2, p->k_sh * 2, p->k_sb * 2,
                     64, 64, true, BF16);
   if (rc) return rc;
-  rc = make_tmap_4d(&tmV, p->v, 2, kD, p->sk, p->hkv, p->batch, p->v_ss * 2, p->v_sh * 2, p->v_sb * 2,
+  rc = make_tmap_4d(&tmV, p->v, 2, p->d, p->sk, p->hkv, p->batch, p->v_ss * 2, p->v_sh * 2, p->v_sb * 2,
                     64, 64, true, BF16);
   if (rc) return rc;
   int* status = wait_status_ptr();
@@ -1298,7 +1308,7 @@ bool sm100_bwd_supported(const bsa_bwd_params* bp, const char** why) {
   const bsa_fwd_params* p = &bp->f;
   auto no = [&](const char* w) { *why = w; return false; };
   if (!(p->dtype == BSA_F16 || p->dtype == BSA_BF16)) return no("dtype is not f16/bf16");
-  if (p->d != 128 && p->d != 64) return no("head dim is not 64 or 128");
+  if (p->d < 16 || p->d > 128 || p->d % 8) return no("head dim is not a multiple of 8 in [16, 128]");
   if (p->block_size != kBS) return no("block size is not 64");
   if (p->sk > kMaxBlocks * kBS || p->sq > kMaxBlocks * kBS) return no("more than 65536 positions");
   if ((p->hq / p->hkv) * cdiv_i(p->sq, kBS) > kMaxEntries)
@@ -1321,7 +1331,8 @@ bool sm100_bwd_supported(const bsa_bwd_params* bp, const char** why) {
 
 int sm100_bwd(const bsa_bwd_params* bp, cudaStream_t s) {
   const bool bf16 = bp->f.dtype == BSA_BF16;
-  if (bp->f.d == 128) return bf16 ? launch_bwd<true, 128>(bp, s) : launch_bwd<false, 128>(bp, s);
+  // two kernel widths; a narrower head is padded with the zeros TMA supplies for out-of-range columns
+  if (bp->f.d > 64) return bf16 ? launch_bwd<true, 128>(bp, s) : launch_bwd<false, 128>(bp, s);
   return bf16 ? launch_bwd<true, 64>(bp, s) : launch_bwd<false, 64>(bp, s);
 }
 

@@ -606,7 +606,7 @@ def _backward(ctx, do: Tensor, dlse: Optional[Tensor], dq=None, dk=None, dv=None
     delta = torch.empty((2, q.size(0), q.size(3 - seq_dim), sq_pad), dtype=torch.float32, device=q.device)
     bp.delta = _lib.ptr(delta)
     ds_ws = None
-    if (ctx.bwd_impl != _lib.IMPL_GENERIC and plan.block_size == 64 and q.size(3) in (64, 128)
+    if (ctx.bwd_impl != _lib.IMPL_GENERIC and plan.block_size == 64 and q.size(3) % 8 == 0 and q.size(3) <= 128
             and q.dtype in (torch.float16, torch.bfloat16)):
         # dS hand-over between the two tensor-core backward kernels (five products per block instead
         # of seven) when its scratch, one 8 KB tile per attended block and (batch, head), is affordable

@@ -195,6 +195,15 @@ BWD_CASES = [
 
 
 @pytest.mark.parametrize("route", ["ds_handover", "recompute"])
+@pytest.mark.parametrize("D", [48, 96, 80])
+@pytest.mark.parametrize("B,Hq,Hkv,Sq,Sk,dtype,seq_dim,pk", [BWD_CASES[1], BWD_CASES[2], BWD_CASES[3], BWD_CASES[5]])
+def test_sm100_backward_other_head_dims(B, Hq, Hkv, Sq, Sk, dtype, seq_dim, pk, D, route, monkeypatch):
+    """Head dims between the kernels' two widths (64, 128): the tensor maps carry the real head dim,
+    the columns up to the width come back as zeros and only the real columns of dQ/dK/dV are stored."""
+    test_sm100_backward_vs_oracle(B, Hq, Hkv, Sq, Sk, dtype, seq_dim, pk, D, route, monkeypatch)
+
+
+@pytest.mark.parametrize("route", ["ds_handover", "recompute"])
 @pytest.mark.parametrize("D", [128, 64])
 @pytest.mark.parametrize("B,Hq,Hkv,Sq,Sk,dtype,seq_dim,pk", BWD_CASES)
 def test_sm100_backward_vs_oracle(B, Hq, Hkv, Sq, Sk, dtype, seq_dim, pk, D, route, monkeypatch):
