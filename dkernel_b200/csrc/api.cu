@@ -87,7 +87,13 @@ int bsa_bwd(const bsa_bwd_params* p, void* stream) {
   if (rc) return rc;
   BSA_CHECK_ARG(p->f.lse && p->d_o && p->dq && p->dk && p->dv && p->delta && p->ccol && p->row,
                 "bsa_bwd: null pointer (lse, dO, dQ, dK, dV, delta and the CSC layout are required)");
-  BSA_CHECK_ARG(p->f.fine_block == 0, "bsa_bwd: pass the pattern's own layout, not a coarsened fine-block one");
+  // A pattern with 16- or 32-token blocks coarsened to 64-token blocks (col_bits) is served by the
+  // tensor-core kernels only, and only with the dS hand-over: the dK/dV kernel applies the bit masks and the
+  // dQ kernel reads the masked dS tiles.
+  BSA_CHECK_ARG(p->f.fine_block == 0 || ((p->f.fine_block == 16 || p->f.fine_block == 32) && p->f.col_bits &&
+                                         p->ds_ws && p->f.impl != BSA_IMPL_GENERIC),
+                "bsa_bwd: a coarsened fine-block layout needs col_bits, a dS workspace and the tensor-core kernels; "
+                "pass the pattern's own layout otherwise");
   BSA_CHECK_ARG(!p->f.q_start && !p->f.k_start && p->f.row_mode == BSA_ROWS_BY_TILE,
                 "bsa_bwd: padded / packed batches have no backward "
                 "(as in dkernel/ops/__init__.py:57-58,79-80)");
@@ -99,7 +105,7 @@ int bsa_bwd(const bsa_bwd_params* p, void* stream) {
   if (p->f.impl != BSA_IMPL_GENERIC) {
     const char* why = nullptr;
     if (sm100_bwd_supported(p, &why)) return sm100_bwd(p, s);
-    if (p->f.impl == BSA_IMPL_SM100) {
+    if (p->f.impl == BSA_IMPL_SM100 || p->f.fine_block != 0) {
       set_error("bsa_bwd: the tcgen05 kernel does not serve this call: %s", why ? why : "?");
       return BSA_E_UNSUPPORTED;
     }

@@ -527,6 +527,18 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ Tmap4 tmQ, const __grid_constant__
           for (int c = 0; c < 16; ++c)
             if (c < c0) sv[c] = 0xff800000u;
         }
+        if (p.fine_block) {
+          // a pattern with 16- or 32-token blocks, coarsened: bit a * (64 / fb) + b of the entry's mask
+          // says whether q sub-block a attends kv sub-block b (this thread: one kv row, 16 q columns)
+          const int sh = p.fine_block == 16 ? 4 : 5, kf = 64 >> sh;
+          const int hq_ = hk * G + (int)((ent >> 16) & 0xffu);
+          const uint32_t bits = (uint32_t)__ldg(p.col_bits + (int64_t)pattern_head(hq_, p.h_pat, p.hq, p.hkv) *
+                                                             p.col_bits_sh + tl->cidx[e][t]) >>
+                                ((r_kv & 63) >> sh);
+#pragma unroll
+          for (int c = 0; c < 16; ++c)
+            if (!((bits >> (((qtr * 16 + c) >> sh) * kf)) & 1u)) sv[c] = 0xff800000u;
+        }
 #pragma unroll
         for (int c4 = 0; c4 < 4; ++c4) {
           const float4 l4 = *reinterpret_cast<const float4*>(lse_s + c4 * 4);
@@ -1310,6 +1322,8 @@ bool sm100_bwd_supported(const bsa_bwd_params* bp, const char** why) {
   if (!(p->dtype == BSA_F16 || p->dtype == BSA_BF16)) return no("dtype is not f16/bf16");
   if (p->d < 16 || p->d > 128 || p->d % 8) return no("head dim is not a multiple of 8 in [16, 128]");
   if (p->block_size != kBS) return no("block size is not 64");
+  if (p->fine_block != 0 && !((p->fine_block == 16 || p->fine_block == 32) && p->col_bits && bp->ds_ws))
+    return no("a fine-block pattern needs col_bits and the dS workspace");
   if (p->sk > kMaxBlocks * kBS || p->sq > kMaxBlocks * kBS) return no("more than 65536 positions");
   if ((p->hq / p->hkv) * cdiv_i(p->sq, kBS) > kMaxEntries)
     return no("group size x q blocks exceeds the per-CTA list capacity");

@@ -570,6 +570,14 @@ def _backward(ctx, do: Tensor, dlse: Optional[Tensor], dq=None, dk=None, dv=None
     seq_dim, plan = ctx.seq_dim, ctx.plan
     if ctx.bwd_impl != _lib.IMPL_GENERIC:
         plan = plan.for_kernels(q, backward=True)
+        if (plan.block_size in (16, 32) and q.dtype in (torch.float16, torch.bfloat16)
+                and q.size(-1) % 8 == 0 and q.size(-1) <= 128):
+            # 16/32-token blocks: the tensor-core kernels take the pattern coarsened to 64-token blocks
+            # with a bit mask per block, which needs the dS hand-over (the dQ kernel then reads dS
+            # tiles that are already masked); without room for its scratch the generic kernels serve it
+            coarse = plan._coarsened()
+            if 0 < q.size(0) * q.size(3 - seq_dim) * coarse.max_head_nnz() * 8192 <= _DS_WS_MAX_BYTES:
+                plan = coarse
     do = _tma_friendly(do)
     if dq is None:
         dq = torch.empty_like(q, memory_format=torch.contiguous_format)

@@ -134,8 +134,8 @@ typedef struct {
   int32_t dtype;              /* BSA_F16 / BSA_BF16 / BSA_F32                   */
   int32_t impl;               /* BSA_IMPL_*                                     */
   float sm_scale;
-  /* Patterns with 16- or 32-token blocks on the tensor-core forward (BSA_IMPL_SM100 /
-   * AUTO only): crow/col describe the pattern coarsened to block_size = 64, fine_block is
+  /* Patterns with 16- or 32-token blocks on the tensor-core forward, and on the tensor-core
+   * backward when bsa_bwd_params.ds_ws is given (BSA_IMPL_SM100 / AUTO only): crow/col describe the pattern coarsened to block_size = 64, fine_block is
    * the pattern's own block size and col_bits holds, for every entry of col, one bit per
    * (sub-row a, sub-column b) pair of the 64 x 64 block, bit a * (64 / fine_block) + b.
    * 0 / NULL = the pattern's blocks are the kernel's.  The reference runs such patterns

@@ -381,11 +381,14 @@ FINE_CASES = [
 ]
 
 
+@pytest.mark.parametrize("bwd", ["sm100", "generic"])
 @pytest.mark.parametrize("B,Hq,Hkv,Sq,Sk,D,dtype,seq_dim,pk", FINE_CASES)
-def test_sm100_forward_with_16_and_32_token_blocks(B, Hq, Hkv, Sq, Sk, D, dtype, seq_dim, pk):
+def test_sm100_forward_with_16_and_32_token_blocks(B, Hq, Hkv, Sq, Sk, D, dtype, seq_dim, pk, bwd):
     """Patterns with blocks finer than the kernel's 64-token tiles: the layout is coarsened to
-    64 x 64 blocks on the host side and the kernel masks with one bit per sub-block; forward on the
-    tensor cores (impl="sm100" would raise otherwise), backward on the CUDA-core kernels."""
+    64 x 64 blocks on the host side and the kernels mask with one bit per sub-block; forward on the
+    tensor cores (impl="sm100" would raise otherwise); backward on the tensor cores too (the dK/dV
+    kernel applies the masks and hands masked dS tiles to the dQ kernel; bwd_impl="sm100" would raise
+    otherwise), or on the CUDA-core kernels from the pattern's own layout."""
     from helpers import assert_grad_close
     from dkernel_b200 import _lib
     bs = pk["block_size"]
@@ -401,7 +404,7 @@ def test_sm100_forward_with_16_and_32_token_blocks(B, Hq, Hkv, Sq, Sk, D, dtype,
     ref, ref_lse = O.masked_dense_attention(qf, kf, vf, dense[None].to(torch.uint8), None, seq_dim=seq_dim,
                                             return_lse=True)
     ref.backward(do.float())
-    mod = _module(Hq, Sk, pk, seq_dim=seq_dim, impl="sm100", bwd_impl="generic")
+    mod = _module(Hq, Sk, pk, seq_dim=seq_dim, impl="sm100", bwd_impl=bwd)
     assert mod._plan().for_kernels(q.cuda()).fine_block == bs
     qg, kg, vg = (t.cuda().requires_grad_() for t in (q, k, v))
     out, lse = mod(qg, kg, vg, return_lse=True)
