@@ -450,3 +450,49 @@ def test_sm100_fine_block_user_pattern_varlen_and_padded():
     _wait_status_clean()
     assert_out_close(out, ref)
     assert_lse_close(lse, ref_lse)
+
+
+def test_sm100_random_sweep_against_cuda_core_kernels():
+    """Seeded random sweep over shapes and patterns (head dims, GQA ratios, block sizes 16-128, odd
+    lengths, Sq < Sk, causal or not, both layouts, both 16-bit types): forward, LSE and all three
+    gradients of the tensor-core kernels against the CUDA-core kernels on the same inputs."""
+    from helpers import assert_grad_close
+    rng = np.random.default_rng(2024)
+    ran = 0
+    for trial in range(24):
+        D = int(rng.choice([48, 64, 96, 128]))
+        Hkv = int(rng.choice([1, 2, 3]))
+        G = int(rng.choice([1, 2, 4]))
+        Hq = Hkv * G
+        bs = int(rng.choice([16, 32, 64, 128]))
+        Sk = int(rng.integers(1, 1500))
+        Sq = Sk if rng.random() < 0.7 else int(rng.integers(1, Sk + 1))
+        causal = bool(rng.random() < 0.8)
+        seq_dim = int(rng.choice([1, 2]))
+        dtype = torch.bfloat16 if rng.random() < 0.6 else torch.float16
+        B = int(rng.choice([1, 2]))
+        pk = dict(block_size=bs, local_blocks=int(rng.integers(1, 6)), vert_stride=int(rng.integers(1, 7)),
+                  num_kv_heads=Hkv, causal=causal)
+        if Hkv == 1 and rng.random() < 0.5:
+            pk["homo_head"] = True      # one pattern for all heads (the generator wants num_kv_heads = 1 with it)
+        max_seq = (Sk + bs - 1) // bs * bs
+        shape = (lambda h, s: (B, h, s, D)) if seq_dim == 2 else (lambda h, s: (B, s, h, D))
+        q, k, v, do = seeded_qkv(100 + trial, shape(Hq, Sq), shape(Hkv, Sk), dtype, device="cuda", with_do=True)
+        res = {}
+        for name in ("sm100", "generic"):
+            mod = _module(Hq, max_seq, pk, seq_dim=seq_dim, impl=name, bwd_impl=name)
+            qg, kg, vg = (t.clone().requires_grad_() for t in (q, k, v))
+            out, lse = mod(qg, kg, vg, return_lse=True)
+            out.backward(do)
+            res[name] = (out, lse, qg.grad, kg.grad, vg.grad)
+        _wait_status_clean()
+        what = f"trial {trial}: D={D} Hq={Hq} Hkv={Hkv} bs={bs} Sq={Sq} Sk={Sk} causal={causal} seq_dim={seq_dim} {dtype}"
+        a, b_ = res["sm100"], res["generic"]
+        assert (a[0].float() - b_[0].float()).abs().max().item() <= 2e-2, what
+        fin = torch.isfinite(b_[1])
+        assert torch.equal(torch.isfinite(a[1]), fin), what
+        assert (a[1][fin] - b_[1][fin]).abs().max().item() <= 1e-3 if fin.any() else True, what
+        for x, y, n in zip(a[2:], b_[2:], ("dq", "dk", "dv")):
+            assert_grad_close(x, y, f"{n} ({what})", 3e-2)
+        ran += 1
+    assert ran == 24
