@@ -333,13 +333,24 @@ def ring_backward(q: Tensor, k: Tensor, v: Tensor, o: Tensor, lse: Tensor, do: T
     so the pair's contributions simply add up).  dQ accumulates locally in fp32.  The K/V chunks
     travel round the ring as in the forward pass; the dK/dV contribution a rank computes for
     another rank's chunk is sent straight to that rank (one message per chunk pair, in the
-    gradients' own dtype), which adds the messages to its fp32 accumulator in step order, so the
-    result does not depend on timing."""
+    gradients' own dtype) while the next pair is computed; the owner adds the messages to its fp32
+    accumulator in step order, so the result does not depend on timing."""
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     peer = (lambda r_: dist.get_global_rank(group, r_)) if group is not None else (lambda r_: r_)
     kv = torch.stack([k, v]).contiguous()
     dkv = torch.zeros(kv.shape, dtype=torch.float32, device=kv.device)
     dq = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
+    pending = None      # (requests, received contribution, sent tensor) of the previous step's messages
+
+    def settle(p):
+        # the previous step's dK/dV messages travelled while this step's pair was computed
+        if p is None:
+            return
+        for r_ in p[0]:
+            r_.wait()
+        if p[1] is not None:
+            dkv.add_(p[1])
+
     for t, s, active in ring_steps(rank, world, causal):
         reqs, nxt = [], None
         if t < world - 1:
@@ -354,6 +365,7 @@ def ring_backward(q: Tensor, k: Tensor, v: Tensor, o: Tensor, lse: Tensor, do: T
                 dkv[1] += dv_p
             else:
                 part = torch.stack([dk_p, dv_p])
+        settle(pending)
         # this step's chunk belongs to rank s; the rank that holds MY chunk now is (rank + t) % world
         src = (rank + t) % world
         src_active = t > 0 and ((not causal) or rank <= src)     # does it compute a pair with my chunk?
@@ -363,14 +375,12 @@ def ring_backward(q: Tensor, k: Tensor, v: Tensor, o: Tensor, lse: Tensor, do: T
         if src_active:
             got = torch.empty((2,) + tuple(k.shape), dtype=k.dtype, device=k.device)
             ops.append(dist.P2POp(dist.irecv, got, peer(src), group))
-        for r_ in (dist.batch_isend_irecv(ops) if ops else []):
-            r_.wait()
-        if got is not None:
-            dkv += got
+        pending = (dist.batch_isend_irecv(ops) if ops else [], got, part)
         for r_ in reqs:
             r_.wait()
         if nxt is not None:
             kv = nxt
+    settle(pending)
     return dq.to(q.dtype), dkv[0].to(k.dtype), dkv[1].to(v.dtype)
 
 
