@@ -213,7 +213,9 @@ def setup_dist(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    args.bound_cpus = bind_to_gpu_cpus(local_rank) if world > 1 else None
+    # also at one GPU: on a two-socket host the pinned staging buffers of the end-to-end step should
+    # sit on the GPU's own NUMA node
+    args.bound_cpus = bind_to_gpu_cpus(local_rank)
     if world > 1:
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
