@@ -32,7 +32,11 @@ def _worker(rank, world, port, ret):
     os.environ["MASTER_PORT"] = str(port)
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    # a short collective timeout: if one rank fails an assertion and leaves, the others stop after
+    # three minutes instead of the default ten
+    import datetime
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
+                            timeout=datetime.timedelta(seconds=180))
     try:
         from oracle import dkernel_oracle as O
         from dkernel_b200 import LocalStrideSparseAttention, _lib
